@@ -1,0 +1,171 @@
+// Internal definitions of libodla_b200.so: the recorded graph, the launch plan and the
+// per-GPU replicas.  The opaque ODLA handle types are defined here, privately, in the same
+// spirit as ODLA/platforms/dnnl/odla_dnnl.h:43-108 and
+// ODLA/platforms/tensorrt/odla_tensorrt.h:183-312 in the reference.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <functional>
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../../include/odla_b200.h"
+#include "kernels.h"
+
+namespace b200 {
+
+// ---------------------------------------------------------------- logging ----
+void log_msg(const char* file, int line, const char* func, odla_log_level lvl, const char* fmt, ...);
+#define B2_LOG(lvl, ...) ::b200::log_msg(__FILE__, __LINE__, __func__, lvl, __VA_ARGS__)
+#define B2_ERR(...) B2_LOG(ODLA_LOG_LEVEL_ERROR, __VA_ARGS__)
+#define B2_WARN(...) B2_LOG(ODLA_LOG_LEVEL_WARN, __VA_ARGS__)
+#define B2_INFO(...) B2_LOG(ODLA_LOG_LEVEL_INFO, __VA_ARGS__)
+#define B2_DEBUG(...) B2_LOG(ODLA_LOG_LEVEL_DEBUG, __VA_ARGS__)
+
+// Host-side fault injection for tests: the environment variable ODLA_B200_INJECT holds
+// "<site>@<n>" with site one of h2d, launch, d2h, peer, alloc; the n-th call (1-based) of
+// that site reports cudaErrorUnknown without touching the device.
+bool inject_fault(const char* site);
+
+// Evaluates a CUDA runtime call; on failure logs and makes the enclosing function return `ret`.
+#define B2_CUDA(site, expr, ret)                                                        \
+  do {                                                                                  \
+    cudaError_t e__ = ::b200::inject_fault(site) ? cudaErrorUnknown : (expr);           \
+    if (e__ != cudaSuccess) {                                                           \
+      B2_ERR("CUDA call failed (%s): %s -> %s", site, #expr, cudaGetErrorString(e__));  \
+      return ret;                                                                       \
+    }                                                                                   \
+  } while (0)
+
+// ------------------------------------------------------------ graph nodes ----
+enum OpKind {
+  OP_ARG, OP_CONST, OP_CONV, OP_GEMM, OP_MAXPOOL, OP_AVGPOOL, OP_BATCHNORM, OP_UNARY, OP_BINARY,
+  OP_SOFTMAX, OP_REDUCE_MEAN, OP_LAYERNORM, OP_QUANTIZE, OP_DEQUANTIZE, OP_RESHAPE, OP_TRANSPOSE,
+  OP_CONCAT, OP_RESIZE, OP_GATHER, OP_SLICE, OP_CAST
+};
+const char* op_name(OpKind k);
+
+int elem_size(odla_element_type t);
+bool is_float_type(odla_element_type t);
+int64_t numel(const odla_value_shape& s);
+int storage_size(int dt);  // bytes per element of a DT_* storage type
+
+}  // namespace b200
+
+struct _odla_value {
+  std::string name;
+  odla_value_type type;            // as seen through the API (shape includes the batch)
+  b200::OpKind kind = b200::OP_ARG;
+  std::vector<odla_value> in;      // operands (may hold nullptr for absent optionals)
+  std::vector<int64_t> ia;         // integer attributes, meaning depends on kind
+  std::vector<float> fa;           // float attributes
+  const void* host = nullptr;      // caller-owned constant data (read at plan time only)
+  int index = 0;                   // position in the computation's node list
+  bool is_output = false;
+  bool poison = false;             // produced by a failed builder call
+};
+
+namespace b200 {
+
+// One entry of the launch list.  `fn` issues exactly the kernels of this entry on `stream`.
+struct Launch {
+  std::string op;     // kernel family
+  std::string name;   // id of the value it materialises
+  double flops = 0, bytes = 0;
+  int n_kernels = 1;
+  // returns 0 on success
+  std::function<int(cudaStream_t)> fn;
+  // profiling accumulators
+  double prof_ms = 0;
+  long long prof_n = 0;
+};
+
+// Where a value lives inside a replica's arena.
+struct Slot {
+  int64_t offset = -1, bytes = 0;
+  int dt = DT_F32;                 // storage type
+  bool constant = false;           // lives in the constant pool instead of the arena
+};
+
+// A plan specialised for one batch size on one GPU.
+struct Plan {
+  int64_t batch = 0;               // extent of dim 0 this plan was built for
+  int device = 0;
+  std::vector<Launch> launches;
+  std::map<const _odla_value*, Slot> slots;
+  char* arena = nullptr;           // activations and staging
+  int64_t arena_bytes = 0;
+  char* consts = nullptr;          // converted / repacked constants
+  int64_t const_bytes = 0;
+  int* status = nullptr;           // device word: non-zero when a bounded wait expired
+  std::vector<void*> extra_allocs; // uploaded constants and scratch
+  std::vector<UmmaLaunch*> umma;   // prepared tensor-core launches (own their tensor maps)
+  cudaGraphExec_t graph = nullptr; // captured launch list (optional)
+  bool graph_failed = false;       // capture was tried and refused: stay on plain launches
+  // How arguments enter and outputs leave the arena.  `stage` is where the caller's bytes land
+  // (API element type); it equals `slot` when no conversion kernel is needed.
+  struct Io {
+    const _odla_value* v = nullptr;
+    int64_t slot = -1, stage = -1;
+    int64_t api_bytes = 0;         // bytes of this shard in the API element type
+    bool per_shard = true;         // false: independent of the batch, identical on every GPU
+    int64_t user_offset = 0;       // byte offset of this shard inside the caller's buffer
+    const void* const_host = nullptr;  // output that is a constant: copied straight from here
+  };
+  std::vector<Io> inputs, outputs;
+  ~Plan();
+};
+
+struct Replica {
+  int device = 0;
+  int64_t shard_start = 0, shard_batch = 0;  // rows [start, start+batch) of dim 0
+  int* host_status = nullptr;      // pinned copy of the plan's device status word
+  std::unique_ptr<Plan> plan;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ev_begin = nullptr, ev_end = nullptr;
+};
+
+}  // namespace b200
+
+struct _odla_computation {
+  std::vector<std::unique_ptr<_odla_value>> nodes;
+  std::vector<odla_value> args, outs;
+  std::map<std::string, odla_value> by_name;
+  std::string first_error;         // first builder failure; reported at context/execute time
+  odla_status error_status = ODLA_SUCCESS;
+  // properties (odla_SetComputationItem)
+  int float_mode = b200::DT_F32;         // DT_F32, DT_F16 (ODLA_FP16_MODE) or DT_BF16 (ODLA_BF16_MODE)
+  int n_gpus = 0;                  // ODLA_PROCESSOR_NUM; 0 = all visible
+  bool use_graph = true;           // ODLA_AGGREGATE_OPS / ODLA_B200_GRAPH
+  int first_device = 0;
+  std::vector<odla_value_quant_info> quant_table;
+  // built lazily at first context / execute
+  bool planned = false;
+  bool shardable = true;           // dim 0 of every argument/output is an independent batch
+  std::vector<b200::Replica> replicas;
+  ~_odla_computation();
+};
+
+struct _odla_context {
+  odla_computation comp = nullptr;
+  std::map<const _odla_value*, const void*> in;
+  std::map<const _odla_value*, void*> out;
+  float last_ms = -1.f;
+  long long last_launches = 0;
+  bool profiling = false;
+};
+
+struct _odla_device {
+  int index = 0;
+};
+
+namespace b200 {
+// Builds replicas and plans for `comp` (idempotent).  Defined in plan.cc.
+odla_status ensure_planned(_odla_computation* comp);
+odla_status execute(_odla_computation* comp, _odla_context* ctx);
+int visible_devices();
+extern thread_local int g_current_device;  // set by odla_SetCurrentDevice, -1 = unset
+}  // namespace b200

@@ -1,0 +1,55 @@
+// Raw kernel entry points of the C ABI (declared in include/odla_b200.h): thin wrappers that
+// let a caller that already holds device memory run one kernel without building a graph.
+#include <cstdio>
+
+#include "common.h"
+
+using namespace b200;
+
+extern "C" int odla_b200_conv_umma(const odla_b200_conv_desc* d, const void* x, const void* w, const float* mul, const float* add,
+                                   const void* residual, void* y, void* stream) {
+  if (!d || !x || !w || !y) return -1;
+  if (visible_devices() <= 0) {
+    fprintf(stderr, "[odla_b200] odla_b200_conv_umma: no CUDA device (there is no CPU fallback)\n");
+    return -2;
+  }
+  int in_dt = d->dtype == 0 ? DT_F16 : d->dtype == 1 ? DT_BF16 : d->dtype == 2 ? DT_S8 : -1;
+  if (in_dt < 0) return -1;
+  UmmaConv c{d->n, d->h, d->w, d->c, d->k, d->r, d->s, d->p, d->q, d->stride_h, d->stride_w, d->pad_top, d->pad_left, in_dt};
+  if (!umma_conv_supported(c)) return -1;
+  Epilogue ep;
+  ep.mul = mul;
+  ep.add1 = add;
+  ep.res = residual;
+  ep.res_dt = d->res_kind == 0 ? in_dt : d->res_kind == 1 ? DT_F32 : DT_S8;
+  if (ep.res_dt == DT_S8 && d->res_kind == 0) ep.res_dt = DT_S8;
+  ep.res_scale = d->res_scale;
+  ep.act = d->act == 1 ? ACT_RELU : d->act == 2 ? ACT_LEAKY : ACT_NONE;
+  ep.act_a = d->alpha;
+  switch (d->out_kind) {
+    case 0: ep.out_dt = in_dt == DT_S8 ? DT_F32 : in_dt; break;
+    case 1: ep.out_dt = DT_F32; break;
+    case 2: ep.out_dt = DT_S8; ep.out_scale = d->out_scale; break;
+    case 3: if (in_dt != DT_S8) return -1; ep.out_dt = DT_S32; break;
+    default: return -1;
+  }
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int* status = nullptr;
+  if (cudaMalloc((void**)&status, 256) != cudaSuccess) return -2;
+  cudaMemsetAsync(status, 0, 256, (cudaStream_t)stream);
+  UmmaLaunch* L = umma_conv_prepare(c, x, w, y, ep, status, sms);
+  if (!L) { cudaFree(status); return -2; }
+  int rc = umma_conv_run(L, (cudaStream_t)stream);
+  int host_status[2] = {0, 0};
+  if (rc == 0 && cudaMemcpyAsync(host_status, status, sizeof(host_status), cudaMemcpyDeviceToHost, (cudaStream_t)stream) != cudaSuccess) rc = -2;
+  if (cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess) rc = -2;
+  umma_conv_destroy(L);
+  cudaFree(status);
+  if (rc == 0 && host_status[0] != 0) {
+    fprintf(stderr, "[odla_b200] odla_b200_conv_umma: bounded wait expired (code %d, block %d)\n", host_status[0], host_status[1]);
+    return -3;
+  }
+  return rc;
+}

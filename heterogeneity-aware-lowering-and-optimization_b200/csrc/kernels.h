@@ -1,0 +1,143 @@
+// Launchers of the CUDA kernels.  Every launcher enqueues on `stream` and returns 0, or a
+// negative code (-1 bad argument, -2 CUDA error).  Pointers are device pointers.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace b200 {
+
+// Storage element types of tensors held in HBM.
+enum { DT_F32 = 0, DT_F16 = 1, DT_BF16 = 2, DT_S8 = 3, DT_U8 = 4, DT_S32 = 5, DT_S64 = 6 };
+
+enum { ACT_NONE = 0, ACT_RELU = 1, ACT_LEAKY = 2, ACT_CLAMP = 3, ACT_GELU_ERF = 4, ACT_GELU_TANH = 5 };
+
+// Epilogue applied to every accumulator of a convolution / GEMM, in this fixed order and with
+// every fp32 operation rounded separately (no fused multiply-add), so that the int8 path
+// reproduces a node-by-node fp32 evaluation of the quantised graph bit for bit:
+//   t = (float)acc
+//   if mul        : t = t * mul[col]
+//   if alpha != 1 : t = t * alpha
+//   if add1       : t = t + add1[col]          (convolution bias, or beta*C of a Gemm)
+//   if add2       : t = t + add2[col]          (the per-channel Add that carries a folded BN)
+//   if add_full   : t = t + beta_full * add_full[row, col]     (Gemm with a full-matrix C)
+//   if act_first  : t = act(t)
+//   if res        : t = t + (res_dt == DT_S8 ? (float)res * res_scale : (float)res)
+//   if !act_first : t = act(t)
+//   store         : float types round to nearest even; DT_S8 stores sat(rne(t / out_scale));
+//                   DT_S32 stores the raw accumulator (int8 inputs only).
+struct Epilogue {
+  const float* mul = nullptr;
+  float alpha = 1.f;
+  const float* add1 = nullptr;
+  const float* add2 = nullptr;
+  const void* add_full = nullptr;  // same storage type as the float mode of the graph
+  int add_full_dt = DT_F32;
+  float beta_full = 1.f;
+  const void* res = nullptr;
+  int res_dt = DT_F32;
+  float res_scale = 1.f;
+  int act = ACT_NONE;
+  int act_first = 0;
+  float act_a = 0.f, act_b = 0.f;
+  int out_dt = DT_F32;
+  float out_scale = 1.f;
+};
+
+// 2-d convolution geometry.  Data is addressed through element strides so NHWC and NCHW share
+// the SIMT kernel: x[n*xs_n + h*xs_h + w*xs_w + c*xs_c], same for y; the filter is
+// w[k*ws_k + c*ws_c + r*ws_r + s*ws_s].
+struct ConvGeom {
+  int N, H, W, C, K, R, S, P, Q, stride_h, stride_w, pad_t, pad_l, groups;
+  int64_t xs_n, xs_h, xs_w, xs_c, ys_n, ys_h, ys_w, ys_c, ws_k, ws_c, ws_r, ws_s;
+};
+
+// Direct convolution on the CUDA cores; in_dt = DT_F32, DT_F16, DT_BF16 (fp32 accumulate, k
+// ascending within taps in (r,s,c) order) or DT_S8 (int32 accumulate); the filter has the same
+// type as the input.  Fallback for shapes the tensor-core kernel does not take.
+int conv_simt(const ConvGeom& g, int in_dt, const void* x, const void* w, void* y, const Epilogue& ep,
+              cudaStream_t stream);
+
+// Batched GEMM on the CUDA cores: C[b] = op(A[b]) op(B[b]); element strides given; epilogue col =
+// n index.  A/B same storage type (as conv_simt).  b_batch_stride may be 0 (shared B).
+struct GemmGeom {
+  int64_t batch, M, N, K;
+  int64_t a_row, a_col, a_batch;  // A element (m,k) at m*a_row + k*a_col
+  int64_t b_row, b_col, b_batch;  // B element (k,n) at k*b_row + n*b_col
+};
+int gemm_simt(const GemmGeom& g, int in_dt, const void* A, const void* B, void* C, const Epilogue& ep,
+              cudaStream_t stream);
+
+// ---- tensor-core path (kernels_umma.cu) ----
+// NHWC implicit-GEMM convolution: x [N,H,W,C], w repacked to [K][R*S*C] (K-major), y [N,P,Q,K].
+// A 1x1/stride-1 convolution with H=W=1 is a plain GEMM, which is how Gemm uses it.
+struct UmmaConv {
+  int N, H, W, C, K, R, S, P, Q, stride_h, stride_w, pad_t, pad_l;
+  int in_dt;  // DT_F16, DT_BF16 or DT_S8
+};
+// True when the tensor-core kernel can run this problem.
+bool umma_conv_supported(const UmmaConv& p);
+// Opaque prepared launch (tensor maps live in it).  Create once at plan time.
+struct UmmaLaunch;
+UmmaLaunch* umma_conv_prepare(const UmmaConv& p, const void* x, const void* w, void* y, const Epilogue& ep,
+                              int* status_word, int device_sms);
+int umma_conv_run(UmmaLaunch* l, cudaStream_t stream);
+void umma_conv_destroy(UmmaLaunch* l);
+
+// ---- memory-bound kernels (kernels_simt.cu) ----
+struct PoolGeom {
+  int N, H, W, C, P, Q, R, S, stride_h, stride_w, pad_t, pad_l;
+  int64_t xs_n, xs_h, xs_w, xs_c, ys_n, ys_h, ys_w, ys_c;
+};
+int pool2d(const PoolGeom& g, int dt, bool is_max, const void* x, void* y, cudaStream_t stream);
+
+enum { UN_RELU = 0, UN_LEAKY, UN_CLAMP, UN_GELU_ERF, UN_GELU_TANH, UN_ERF, UN_SIGMOID, UN_TANH, UN_EXP,
+       UN_LOG, UN_SQRT, UN_RSQRT, UN_ABS, UN_NEG, UN_RECIP, UN_ROUND, UN_IDENTITY };
+int unary(int op, int dt_in, int dt_out, const void* x, void* y, int64_t n, float a, float b, cudaStream_t stream);
+
+enum { BIN_ADD = 0, BIN_SUB, BIN_MUL, BIN_DIV, BIN_POW, BIN_PRELU };
+// Broadcasting binary op; shapes right-aligned to `rank` (<= 8); lhs/rhs strides are 0 on
+// broadcast dimensions.  Optional fused activation afterwards (ACT_*).
+struct BinaryGeom {
+  int rank;
+  int64_t oshape[8], lstride[8], rstride[8];
+};
+int binary(int op, const BinaryGeom& g, int dt_l, int dt_r, int dt_out, const void* l, const void* r, void* y,
+           int act, float act_a, cudaStream_t stream);
+
+// y = x * a[c] + b[c] over (outer, C, inner) with fp32 a, b.
+int channel_affine(int dt, const void* x, void* y, const float* a, const float* b, int64_t outer, int64_t C,
+                   int64_t inner, cudaStream_t stream);
+
+int softmax(int dt, const void* x, void* y, int64_t outer, int64_t dim, int64_t inner, bool log_form,
+            cudaStream_t stream);
+// Mean over one axis, sum in ascending order then a single division (bit-reproducible).
+int reduce_mean_axis(int dt_in, int dt_out, const void* x, void* y, int64_t before, int64_t dim, int64_t after,
+                     cudaStream_t stream);
+int layernorm(int dt, const void* x, void* y, const float* gamma, const float* beta, int64_t rows, int64_t dim,
+              float eps, cudaStream_t stream);
+
+// q = sat(rne(x / scale[a]) + zp[a]); x = (q - zp[a]) * scale[a]; (outer, adim, inner) split.
+int quantize(int dt_in, const void* x, void* q, const float* scale, const int* zp, int64_t outer, int64_t adim,
+             int64_t inner, bool per_axis, bool is_unsigned, cudaStream_t stream);
+int dequantize(int dt_out, const void* q, void* x, const float* scale, const int* zp, int64_t outer,
+               int64_t adim, int64_t inner, bool per_axis, bool is_unsigned, cudaStream_t stream);
+
+// Type conversion between storage types (float<->float, int<->float with saturation to int8).
+int convert(int dt_in, int dt_out, const void* x, void* y, int64_t n, cudaStream_t stream);
+
+// Generic gather-style movement: out[e] = in[src(e)] with src given by per-dimension strides and
+// an element offset (covers transpose, slice, concat parts, broadcast).  esz in bytes.
+struct MoveGeom {
+  int rank;
+  int64_t oshape[8], istride[8], ostride[8];
+  int64_t in_offset, out_offset;
+};
+int move(const MoveGeom& g, int esz, const void* x, void* y, cudaStream_t stream);
+int resize_nearest(int esz, const void* x, void* y, int N, int H, int W, int C, int P, int Q, bool nhwc,
+                   cudaStream_t stream);
+// out[o, k, :] = in[o, idx[k], :]; idx int32 or int64.
+int gather(int esz, const void* x, const void* idx, int idx_dt, void* y, int64_t outer, int64_t axis_dim,
+           int64_t n_idx, int64_t inner, cudaStream_t stream);
+
+}  // namespace b200

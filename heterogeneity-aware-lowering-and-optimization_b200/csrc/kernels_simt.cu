@@ -1,0 +1,608 @@
+// CUDA-core kernels of libodla_b200: the memory-bound operators (pooling, soft-max, layer norm,
+// element-wise, quantise / dequantise, layout moves) and a direct convolution / GEMM used where
+// the tensor-core kernel does not apply (fp32 graphs, channel counts that break TMA alignment,
+// grouped or NCHW convolutions).  Memory-bound kernels move 16 bytes per thread along the
+// innermost (channel) dimension where the layout allows it and size their grids in multiples of
+// the SM count.
+#include <cstdio>
+
+#include "epilogue.cuh"
+
+namespace b200 {
+namespace {
+
+int g_sm_count_cache[16] = {0};
+int sm_count() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (dev < 0 || dev >= 16) return 148;
+  if (!g_sm_count_cache[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    g_sm_count_cache[dev] = n;
+  }
+  return g_sm_count_cache[dev];
+}
+// Grid for a grid-stride loop over `work` items with `threads` per block: enough blocks to cover
+// the work, capped at 16 resident blocks per SM, rounded up to a multiple of the SM count.
+int grid_for(int64_t work, int threads) {
+  int sms = sm_count();
+  int64_t need = (work + threads - 1) / threads;
+  int64_t cap = (int64_t)sms * 16;
+  if (need >= cap) return (int)cap;
+  if (need <= sms) return (int)(need > 0 ? need : 1);
+  return (int)(((need + sms - 1) / sms) * sms);
+}
+int check_launch() {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    fprintf(stderr, "[odla_b200] kernel launch failed: %s\n", cudaGetErrorString(e));
+    return -2;
+  }
+  return 0;
+}
+
+// ------------------------------------------------------------ direct convolution ----
+template <typename T, typename ACC>
+__device__ __forceinline__ ACC mac(ACC acc, T a, T b);
+template <> __device__ __forceinline__ float mac<float, float>(float acc, float a, float b) { return fmaf(a, b, acc); }
+template <> __device__ __forceinline__ float mac<__half, float>(float acc, __half a, __half b) {
+  return fmaf(__half2float(a), __half2float(b), acc);
+}
+template <> __device__ __forceinline__ float mac<__nv_bfloat16, float>(float acc, __nv_bfloat16 a, __nv_bfloat16 b) {
+  return fmaf(__bfloat162float(a), __bfloat162float(b), acc);
+}
+template <> __device__ __forceinline__ int mac<int8_t, int>(int acc, int8_t a, int8_t b) { return acc + (int)a * (int)b; }
+
+template <typename ACC>
+__device__ __forceinline__ void store_result(const Epilogue& ep, void* y, int64_t yidx, ACC acc, int64_t row, int col,
+                                             int64_t ld) {
+  if (ep.out_dt == DT_S32) { ((int32_t*)y)[yidx] = (int32_t)acc; return; }
+  float t = epilogue_value(ep, (float)acc, row, col, ld);
+  store_from_float(y, ep.out_dt, yidx, t);
+}
+
+// One thread per output element, output channel fastest so filter reads coalesce for HWIO.
+template <typename T, typename ACC>
+__global__ void conv_direct_kernel(ConvGeom g, const T* __restrict__ x, const T* __restrict__ w, void* y, Epilogue ep) {
+  int64_t total = (int64_t)g.N * g.P * g.Q * g.K;
+  int cg = g.C / g.groups, kg = g.K / g.groups;
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    int k = (int)(e % g.K);
+    int64_t pix = e / g.K;
+    int q = (int)(pix % g.Q);
+    int p = (int)((pix / g.Q) % g.P);
+    int n = (int)(pix / ((int64_t)g.Q * g.P));
+    int grp = k / kg;
+    ACC acc = 0;
+    for (int r = 0; r < g.R; ++r) {
+      int h = p * g.stride_h - g.pad_t + r;
+      if (h < 0 || h >= g.H) continue;
+      for (int s = 0; s < g.S; ++s) {
+        int ww = q * g.stride_w - g.pad_l + s;
+        if (ww < 0 || ww >= g.W) continue;
+        const T* xp = x + n * g.xs_n + h * g.xs_h + ww * g.xs_w + (int64_t)grp * cg * g.xs_c;
+        const T* wp = w + k * g.ws_k + r * g.ws_r + s * g.ws_s;
+        for (int c = 0; c < cg; ++c) acc = mac<T, ACC>(acc, xp[c * g.xs_c], wp[c * g.ws_c]);
+      }
+    }
+    int64_t yidx = n * g.ys_n + p * g.ys_h + q * g.ys_w + k * g.ys_c;
+    // Residual / full-matrix operands are addressed like a dense [pixels, K] matrix (NHWC).
+    store_result<ACC>(ep, y, yidx, acc, pix, k, g.K);
+  }
+}
+
+template <typename T, typename ACC>
+__global__ void gemm_direct_kernel(GemmGeom g, const T* __restrict__ A, const T* __restrict__ B, void* C, Epilogue ep) {
+  int64_t total = g.batch * g.M * g.N;
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    int n = (int)(e % g.N);
+    int64_t m = (e / g.N) % g.M;
+    int64_t b = e / (g.N * g.M);
+    const T* a = A + b * g.a_batch + m * g.a_row;
+    const T* bb = B + b * g.b_batch + n * g.b_col;
+    ACC acc = 0;
+    for (int64_t k = 0; k < g.K; ++k) acc = mac<T, ACC>(acc, a[k * g.a_col], bb[k * g.b_row]);
+    store_result<ACC>(ep, C, e, acc, b * g.M + m, n, g.N);
+  }
+}
+
+// ------------------------------------------------------------------ pooling ----
+template <bool IS_MAX>
+__global__ void pool_generic_kernel(PoolGeom g, int dt, const void* x, void* y) {
+  int64_t total = (int64_t)g.N * g.P * g.Q * g.C;
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    int c = (int)(e % g.C);
+    int64_t pix = e / g.C;
+    int q = (int)(pix % g.Q), p = (int)((pix / g.Q) % g.P), n = (int)(pix / ((int64_t)g.Q * g.P));
+    float acc = IS_MAX ? -3.402823466e+38f : 0.f;
+    int cnt = 0;
+    for (int r = 0; r < g.R; ++r) {
+      int h = p * g.stride_h - g.pad_t + r;
+      if (h < 0 || h >= g.H) continue;
+      for (int s = 0; s < g.S; ++s) {
+        int w = q * g.stride_w - g.pad_l + s;
+        if (w < 0 || w >= g.W) continue;
+        float v = load_as_float(x, dt, n * g.xs_n + h * g.xs_h + w * g.xs_w + c * g.xs_c);
+        if (IS_MAX) acc = fmaxf(acc, v); else acc = __fadd_rn(acc, v);
+        ++cnt;
+      }
+    }
+    if (!IS_MAX) acc = __fdiv_rn(acc, (float)(cnt ? cnt : 1));
+    store_from_float(y, dt, n * g.ys_n + p * g.ys_h + q * g.ys_w + c * g.ys_c, acc);
+  }
+}
+// NHWC max pooling, 16 bytes per thread along C (8 halves or 16 int8 values).
+template <typename VT, int VEC>
+struct VecMax;
+template <> struct VecMax<__half, 8> {
+  static __device__ __forceinline__ void init(uint4& a) { a.x = a.y = a.z = a.w = 0xFBFFFBFFu; }
+  static __device__ __forceinline__ void upd(uint4& a, const uint4& v) {
+    __half2* pa = (__half2*)&a; const __half2* pv = (const __half2*)&v;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) pa[i] = __hmax2(pa[i], pv[i]);
+  }
+};
+template <> struct VecMax<__nv_bfloat16, 8> {
+  static __device__ __forceinline__ void init(uint4& a) { a.x = a.y = a.z = a.w = 0xFF7FFF7Fu; }
+  static __device__ __forceinline__ void upd(uint4& a, const uint4& v) {
+    __nv_bfloat162* pa = (__nv_bfloat162*)&a; const __nv_bfloat162* pv = (const __nv_bfloat162*)&v;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) pa[i] = __hmax2(pa[i], pv[i]);
+  }
+};
+template <> struct VecMax<int8_t, 16> {
+  static __device__ __forceinline__ void init(uint4& a) { a.x = a.y = a.z = a.w = 0x80808080u; }
+  static __device__ __forceinline__ void upd(uint4& a, const uint4& v) {
+    a.x = __vmaxs4(a.x, v.x); a.y = __vmaxs4(a.y, v.y); a.z = __vmaxs4(a.z, v.z); a.w = __vmaxs4(a.w, v.w);
+  }
+};
+template <> struct VecMax<float, 4> {
+  static __device__ __forceinline__ void init(uint4& a) { float* f = (float*)&a; f[0] = f[1] = f[2] = f[3] = -3.402823466e+38f; }
+  static __device__ __forceinline__ void upd(uint4& a, const uint4& v) {
+    float* pa = (float*)&a; const float* pv = (const float*)&v;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) pa[i] = fmaxf(pa[i], pv[i]);
+  }
+};
+template <typename T, int VEC>
+__global__ void maxpool_nhwc_vec_kernel(PoolGeom g, const T* __restrict__ x, T* __restrict__ y) {
+  int cv = g.C / VEC;
+  int64_t total = (int64_t)g.N * g.P * g.Q * cv;
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    int c = (int)(e % cv) * VEC;
+    int64_t pix = e / cv;
+    int q = (int)(pix % g.Q), p = (int)((pix / g.Q) % g.P), n = (int)(pix / ((int64_t)g.Q * g.P));
+    uint4 acc;
+    VecMax<T, VEC>::init(acc);
+    for (int r = 0; r < g.R; ++r) {
+      int h = p * g.stride_h - g.pad_t + r;
+      if (h < 0 || h >= g.H) continue;
+      for (int s = 0; s < g.S; ++s) {
+        int w = q * g.stride_w - g.pad_l + s;
+        if (w < 0 || w >= g.W) continue;
+        uint4 v = *(const uint4*)(x + ((int64_t)(n * g.H + h) * g.W + w) * g.C + c);
+        VecMax<T, VEC>::upd(acc, v);
+      }
+    }
+    *(uint4*)(y + pix * g.C + c) = acc;
+  }
+}
+
+// -------------------------------------------------------------- element-wise ----
+__device__ __forceinline__ float unary_one(int op, float x, float a, float b) {
+  switch (op) {
+    case UN_RELU: return x > 0.f ? x : 0.f;
+    case UN_LEAKY: return x < 0.f ? __fmul_rn(a, x) : x;
+    case UN_CLAMP: return x < a ? a : (x > b ? b : x);
+    case UN_GELU_ERF: return apply_act(ACT_GELU_ERF, x, 0.f, 0.f);
+    case UN_GELU_TANH: return apply_act(ACT_GELU_TANH, x, 0.f, 0.f);
+    case UN_ERF: return erff(x);
+    case UN_SIGMOID: return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x)));
+    case UN_TANH: return tanhf(x);
+    case UN_EXP: return expf(x);
+    case UN_LOG: return logf(x);
+    case UN_SQRT: return __fsqrt_rn(x);
+    case UN_RSQRT: return __fdiv_rn(1.0f, __fsqrt_rn(x));
+    case UN_ABS: return fabsf(x);
+    case UN_NEG: return -x;
+    case UN_RECIP: return __fdiv_rn(1.0f, x);
+    case UN_ROUND: return rintf(x);
+  }
+  return x;
+}
+__global__ void unary_kernel(int op, int dt_in, int dt_out, const void* x, void* y, int64_t n, float a, float b) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    store_from_float(y, dt_out, i, unary_one(op, load_as_float(x, dt_in, i), a, b));
+}
+// 16-byte path for fp16 -> fp16.
+__global__ void unary_h8_kernel(int op, const uint4* __restrict__ x, uint4* __restrict__ y, int64_t n8, float a, float b) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
+    uint4 v = x[i];
+    __half* h = (__half*)&v;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(unary_one(op, __half2float(h[j]), a, b));
+    y[i] = v;
+  }
+}
+__device__ __forceinline__ float binary_one(int op, float x, float y) {
+  switch (op) {
+    case BIN_ADD: return __fadd_rn(x, y);
+    case BIN_SUB: return __fsub_rn(x, y);
+    case BIN_MUL: return __fmul_rn(x, y);
+    case BIN_DIV: return __fdiv_rn(x, y);
+    case BIN_POW: return powf(x, y);
+    case BIN_PRELU: return x < 0.f ? __fmul_rn(x, y) : x;
+  }
+  return x;
+}
+__global__ void binary_kernel(int op, BinaryGeom g, int dt_l, int dt_r, int dt_out, const void* l, const void* r, void* y,
+                              int64_t total, int act, float act_a) {
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    int64_t rem = e, li = 0, ri = 0;
+    for (int d = g.rank - 1; d >= 0; --d) {
+      int64_t p = rem % g.oshape[d];
+      rem /= g.oshape[d];
+      li += p * g.lstride[d];
+      ri += p * g.rstride[d];
+    }
+    float v = binary_one(op, load_as_float(l, dt_l, li), load_as_float(r, dt_r, ri));
+    store_from_float(y, dt_out, e, apply_act(act, v, act_a, 0.f));
+  }
+}
+// Same-shape fp16 fast path, 16 bytes per thread.
+__global__ void binary_same_h8_kernel(int op, const uint4* __restrict__ l, const uint4* __restrict__ r, uint4* __restrict__ y,
+                                      int64_t n8, int act, float act_a) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
+    uint4 a = l[i], b = r[i];
+    __half* ha = (__half*)&a;
+    const __half* hb = (const __half*)&b;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      ha[j] = __float2half_rn(apply_act(act, binary_one(op, __half2float(ha[j]), __half2float(hb[j])), act_a, 0.f));
+    y[i] = a;
+  }
+}
+__global__ void channel_affine_kernel(int dt, const void* x, void* y, const float* a, const float* b, int64_t total, int64_t C,
+                                      int64_t inner) {
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    int c = (int)((e / inner) % C);
+    store_from_float(y, dt, e, __fadd_rn(__fmul_rn(load_as_float(x, dt, e), a[c]), b[c]));
+  }
+}
+
+// ------------------------------------------------------ soft-max / reductions ----
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+// One warp per row along a contiguous last axis.
+__global__ void softmax_rows_kernel(int dt, const void* x, void* y, int64_t rows, int64_t dim, int log_form) {
+  int lane = threadIdx.x & 31;
+  int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t row = warp; row < rows; row += nwarps) {
+    int64_t base = row * dim;
+    float mx = -3.402823466e+38f;
+    for (int64_t d = lane; d < dim; d += 32) mx = fmaxf(mx, load_as_float(x, dt, base + d));
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int64_t d = lane; d < dim; d += 32) sum += expf(load_as_float(x, dt, base + d) - mx);
+    sum = warp_sum(sum);
+    float lsum = logf(sum);
+    for (int64_t d = lane; d < dim; d += 32) {
+      float v = load_as_float(x, dt, base + d) - mx;
+      store_from_float(y, dt, base + d, log_form ? v - lsum : __fdiv_rn(expf(v), sum));
+    }
+  }
+}
+// Strided axis: one thread per (outer, inner) pair.
+__global__ void softmax_strided_kernel(int dt, const void* x, void* y, int64_t outer, int64_t dim, int64_t inner, int log_form) {
+  int64_t total = outer * inner;
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    int64_t base = (e / inner) * dim * inner + e % inner;
+    float mx = -3.402823466e+38f, sum = 0.f;
+    for (int64_t d = 0; d < dim; ++d) mx = fmaxf(mx, load_as_float(x, dt, base + d * inner));
+    for (int64_t d = 0; d < dim; ++d) sum += expf(load_as_float(x, dt, base + d * inner) - mx);
+    float lsum = logf(sum);
+    for (int64_t d = 0; d < dim; ++d) {
+      float v = load_as_float(x, dt, base + d * inner) - mx;
+      store_from_float(y, dt, base + d * inner, log_form ? v - lsum : __fdiv_rn(expf(v), sum));
+    }
+  }
+}
+__global__ void reduce_mean_axis_kernel(int dt_in, int dt_out, const void* x, void* y, int64_t before, int64_t dim, int64_t after) {
+  int64_t total = before * after;
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    int64_t i = e / after, k = e % after;
+    float s = load_as_float(x, dt_in, (i * dim) * after + k);
+    for (int64_t j = 1; j < dim; ++j) s = __fadd_rn(s, load_as_float(x, dt_in, (i * dim + j) * after + k));
+    store_from_float(y, dt_out, e, __fdiv_rn(s, (float)dim));
+  }
+}
+__global__ void layernorm_kernel(int dt, const void* x, void* y, const float* gamma, const float* beta, int64_t rows, int64_t dim,
+                                 float eps) {
+  int lane = threadIdx.x & 31;
+  int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t row = warp; row < rows; row += nwarps) {
+    int64_t base = row * dim;
+    float s = 0.f;
+    for (int64_t d = lane; d < dim; d += 32) s += load_as_float(x, dt, base + d);
+    float mean = warp_sum(s) / (float)dim;
+    float v = 0.f;
+    for (int64_t d = lane; d < dim; d += 32) { float t = load_as_float(x, dt, base + d) - mean; v += t * t; }
+    float inv = 1.0f / sqrtf(warp_sum(v) / (float)dim + eps);
+    for (int64_t d = lane; d < dim; d += 32) {
+      float t = (load_as_float(x, dt, base + d) - mean) * inv;
+      store_from_float(y, dt, base + d, t * (gamma ? gamma[d] : 1.f) + (beta ? beta[d] : 0.f));
+    }
+  }
+}
+
+// ------------------------------------------------------------- quantisation ----
+__global__ void quantize_kernel(int dt_in, const void* x, void* q, const float* scale, const int* zp, int64_t total, int64_t adim,
+                                int64_t inner, int per_axis, int is_unsigned) {
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    int a = per_axis ? (int)((e / inner) % adim) : 0;
+    float r = rintf(__fdiv_rn(load_as_float(x, dt_in, e), scale[a]));
+    if (zp) r = __fadd_rn(r, (float)zp[a]);
+    if (is_unsigned) ((uint8_t*)q)[e] = sat_u8(r); else ((int8_t*)q)[e] = sat_s8(r);
+  }
+}
+// Per-tensor fp32 -> int8, 16 elements per thread (four 16-byte loads, one 16-byte store).
+__global__ void quantize_f32_s8_vec_kernel(const float4* __restrict__ x, uint4* __restrict__ q, const float* scale, int64_t n16) {
+  float s = scale[0];
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n16; i += (int64_t)gridDim.x * blockDim.x) {
+    uint4 out;
+    uint32_t* o = (uint32_t*)&out;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float4 v = x[i * 4 + j];
+      int a = sat_s8(rintf(__fdiv_rn(v.x, s))), b = sat_s8(rintf(__fdiv_rn(v.y, s)));
+      int c = sat_s8(rintf(__fdiv_rn(v.z, s))), d = sat_s8(rintf(__fdiv_rn(v.w, s)));
+      o[j] = (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) | ((uint32_t)(d & 0xff) << 24);
+    }
+    q[i] = out;
+  }
+}
+__global__ void dequantize_kernel(int dt_out, const void* q, void* x, const float* scale, const int* zp, int64_t total, int64_t adim,
+                                  int64_t inner, int per_axis, int is_unsigned) {
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    int a = per_axis ? (int)((e / inner) % adim) : 0;
+    float v = is_unsigned ? (float)((const uint8_t*)q)[e] : (float)((const int8_t*)q)[e];
+    if (zp) v = __fsub_rn(v, (float)zp[a]);
+    store_from_float(x, dt_out, e, __fmul_rn(v, scale[a]));
+  }
+}
+__global__ void convert_kernel(int dt_in, int dt_out, const void* x, void* y, int64_t n) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    if (dt_in == DT_S64 && dt_out == DT_S32) { ((int32_t*)y)[i] = (int32_t)((const long long*)x)[i]; continue; }
+    if (dt_in == DT_S32 && dt_out == DT_S64) { ((long long*)y)[i] = ((const int32_t*)x)[i]; continue; }
+    store_from_float(y, dt_out, i, load_as_float(x, dt_in, i));
+  }
+}
+// fp32 -> fp16, 8 elements per thread.
+__global__ void convert_f32_f16_vec_kernel(const float4* __restrict__ x, uint4* __restrict__ y, int64_t n8) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
+    float4 a = x[2 * i], b = x[2 * i + 1];
+    uint4 o;
+    __half2* h = (__half2*)&o;
+    h[0] = __floats2half2_rn(a.x, a.y); h[1] = __floats2half2_rn(a.z, a.w);
+    h[2] = __floats2half2_rn(b.x, b.y); h[3] = __floats2half2_rn(b.z, b.w);
+    y[i] = o;
+  }
+}
+
+// ------------------------------------------------------------- data movement ----
+template <typename T>
+__global__ void move_kernel(MoveGeom g, const T* __restrict__ x, T* __restrict__ y, int64_t total) {
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    int64_t rem = e, si = g.in_offset, di = g.out_offset;
+    for (int d = g.rank - 1; d >= 0; --d) {
+      int64_t p = rem % g.oshape[d];
+      rem /= g.oshape[d];
+      si += p * g.istride[d];
+      di += p * g.ostride[d];
+    }
+    y[di] = x[si];
+  }
+}
+template <typename T>
+__global__ void resize_nearest_kernel(const T* __restrict__ x, T* __restrict__ y, int N, int H, int W, int C, int P, int Q, int nhwc) {
+  int64_t total = (int64_t)N * P * Q * C;
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    int c, q, p, n;
+    if (nhwc) { c = (int)(e % C); q = (int)((e / C) % Q); p = (int)((e / ((int64_t)C * Q)) % P); n = (int)(e / ((int64_t)C * Q * P)); }
+    else { q = (int)(e % Q); p = (int)((e / Q) % P); c = (int)((e / ((int64_t)Q * P)) % C); n = (int)(e / ((int64_t)Q * P * C)); }
+    int h = (int)roundf(((float)p + 0.5f) * (float)H / (float)P - 0.5f);
+    int w = (int)roundf(((float)q + 0.5f) * (float)W / (float)Q - 0.5f);
+    h = min(max(h, 0), H - 1);
+    w = min(max(w, 0), W - 1);
+    int64_t src = nhwc ? (((int64_t)n * H + h) * W + w) * C + c : (((int64_t)n * C + c) * H + h) * W + w;
+    y[e] = x[src];
+  }
+}
+template <typename T>
+__global__ void gather_kernel(const T* __restrict__ x, const void* idx, int idx_dt, T* __restrict__ y, int64_t outer, int64_t axis_dim,
+                              int64_t n_idx, int64_t inner) {
+  int64_t total = outer * n_idx * inner;
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    int64_t i = e % inner, k = (e / inner) % n_idx, o = e / (inner * n_idx);
+    int64_t id = idx_dt == DT_S64 ? ((const long long*)idx)[k] : (int64_t)((const int32_t*)idx)[k];
+    if (id < 0) id += axis_dim;
+    id = id < 0 ? 0 : (id >= axis_dim ? axis_dim - 1 : id);
+    y[e] = x[(o * axis_dim + id) * inner + i];
+  }
+}
+
+template <template <typename> class K, typename... Args>
+int dispatch_esz(int esz, int grid, int threads, cudaStream_t s, Args... args);
+
+}  // namespace
+
+// ----------------------------------------------------------------- launchers ----
+int conv_simt(const ConvGeom& g, int in_dt, const void* x, const void* w, void* y, const Epilogue& ep, cudaStream_t s) {
+  int64_t total = (int64_t)g.N * g.P * g.Q * g.K;
+  if (total <= 0) return 0;
+  int grid = grid_for(total, 256);
+  switch (in_dt) {
+    case DT_F32: conv_direct_kernel<float, float><<<grid, 256, 0, s>>>(g, (const float*)x, (const float*)w, y, ep); break;
+    case DT_F16: conv_direct_kernel<__half, float><<<grid, 256, 0, s>>>(g, (const __half*)x, (const __half*)w, y, ep); break;
+    case DT_BF16: conv_direct_kernel<__nv_bfloat16, float><<<grid, 256, 0, s>>>(g, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, y, ep); break;
+    case DT_S8: conv_direct_kernel<int8_t, int><<<grid, 256, 0, s>>>(g, (const int8_t*)x, (const int8_t*)w, y, ep); break;
+    default: return -1;
+  }
+  return check_launch();
+}
+int gemm_simt(const GemmGeom& g, int in_dt, const void* A, const void* B, void* C, const Epilogue& ep, cudaStream_t s) {
+  int64_t total = g.batch * g.M * g.N;
+  if (total <= 0) return 0;
+  int grid = grid_for(total, 256);
+  switch (in_dt) {
+    case DT_F32: gemm_direct_kernel<float, float><<<grid, 256, 0, s>>>(g, (const float*)A, (const float*)B, C, ep); break;
+    case DT_F16: gemm_direct_kernel<__half, float><<<grid, 256, 0, s>>>(g, (const __half*)A, (const __half*)B, C, ep); break;
+    case DT_BF16: gemm_direct_kernel<__nv_bfloat16, float><<<grid, 256, 0, s>>>(g, (const __nv_bfloat16*)A, (const __nv_bfloat16*)B, C, ep); break;
+    case DT_S8: gemm_direct_kernel<int8_t, int><<<grid, 256, 0, s>>>(g, (const int8_t*)A, (const int8_t*)B, C, ep); break;
+    default: return -1;
+  }
+  return check_launch();
+}
+int pool2d(const PoolGeom& g, int dt, bool is_max, const void* x, void* y, cudaStream_t s) {
+  int64_t total = (int64_t)g.N * g.P * g.Q * g.C;
+  if (total <= 0) return 0;
+  bool nhwc_dense = g.xs_c == 1 && g.xs_w == g.C && g.xs_h == (int64_t)g.W * g.C && g.ys_c == 1 && g.ys_w == g.C &&
+                    g.ys_h == (int64_t)g.Q * g.C && g.ys_n == (int64_t)g.P * g.Q * g.C && g.xs_n == (int64_t)g.H * g.W * g.C;
+  bool aligned = ((uintptr_t)x % 16 == 0) && ((uintptr_t)y % 16 == 0);
+  if (is_max && nhwc_dense && aligned) {
+    if (dt == DT_F16 && g.C % 8 == 0) { maxpool_nhwc_vec_kernel<__half, 8><<<grid_for(total / 8, 256), 256, 0, s>>>(g, (const __half*)x, (__half*)y); return check_launch(); }
+    if (dt == DT_BF16 && g.C % 8 == 0) { maxpool_nhwc_vec_kernel<__nv_bfloat16, 8><<<grid_for(total / 8, 256), 256, 0, s>>>(g, (const __nv_bfloat16*)x, (__nv_bfloat16*)y); return check_launch(); }
+    if (dt == DT_S8 && g.C % 16 == 0) { maxpool_nhwc_vec_kernel<int8_t, 16><<<grid_for(total / 16, 256), 256, 0, s>>>(g, (const int8_t*)x, (int8_t*)y); return check_launch(); }
+    if (dt == DT_F32 && g.C % 4 == 0) { maxpool_nhwc_vec_kernel<float, 4><<<grid_for(total / 4, 256), 256, 0, s>>>(g, (const float*)x, (float*)y); return check_launch(); }
+  }
+  if (is_max) pool_generic_kernel<true><<<grid_for(total, 256), 256, 0, s>>>(g, dt, x, y);
+  else pool_generic_kernel<false><<<grid_for(total, 256), 256, 0, s>>>(g, dt, x, y);
+  return check_launch();
+}
+int unary(int op, int dt_in, int dt_out, const void* x, void* y, int64_t n, float a, float b, cudaStream_t s) {
+  if (n <= 0) return 0;
+  if (dt_in == DT_F16 && dt_out == DT_F16 && n % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0) {
+    unary_h8_kernel<<<grid_for(n / 8, 256), 256, 0, s>>>(op, (const uint4*)x, (uint4*)y, n / 8, a, b);
+    return check_launch();
+  }
+  unary_kernel<<<grid_for(n, 256), 256, 0, s>>>(op, dt_in, dt_out, x, y, n, a, b);
+  return check_launch();
+}
+int binary(int op, const BinaryGeom& g, int dt_l, int dt_r, int dt_out, const void* l, const void* r, void* y, int act, float act_a,
+           cudaStream_t s) {
+  int64_t total = 1;
+  bool same = true;
+  int64_t acc = 1;
+  for (int d = g.rank - 1; d >= 0; --d) {
+    total *= g.oshape[d];
+    if (g.oshape[d] != 1 && (g.lstride[d] != acc || g.rstride[d] != acc)) same = false;
+    acc *= g.oshape[d];
+  }
+  if (total <= 0) return 0;
+  if (same && dt_l == DT_F16 && dt_r == DT_F16 && dt_out == DT_F16 && total % 8 == 0 && (uintptr_t)l % 16 == 0 &&
+      (uintptr_t)r % 16 == 0 && (uintptr_t)y % 16 == 0) {
+    binary_same_h8_kernel<<<grid_for(total / 8, 256), 256, 0, s>>>(op, (const uint4*)l, (const uint4*)r, (uint4*)y, total / 8, act, act_a);
+    return check_launch();
+  }
+  binary_kernel<<<grid_for(total, 256), 256, 0, s>>>(op, g, dt_l, dt_r, dt_out, l, r, y, total, act, act_a);
+  return check_launch();
+}
+int channel_affine(int dt, const void* x, void* y, const float* a, const float* b, int64_t outer, int64_t C, int64_t inner, cudaStream_t s) {
+  int64_t total = outer * C * inner;
+  if (total <= 0) return 0;
+  channel_affine_kernel<<<grid_for(total, 256), 256, 0, s>>>(dt, x, y, a, b, total, C, inner);
+  return check_launch();
+}
+int softmax(int dt, const void* x, void* y, int64_t outer, int64_t dim, int64_t inner, bool log_form, cudaStream_t s) {
+  if (outer * dim * inner <= 0) return 0;
+  if (inner == 1) softmax_rows_kernel<<<grid_for(outer * 32, 256), 256, 0, s>>>(dt, x, y, outer, dim, log_form);
+  else softmax_strided_kernel<<<grid_for(outer * inner, 128), 128, 0, s>>>(dt, x, y, outer, dim, inner, log_form);
+  return check_launch();
+}
+int reduce_mean_axis(int dt_in, int dt_out, const void* x, void* y, int64_t before, int64_t dim, int64_t after, cudaStream_t s) {
+  if (before * after <= 0) return 0;
+  reduce_mean_axis_kernel<<<grid_for(before * after, 128), 128, 0, s>>>(dt_in, dt_out, x, y, before, dim, after);
+  return check_launch();
+}
+int layernorm(int dt, const void* x, void* y, const float* gamma, const float* beta, int64_t rows, int64_t dim, float eps, cudaStream_t s) {
+  if (rows * dim <= 0) return 0;
+  layernorm_kernel<<<grid_for(rows * 32, 256), 256, 0, s>>>(dt, x, y, gamma, beta, rows, dim, eps);
+  return check_launch();
+}
+int quantize(int dt_in, const void* x, void* q, const float* scale, const int* zp, int64_t outer, int64_t adim, int64_t inner,
+             bool per_axis, bool is_unsigned, cudaStream_t s) {
+  int64_t total = outer * adim * inner;
+  if (total <= 0) return 0;
+  if (dt_in == DT_F32 && !per_axis && !zp && !is_unsigned && total % 16 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)q % 16 == 0) {
+    quantize_f32_s8_vec_kernel<<<grid_for(total / 16, 256), 256, 0, s>>>((const float4*)x, (uint4*)q, scale, total / 16);
+    return check_launch();
+  }
+  quantize_kernel<<<grid_for(total, 256), 256, 0, s>>>(dt_in, x, q, scale, zp, total, adim, inner, per_axis, is_unsigned);
+  return check_launch();
+}
+int dequantize(int dt_out, const void* q, void* x, const float* scale, const int* zp, int64_t outer, int64_t adim, int64_t inner,
+               bool per_axis, bool is_unsigned, cudaStream_t s) {
+  int64_t total = outer * adim * inner;
+  if (total <= 0) return 0;
+  dequantize_kernel<<<grid_for(total, 256), 256, 0, s>>>(dt_out, q, x, scale, zp, total, adim, inner, per_axis, is_unsigned);
+  return check_launch();
+}
+int convert(int dt_in, int dt_out, const void* x, void* y, int64_t n, cudaStream_t s) {
+  if (n <= 0) return 0;
+  if (dt_in == DT_F32 && dt_out == DT_F16 && n % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0) {
+    convert_f32_f16_vec_kernel<<<grid_for(n / 8, 256), 256, 0, s>>>((const float4*)x, (uint4*)y, n / 8);
+    return check_launch();
+  }
+  convert_kernel<<<grid_for(n, 256), 256, 0, s>>>(dt_in, dt_out, x, y, n);
+  return check_launch();
+}
+int move(const MoveGeom& g, int esz, const void* x, void* y, cudaStream_t s) {
+  int64_t total = 1;
+  for (int d = 0; d < g.rank; ++d) total *= g.oshape[d];
+  if (total <= 0) return 0;
+  int grid = grid_for(total, 256);
+  switch (esz) {
+    case 1: move_kernel<uint8_t><<<grid, 256, 0, s>>>(g, (const uint8_t*)x, (uint8_t*)y, total); break;
+    case 2: move_kernel<uint16_t><<<grid, 256, 0, s>>>(g, (const uint16_t*)x, (uint16_t*)y, total); break;
+    case 4: move_kernel<uint32_t><<<grid, 256, 0, s>>>(g, (const uint32_t*)x, (uint32_t*)y, total); break;
+    case 8: move_kernel<uint64_t><<<grid, 256, 0, s>>>(g, (const uint64_t*)x, (uint64_t*)y, total); break;
+    default: return -1;
+  }
+  return check_launch();
+}
+int resize_nearest(int esz, const void* x, void* y, int N, int H, int W, int C, int P, int Q, bool nhwc, cudaStream_t s) {
+  int64_t total = (int64_t)N * P * Q * C;
+  if (total <= 0) return 0;
+  int grid = grid_for(total, 256);
+  switch (esz) {
+    case 1: resize_nearest_kernel<uint8_t><<<grid, 256, 0, s>>>((const uint8_t*)x, (uint8_t*)y, N, H, W, C, P, Q, nhwc); break;
+    case 2: resize_nearest_kernel<uint16_t><<<grid, 256, 0, s>>>((const uint16_t*)x, (uint16_t*)y, N, H, W, C, P, Q, nhwc); break;
+    case 4: resize_nearest_kernel<uint32_t><<<grid, 256, 0, s>>>((const uint32_t*)x, (uint32_t*)y, N, H, W, C, P, Q, nhwc); break;
+    default: return -1;
+  }
+  return check_launch();
+}
+int gather(int esz, const void* x, const void* idx, int idx_dt, void* y, int64_t outer, int64_t axis_dim, int64_t n_idx, int64_t inner,
+           cudaStream_t s) {
+  int64_t total = outer * n_idx * inner;
+  if (total <= 0) return 0;
+  int grid = grid_for(total, 256);
+  switch (esz) {
+    case 1: gather_kernel<uint8_t><<<grid, 256, 0, s>>>((const uint8_t*)x, idx, idx_dt, (uint8_t*)y, outer, axis_dim, n_idx, inner); break;
+    case 2: gather_kernel<uint16_t><<<grid, 256, 0, s>>>((const uint16_t*)x, idx, idx_dt, (uint16_t*)y, outer, axis_dim, n_idx, inner); break;
+    case 4: gather_kernel<uint32_t><<<grid, 256, 0, s>>>((const uint32_t*)x, idx, idx_dt, (uint32_t*)y, outer, axis_dim, n_idx, inner); break;
+    default: return -1;
+  }
+  return check_launch();
+}
+
+}  // namespace b200

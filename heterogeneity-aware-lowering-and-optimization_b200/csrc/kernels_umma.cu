@@ -1,0 +1,563 @@
+// NHWC implicit-GEMM convolution and GEMM on the Blackwell tensor cores (sm_100a).
+//
+//   D[M, K_out] = A[M, R*S*C] * B[K_out, R*S*C]^T       M = N*P*Q output pixels
+//
+// A is never materialised: a TMA load in im2col mode (cp.async.bulk.tensor.4d...im2col) gathers,
+// for one filter tap (r,s) and one chunk of input channels, the 128 input pixels that feed 128
+// consecutive output pixels, applying stride and zero padding in hardware.  A 1x1 / stride-1 /
+// unpadded convolution and a plain GEMM use an ordinary tiled 2-d load instead.  B (filters
+// repacked to [K_out][R*S][C]) comes through a tiled 3-d load, so the channel tail of a tap is
+// zero-filled rather than running into the next tap.  Both land in shared memory in the
+// 128/64/32-byte swizzled K-major layout that tcgen05.mma reads through shared-memory descriptors.
+//
+// One persistent CTA per SM walks its tiles (128 pixels x BN channels):
+//   warp 0      producer: waits for a free stage, arms its mbarrier with the byte count, issues TMA
+//   warp 1      allocates tensor memory, issues tcgen05.mma (one lane), commits to mbarriers
+//   warps 2..5  epilogue: tcgen05.ld the fp32 / int32 accumulators (one TMEM lane = one output pixel
+//               per thread), apply the fused epilogue, store NHWC rows with 16-byte stores
+// Two accumulator buffers in tensor memory let the epilogue of tile i overlap the MMAs of tile i+1.
+//
+// Every mbarrier wait is bounded: when the limit expires the waiter records a code in the
+// plan's status word, raises a CTA-wide abort flag, and every role falls through to the common
+// exit where tensor memory is released.  The host reports ODLA_TIMEOUT.
+#include <cuda.h>
+
+#include <cstdio>
+#include <cstring>
+
+#include "epilogue.cuh"
+
+namespace b200 {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int kThreads = 192;
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+struct UmmaParams {
+  int M_total, K_out, C, R, S, P, Q;
+  int stride_h, stride_w, pad_t, pad_l;
+  int im2col;          // 1: im2col TMA for A, 0: tiled 2-d TMA
+  int kbe;             // elements of K per stage
+  int kb_bytes;        // bytes of K per stage: 128, 64 or 32 (= swizzle span)
+  int chunks_per_tap;  // ceil(C / kbe)
+  int num_kb;          // R*S*chunks_per_tap
+  int BN, stages, m_tiles, n_tiles, total_tiles;
+  uint32_t idesc;      // tcgen05 instruction descriptor
+  uint32_t desc_hi;    // upper 32 bits of the shared-memory matrix descriptors
+  int acc_int;         // accumulators are int32
+  int tmem_cols;
+  void* y;
+  int* status;
+  Epilogue ep;
+};
+
+// ---------------------------------------------------------------- PTX wrappers ----
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false when the limit expired or another role already aborted.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023) == 1023 && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  if (status) { atomicCAS(status, 0, code); status[1] = (int)blockIdx.x; }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
+               "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_u32(dst)),
+               "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+__device__ __forceinline__ void tma_load_im2col_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c, int w, int h, int n,
+                                                   uint16_t off_w, uint16_t off_h) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};" ::"r"(
+          smem_u32(dst)),
+      "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
+// ------------------------------------------------------------------- epilogue ----
+// One thread owns one output pixel (row) and 32 consecutive channels held in v[].
+__device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, float* v, int64_t row, int col0, int ncols) {
+  const Epilogue& ep = p.ep;
+  if (ep.mul) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(v[j], __ldg(ep.mul + min(col0 + j, p.K_out - 1)));
+  }
+  if (ep.alpha != 1.f) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(v[j], ep.alpha);
+  }
+  if (ep.add1) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], __ldg(ep.add1 + min(col0 + j, p.K_out - 1)));
+  }
+  if (ep.add2) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], __ldg(ep.add2 + min(col0 + j, p.K_out - 1)));
+  }
+  if (ep.add_full) {
+    for (int j = 0; j < ncols; ++j)
+      v[j] = __fadd_rn(v[j], __fmul_rn(ep.beta_full, load_as_float(ep.add_full, ep.add_full_dt, row * p.K_out + col0 + j)));
+  }
+  if (ep.act != ACT_NONE && ep.act_first) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = apply_act(ep.act, v[j], ep.act_a, ep.act_b);
+  }
+  if (ep.res) {
+    int64_t base = row * p.K_out + col0;
+    if (ncols == 32 && ep.res_dt == DT_F16 && ((p.K_out & 7) == 0)) {
+      const uint4* rp = (const uint4*)((const __half*)ep.res + base);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 u = __ldg(rp + q);
+        const __half2* h = (const __half2*)&u;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          float2 f = __half22float2(h[t]);
+          v[q * 8 + 2 * t] = __fadd_rn(v[q * 8 + 2 * t], f.x);
+          v[q * 8 + 2 * t + 1] = __fadd_rn(v[q * 8 + 2 * t + 1], f.y);
+        }
+      }
+    } else if (ncols == 32 && ep.res_dt == DT_S8 && ((p.K_out & 15) == 0)) {
+      const uint4* rp = (const uint4*)((const int8_t*)ep.res + base);
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        uint4 u = __ldg(rp + q);
+        const int8_t* b = (const int8_t*)&u;
+#pragma unroll
+        for (int t = 0; t < 16; ++t) v[q * 16 + t] = __fadd_rn(v[q * 16 + t], __fmul_rn((float)b[t], ep.res_scale));
+      }
+    } else {
+      for (int j = 0; j < ncols; ++j) {
+        float r = load_as_float(ep.res, ep.res_dt, base + j);
+        if (ep.res_dt == DT_S8) r = __fmul_rn(r, ep.res_scale);
+        v[j] = __fadd_rn(v[j], r);
+      }
+    }
+  }
+  if (ep.act != ACT_NONE && !ep.act_first) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = apply_act(ep.act, v[j], ep.act_a, ep.act_b);
+  }
+  // ---- store ----
+  int64_t obase = row * p.K_out + col0;
+  if (ep.out_dt == DT_F16) {
+    __half* out = (__half*)p.y + obase;
+    if (ncols == 32 && ((p.K_out & 7) == 0)) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 u;
+        __half2* h = (__half2*)&u;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) h[t] = __floats2half2_rn(v[q * 8 + 2 * t], v[q * 8 + 2 * t + 1]);
+        ((uint4*)out)[q] = u;
+      }
+    } else {
+      for (int j = 0; j < ncols; ++j) out[j] = __float2half_rn(v[j]);
+    }
+  } else if (ep.out_dt == DT_BF16) {
+    __nv_bfloat16* out = (__nv_bfloat16*)p.y + obase;
+    if (ncols == 32 && ((p.K_out & 7) == 0)) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 u;
+        __nv_bfloat162* h = (__nv_bfloat162*)&u;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) h[t] = __floats2bfloat162_rn(v[q * 8 + 2 * t], v[q * 8 + 2 * t + 1]);
+        ((uint4*)out)[q] = u;
+      }
+    } else {
+      for (int j = 0; j < ncols; ++j) out[j] = __float2bfloat16_rn(v[j]);
+    }
+  } else if (ep.out_dt == DT_S8) {
+    int8_t* out = (int8_t*)p.y + obase;
+    if (ncols == 32 && ((p.K_out & 15) == 0)) {
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        uint4 u;
+        uint32_t* w = (uint32_t*)&u;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          uint32_t packed = 0;
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {
+            int qv = sat_s8(rintf(__fdiv_rn(v[q * 16 + t * 4 + b], ep.out_scale)));
+            packed |= (uint32_t)(qv & 0xff) << (8 * b);
+          }
+          w[t] = packed;
+        }
+        ((uint4*)out)[q] = u;
+      }
+    } else {
+      for (int j = 0; j < ncols; ++j) out[j] = sat_s8(rintf(__fdiv_rn(v[j], ep.out_scale)));
+    }
+  } else {  // DT_F32
+    float* out = (float*)p.y + obase;
+    if (ncols == 32 && ((p.K_out & 3) == 0)) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) ((float4*)out)[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+    } else {
+      for (int j = 0; j < ncols; ++j) out[j] = v[j];
+    }
+  }
+}
+
+// --------------------------------------------------------------------- kernel ----
+__global__ void __launch_bounds__(kThreads, 1)
+umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const UmmaParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // operand stages start on a 1024-byte boundary (the 128-byte swizzle repeats every 1024 bytes)
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int a_bytes = BM * p.kb_bytes, b_bytes = p.BN * p.kb_bytes, stage_bytes = a_bytes + b_bytes;
+  uint8_t* ctrl = smem + (size_t)p.stages * stage_bytes;
+  uint64_t* full_bar = (uint64_t*)ctrl;            // [stages]
+  uint64_t* empty_bar = full_bar + 16;             // [stages]
+  uint64_t* tfull_bar = empty_bar + 16;            // [2]
+  uint64_t* tempty_bar = tfull_bar + 2;            // [2]
+  uint32_t* tmem_slot = (uint32_t*)(tempty_bar + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], 4); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)p.tmem_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer ----
+    if (elect_one()) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * p.BN;
+        int w0 = 0, h0 = 0, img = 0;
+        if (p.im2col) {
+          const int pq = p.P * p.Q;
+          img = m0 / pq;
+          const int rem = m0 - img * pq;
+          const int op = rem / p.Q, oq = rem - op * p.Q;
+          w0 = oq * p.stride_w - p.pad_l;
+          h0 = op * p.stride_h - p.pad_t;
+        }
+        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+          const int s = it % p.stages;
+          const uint32_t ph = (it / p.stages) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
+          const int tap = kb / p.chunks_per_tap, c0 = (kb - tap * p.chunks_per_tap) * p.kbe;
+          uint8_t* sa = smem + (size_t)s * stage_bytes;
+          uint8_t* sb = sa + a_bytes;
+          mbar_expect_tx(&full_bar[s], (uint32_t)stage_bytes);
+          if (p.im2col) {
+            const int fr = tap / p.S, fs = tap - fr * p.S;
+            tma_load_im2col_4d(sa, &tmA, &full_bar[s], c0, w0, h0, img, (uint16_t)fs, (uint16_t)fr);
+          } else {
+            tma_load_2d(sa, &tmA, &full_bar[s], c0, m0);
+          }
+          tma_load_3d(sb, &tmB, &full_bar[s], c0, tap, n0);
+        }
+      }
+      if (!ok) {
+        // give copies already in flight a bounded chance to land before shared memory goes away
+        for (int s = 0; s < p.stages; ++s)
+          for (uint32_t i = 0; i < 4096; ++i)
+            if (mbar_try_wait(&full_bar[s], 0) || mbar_try_wait(&full_bar[s], 1)) break;
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer ----
+    if (elect_one()) {
+      uint32_t it = 0, tcount = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++tcount) {
+        const uint32_t acc = tcount & 1, acc_ph = (tcount >> 1) & 1;
+        if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1, abort_flag, p.status, 2)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * (uint32_t)p.BN;
+        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+          const int s = it % p.stages;
+          const uint32_t ph = (it / p.stages) & 1;
+          if (!mbar_wait(&full_bar[s], ph, abort_flag, p.status, 3)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + (size_t)s * stage_bytes), sb = sa + a_bytes;
+          const uint64_t da = ((uint64_t)p.desc_hi << 32) | (uint64_t)((sa & 0x3FFFF) >> 4) | (1ull << 16);
+          const uint64_t db = ((uint64_t)p.desc_hi << 32) | (uint64_t)((sb & 0x3FFFF) >> 4) | (1ull << 16);
+          const int ksteps = p.kb_bytes >> 5;  // 32 bytes of K per instruction
+          for (int k = 0; k < ksteps; ++k) {
+            const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
+            if (p.acc_int) umma_i8(tmem_d, da + 2 * k, db + 2 * k, p.idesc, accum);
+            else umma_f16(tmem_d, da + 2 * k, db + 2 * k, p.idesc, accum);
+          }
+          umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
+        }
+        if (ok) umma_commit(&tfull_bar[acc]);  // accumulator complete
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue ----
+    const int quarter = warp & 3;  // the TMEM lanes this warp may read: 32*quarter .. +31
+    uint32_t tcount = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++tcount) {
+      const uint32_t acc = tcount & 1, acc_ph = (tcount >> 1) & 1;
+      const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * p.BN;
+      if (!mbar_wait(&tfull_bar[acc], acc_ph, abort_flag, p.status, 4)) { ok = false; break; }
+      tc_fence_after();
+      const int64_t row = (int64_t)m0 + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * (uint32_t)p.BN;
+      for (int c = 0; c < p.BN; c += 32) {
+        const int col0 = n0 + c;
+        if (col0 >= p.K_out) break;  // uniform across the warp
+        uint32_t r[32];
+        tmem_ld32(taddr + (uint32_t)c, r);
+        tmem_ld_wait();
+        if (row < p.M_total) {
+          const int ncols = min(32, p.K_out - col0);
+          if (p.ep.out_dt == DT_S32) {
+            int32_t* out = (int32_t*)p.y + row * p.K_out + col0;
+            for (int j = 0; j < ncols; ++j) out[j] = (int32_t)r[j];
+          } else {
+            float v[32];
+            if (p.acc_int) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = (float)(int32_t)r[j];
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            }
+            epilogue_chunk(p, v, row, col0, ncols);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+    }
+  }
+  // ------------------------------------------------------------------ teardown ----
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols) : "memory");
+  }
+}
+
+// ------------------------------------------------------------- host: tensor maps ----
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const int*, const int*,
+                                   cuuint32_t, cuuint32_t, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode_tiled = nullptr;
+EncodeIm2colFn g_encode_im2col = nullptr;
+bool load_driver_entry_points() {
+  if (g_encode_tiled && g_encode_im2col) return true;
+  void* f = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess || !f) return false;
+  g_encode_tiled = (EncodeTiledFn)f;
+  f = nullptr;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &f, cudaEnableDefault, &q) != cudaSuccess || !f) return false;
+  g_encode_im2col = (EncodeIm2colFn)f;
+  return true;
+}
+int elem_bytes(int dt) { return dt == DT_S8 ? 1 : 2; }
+int pick_kb_bytes(int c_bytes) { return c_bytes > 64 ? 128 : (c_bytes > 32 ? 64 : 32); }
+int pick_bn(int k_out) { return k_out <= 64 ? 64 : (k_out <= 128 ? 128 : 256); }
+
+}  // namespace
+
+struct UmmaLaunch {
+  CUtensorMap tmA, tmB;
+  UmmaParams p;
+  int grid;
+  size_t smem;
+};
+
+bool umma_conv_supported(const UmmaConv& c) {
+  if (c.in_dt != DT_F16 && c.in_dt != DT_BF16 && c.in_dt != DT_S8) return false;
+  int es = elem_bytes(c.in_dt);
+  if (((int64_t)c.C * es) % 16 != 0) return false;   // TMA strides and channel coordinates must be 16-byte multiples
+  if (c.C * es < 32) return false;
+  if (c.K < 1 || c.R < 1 || c.S < 1 || c.R * c.S > 4096) return false;
+  if (c.stride_h < 1 || c.stride_w < 1 || c.stride_h > 8 || c.stride_w > 8) return false;
+  if (c.pad_t > 127 || c.pad_l > 127 || c.R > 128 || c.S > 128) return false;  // im2col corners are 8-bit
+  if ((int64_t)c.N * c.P * c.Q >= (1ll << 31)) return false;
+  if (c.H < 1 || c.W < 1 || c.P < 1 || c.Q < 1) return false;
+  return true;
+}
+
+UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, void* y, const Epilogue& ep, int* status, int sms) {
+  if (!umma_conv_supported(c) || !load_driver_entry_points()) return nullptr;
+  auto* L = new UmmaLaunch();
+  UmmaParams& p = L->p;
+  const int es = elem_bytes(c.in_dt);
+  p.M_total = c.N * c.P * c.Q; p.K_out = c.K; p.C = c.C; p.R = c.R; p.S = c.S; p.P = c.P; p.Q = c.Q;
+  p.stride_h = c.stride_h; p.stride_w = c.stride_w; p.pad_t = c.pad_t; p.pad_l = c.pad_l;
+  p.im2col = !(c.R == 1 && c.S == 1 && c.stride_h == 1 && c.stride_w == 1 && c.pad_t == 0 && c.pad_l == 0 && c.P == c.H && c.Q == c.W);
+  p.kb_bytes = pick_kb_bytes(c.C * es);
+  p.kbe = p.kb_bytes / es;
+  p.chunks_per_tap = (c.C + p.kbe - 1) / p.kbe;
+  p.num_kb = c.R * c.S * p.chunks_per_tap;
+  p.BN = pick_bn(c.K);
+  p.m_tiles = (p.M_total + BM - 1) / BM;
+  p.n_tiles = (c.K + p.BN - 1) / p.BN;
+  p.total_tiles = p.m_tiles * p.n_tiles;
+  const int stage_bytes = (BM + p.BN) * p.kb_bytes;
+  p.stages = (200 * 1024) / stage_bytes;
+  if (p.stages > 8) p.stages = 8;
+  if (p.stages > p.num_kb + 1) p.stages = p.num_kb + 1 > 2 ? p.num_kb + 1 : 2;
+  p.acc_int = c.in_dt == DT_S8;
+  p.tmem_cols = 2 * p.BN;  // 128, 256 or 512: powers of two >= 32
+  const uint32_t fmt = c.in_dt == DT_BF16 ? 1u : (c.in_dt == DT_S8 ? 1u : 0u);      // bf16 / signed 8-bit / f16
+  const uint32_t cfmt = p.acc_int ? 2u : 1u;                                        // s32 / f32 accumulators
+  p.idesc = (cfmt << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(p.BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+  const uint32_t layout = p.kb_bytes == 128 ? 2u : (p.kb_bytes == 64 ? 4u : 6u);    // swizzle mode of the operand tiles
+  const uint32_t sbo = (uint32_t)(8 * p.kb_bytes) >> 4;                             // 8-row group pitch, 16-byte units
+  p.desc_hi = sbo | (1u << 14) | (layout << 29);                                    // bits 32-45 SBO, 46-47 version 1, 61-63 layout
+  p.y = y; p.status = status; p.ep = ep;
+  L->grid = p.total_tiles < sms ? p.total_tiles : sms;
+  L->smem = (size_t)p.stages * stage_bytes + 1024 /*alignment slack*/ + 512 /*barriers*/;
+
+  const CUtensorMapDataType dt = c.in_dt == DT_S8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : (c.in_dt == DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+  const CUtensorMapSwizzle sw = p.kb_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (p.kb_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+  CUresult r;
+  if (p.im2col) {
+    cuuint64_t dims[4] = {(cuuint64_t)c.C, (cuuint64_t)c.W, (cuuint64_t)c.H, (cuuint64_t)c.N};
+    cuuint64_t strides[3] = {(cuuint64_t)c.C * es, (cuuint64_t)c.W * c.C * es, (cuuint64_t)c.H * c.W * c.C * es};
+    // The box of filter-window origins: from -pad to the last origin that still yields an output.
+    int lower[2] = {-c.pad_l, -c.pad_t};
+    // The last origin is (Q-1)*stride - pad; the upper corner is that position relative to W-1 (H-1).
+    int upper[2] = {(c.Q - 1) * c.stride_w - c.pad_l - (c.W - 1), (c.P - 1) * c.stride_h - c.pad_t - (c.H - 1)};
+    if (upper[0] < -128 || upper[0] > 127 || upper[1] < -128 || upper[1] > 127) { delete L; return nullptr; }
+    cuuint32_t estr[4] = {1, (cuuint32_t)c.stride_w, (cuuint32_t)c.stride_h, 1};
+    r = g_encode_im2col(&L->tmA, dt, 4, (void*)x, dims, strides, lower, upper, (cuuint32_t)p.kbe, (cuuint32_t)BM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS) {
+      // Drivers up to 13.1 encode small im2col tensors (< 128 KiB) with a flag that makes the load
+      // misbehave; CUTLASS clears bit 21 of the second descriptor word in that case
+      // (cute/atom/copy_traits_sm90_im2col.hpp), and so does this library.
+      int drv = 0;
+      cudaDriverGetVersion(&drv);
+      if (drv <= 13010 && (int64_t)c.N * c.H * c.W * c.C * es < 131072) ((uint64_t*)&L->tmA)[1] &= ~(1ull << 21);
+    }
+  } else {
+    cuuint64_t dims[2] = {(cuuint64_t)c.C, (cuuint64_t)p.M_total};
+    cuuint64_t strides[1] = {(cuuint64_t)c.C * es};
+    cuuint32_t box[2] = {(cuuint32_t)p.kbe, (cuuint32_t)BM};
+    cuuint32_t estr[2] = {1, 1};
+    r = g_encode_tiled(&L->tmA, dt, 2, (void*)x, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
+  if (r != CUDA_SUCCESS) { fprintf(stderr, "[odla_b200] tensor map (A) encode failed: %d\n", (int)r); delete L; return nullptr; }
+  {
+    cuuint64_t dims[3] = {(cuuint64_t)c.C, (cuuint64_t)(c.R * c.S), (cuuint64_t)c.K};
+    cuuint64_t strides[2] = {(cuuint64_t)c.C * es, (cuuint64_t)c.R * c.S * c.C * es};
+    cuuint32_t box[3] = {(cuuint32_t)p.kbe, 1, (cuuint32_t)p.BN};
+    cuuint32_t estr[3] = {1, 1, 1};
+    r = g_encode_tiled(&L->tmB, dt, 3, (void*)w, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
+  if (r != CUDA_SUCCESS) { fprintf(stderr, "[odla_b200] tensor map (B) encode failed: %d\n", (int)r); delete L; return nullptr; }
+  static bool attr_set[16] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 16 && !attr_set[dev]) {
+    if (cudaFuncSetAttribute(umma_conv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) { cudaGetLastError(); delete L; return nullptr; }
+    attr_set[dev] = true;
+  }
+  return L;
+}
+
+int umma_conv_run(UmmaLaunch* L, cudaStream_t stream) {
+  if (!L) return -1;
+  if (L->p.total_tiles <= 0) return 0;
+  umma_conv_kernel<<<L->grid, kThreads, L->smem, stream>>>(L->tmA, L->tmB, L->p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { fprintf(stderr, "[odla_b200] umma_conv launch failed: %s\n", cudaGetErrorString(e)); return -2; }
+  return 0;
+}
+void umma_conv_destroy(UmmaLaunch* L) { delete L; }
+
+}  // namespace b200

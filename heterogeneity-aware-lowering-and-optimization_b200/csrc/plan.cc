@@ -1,0 +1,1154 @@
+// Planning and execution.
+//
+// The recorded graph is turned, once per (GPU, shard batch), into a flat launch list:
+//   1. analysis   - use counts, which values carry the batch, which chains fold into a
+//                   convolution / GEMM epilogue (per-channel Add that carries a folded BN, residual
+//                   Add, Relu/LeakyRelu/Clamp/Gelu, Quantize) and which Dequantize nodes are
+//                   absorbed by their consumers (int8 operands, int8 residuals);
+//   2. placement  - liveness-based offsets inside one arena per plan;
+//   3. emission   - constants are converted / repacked on the host and uploaded once, tensor maps
+//                   are encoded, and each entry becomes a closure that enqueues its kernel.
+// odla_ExecuteComputation then shards dim 0 of every argument over the replicas (one per GPU,
+// weights replicated), and per GPU enqueues host-to-device copies, the launch list (replayed as a
+// CUDA graph when possible) and the copies of the output shards, on that GPU's own stream.  No
+// collective is involved: every op of a shardable graph is independent across the batch.
+#include <algorithm>
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+#include <functional>
+#include <set>
+
+#include "common.h"
+
+namespace b200 {
+
+int visible_devices() {
+  static int n = [] {
+    int c = 0;
+    if (cudaGetDeviceCount(&c) != cudaSuccess) { cudaGetLastError(); return 0; }
+    return c;
+  }();
+  return n;
+}
+
+Plan::~Plan() {
+  cudaSetDevice(device);
+  if (graph) cudaGraphExecDestroy(graph);
+  for (auto& l : launches) l.fn = nullptr;
+  for (auto* u : umma) umma_conv_destroy(u);
+  for (void* p : extra_allocs) cudaFree(p);
+  if (arena) cudaFree(arena);
+  if (status) cudaFree(status);
+}
+
+namespace {
+
+typedef const _odla_value* V;
+
+// ---- host-side numeric helpers (constants are converted before upload) ----
+uint16_t f2h(float f) {
+  uint32_t u; memcpy(&u, &f, 4);
+  uint32_t s = (u >> 16) & 0x8000; int32_t e = (int32_t)((u >> 23) & 0xff) - 127 + 15; uint32_t m = u & 0x7fffff;
+  if (((u >> 23) & 0xff) == 0xff) return (uint16_t)(s | 0x7c00 | (m ? 0x200 : 0));
+  if (e >= 31) return (uint16_t)(s | 0x7c00);
+  if (e <= 0) {
+    if (e < -10) return (uint16_t)s;
+    m |= 0x800000; int sh = 14 - e; uint32_t r = m >> sh, rem = m & ((1u << sh) - 1), half = 1u << (sh - 1);
+    if (rem > half || (rem == half && (r & 1))) ++r;
+    return (uint16_t)(s | r);
+  }
+  uint32_t r = ((uint32_t)e << 10) | (m >> 13), rem = m & 0x1fff;
+  if (rem > 0x1000 || (rem == 0x1000 && (r & 1))) ++r;
+  return (uint16_t)(s | r);
+}
+float h2f(uint16_t h) {
+  uint32_t s = (h >> 15) & 1, e = (h >> 10) & 0x1f, m = h & 0x3ff, u;
+  if (e == 0) {
+    if (m == 0) u = s << 31;
+    else { int k = 0; while (!(m & 0x400)) { m <<= 1; ++k; } u = (s << 31) | ((uint32_t)(127 - 15 - k + 1) << 23) | ((m & 0x3ff) << 13); }
+  } else if (e == 31) u = (s << 31) | 0x7f800000u | (m << 13);
+  else u = (s << 31) | ((e - 15 + 127) << 23) | (m << 13);
+  float f; memcpy(&f, &u, 4); return f;
+}
+uint16_t f2bf(float f) {
+  uint32_t u; memcpy(&u, &f, 4);
+  if ((u & 0x7fffffff) > 0x7f800000) return (uint16_t)((u >> 16) | 0x40);
+  u += 0x7fff + ((u >> 16) & 1);
+  return (uint16_t)(u >> 16);
+}
+float bf2f(uint16_t h) { uint32_t u = (uint32_t)h << 16; float f; memcpy(&f, &u, 4); return f; }
+
+int api_dt(odla_element_type t) {  // storage type that holds an API element type verbatim
+  switch (t) {
+    case ODLA_FLOAT32: return DT_F32;
+    case ODLA_FLOAT16: return DT_F16;
+    case ODLA_BFLOAT16: return DT_BF16;
+    case ODLA_INT8: case ODLA_QINT8: return DT_S8;
+    case ODLA_UINT8: case ODLA_QUINT8: case ODLA_BOOL: return DT_U8;
+    case ODLA_INT32: case ODLA_QINT32: case ODLA_UINT32: return DT_S32;
+    case ODLA_INT64: case ODLA_UINT64: return DT_S64;
+    default: return -1;
+  }
+}
+// Reads constant `v` (any supported element type) as fp32.
+std::vector<float> const_as_f32(V v) {
+  int64_t n = numel(v->type.shape);
+  std::vector<float> r((size_t)n);
+  switch (api_dt(v->type.element_type)) {
+    case DT_F32: memcpy(r.data(), v->host, sizeof(float) * (size_t)n); break;
+    case DT_F16: for (int64_t i = 0; i < n; ++i) r[i] = h2f(((const uint16_t*)v->host)[i]); break;
+    case DT_BF16: for (int64_t i = 0; i < n; ++i) r[i] = bf2f(((const uint16_t*)v->host)[i]); break;
+    case DT_S8: for (int64_t i = 0; i < n; ++i) r[i] = ((const int8_t*)v->host)[i]; break;
+    case DT_U8: for (int64_t i = 0; i < n; ++i) r[i] = ((const uint8_t*)v->host)[i]; break;
+    case DT_S32: for (int64_t i = 0; i < n; ++i) r[i] = (float)((const int32_t*)v->host)[i]; break;
+    case DT_S64: for (int64_t i = 0; i < n; ++i) r[i] = (float)((const int64_t*)v->host)[i]; break;
+    default: break;
+  }
+  return r;
+}
+std::vector<uint8_t> f32_to_storage(const std::vector<float>& f, int dt) {
+  std::vector<uint8_t> out(f.size() * (size_t)storage_size(dt));
+  switch (dt) {
+    case DT_F32: memcpy(out.data(), f.data(), out.size()); break;
+    case DT_F16: for (size_t i = 0; i < f.size(); ++i) ((uint16_t*)out.data())[i] = f2h(f[i]); break;
+    case DT_BF16: for (size_t i = 0; i < f.size(); ++i) ((uint16_t*)out.data())[i] = f2bf(f[i]); break;
+    case DT_S8: for (size_t i = 0; i < f.size(); ++i) ((int8_t*)out.data())[i] = (int8_t)std::max(-128.f, std::min(127.f, std::nearbyint(f[i]))); break;
+    case DT_U8: for (size_t i = 0; i < f.size(); ++i) ((uint8_t*)out.data())[i] = (uint8_t)std::max(0.f, std::min(255.f, std::nearbyint(f[i]))); break;
+    case DT_S32: for (size_t i = 0; i < f.size(); ++i) ((int32_t*)out.data())[i] = (int32_t)f[i]; break;
+    case DT_S64: for (size_t i = 0; i < f.size(); ++i) ((int64_t*)out.data())[i] = (int64_t)f[i]; break;
+  }
+  return out;
+}
+
+// A fused convolution / GEMM: root node plus the chain folded into its epilogue.
+struct Fused {
+  V root = nullptr, out = nullptr;
+  bool int8 = false;
+  V x = nullptr;            // data operand actually read (int8 source when int8)
+  V x_scale = nullptr;      // per-tensor activation scale (int8)
+  V w = nullptr;            // constant weights actually read (int8 source when int8)
+  V w_scale = nullptr;      // per-tensor or per-output-channel weight scale (int8)
+  V add_const = nullptr;    // per-channel Add operand
+  V res = nullptr;          // residual tensor actually read
+  V res_scale = nullptr;    // Dequantize scale when the residual is int8
+  int act = ACT_NONE; float act_a = 0, act_b = 0; bool act_first = false;
+  V quant_scale = nullptr;  // absorbed Quantize
+};
+
+struct Item {               // one launch-list entry before emission
+  V out = nullptr;          // value it materialises
+  std::vector<V> reads;     // materialised values it reads (after alias resolution)
+  const Fused* fused = nullptr;
+};
+
+class Builder {
+ public:
+  Builder(_odla_computation* c, Plan* p, int64_t full_batch, int64_t shard, int64_t shard_start)
+      : c_(c), p_(p), B_(full_batch), b_(shard), start_(shard_start) {}
+  odla_status run();
+
+ private:
+  _odla_computation* c_;
+  Plan* p_;
+  int64_t B_, b_, start_;
+  std::map<V, int> users_;
+  std::map<V, std::vector<V>> consumers_;
+  std::map<V, bool> carries_batch_;
+  std::map<V, V> fused_into_;          // node -> root of the chain that swallowed it
+  std::map<V, std::unique_ptr<Fused>> fused_;  // by root
+  std::map<V, int> dq_unabsorbed_;     // Dequantize node -> number of consumers that need it in memory
+  std::map<V, V> alias_;               // reshape output -> source
+  std::map<V, int> dt_;                // storage type of materialised values
+  std::vector<Item> items_;
+  std::map<std::pair<V, int>, void*> const_cache_;
+  std::string err_;
+  odla_status err_status_ = ODLA_SUCCESS;
+
+  odla_status fail(odla_status s, const std::string& m) { if (err_.empty()) { err_ = m; err_status_ = s; } B2_ERR("%s", m.c_str()); return s; }
+  int FS() const { return c_->float_mode; }
+  V resolve(V v) const { auto it = alias_.find(v); while (it != alias_.end()) { v = it->second; it = alias_.find(v); } return v; }
+  // shape of `v` inside this shard
+  odla_value_shape shape(V v) const {
+    odla_value_shape s = v->type.shape;
+    auto it = carries_batch_.find(v);
+    if (it != carries_batch_.end() && it->second && B_ != b_ && s.size > 0) s.dims[0] = s.dims[0] / B_ * b_;
+    return s;
+  }
+  int64_t count(V v) const { return numel(shape(v)); }
+  int storage_of(V v) const {
+    if (is_float_type(v->type.element_type)) return FS();
+    return api_dt(v->type.element_type);
+  }
+  void* dev_ptr(V v) const {
+    v = resolve(v);
+    auto it = p_->slots.find(v);
+    if (it == p_->slots.end() || it->second.offset < 0) return nullptr;
+    return p_->arena + it->second.offset;
+  }
+  void* upload(const void* host, size_t bytes) {
+    void* d = nullptr;
+    if (inject_fault("alloc") || cudaMalloc(&d, bytes ? bytes : 16) != cudaSuccess) { fail(ODLA_MEM_ERROR, "constant allocation failed"); return nullptr; }
+    p_->extra_allocs.push_back(d);
+    if (bytes && cudaMemcpy(d, host, bytes, cudaMemcpyHostToDevice) != cudaSuccess) { fail(ODLA_FAILURE, "constant upload failed"); return nullptr; }
+    p_->const_bytes += (int64_t)bytes;
+    return d;
+  }
+  void* const_dev(V v, int dt) {  // constant converted to storage type dt, uploaded once
+    auto key = std::make_pair(v, dt);
+    auto it = const_cache_.find(key);
+    if (it != const_cache_.end()) return it->second;
+    void* d;
+    if (api_dt(v->type.element_type) == dt) d = upload(v->host, (size_t)(numel(v->type.shape) * storage_size(dt)));
+    else { auto bytes = f32_to_storage(const_as_f32(v), dt); d = upload(bytes.data(), bytes.size()); }
+    const_cache_[key] = d;
+    return d;
+  }
+  float* upload_f32(const std::vector<float>& f) { return (float*)upload(f.data(), f.size() * sizeof(float)); }
+
+  odla_status analyse();
+  void try_fuse(V root);
+  odla_status place();
+  odla_status emit();
+  odla_status emit_fused(const Item& it);
+  odla_status emit_plain(const Item& it);
+  void add_launch(const char* op, V out, double flops, double bytes, std::function<int(cudaStream_t)> fn) {
+    Launch l; l.op = op; l.name = out->name; l.flops = flops; l.bytes = bytes; l.fn = std::move(fn);
+    p_->launches.push_back(std::move(l));
+  }
+  double tensor_bytes(V v) const { return (double)count(v) * storage_size(dt_.count(resolve(v)) ? dt_.at(resolve(v)) : storage_of(v)); }
+};
+
+bool is_per_tensor_dq(V v) {
+  return v && v->kind == OP_DEQUANTIZE && !v->in[2] && numel(v->in[1]->type.shape) == 1 &&
+         (v->in[0]->type.element_type == ODLA_INT8);
+}
+
+odla_status Builder::analyse() {
+  // users / consumers
+  for (auto& n : c_->nodes)
+    for (auto i : n->in)
+      if (i) { users_[i]++; consumers_[i].push_back(n.get()); }
+  // batch propagation and shardability
+  for (auto& n : c_->nodes) {
+    V v = n.get();
+    bool cb = v->kind == OP_ARG;
+    for (auto i : v->in) if (i && carries_batch_[i]) cb = true;
+    carries_batch_[v] = cb;
+  }
+  if (B_ != b_) {
+    for (auto& n : c_->nodes) {
+      V v = n.get();
+      if (!carries_batch_[v]) continue;
+      if (v->type.shape.size == 0 || v->type.shape.dims[0] % B_ != 0) return fail(ODLA_INTERNAL_LOGIC_ERR, "value '" + v->name + "' does not scale with the batch");
+    }
+  }
+  // fusion roots
+  for (auto& n : c_->nodes)
+    if (n->kind == OP_CONV || n->kind == OP_GEMM) try_fuse(n.get());
+  // which Dequantize nodes still need to exist in memory
+  for (auto& n : c_->nodes) {
+    V v = n.get();
+    if (v->kind != OP_DEQUANTIZE) continue;
+    int need = v->is_output ? 1 : 0;
+    for (V cons : consumers_[v]) {
+      bool absorbed = false;
+      auto fi = fused_into_.find(cons);
+      V root = cons->kind == OP_CONV || cons->kind == OP_GEMM ? cons : (fi != fused_into_.end() ? fi->second : nullptr);
+      if (root && fused_.count(root)) {
+        const Fused& f = *fused_[root];
+        if (f.int8 && (root->in[0] == v || root->in[1] == v) && cons == root) absorbed = true;
+        if (f.res_scale && cons != root && (cons->in[0] == v || cons->in[1] == v) && f.res == v->in[0]) absorbed = true;
+      }
+      if (!absorbed) ++need;
+    }
+    dq_unabsorbed_[v] = need;
+  }
+  // launch items in topological order
+  for (auto& n : c_->nodes) {
+    V v = n.get();
+    if (v->kind == OP_CONST) continue;
+    if (v->kind == OP_ARG) { dt_[v] = storage_of(v); continue; }
+    if (v->kind == OP_RESHAPE) { alias_[v] = v->in[0]; continue; }
+    auto fi = fused_into_.find(v);
+    if (fi != fused_into_.end() && fused_[fi->second]->out != v) continue;  // swallowed, not the chain end
+    if (v->kind == OP_DEQUANTIZE && dq_unabsorbed_[v] == 0) continue;
+    Item it;
+    it.out = v;
+    V root = (v->kind == OP_CONV || v->kind == OP_GEMM) ? v : (fi != fused_into_.end() ? fi->second : nullptr);
+    if (root && fused_.count(root)) {
+      const Fused* f = fused_[root].get();
+      it.fused = f;
+      it.reads.push_back(f->x);
+      if (f->w->kind != OP_CONST) it.reads.push_back(f->w);
+      if (f->res) it.reads.push_back(f->res);
+      if (root->kind == OP_GEMM && root->in[2] && root->in[2]->kind != OP_CONST) it.reads.push_back(root->in[2]);
+      dt_[v] = f->quant_scale ? DT_S8 : FS();
+    } else {
+      for (auto i : v->in) if (i && i->kind != OP_CONST) it.reads.push_back(i);
+      dt_[v] = storage_of(v);
+    }
+    items_.push_back(std::move(it));
+  }
+  // reshape of a constant has no producer item: treat as constant view
+  return ODLA_SUCCESS;
+}
+
+void Builder::try_fuse(V root) {
+  auto f = std::make_unique<Fused>();
+  f->root = root;
+  f->x = root->in[0];
+  f->w = root->in[1];
+  int64_t K;  // output channels / columns
+  if (root->kind == OP_CONV) K = root->ia[0] ? root->type.shape.dims[3] : root->type.shape.dims[1];
+  else K = root->type.shape.dims[root->type.shape.size - 1];
+  bool channel_last = root->kind == OP_GEMM || root->ia[0];
+  // int8 operands
+  V xin = root->in[0], win = root->in[1];
+  if (is_per_tensor_dq(xin) && win && win->kind == OP_DEQUANTIZE && !win->in[2] && win->in[0]->kind == OP_CONST &&
+      win->in[0]->type.element_type == ODLA_INT8 && channel_last &&
+      (numel(win->in[1]->type.shape) == 1 || numel(win->in[1]->type.shape) == K) &&
+      (root->kind == OP_CONV ? root->ia[1] == 1 : root->type.shape.size == 2)) {
+    f->int8 = true;
+    f->x = xin->in[0];
+    f->x_scale = xin->in[1];
+    f->w = win->in[0];
+    f->w_scale = win->in[1];
+  }
+  V cur = root;
+  fused_into_[root] = root;
+  while (channel_last) {
+    if (cur->is_output || users_[cur] != 1) break;
+    V nxt = consumers_[cur][0];
+    if (nxt->kind == OP_BINARY && nxt->ia[0] == BIN_ADD) {
+      V other = nxt->in[0] == cur ? nxt->in[1] : nxt->in[0];
+      if (other == cur) break;
+      const auto& os = other->type.shape;
+      bool per_channel = other->kind == OP_CONST && numel(os) == K && os.dims[os.size - 1] == K;
+      bool same_shape = numel(other->type.shape) == numel(cur->type.shape) && other->kind != OP_CONST;
+      if (per_channel && !f->add_const && !f->res && f->act == ACT_NONE) f->add_const = other;
+      else if (same_shape && !f->res && other->index < nxt->index) {
+        if (is_per_tensor_dq(other)) { f->res = other->in[0]; f->res_scale = other->in[1]; }
+        else f->res = other;
+        if (f->act != ACT_NONE) f->act_first = true;
+      } else break;
+    } else if (nxt->kind == OP_UNARY && f->act == ACT_NONE &&
+               (nxt->ia[0] == UN_RELU || nxt->ia[0] == UN_LEAKY || nxt->ia[0] == UN_CLAMP || nxt->ia[0] == UN_GELU_ERF || nxt->ia[0] == UN_GELU_TANH)) {
+      f->act = nxt->ia[0] == UN_RELU ? ACT_RELU : nxt->ia[0] == UN_LEAKY ? ACT_LEAKY : nxt->ia[0] == UN_CLAMP ? ACT_CLAMP
+               : nxt->ia[0] == UN_GELU_ERF ? ACT_GELU_ERF : ACT_GELU_TANH;
+      f->act_a = nxt->fa[0];
+      f->act_b = nxt->fa[1];
+    } else if (nxt->kind == OP_QUANTIZE && !nxt->in[2] && numel(nxt->in[1]->type.shape) == 1 && nxt->type.element_type == ODLA_INT8) {
+      f->quant_scale = nxt->in[1];
+      fused_into_[nxt] = root;
+      cur = nxt;
+      break;
+    } else break;
+    fused_into_[nxt] = root;
+    cur = nxt;
+  }
+  f->out = cur;
+  fused_[root] = std::move(f);
+}
+
+// First-fit free-list allocator over byte offsets (1 KiB granularity).
+struct Arena {
+  std::vector<std::pair<int64_t, int64_t>> free_;  // (offset, size), sorted by offset
+  int64_t top = 0;
+  static int64_t round(int64_t b) { return (b + 1023) / 1024 * 1024; }
+  int64_t alloc(int64_t bytes) {
+    bytes = round(bytes ? bytes : 1);
+    int best = -1;
+    for (size_t i = 0; i < free_.size(); ++i)
+      if (free_[i].second >= bytes && (best < 0 || free_[i].second < free_[best].second)) best = (int)i;
+    if (best >= 0) {
+      int64_t off = free_[best].first;
+      if (free_[best].second == bytes) free_.erase(free_.begin() + best);
+      else { free_[best].first += bytes; free_[best].second -= bytes; }
+      return off;
+    }
+    // grow: merge with a trailing free block if it touches the top
+    if (!free_.empty() && free_.back().first + free_.back().second == top) {
+      int64_t off = free_.back().first;
+      top = off + bytes;
+      free_.pop_back();
+      return off;
+    }
+    int64_t off = top;
+    top += bytes;
+    return off;
+  }
+  void release(int64_t off, int64_t bytes) {
+    bytes = round(bytes ? bytes : 1);
+    auto it = std::lower_bound(free_.begin(), free_.end(), std::make_pair(off, (int64_t)0));
+    it = free_.insert(it, {off, bytes});
+    if (it + 1 != free_.end() && it->first + it->second == (it + 1)->first) { it->second += (it + 1)->second; free_.erase(it + 1); }
+    if (it != free_.begin() && (it - 1)->first + (it - 1)->second == it->first) { (it - 1)->second += it->second; free_.erase(it); }
+  }
+};
+
+
+odla_status Builder::place() {
+  Arena arena;
+  // last use of every materialised value (index into items_; outputs and arguments live to the end)
+  std::map<V, int> last;
+  for (size_t i = 0; i < items_.size(); ++i)
+    for (V r : items_[i].reads) last[resolve(r)] = (int)i;
+  auto bytes_of = [&](V v) { return count(v) * storage_size(dt_[v]); };
+  for (V a : c_->args) {
+    Slot s; s.dt = dt_[a]; s.bytes = bytes_of(a); s.offset = arena.alloc(s.bytes);
+    p_->slots[a] = s;
+  }
+  std::set<V> outputs;
+  for (V o : c_->outs) outputs.insert(resolve(o));
+  for (size_t i = 0; i < items_.size(); ++i) {
+    V v = items_[i].out;
+    Slot s; s.dt = dt_[v]; s.bytes = bytes_of(v); s.offset = arena.alloc(s.bytes);
+    p_->slots[v] = s;
+    for (V r : items_[i].reads) {
+      V rr = resolve(r);
+      if (rr->kind == OP_ARG || rr->kind == OP_CONST || outputs.count(rr)) continue;
+      auto li = last.find(rr);
+      if (li != last.end() && li->second == (int)i) {
+        auto& sl = p_->slots[rr];
+        if (sl.offset >= 0) arena.release(sl.offset, sl.bytes);
+        li->second = -1;  // released once even if read twice by this item
+      }
+    }
+    if (!last.count(v) && !outputs.count(v)) arena.release(s.offset, s.bytes);  // never read: reuse at once
+  }
+  // staging for arguments / outputs whose API element type differs from the storage type
+  for (V a : c_->args) {
+    Plan::Io io; io.v = a; io.slot = p_->slots[a].offset;
+    io.api_bytes = count(a) * elem_size(a->type.element_type);
+    io.per_shard = true;
+    io.user_offset = B_ ? numel(a->type.shape) / B_ * start_ * elem_size(a->type.element_type) : 0;
+    io.stage = api_dt(a->type.element_type) == dt_[a] ? io.slot : arena.alloc(io.api_bytes);
+    p_->inputs.push_back(io);
+  }
+  for (V o : c_->outs) {
+    Plan::Io io; io.v = o;
+    V r = resolve(o);
+    io.api_bytes = count(o) * elem_size(o->type.element_type);
+    io.per_shard = carries_batch_[o];
+    io.user_offset = io.per_shard && B_ ? numel(o->type.shape) / B_ * start_ * elem_size(o->type.element_type) : 0;
+    if (r->kind == OP_CONST) io.const_host = r->host;
+    else {
+      io.slot = p_->slots[r].offset;
+      io.stage = api_dt(o->type.element_type) == dt_[r] ? io.slot : arena.alloc(io.api_bytes);
+    }
+    p_->outputs.push_back(io);
+  }
+  p_->arena_bytes = arena.top;
+  if (inject_fault("alloc") || cudaMalloc((void**)&p_->arena, (size_t)std::max<int64_t>(p_->arena_bytes, 1024)) != cudaSuccess)
+    return fail(ODLA_MEM_ERROR, "arena allocation failed");
+  if (cudaMalloc((void**)&p_->status, 256) != cudaSuccess) return fail(ODLA_MEM_ERROR, "status word allocation failed");
+  cudaMemset(p_->status, 0, 256);
+  return ODLA_SUCCESS;
+}
+
+odla_status Builder::emit_fused(const Item& it) {
+  const Fused& f = *it.fused;
+  V root = f.root;
+  int in_dt = f.int8 ? DT_S8 : FS();
+  if (dt_[resolve(f.x)] != in_dt) return fail(ODLA_UNSUPPORTED_DATATYPE, "'" + root->name + "': operand storage type does not match the compute type");
+  if (in_dt == DT_U8 || in_dt == DT_S32 || in_dt == DT_S64) return fail(ODLA_UNSUPPORTED_DATATYPE, "'" + root->name + "': integer convolution needs Dequantize operands");
+  const void* x = dev_ptr(f.x);
+  void* y = dev_ptr(f.out);
+  int64_t K = root->kind == OP_CONV ? (root->ia[0] ? root->type.shape.dims[3] : root->type.shape.dims[1])
+                                    : root->type.shape.dims[root->type.shape.size - 1];
+  Epilogue ep;
+  if (f.int8) {
+    auto sx = const_as_f32(f.x_scale), sw = const_as_f32(f.w_scale);
+    std::vector<float> m((size_t)K);
+    for (int64_t k = 0; k < K; ++k) m[k] = sx[0] * sw[sw.size() == 1 ? 0 : k];
+    ep.mul = upload_f32(m);
+  }
+  if (f.add_const) ep.add2 = (const float*)const_dev(f.add_const, DT_F32);
+  if (f.res) {
+    ep.res = dev_ptr(f.res);
+    ep.res_dt = dt_[resolve(f.res)];
+    if (f.res_scale) ep.res_scale = const_as_f32(f.res_scale)[0];
+    else if (ep.res_dt == DT_S8 || ep.res_dt == DT_U8) return fail(ODLA_UNSUPPORTED_DATATYPE, "'" + root->name + "': integer residual without Dequantize");
+  }
+  ep.act = f.act; ep.act_a = f.act_a; ep.act_b = f.act_b; ep.act_first = f.act_first;
+  ep.out_dt = dt_[f.out];
+  if (f.quant_scale) ep.out_scale = const_as_f32(f.quant_scale)[0];
+  bool allow_umma = !getenv("ODLA_B200_NO_UMMA");
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, p_->device);
+
+  if (root->kind == OP_CONV) {
+    bool nhwc = root->ia[0] != 0;
+    int groups = (int)root->ia[1];
+    odla_value_shape xs = shape(root->in[0]), os = shape(root);
+    const odla_value_shape& ws = root->in[1]->type.shape;
+    if (f.w->kind != OP_CONST) return fail(ODLA_UNSUPPORTED_OP, "'" + root->name + "': convolution filters must be constants");
+    ConvGeom g{};
+    g.N = (int)xs.dims[0];
+    g.H = (int)(nhwc ? xs.dims[1] : xs.dims[2]); g.W = (int)(nhwc ? xs.dims[2] : xs.dims[3]); g.C = (int)(nhwc ? xs.dims[3] : xs.dims[1]);
+    g.R = (int)(nhwc ? ws.dims[0] : ws.dims[2]); g.S = (int)(nhwc ? ws.dims[1] : ws.dims[3]); g.K = (int)K;
+    g.P = (int)(nhwc ? os.dims[1] : os.dims[2]); g.Q = (int)(nhwc ? os.dims[2] : os.dims[3]);
+    g.stride_h = (int)root->ia[2]; g.stride_w = (int)root->ia[3]; g.pad_t = (int)root->ia[4]; g.pad_l = (int)root->ia[5];
+    g.groups = groups;
+    int cg = g.C / groups;
+    if (root->in[2]) {
+      if (root->in[2]->kind != OP_CONST) return fail(ODLA_UNSUPPORTED_OP, "'" + root->name + "': convolution bias must be a constant");
+      ep.add1 = (const float*)const_dev(root->in[2], DT_F32);
+    }
+    double flops = 2.0 * g.N * g.P * g.Q * (double)K * g.R * g.S * cg;
+    double bytes = tensor_bytes(f.x) + tensor_bytes(f.out) + (double)numel(ws) * storage_size(in_dt) + (f.res ? tensor_bytes(f.res) : 0);
+    UmmaConv uc{g.N, g.H, g.W, g.C, g.K, g.R, g.S, g.P, g.Q, g.stride_h, g.stride_w, g.pad_t, g.pad_l, in_dt};
+    if (allow_umma && nhwc && groups == 1 && umma_conv_supported(uc)) {
+      // filters HWIO -> [K][R*S*C] so that each output channel's taps are contiguous (K-major B operand)
+      auto wf = const_as_f32(f.w);
+      std::vector<float> w2(wf.size());
+      int64_t rsc = (int64_t)g.R * g.S * g.C;
+      for (int64_t t = 0; t < rsc; ++t)
+        for (int64_t k = 0; k < K; ++k) w2[(size_t)(k * rsc + t)] = wf[(size_t)(t * K + k)];
+      auto wb = f32_to_storage(w2, in_dt);
+      void* wd = upload(wb.data(), wb.size());
+      if (!wd) return err_status_;
+      UmmaLaunch* ul = umma_conv_prepare(uc, x, wd, y, ep, p_->status, sms);
+      if (!ul) return fail(ODLA_FAILURE, "'" + root->name + "': tensor-map encoding failed");
+      p_->umma.push_back(ul);
+      add_launch("conv_umma", f.out, flops, bytes, [ul](cudaStream_t s) { return umma_conv_run(ul, s); });
+      return ODLA_SUCCESS;
+    }
+    const void* wd = const_dev(f.w, in_dt);
+    if (!wd) return err_status_;
+    if (nhwc) {
+      g.xs_c = 1; g.xs_w = g.C; g.xs_h = (int64_t)g.W * g.C; g.xs_n = (int64_t)g.H * g.W * g.C;
+      g.ys_c = 1; g.ys_w = g.K; g.ys_h = (int64_t)g.Q * g.K; g.ys_n = (int64_t)g.P * g.Q * g.K;
+      g.ws_k = 1; g.ws_c = g.K; g.ws_s = (int64_t)cg * g.K; g.ws_r = (int64_t)g.S * cg * g.K;
+    } else {
+      g.xs_w = 1; g.xs_h = g.W; g.xs_c = (int64_t)g.H * g.W; g.xs_n = (int64_t)g.C * g.H * g.W;
+      g.ys_w = 1; g.ys_h = g.Q; g.ys_c = (int64_t)g.P * g.Q; g.ys_n = (int64_t)g.K * g.P * g.Q;
+      g.ws_s = 1; g.ws_r = g.S; g.ws_c = (int64_t)g.R * g.S; g.ws_k = (int64_t)cg * g.R * g.S;
+      if (f.res || ep.add_full) return fail(ODLA_INTERNAL_LOGIC_ERR, "'" + root->name + "': NCHW chain fused unexpectedly");
+    }
+    add_launch("conv_simt", f.out, flops, bytes, [=](cudaStream_t s) { return conv_simt(g, in_dt, x, wd, y, ep, s); });
+    return ODLA_SUCCESS;
+  }
+
+  // ---- Gemm ----
+  V A = root->in[0], Bv = root->in[1], C = root->in[2];
+  odla_value_shape as = shape(A);
+  odla_value_shape bs = f.w->kind == OP_CONST ? f.w->type.shape : shape(Bv);
+  bool ta = root->ia[0] != 0, tb = root->ia[1] != 0;
+  float alpha = root->fa[0], beta = root->fa[1];
+  int ra = as.size, rb = bs.size;
+  int64_t batch = 1, bbatch = 1;
+  for (int i = 0; i < ra - 2; ++i) batch *= as.dims[i];
+  for (int i = 0; i < rb - 2; ++i) bbatch *= bs.dims[i];
+  int64_t ar = as.dims[ra - 2], ac = as.dims[ra - 1], br = bs.dims[rb - 2], bc = bs.dims[rb - 1];
+  int64_t M = ta ? ac : ar, Kd = ta ? ar : ac, N = tb ? br : bc;
+  if ((tb ? bc : br) != Kd) return fail(ODLA_INVALID_PARAM, "'" + root->name + "': Gemm inner dimensions differ");
+  if (bbatch != batch && bbatch != 1) return fail(ODLA_INVALID_PARAM, "'" + root->name + "': Gemm batch dimensions differ");
+  if (count(root) != batch * M * N) return fail(ODLA_INVALID_PARAM, "'" + root->name + "': Gemm output_dims do not match the operands");
+  ep.alpha = alpha;
+  if (C && beta != 0.f) {
+    int64_t cn = C->kind == OP_CONST ? numel(C->type.shape) : count(C);
+    if (C->kind == OP_CONST && (cn == 1 || cn == N)) {
+      auto cf = const_as_f32(C);
+      std::vector<float> v((size_t)N);
+      for (int64_t j = 0; j < N; ++j) v[j] = beta * cf[cn == 1 ? 0 : j];
+      ep.add1 = upload_f32(v);
+    } else if (cn == batch * M * N) {
+      if (C->kind == OP_CONST) { ep.add_full = const_dev(C, DT_F32); ep.add_full_dt = DT_F32; }
+      else { ep.add_full = dev_ptr(C); ep.add_full_dt = dt_[resolve(C)]; }
+      ep.beta_full = beta;
+    } else return fail(ODLA_UNSUPPORTED_OP, "'" + root->name + "': Gemm C must be a constant scalar / row vector or a full matrix");
+  }
+  double flops = 2.0 * batch * M * N * Kd;
+  double bytes = tensor_bytes(f.x) + tensor_bytes(f.out) + (double)(br * bc * bbatch) * storage_size(in_dt);
+  if (allow_umma && !ta && f.w->kind == OP_CONST && bbatch == 1) {
+    int64_t Mt = batch * M;
+    UmmaConv uc{1, 1, (int)Mt, (int)Kd, (int)N, 1, 1, 1, (int)Mt, 1, 1, 0, 0, in_dt};
+    if (Mt < (1ll << 31) && umma_conv_supported(uc)) {
+      auto wf = const_as_f32(f.w);
+      std::vector<float> w2;
+      if (tb) w2 = wf;  // already [N][K]
+      else { w2.resize(wf.size()); for (int64_t k = 0; k < Kd; ++k) for (int64_t n = 0; n < N; ++n) w2[(size_t)(n * Kd + k)] = wf[(size_t)(k * N + n)]; }
+      auto wb = f32_to_storage(w2, in_dt);
+      void* wd = upload(wb.data(), wb.size());
+      if (!wd) return err_status_;
+      UmmaLaunch* ul = umma_conv_prepare(uc, x, wd, y, ep, p_->status, sms);
+      if (!ul) return fail(ODLA_FAILURE, "'" + root->name + "': tensor-map encoding failed");
+      p_->umma.push_back(ul);
+      add_launch("gemm_umma", f.out, flops, bytes, [ul](cudaStream_t s) { return umma_conv_run(ul, s); });
+      return ODLA_SUCCESS;
+    }
+  }
+  GemmGeom g{};
+  g.batch = batch; g.M = M; g.N = N; g.K = Kd;
+  g.a_row = ta ? 1 : ac; g.a_col = ta ? ac : 1; g.a_batch = ar * ac;
+  g.b_row = tb ? 1 : bc; g.b_col = tb ? bc : 1; g.b_batch = bbatch == 1 ? 0 : br * bc;
+  const void* bp;
+  if (f.w->kind == OP_CONST) bp = const_dev(f.w, in_dt);
+  else {
+    if (dt_[resolve(f.w)] != in_dt) return fail(ODLA_UNSUPPORTED_DATATYPE, "'" + root->name + "': Gemm operand types differ");
+    bp = dev_ptr(f.w);
+  }
+  if (!bp) return err_status_;
+  add_launch("gemm_simt", f.out, flops, bytes, [=](cudaStream_t s) { return gemm_simt(g, in_dt, x, bp, y, ep, s); });
+  return ODLA_SUCCESS;
+}
+
+odla_status Builder::emit_plain(const Item& it) {
+  V v = it.out;
+  void* y = dev_ptr(v);
+  int odt = dt_[v];
+  // operand pointer + storage type; constants are uploaded (float constants as fp32 unless `want` says otherwise)
+  auto operand = [&](V o, int* dt, int want = -1) -> const void* {
+    V r = resolve(o);
+    if (r->kind == OP_CONST) {
+      int d = want >= 0 ? want : (is_float_type(r->type.element_type) ? DT_F32 : api_dt(r->type.element_type));
+      *dt = d;
+      return const_dev(r, d);
+    }
+    *dt = dt_[r];
+    return dev_ptr(r);
+  };
+  odla_value_shape os = shape(v);
+  double out_bytes = tensor_bytes(v);
+  switch (v->kind) {
+    case OP_MAXPOOL: case OP_AVGPOOL: {
+      V xin = v->in[0];
+      int xdt; const void* x = operand(xin, &xdt, odt);
+      if (xdt != odt) return fail(ODLA_INTERNAL_LOGIC_ERR, "'" + v->name + "': pooling changes the storage type");
+      bool nhwc = v->ia[0] != 0;
+      odla_value_shape xs = shape(xin);
+      PoolGeom g{};
+      g.N = (int)xs.dims[0];
+      g.H = (int)(nhwc ? xs.dims[1] : xs.dims[2]); g.W = (int)(nhwc ? xs.dims[2] : xs.dims[3]); g.C = (int)(nhwc ? xs.dims[3] : xs.dims[1]);
+      g.P = (int)(nhwc ? os.dims[1] : os.dims[2]); g.Q = (int)(nhwc ? os.dims[2] : os.dims[3]);
+      g.R = (int)v->ia[1]; g.S = (int)v->ia[2]; g.stride_h = (int)v->ia[3]; g.stride_w = (int)v->ia[4]; g.pad_t = (int)v->ia[5]; g.pad_l = (int)v->ia[6];
+      if (nhwc) {
+        g.xs_c = 1; g.xs_w = g.C; g.xs_h = (int64_t)g.W * g.C; g.xs_n = (int64_t)g.H * g.W * g.C;
+        g.ys_c = 1; g.ys_w = g.C; g.ys_h = (int64_t)g.Q * g.C; g.ys_n = (int64_t)g.P * g.Q * g.C;
+      } else {
+        g.xs_w = 1; g.xs_h = g.W; g.xs_c = (int64_t)g.H * g.W; g.xs_n = (int64_t)g.C * g.H * g.W;
+        g.ys_w = 1; g.ys_h = g.Q; g.ys_c = (int64_t)g.P * g.Q; g.ys_n = (int64_t)g.C * g.P * g.Q;
+      }
+      bool is_max = v->kind == OP_MAXPOOL;
+      if (!is_max && (odt == DT_S8 || odt == DT_U8)) return fail(ODLA_UNSUPPORTED_DATATYPE, "'" + v->name + "': average pooling of integers");
+      add_launch(is_max ? "maxpool" : "avgpool", v, 0, tensor_bytes(xin) + out_bytes, [=](cudaStream_t s) { return pool2d(g, odt, is_max, x, y, s); });
+      return ODLA_SUCCESS;
+    }
+    case OP_BATCHNORM: {
+      int xdt; const void* x = operand(v->in[0], &xdt);
+      bool nhwc = v->ia[0] != 0;
+      int64_t C = nhwc ? os.dims[os.size - 1] : os.dims[1], inner = 1;
+      if (!nhwc) for (int i = 2; i < os.size; ++i) inner *= os.dims[i];
+      int64_t outer = count(v) / (C * inner);
+      auto mean = const_as_f32(v->in[1]), var = const_as_f32(v->in[2]);
+      std::vector<float> a((size_t)C), b((size_t)C);
+      std::vector<float> sc = v->in[3] ? const_as_f32(v->in[3]) : std::vector<float>(), of = v->in[4] ? const_as_f32(v->in[4]) : std::vector<float>();
+      for (int64_t c = 0; c < C; ++c) {
+        float inv = 1.0f / std::sqrt(var[c] + v->fa[0]);
+        float s = v->in[3] ? sc[c] : v->fa[1], o = v->in[4] ? of[c] : v->fa[2];
+        a[c] = s * inv;
+        b[c] = -s * mean[c] * inv + o;
+      }
+      const float* ad = upload_f32(a); const float* bd = upload_f32(b);
+      if (xdt != odt) return fail(ODLA_INTERNAL_LOGIC_ERR, "'" + v->name + "': batchnorm changes the storage type");
+      add_launch("batchnorm", v, 0, 2 * out_bytes, [=](cudaStream_t s) { return channel_affine(odt, x, y, ad, bd, outer, C, inner, s); });
+      return ODLA_SUCCESS;
+    }
+    case OP_UNARY: {
+      int xdt; const void* x = operand(v->in[0], &xdt);
+      int op = (int)v->ia[0]; float a = v->fa[0], b = v->fa[1]; int64_t n = count(v);
+      add_launch("unary", v, 0, tensor_bytes(v->in[0]) + out_bytes, [=](cudaStream_t s) { return unary(op, xdt, odt, x, y, n, a, b, s); });
+      return ODLA_SUCCESS;
+    }
+    case OP_BINARY: {
+      int ldt, rdt; const void* l = operand(v->in[0], &ldt); const void* r = operand(v->in[1], &rdt);
+      odla_value_shape ls = resolve(v->in[0])->kind == OP_CONST ? v->in[0]->type.shape : shape(v->in[0]);
+      odla_value_shape rs = resolve(v->in[1])->kind == OP_CONST ? v->in[1]->type.shape : shape(v->in[1]);
+      if (os.size > 8) return fail(ODLA_UNSUPPORTED_OP, "'" + v->name + "': rank above 8");
+      BinaryGeom g{};
+      g.rank = os.size;
+      int64_t la = 1, ra = 1;
+      for (int d = os.size - 1; d >= 0; --d) {
+        int li = d - (os.size - ls.size), ri = d - (os.size - rs.size);
+        int64_t ld = li >= 0 ? ls.dims[li] : 1, rd = ri >= 0 ? rs.dims[ri] : 1;
+        g.oshape[d] = os.dims[d];
+        g.lstride[d] = ld == os.dims[d] ? la : 0;
+        g.rstride[d] = rd == os.dims[d] ? ra : 0;
+        if (os.dims[d] == 1) { g.lstride[d] = g.rstride[d] = 0; }
+        la *= ld; ra *= rd;
+      }
+      // keep dense strides for size-1 dims out of the "same shape" test: recompute with 0 allowed
+      int op = (int)v->ia[0];
+      add_launch("binary", v, 0, out_bytes * 3, [=](cudaStream_t s) { return binary(op, g, ldt, rdt, odt, l, r, y, ACT_NONE, 0.f, s); });
+      return ODLA_SUCCESS;
+    }
+    case OP_SOFTMAX: {
+      int xdt; const void* x = operand(v->in[0], &xdt);
+      int axis = (int)v->ia[0]; bool lg = v->ia[1] != 0;
+      int64_t outer = 1, inner = 1, dim = os.dims[axis];
+      for (int i = 0; i < axis; ++i) outer *= os.dims[i];
+      for (int i = axis + 1; i < os.size; ++i) inner *= os.dims[i];
+      if (xdt != odt) return fail(ODLA_INTERNAL_LOGIC_ERR, "'" + v->name + "': softmax changes the storage type");
+      add_launch("softmax", v, 0, 2 * out_bytes, [=](cudaStream_t s) { return softmax(odt, x, y, outer, dim, inner, lg, s); });
+      return ODLA_SUCCESS;
+    }
+    case OP_REDUCE_MEAN: {
+      int xdt; const void* x = operand(v->in[0], &xdt);
+      odla_value_shape xs = shape(v->in[0]);
+      std::vector<int64_t> d(xs.dims, xs.dims + xs.size);
+      struct Pass { const void* src; void* dst; int sdt, ddt; int64_t before, dim, after; };
+      std::vector<Pass> passes;
+      const void* cur = x; int cdt = xdt;
+      size_t n_axes = v->ia.size() - 1;
+      if (n_axes == 0) return fail(ODLA_INVALID_PARAM, "'" + v->name + "': ReduceMean without axes");
+      for (size_t k = 0; k < n_axes; ++k) {
+        int64_t a = v->ia[1 + k], before = 1, after = 1;
+        for (int64_t i = 0; i < (int64_t)d.size(); ++i) { if (i < a) before *= d[i]; else if (i > a) after *= d[i]; }
+        bool lastp = k + 1 == n_axes;
+        void* dst = y; int ddt = odt;
+        if (!lastp) {  // intermediate passes keep fp32 so that the order of roundings equals the reference's
+          void* t = nullptr;
+          if (cudaMalloc(&t, (size_t)(before * after * 4)) != cudaSuccess) return fail(ODLA_MEM_ERROR, "scratch allocation failed");
+          p_->extra_allocs.push_back(t);
+          dst = t; ddt = DT_F32;
+        }
+        passes.push_back({cur, dst, cdt, ddt, before, d[a], after});
+        d[a] = 1; cur = dst; cdt = ddt;
+      }
+      add_launch("reduce_mean", v, 0, tensor_bytes(v->in[0]) + out_bytes, [=](cudaStream_t s) {
+        for (auto& p : passes) { int r = reduce_mean_axis(p.sdt, p.ddt, p.src, p.dst, p.before, p.dim, p.after, s); if (r) return r; }
+        return 0;
+      });
+      p_->launches.back().n_kernels = (int)passes.size();
+      return ODLA_SUCCESS;
+    }
+    case OP_LAYERNORM: {
+      int xdt; const void* x = operand(v->in[0], &xdt);
+      int64_t dim = 1; for (int i = os.size - (int)v->ia[0]; i < os.size; ++i) dim *= os.dims[i];
+      int64_t rows = count(v) / dim;
+      const float* g = v->in[1] ? (const float*)const_dev(v->in[1], DT_F32) : nullptr;
+      const float* b = v->in[2] ? (const float*)const_dev(v->in[2], DT_F32) : nullptr;
+      float eps = v->fa[0];
+      if (xdt != odt) return fail(ODLA_INTERNAL_LOGIC_ERR, "'" + v->name + "': layernorm changes the storage type");
+      add_launch("layernorm", v, 0, 2 * out_bytes, [=](cudaStream_t s) { return layernorm(odt, x, y, g, b, rows, dim, eps, s); });
+      return ODLA_SUCCESS;
+    }
+    case OP_QUANTIZE: case OP_DEQUANTIZE: {
+      bool q = v->kind == OP_QUANTIZE;
+      int xdt; const void* x = operand(v->in[0], &xdt);
+      const float* sc = (const float*)const_dev(v->in[1], DT_F32);
+      const int* zp = v->in[2] ? (const int*)const_dev(v->in[2], DT_S32) : nullptr;
+      int64_t ns = numel(v->in[1]->type.shape);
+      bool per_axis = ns > 1;
+      int64_t outer = 1, adim = 1, inner = count(v);
+      if (per_axis) {
+        int axis = (int)v->ia[0];
+        if (os.dims[axis] != ns) return fail(ODLA_INVALID_PARAM, "'" + v->name + "': scale count differs from the axis extent");
+        outer = 1; inner = 1; adim = os.dims[axis];
+        for (int i = 0; i < axis; ++i) outer *= os.dims[i];
+        for (int i = axis + 1; i < os.size; ++i) inner *= os.dims[i];
+      }
+      if (q) {
+        bool uns = odt == DT_U8;
+        add_launch("quantize", v, 0, tensor_bytes(v->in[0]) + out_bytes, [=](cudaStream_t s) { return quantize(xdt, x, y, sc, zp, outer, adim, inner, per_axis, uns, s); });
+      } else {
+        if (xdt != DT_S8 && xdt != DT_U8) return fail(ODLA_UNSUPPORTED_DATATYPE, "'" + v->name + "': Dequantize input must be int8 / uint8");
+        bool uns = xdt == DT_U8;
+        add_launch("dequantize", v, 0, tensor_bytes(v->in[0]) + out_bytes, [=](cudaStream_t s) { return dequantize(odt, x, y, sc, zp, outer, adim, inner, per_axis, uns, s); });
+      }
+      return ODLA_SUCCESS;
+    }
+    case OP_TRANSPOSE: {
+      int xdt; const void* x = operand(v->in[0], &xdt, odt);
+      odla_value_shape xs = shape(v->in[0]);
+      if (xs.size > 8) return fail(ODLA_UNSUPPORTED_OP, "'" + v->name + "': rank above 8");
+      int64_t istr[ODLA_MAX_DIMENSION], a = 1;
+      for (int i = xs.size - 1; i >= 0; --i) { istr[i] = a; a *= xs.dims[i]; }
+      MoveGeom g{};
+      g.rank = xs.size;
+      a = 1;
+      for (int i = xs.size - 1; i >= 0; --i) { g.oshape[i] = xs.dims[v->ia[i]]; g.istride[i] = istr[v->ia[i]]; g.ostride[i] = a; a *= g.oshape[i]; }
+      int esz = storage_size(odt);
+      add_launch("transpose", v, 0, 2 * out_bytes, [=](cudaStream_t s) { return move(g, esz, x, y, s); });
+      return ODLA_SUCCESS;
+    }
+    case OP_CONCAT: {
+      int axis = (int)v->ia[0];
+      int64_t outer = 1, inner = 1, off = 0;
+      for (int i = 0; i < axis; ++i) outer *= os.dims[i];
+      for (int i = axis + 1; i < os.size; ++i) inner *= os.dims[i];
+      struct Part { const void* x; MoveGeom g; };
+      std::vector<Part> parts;
+      for (V in : v->in) {
+        int xdt; const void* x = operand(in, &xdt, odt);
+        if (xdt != odt) return fail(ODLA_INTERNAL_LOGIC_ERR, "'" + v->name + "': concat inputs have different storage types");
+        odla_value_shape is = resolve(in)->kind == OP_CONST ? in->type.shape : shape(in);
+        MoveGeom g{};
+        g.rank = 3;
+        g.oshape[0] = outer; g.oshape[1] = is.dims[axis]; g.oshape[2] = inner;
+        g.istride[0] = is.dims[axis] * inner; g.istride[1] = inner; g.istride[2] = 1;
+        g.ostride[0] = os.dims[axis] * inner; g.ostride[1] = inner; g.ostride[2] = 1;
+        g.out_offset = off * inner;
+        off += is.dims[axis];
+        parts.push_back({x, g});
+      }
+      int esz = storage_size(odt);
+      add_launch("concat", v, 0, 2 * out_bytes, [=](cudaStream_t s) {
+        for (auto& p : parts) { int r = move(p.g, esz, p.x, y, s); if (r) return r; }
+        return 0;
+      });
+      p_->launches.back().n_kernels = (int)parts.size();
+      return ODLA_SUCCESS;
+    }
+    case OP_RESIZE: {
+      int xdt; const void* x = operand(v->in[0], &xdt, odt);
+      odla_value_shape xs = shape(v->in[0]);
+      // No layout argument exists: a tensor whose dim 1 is unchanged while dim 2 or 3 changes is NCHW.
+      bool nchw = xs.dims[1] == os.dims[1] && (xs.dims[2] != os.dims[2] || xs.dims[3] != os.dims[3]);
+      if (!nchw && xs.dims[3] != os.dims[3]) return fail(ODLA_UNSUPPORTED_OP, "'" + v->name + "': resize must keep the channel extent");
+      if (xs.dims[0] != os.dims[0]) return fail(ODLA_UNSUPPORTED_OP, "'" + v->name + "': resize must keep the batch extent");
+      int N = (int)xs.dims[0], H = (int)(nchw ? xs.dims[2] : xs.dims[1]), W = (int)(nchw ? xs.dims[3] : xs.dims[2]), C = (int)(nchw ? xs.dims[1] : xs.dims[3]);
+      int P = (int)(nchw ? os.dims[2] : os.dims[1]), Q = (int)(nchw ? os.dims[3] : os.dims[2]);
+      int esz = storage_size(odt);
+      add_launch("resize", v, 0, tensor_bytes(v->in[0]) + out_bytes, [=](cudaStream_t s) { return resize_nearest(esz, x, y, N, H, W, C, P, Q, !nchw, s); });
+      return ODLA_SUCCESS;
+    }
+    case OP_GATHER: {
+      int xdt, idt; const void* x = operand(v->in[0], &xdt, odt); const void* idx = operand(v->in[1], &idt);
+      if (idt != DT_S32 && idt != DT_S64) return fail(ODLA_UNSUPPORTED_DATATYPE, "'" + v->name + "': gather indices must be int32 or int64");
+      odla_value_shape xs = resolve(v->in[0])->kind == OP_CONST ? v->in[0]->type.shape : shape(v->in[0]);
+      int axis = (int)v->ia[0];
+      int64_t outer = 1, inner = 1, adim = xs.dims[axis];
+      for (int i = 0; i < axis; ++i) outer *= xs.dims[i];
+      for (int i = axis + 1; i < xs.size; ++i) inner *= xs.dims[i];
+      int64_t n_idx = resolve(v->in[1])->kind == OP_CONST ? numel(v->in[1]->type.shape) : count(v->in[1]);
+      int esz = storage_size(odt);
+      add_launch("gather", v, 0, 2 * out_bytes, [=](cudaStream_t s) { return gather(esz, x, idx, idt, y, outer, adim, n_idx, inner, s); });
+      return ODLA_SUCCESS;
+    }
+    case OP_SLICE: {
+      int xdt; const void* x = operand(v->in[0], &xdt, odt);
+      odla_value_shape xs = shape(v->in[0]);
+      if (xs.size > 8) return fail(ODLA_UNSUPPORTED_OP, "'" + v->name + "': rank above 8");
+      MoveGeom g{};
+      g.rank = xs.size;
+      int64_t a = 1, oa = 1;
+      for (int i = xs.size - 1; i >= 0; --i) {
+        g.oshape[i] = os.dims[i];
+        g.istride[i] = a * v->ia[xs.size + i];
+        g.in_offset += v->ia[i] * a;
+        g.ostride[i] = oa;
+        a *= xs.dims[i]; oa *= os.dims[i];
+      }
+      int esz = storage_size(odt);
+      add_launch("slice", v, 0, 2 * out_bytes, [=](cudaStream_t s) { return move(g, esz, x, y, s); });
+      return ODLA_SUCCESS;
+    }
+    case OP_CAST: {
+      int xdt; const void* x = operand(v->in[0], &xdt);
+      int64_t n = count(v);
+      add_launch("cast", v, 0, tensor_bytes(v->in[0]) + out_bytes, [=](cudaStream_t s) { return convert(xdt, odt, x, y, n, s); });
+      return ODLA_SUCCESS;
+    }
+    default: break;
+  }
+  return fail(ODLA_UNSUPPORTED_OP, std::string("no kernel for op '") + op_name(v->kind) + "' (value '" + v->name + "')");
+}
+
+odla_status Builder::emit() {
+  // argument conversions first
+  for (auto& io : p_->inputs) {
+    if (io.stage == io.slot) continue;
+    const void* src = p_->arena + io.stage; void* dst = p_->arena + io.slot;
+    int sdt = api_dt(io.v->type.element_type), ddt = dt_[io.v];
+    int64_t n = count(io.v);
+    add_launch("convert_in", io.v, 0, (double)io.api_bytes + (double)n * storage_size(ddt), [=](cudaStream_t s) { return convert(sdt, ddt, src, dst, n, s); });
+  }
+  for (auto& it : items_) {
+    odla_status st = it.fused ? emit_fused(it) : emit_plain(it);
+    if (st != ODLA_SUCCESS) return st;
+    if (!err_.empty()) return err_status_;
+  }
+  for (auto& io : p_->outputs) {
+    if (io.const_host || io.stage == io.slot) continue;
+    V r = resolve(io.v);
+    const void* src = p_->arena + io.slot; void* dst = p_->arena + io.stage;
+    int sdt = dt_[r], ddt = api_dt(io.v->type.element_type);
+    int64_t n = count(io.v);
+    Launch l; l.op = "convert_out"; l.name = io.v->name; l.bytes = (double)io.api_bytes + (double)n * storage_size(sdt);
+    l.fn = [=](cudaStream_t s) { return convert(sdt, ddt, src, dst, n, s); };
+    p_->launches.push_back(std::move(l));
+  }
+  return ODLA_SUCCESS;
+}
+
+odla_status Builder::run() {
+  for (V a : c_->args) if (api_dt(a->type.element_type) < 0) return fail(ODLA_UNSUPPORTED_DATATYPE, "argument '" + a->name + "' has an unsupported element type");
+  odla_status s = analyse();
+  if (s != ODLA_SUCCESS) return s;
+  s = place();
+  if (s != ODLA_SUCCESS) return s;
+  s = emit();
+  if (s != ODLA_SUCCESS) return s;
+  return err_.empty() ? ODLA_SUCCESS : err_status_;
+}
+
+// dim 0 can be split across GPUs only when no op mixes rows of the batch.
+bool graph_shardable(_odla_computation* c, int64_t* batch_out) {
+  if (c->args.empty()) return false;
+  int64_t B = c->args[0]->type.shape.size ? c->args[0]->type.shape.dims[0] : 1;
+  *batch_out = B;
+  for (V a : c->args) if (a->type.shape.size == 0 || a->type.shape.dims[0] != B) return false;
+  std::map<V, bool> cb;
+  for (auto& n : c->nodes) {
+    V v = n.get();
+    bool b = v->kind == OP_ARG;
+    for (auto i : v->in) if (i && cb[i]) b = true;
+    cb[v] = b;
+    if (!b) continue;
+    const auto& s = v->type.shape;
+    if (s.size == 0 || s.dims[0] % B != 0) return false;
+    switch (v->kind) {
+      case OP_TRANSPOSE: if (v->ia[0] != 0) return false; break;
+      case OP_SOFTMAX: if (v->ia[0] == 0) return false; break;
+      case OP_REDUCE_MEAN: for (size_t k = 1; k < v->ia.size(); ++k) if (v->ia[k] == 0) return false; break;
+      case OP_CONCAT: if (v->ia[0] == 0) return false; break;
+      case OP_LAYERNORM: if ((int)v->ia[0] >= s.size) return false; break;
+      case OP_SLICE: if (v->ia[0] != 0 || s.dims[0] != v->in[0]->type.shape.dims[0]) return false; break;
+      case OP_GATHER: if (cb[v->in[0]] && v->ia[0] == 0) return false; break;
+      case OP_QUANTIZE: case OP_DEQUANTIZE: if (numel(v->in[1]->type.shape) > 1 && v->ia[0] == 0) return false; break;
+      case OP_GEMM: if (v->in[1] && cb[v->in[1]] && v->type.shape.size == 2) return false; if (v->ia[0] && v->type.shape.size == 2) return false; break;
+      case OP_RESHAPE: {
+        // rows stay whole only if the per-row element count is the same integer before and after
+        const auto& is = v->in[0]->type.shape;
+        if (is.size == 0 || is.dims[0] % B != 0) return false;
+        break;
+      }
+      default: break;
+    }
+  }
+  for (V o : c->outs) if (cb[o] && (o->type.shape.size == 0 || o->type.shape.dims[0] % B != 0)) return false;
+  return true;
+}
+
+}  // namespace
+
+odla_status ensure_planned(_odla_computation* c) {
+  if (c->planned) return ODLA_SUCCESS;
+  int visible = visible_devices();
+  if (visible <= 0) {
+    B2_ERR("no CUDA device is visible: libodla_b200 has no CPU fallback");
+    return ODLA_FAILURE;
+  }
+  for (auto& r : c->replicas) {
+    cudaSetDevice(r.device);
+    r.plan.reset();
+    if (r.host_status) cudaFreeHost(r.host_status);
+    if (r.ev_begin) cudaEventDestroy(r.ev_begin);
+    if (r.ev_end) cudaEventDestroy(r.ev_end);
+    if (r.stream) cudaStreamDestroy(r.stream);
+  }
+  c->replicas.clear();
+  int64_t B = 1;
+  c->shardable = graph_shardable(c, &B);
+  int want = c->n_gpus > 0 ? c->n_gpus : visible;
+  int G = c->shardable ? (int)std::min<int64_t>(std::min(want, visible), std::max<int64_t>(B, 1)) : 1;
+  if (G < 1) G = 1;
+  c->replicas.resize((size_t)G);
+  int64_t start = 0;
+  for (int i = 0; i < G; ++i) {
+    Replica& r = c->replicas[i];
+    r.device = (c->first_device + i) % visible;
+    r.shard_batch = c->shardable ? B / G + (i < B % G ? 1 : 0) : B;
+    r.shard_start = start;
+    start += r.shard_batch;
+    B2_CUDA("setdevice", cudaSetDevice(r.device), ODLA_FAILURE);
+    B2_CUDA("stream", cudaStreamCreateWithFlags(&r.stream, cudaStreamNonBlocking), ODLA_FAILURE);
+    B2_CUDA("event", cudaEventCreate(&r.ev_begin), ODLA_FAILURE);
+    B2_CUDA("event", cudaEventCreate(&r.ev_end), ODLA_FAILURE);
+    B2_CUDA("alloc", cudaMallocHost((void**)&r.host_status, 256), ODLA_MEM_ERROR);
+    memset(r.host_status, 0, 256);
+    r.plan = std::make_unique<Plan>();
+    r.plan->device = r.device;
+    r.plan->batch = r.shard_batch;
+    Builder b(c, r.plan.get(), c->shardable ? B : r.shard_batch, r.shard_batch, r.shard_start);
+    odla_status s = b.run();
+    if (s != ODLA_SUCCESS) { c->replicas.clear(); return s; }
+    B2_INFO("GPU %d: rows [%lld,%lld), %zu launches, arena %.1f MiB, constants %.1f MiB", r.device, (long long)r.shard_start,
+            (long long)(r.shard_start + r.shard_batch), r.plan->launches.size(), r.plan->arena_bytes / 1048576.0, r.plan->const_bytes / 1048576.0);
+  }
+  // peer access between every pair, for device-resident outputs gathered over NVLink
+  for (int i = 0; i < G; ++i)
+    for (int j = 0; j < G; ++j) {
+      if (i == j) continue;
+      int can = 0;
+      cudaDeviceCanAccessPeer(&can, c->replicas[i].device, c->replicas[j].device);
+      if (can) { cudaSetDevice(c->replicas[i].device); cudaError_t e = cudaDeviceEnablePeerAccess(c->replicas[j].device, 0); if (e != cudaSuccess) cudaGetLastError(); }
+    }
+  c->planned = true;
+  return ODLA_SUCCESS;
+}
+
+namespace {
+// Which device owns `p`, or -1 for host memory.
+int pointer_device(const void* p) {
+  cudaPointerAttributes at;
+  if (cudaPointerGetAttributes(&at, p) != cudaSuccess) { cudaGetLastError(); return -1; }
+  if (at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged) return at.device;
+  return -1;
+}
+int run_launches(Replica& r, _odla_context* ctx, bool use_graph, long long* n_launched) {
+  Plan& p = *r.plan;
+  if (ctx->profiling) {
+    cudaEvent_t a, b;
+    cudaEventCreate(&a); cudaEventCreate(&b);
+    for (auto& l : p.launches) {
+      cudaEventRecord(a, r.stream);
+      int rc = inject_fault("launch") ? -2 : l.fn(r.stream);
+      cudaEventRecord(b, r.stream);
+      if (rc) { cudaEventDestroy(a); cudaEventDestroy(b); return rc; }
+      cudaEventSynchronize(b);
+      float ms = 0; cudaEventElapsedTime(&ms, a, b);
+      l.prof_ms += ms; l.prof_n++;
+      *n_launched += l.n_kernels;
+    }
+    cudaEventDestroy(a); cudaEventDestroy(b);
+    return 0;
+  }
+  if (use_graph && !p.graph && !p.graph_failed && !p.launches.empty()) {
+    cudaGraph_t g = nullptr;
+    bool ok = cudaStreamBeginCapture(r.stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+    if (ok) {
+      int rc = 0;
+      for (auto& l : p.launches) { rc = l.fn(r.stream); if (rc) break; }
+      cudaError_t e = cudaStreamEndCapture(r.stream, &g);
+      ok = rc == 0 && e == cudaSuccess && g;
+      if (ok) ok = cudaGraphInstantiate(&p.graph, g, 0) == cudaSuccess;
+      if (g) cudaGraphDestroy(g);
+    }
+    if (!ok) { cudaGetLastError(); p.graph = nullptr; p.graph_failed = true; B2_WARN("CUDA graph capture refused on GPU %d; using plain launches", r.device); }
+  }
+  if (inject_fault("launch")) return -2;
+  if (use_graph && p.graph) {
+    if (cudaGraphLaunch(p.graph, r.stream) != cudaSuccess) return -2;
+    for (auto& l : p.launches) *n_launched += l.n_kernels;
+    return 0;
+  }
+  for (auto& l : p.launches) {
+    int rc = l.fn(r.stream);
+    if (rc) return rc;
+    *n_launched += l.n_kernels;
+  }
+  return 0;
+}
+}  // namespace
+
+odla_status execute(_odla_computation* c, _odla_context* ctx) {
+  for (V a : c->args)
+    if (!ctx->in.count(a)) { B2_ERR("argument '%s' is not bound", a->name.c_str()); return ODLA_INVALID_PARAM; }
+  odla_status result = ODLA_SUCCESS;
+  long long launched = 0;
+  size_t enq = 0;
+  // enqueue everything on every GPU, then wait; on a failure stop enqueuing and drain what started
+  for (; enq < c->replicas.size() && result == ODLA_SUCCESS; ++enq) {
+    Replica& r = c->replicas[enq];
+    Plan& p = *r.plan;
+    auto fail_here = [&](odla_status s, const char* what) { B2_ERR("GPU %d: %s failed", r.device, what); result = s; };
+    if (cudaSetDevice(r.device) != cudaSuccess) { fail_here(ODLA_FAILURE, "cudaSetDevice"); break; }
+    cudaEventRecord(r.ev_begin, r.stream);
+    for (auto& io : p.inputs) {
+      const char* src = (const char*)ctx->in[io.v] + io.user_offset;
+      int pd = pointer_device(src);
+      cudaError_t e;
+      if (inject_fault("h2d")) e = cudaErrorUnknown;
+      else if (pd >= 0 && pd != r.device) e = cudaMemcpyPeerAsync(p.arena + io.stage, r.device, src, pd, (size_t)io.api_bytes, r.stream);
+      else e = cudaMemcpyAsync(p.arena + io.stage, src, (size_t)io.api_bytes, pd >= 0 ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, r.stream);
+      if (e != cudaSuccess) { fail_here(ODLA_FAILURE, "input copy"); break; }
+    }
+    if (result != ODLA_SUCCESS) break;
+    int rc = run_launches(r, ctx, c->use_graph, &launched);
+    if (rc) { fail_here(ODLA_FAILURE, "kernel launch"); break; }
+    for (auto& io : p.outputs) {
+      auto bound = ctx->out.find(io.v);
+      if (bound == ctx->out.end()) continue;
+      if (!io.per_shard && enq != 0) continue;  // a value that does not depend on the batch: GPU 0 writes it
+      char* dst = (char*)bound->second + io.user_offset;
+      int pd = pointer_device(dst);
+      cudaError_t e;
+      if (inject_fault("d2h")) e = cudaErrorUnknown;
+      else if (io.const_host) {
+        e = cudaMemcpyAsync(dst, io.const_host, (size_t)io.api_bytes, pd >= 0 ? cudaMemcpyHostToDevice : cudaMemcpyHostToHost, r.stream);
+      } else if (pd >= 0 && pd != r.device) {
+        e = inject_fault("peer") ? cudaErrorUnknown : cudaMemcpyPeerAsync(dst, pd, p.arena + io.stage, r.device, (size_t)io.api_bytes, r.stream);
+      } else e = cudaMemcpyAsync(dst, p.arena + io.stage, (size_t)io.api_bytes, pd >= 0 ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, r.stream);
+      if (e != cudaSuccess) { fail_here(ODLA_FAILURE, "output copy"); break; }
+    }
+    if (result != ODLA_SUCCESS) break;
+    cudaMemcpyAsync(r.host_status, p.status, sizeof(int) * 4, cudaMemcpyDeviceToHost, r.stream);
+    cudaEventRecord(r.ev_end, r.stream);
+  }
+  if (result != ODLA_SUCCESS) cudaGetLastError();
+  float worst = 0.f;
+  size_t started = std::min(enq + (result == ODLA_SUCCESS ? 0 : 1), c->replicas.size());
+  for (size_t i = 0; i < started; ++i) {
+    Replica& r = c->replicas[i];
+    cudaSetDevice(r.device);
+    cudaError_t e = cudaStreamSynchronize(r.stream);
+    if (e != cudaSuccess) { B2_ERR("GPU %d: stream synchronise failed: %s", r.device, cudaGetErrorString(e)); if (result == ODLA_SUCCESS) result = ODLA_FAILURE; continue; }
+    if (result == ODLA_SUCCESS) {
+      float ms = 0.f;
+      if (cudaEventElapsedTime(&ms, r.ev_begin, r.ev_end) == cudaSuccess) worst = std::max(worst, ms); else cudaGetLastError();
+      if (r.host_status[0] != 0) {
+        B2_ERR("GPU %d: a bounded wait inside a kernel expired (code %d, detail %d)", r.device, r.host_status[0], r.host_status[1]);
+        cudaMemsetAsync(r.plan->status, 0, 256, r.stream);
+        cudaStreamSynchronize(r.stream);
+        result = ODLA_TIMEOUT;
+      }
+    }
+  }
+  if (result == ODLA_SUCCESS) { ctx->last_ms = worst; ctx->last_launches = launched; }
+  return result;
+}
+
+}  // namespace b200
+
+using namespace b200;
+extern "C" {
+float odla_b200_LastExecuteDeviceMs(odla_context ctx) { return ctx ? ctx->last_ms : -1.f; }
+long long odla_b200_LastExecuteLaunches(odla_context ctx) { return ctx ? ctx->last_launches : 0; }
+odla_status odla_b200_SetProfiling(odla_context ctx, int enabled) {
+  if (!ctx) return ODLA_INVALID_PARAM;
+  ctx->profiling = enabled != 0;
+  if (enabled && ctx->comp)
+    for (auto& r : ctx->comp->replicas)
+      if (r.plan) for (auto& l : r.plan->launches) { l.prof_ms = 0; l.prof_n = 0; }
+  return ODLA_SUCCESS;
+}
+int odla_b200_GetProfile(odla_context ctx, odla_b200_profile_entry* entries, int capacity) {
+  if (!ctx || !ctx->comp || ctx->comp->replicas.empty() || !ctx->comp->replicas[0].plan) return 0;
+  auto& ls = ctx->comp->replicas[0].plan->launches;
+  for (int i = 0; i < (int)ls.size() && i < capacity && entries; ++i) {
+    memset(&entries[i], 0, sizeof(entries[i]));
+    snprintf(entries[i].op, sizeof(entries[i].op), "%s", ls[i].op.c_str());
+    snprintf(entries[i].name, sizeof(entries[i].name), "%s", ls[i].name.c_str());
+    entries[i].total_ms = ls[i].prof_ms; entries[i].launches = ls[i].prof_n;
+    entries[i].flops = ls[i].flops; entries[i].bytes = ls[i].bytes;
+  }
+  return (int)ls.size();
+}
+int odla_b200_DescribePlan(odla_computation c, char* buf, int capacity) {
+  if (!c) return 0;
+  if (ensure_planned(c) != ODLA_SUCCESS) return 0;
+  std::string s;
+  char line[256];
+  for (auto& r : c->replicas) {
+    snprintf(line, sizeof(line), "gpu %d rows [%lld,%lld) arena %lld bytes\n", r.device, (long long)r.shard_start, (long long)(r.shard_start + r.shard_batch), (long long)r.plan->arena_bytes);
+    s += line;
+    for (auto& l : r.plan->launches) { snprintf(line, sizeof(line), "  %-12s %s\n", l.op.c_str(), l.name.c_str()); s += line; }
+  }
+  if (buf && capacity > 0) { snprintf(buf, (size_t)capacity, "%s", s.c_str()); }
+  return (int)s.size() + 1;
+}
+}
