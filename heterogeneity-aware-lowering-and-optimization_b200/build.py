@@ -18,7 +18,7 @@ SOURCES = ["api.cc", "plan.cc", "kabi.cu", "kernels_simt.cu", "kernels_umma.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC,-fvisibility=default,-Wall,-Wno-unused-function", "-x", "cu",
-         "--expt-relaxed-constexpr", "-Xptxas", "-v"]
+         "--expt-relaxed-constexpr", "-Xptxas", "-v"] + (["-DUMMA_DEBUG_TS"] if os.environ.get("UMMA_DEBUG_TS") else []) + (["-DUMMA_EPI_WARPS=" + os.environ["UMMA_EPI_WARPS"]] if os.environ.get("UMMA_EPI_WARPS") else [])
 
 
 def _stale(obj, deps):

@@ -1,6 +1,7 @@
 // Raw kernel entry points of the C ABI (declared in include/odla_b200.h): thin wrappers that
 // let a caller that already holds device memory run one kernel without building a graph.
 #include <cstdio>
+#include <cstdlib>
 
 #include "common.h"
 
@@ -46,10 +47,17 @@ extern "C" int odla_b200_conv_umma(const odla_b200_conv_desc* d, const void* x, 
   if (rc == 0 && cudaMemcpyAsync(host_status, status, sizeof(host_status), cudaMemcpyDeviceToHost, (cudaStream_t)stream) != cudaSuccess) rc = -2;
   if (cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess) rc = -2;
   umma_conv_destroy(L);
-  cudaFree(status);
+  if (getenv("ODLA_B200_DEBUG_TS")) {
+    unsigned long long ts[12];
+    cudaMemcpy(ts, (char*)status + 32, sizeof(ts), cudaMemcpyDeviceToHost);
+    fprintf(stderr, "ts(ns rel. to kernel entry): sync=%lld tma0=%lld full0=%lld commit=%lld tfull=%lld epi_end=%lld teardown=%lld\n", (long long)(ts[0] - ts[7]),
+            (long long)(ts[1] - ts[7]), (long long)(ts[2] - ts[7]), (long long)(ts[3] - ts[7]), (long long)(ts[4] - ts[7]), (long long)(ts[5] - ts[7]), (long long)(ts[6] - ts[7]));
+  }
   if (rc == 0 && host_status[0] != 0) {
     fprintf(stderr, "[odla_b200] odla_b200_conv_umma: bounded wait expired (code %d, block %d)\n", host_status[0], host_status[1]);
+    cudaFree(status);
     return -3;
   }
+  cudaFree(status);
   return rc;
 }

@@ -13,7 +13,7 @@
 // One persistent CTA per SM walks its tiles (128 pixels x BN channels):
 //   warp 0      producer: waits for a free stage, arms its mbarrier with the byte count, issues TMA
 //   warp 1      allocates tensor memory, issues tcgen05.mma (one lane), commits to mbarriers
-//   warps 2..5  epilogue: tcgen05.ld the fp32 / int32 accumulators (one TMEM lane = one output pixel
+//   warps 2..9  epilogue: tcgen05.ld the fp32 / int32 accumulators (one TMEM lane = one output pixel
 //               per thread), apply the fused epilogue, store NHWC rows with 16-byte stores
 // Two accumulator buffers in tensor memory let the epilogue of tile i overlap the MMAs of tile i+1.
 //
@@ -32,7 +32,11 @@ namespace b200 {
 namespace {
 
 constexpr int BM = 128;
-constexpr int kThreads = 192;
+#ifndef UMMA_EPI_WARPS
+#define UMMA_EPI_WARPS 8
+#endif
+constexpr int kEpilogueWarps = UMMA_EPI_WARPS;
+constexpr int kThreads = 64 + 32 * kEpilogueWarps;
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 struct UmmaParams {
@@ -145,129 +149,180 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#ifdef UMMA_DEBUG_TS
+#define TS(i) do { if (blockIdx.x == 0 && p.status) ((unsigned long long*)p.status)[4 + (i)] = gtime(); } while (0)
+#else
+#define TS(i) do {} while (0)
+#endif
 // ------------------------------------------------------------------- epilogue ----
-// One thread owns one output pixel (row) and 32 consecutive channels held in v[].
-__device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, float* v, int64_t row, int col0, int ncols) {
-  const Epilogue& ep = p.ep;
-  if (ep.mul) {
+// One thread owns one output pixel (row) and 32 consecutive channels held in v[] (registers: every
+// index below is a compile-time constant after unrolling).  `full` says all 32 columns exist and
+// the row segment is 16-byte aligned, which allows 16-byte loads and stores.
+__device__ __forceinline__ void load_vec32(const float* __restrict__ src, int col0, int kmax, bool full, float (&out)[32]) {
+  if (full) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(v[j], __ldg(ep.mul + min(col0 + j, p.K_out - 1)));
+    for (int q = 0; q < 8; ++q) {
+      float4 f = __ldg((const float4*)(src + col0) + q);
+      out[4 * q] = f.x; out[4 * q + 1] = f.y; out[4 * q + 2] = f.z; out[4 * q + 3] = f.w;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) out[j] = __ldg(src + min(col0 + j, kmax));
+  }
+}
+__device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, float (&v)[32], int64_t row, int col0, int ncols, const uint4 (&pre)[4], bool use_pre) {
+  const Epilogue& ep = p.ep;
+  const bool full = ncols == 32 && (p.K_out & 15) == 0;
+  const int kmax = p.K_out - 1;
+  const int64_t base = row * p.K_out + col0;
+  // residual first: its latency overlaps the per-channel arithmetic below
+  float rv[32];
+  const bool has_res = ep.res != nullptr;
+  if (has_res) {
+    if (full && ep.res_dt == DT_F16) {
+      const uint4* rp = (const uint4*)((const __half*)ep.res + base);
+      uint4 u[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) u[q] = use_pre ? pre[q] : __ldg(rp + q);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const __half2* h = (const __half2*)&u[q];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) { float2 f = __half22float2(h[t]); rv[q * 8 + 2 * t] = f.x; rv[q * 8 + 2 * t + 1] = f.y; }
+      }
+    } else if (full && ep.res_dt == DT_BF16) {
+      const uint4* rp = (const uint4*)((const __nv_bfloat16*)ep.res + base);
+      uint4 u[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) u[q] = use_pre ? pre[q] : __ldg(rp + q);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const __nv_bfloat162* h = (const __nv_bfloat162*)&u[q];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) { float2 f = __bfloat1622float2(h[t]); rv[q * 8 + 2 * t] = f.x; rv[q * 8 + 2 * t + 1] = f.y; }
+      }
+    } else if (full && ep.res_dt == DT_S8) {
+      const uint4* rp = (const uint4*)((const int8_t*)ep.res + base);
+      uint4 u[2];
+      u[0] = use_pre ? pre[0] : __ldg(rp); u[1] = use_pre ? pre[1] : __ldg(rp + 1);
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const uint32_t* w = (const uint32_t*)&u[q];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+#pragma unroll
+          for (int b = 0; b < 4; ++b) rv[q * 16 + t * 4 + b] = __fmul_rn((float)(int)(int8_t)((w[t] >> (8 * b)) & 0xff), ep.res_scale);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        float r = 0.f;
+        if (j < ncols) {
+          r = load_as_float(ep.res, ep.res_dt, base + j);
+          if (ep.res_dt == DT_S8) r = __fmul_rn(r, ep.res_scale);
+        }
+        rv[j] = r;
+      }
+    }
+  }
+  float cv[32];
+  if (ep.mul) {
+    load_vec32(ep.mul, col0, kmax, full, cv);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(v[j], cv[j]);
   }
   if (ep.alpha != 1.f) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(v[j], ep.alpha);
   }
   if (ep.add1) {
+    load_vec32(ep.add1, col0, kmax, full, cv);
 #pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], __ldg(ep.add1 + min(col0 + j, p.K_out - 1)));
+    for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], cv[j]);
   }
   if (ep.add2) {
+    load_vec32(ep.add2, col0, kmax, full, cv);
 #pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], __ldg(ep.add2 + min(col0 + j, p.K_out - 1)));
+    for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], cv[j]);
   }
   if (ep.add_full) {
-    for (int j = 0; j < ncols; ++j)
-      v[j] = __fadd_rn(v[j], __fmul_rn(ep.beta_full, load_as_float(ep.add_full, ep.add_full_dt, row * p.K_out + col0 + j)));
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < ncols) v[j] = __fadd_rn(v[j], __fmul_rn(ep.beta_full, load_as_float(ep.add_full, ep.add_full_dt, base + j)));
   }
   if (ep.act != ACT_NONE && ep.act_first) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = apply_act(ep.act, v[j], ep.act_a, ep.act_b);
   }
-  if (ep.res) {
-    int64_t base = row * p.K_out + col0;
-    if (ncols == 32 && ep.res_dt == DT_F16 && ((p.K_out & 7) == 0)) {
-      const uint4* rp = (const uint4*)((const __half*)ep.res + base);
+  if (has_res) {
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        uint4 u = __ldg(rp + q);
-        const __half2* h = (const __half2*)&u;
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          float2 f = __half22float2(h[t]);
-          v[q * 8 + 2 * t] = __fadd_rn(v[q * 8 + 2 * t], f.x);
-          v[q * 8 + 2 * t + 1] = __fadd_rn(v[q * 8 + 2 * t + 1], f.y);
-        }
-      }
-    } else if (ncols == 32 && ep.res_dt == DT_S8 && ((p.K_out & 15) == 0)) {
-      const uint4* rp = (const uint4*)((const int8_t*)ep.res + base);
-#pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        uint4 u = __ldg(rp + q);
-        const int8_t* b = (const int8_t*)&u;
-#pragma unroll
-        for (int t = 0; t < 16; ++t) v[q * 16 + t] = __fadd_rn(v[q * 16 + t], __fmul_rn((float)b[t], ep.res_scale));
-      }
-    } else {
-      for (int j = 0; j < ncols; ++j) {
-        float r = load_as_float(ep.res, ep.res_dt, base + j);
-        if (ep.res_dt == DT_S8) r = __fmul_rn(r, ep.res_scale);
-        v[j] = __fadd_rn(v[j], r);
-      }
-    }
+    for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], rv[j]);
   }
   if (ep.act != ACT_NONE && !ep.act_first) {
+    if (ep.act == ACT_RELU) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = apply_act(ep.act, v[j], ep.act_a, ep.act_b);
+      for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = apply_act(ep.act, v[j], ep.act_a, ep.act_b);
+    }
   }
   // ---- store ----
-  int64_t obase = row * p.K_out + col0;
-  if (ep.out_dt == DT_F16) {
-    __half* out = (__half*)p.y + obase;
-    if (ncols == 32 && ((p.K_out & 7) == 0)) {
+  if (ep.out_dt == DT_F16 || ep.out_dt == DT_BF16) {
+    uint4 u[4];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        uint4 u;
-        __half2* h = (__half2*)&u;
+    for (int q = 0; q < 4; ++q) {
+      if (ep.out_dt == DT_F16) {
+        __half2* h = (__half2*)&u[q];
 #pragma unroll
         for (int t = 0; t < 4; ++t) h[t] = __floats2half2_rn(v[q * 8 + 2 * t], v[q * 8 + 2 * t + 1]);
-        ((uint4*)out)[q] = u;
-      }
-    } else {
-      for (int j = 0; j < ncols; ++j) out[j] = __float2half_rn(v[j]);
-    }
-  } else if (ep.out_dt == DT_BF16) {
-    __nv_bfloat16* out = (__nv_bfloat16*)p.y + obase;
-    if (ncols == 32 && ((p.K_out & 7) == 0)) {
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        uint4 u;
-        __nv_bfloat162* h = (__nv_bfloat162*)&u;
+      } else {
+        __nv_bfloat162* h = (__nv_bfloat162*)&u[q];
 #pragma unroll
         for (int t = 0; t < 4; ++t) h[t] = __floats2bfloat162_rn(v[q * 8 + 2 * t], v[q * 8 + 2 * t + 1]);
-        ((uint4*)out)[q] = u;
       }
+    }
+    uint16_t* out = (uint16_t*)p.y + base;
+    if (full) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) ((uint4*)out)[q] = u[q];
     } else {
-      for (int j = 0; j < ncols; ++j) out[j] = __float2bfloat16_rn(v[j]);
+      const uint16_t* e = (const uint16_t*)u;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) if (j < ncols) out[j] = e[j];
     }
   } else if (ep.out_dt == DT_S8) {
-    int8_t* out = (int8_t*)p.y + obase;
-    if (ncols == 32 && ((p.K_out & 15) == 0)) {
+    uint4 u[2];
+    uint32_t* w = (uint32_t*)u;
 #pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        uint4 u;
-        uint32_t* w = (uint32_t*)&u;
+    for (int t = 0; t < 8; ++t) {
+      uint32_t packed = 0;
 #pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          uint32_t packed = 0;
-#pragma unroll
-          for (int b = 0; b < 4; ++b) {
-            int qv = sat_s8(rintf(__fdiv_rn(v[q * 16 + t * 4 + b], ep.out_scale)));
-            packed |= (uint32_t)(qv & 0xff) << (8 * b);
-          }
-          w[t] = packed;
-        }
-        ((uint4*)out)[q] = u;
+      for (int b = 0; b < 4; ++b) {
+        int qv = sat_s8(rintf(__fdiv_rn(v[t * 4 + b], ep.out_scale)));
+        packed |= (uint32_t)(qv & 0xff) << (8 * b);
       }
+      w[t] = packed;
+    }
+    int8_t* out = (int8_t*)p.y + base;
+    if (full) {
+      ((uint4*)out)[0] = u[0];
+      ((uint4*)out)[1] = u[1];
     } else {
-      for (int j = 0; j < ncols; ++j) out[j] = sat_s8(rintf(__fdiv_rn(v[j], ep.out_scale)));
+      const int8_t* e = (const int8_t*)u;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) if (j < ncols) out[j] = e[j];
     }
   } else {  // DT_F32
-    float* out = (float*)p.y + obase;
-    if (ncols == 32 && ((p.K_out & 3) == 0)) {
+    float* out = (float*)p.y + base;
+    if (full) {
 #pragma unroll
       for (int q = 0; q < 8; ++q) ((float4*)out)[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
     } else {
-      for (int j = 0; j < ncols; ++j) out[j] = v[j];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) if (j < ncols) out[j] = v[j];
     }
   }
 }
@@ -276,6 +331,7 @@ __device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, float* v, in
 __global__ void __launch_bounds__(kThreads, 1)
 umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const UmmaParams p) {
   extern __shared__ uint8_t smem_raw[];
+  if (threadIdx.x == 0) TS(7);
   // operand stages start on a 1024-byte boundary (the 128-byte swizzle repeats every 1024 bytes)
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int a_bytes = BM * p.kb_bytes, b_bytes = p.BN * p.kb_bytes, stage_bytes = a_bytes + b_bytes;
@@ -290,7 +346,7 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], 4); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], kEpilogueWarps); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -303,6 +359,7 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) TS(0);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer ----
@@ -335,6 +392,7 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             tma_load_2d(sa, &tmA, &full_bar[s], c0, m0);
           }
           tma_load_3d(sb, &tmB, &full_bar[s], c0, tap, n0);
+          if (it == 0) TS(1);
         }
       }
       if (!ok) {
@@ -359,6 +417,7 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t ph = (it / p.stages) & 1;
           if (!mbar_wait(&full_bar[s], ph, abort_flag, p.status, 3)) { ok = false; break; }
           tc_fence_after();
+          if (it == 0) TS(2);
           const uint32_t sa = smem_u32(smem + (size_t)s * stage_bytes), sb = sa + a_bytes;
           const uint64_t da = ((uint64_t)p.desc_hi << 32) | (uint64_t)((sa & 0x3FFFF) >> 4) | (1ull << 16);
           const uint64_t db = ((uint64_t)p.desc_hi << 32) | (uint64_t)((sb & 0x3FFFF) >> 4) | (1ull << 16);
@@ -371,23 +430,45 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
         }
         if (ok) umma_commit(&tfull_bar[acc]);  // accumulator complete
+        if (tcount == 0) TS(3);
       }
     }
   } else {
     // ---------------------------------------------------------------- epilogue ----
     const int quarter = warp & 3;  // the TMEM lanes this warp may read: 32*quarter .. +31
+    const int cgroup = (warp - 2) >> 2;  // the four warps of a quarter take the 32-column chunks round-robin
     uint32_t tcount = 0;
     bool ok = true;
+    // Residual rows can be fetched before the accumulator is ready: they only depend on the tile.
+    const bool res_vec = p.ep.res && (p.K_out & 15) == 0 && (p.ep.res_dt == DT_F16 || p.ep.res_dt == DT_BF16 || p.ep.res_dt == DT_S8);
+    const int res_q = p.ep.res_dt == DT_S8 ? 2 : 4;       // 16-byte pieces per 32 channels
+    const int res_esz = p.ep.res_dt == DT_S8 ? 1 : 2;
+    constexpr int kGroups = kEpilogueWarps / 4;            // warps per TMEM lane quarter
+    constexpr int kChunksPerWarp = 8 / kGroups;            // BN <= 256 -> at most 8 chunks of 32 columns
     for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++tcount) {
       const uint32_t acc = tcount & 1, acc_ph = (tcount >> 1) & 1;
       const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * p.BN;
+      const int64_t row = (int64_t)m0 + quarter * 32 + lane;
+      uint4 pre[kChunksPerWarp][4] = {};
+      bool pre_ok[kChunksPerWarp];
+#pragma unroll
+      for (int i = 0; i < kChunksPerWarp; ++i) {
+        const int c = (cgroup + kGroups * i) * 32, col0 = n0 + c;
+        pre_ok[i] = res_vec && c < p.BN && row < p.M_total && col0 + 32 <= p.K_out;
+        if (pre_ok[i]) {
+          const uint4* rp = (const uint4*)((const char*)p.ep.res + (row * p.K_out + col0) * res_esz);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) if (q < res_q) pre[i][q] = __ldg(rp + q);
+        }
+      }
       if (!mbar_wait(&tfull_bar[acc], acc_ph, abort_flag, p.status, 4)) { ok = false; break; }
       tc_fence_after();
-      const int64_t row = (int64_t)m0 + quarter * 32 + lane;
+      if (tcount == 0 && threadIdx.x == 64) TS(4);
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * (uint32_t)p.BN;
-      for (int c = 0; c < p.BN; c += 32) {
-        const int col0 = n0 + c;
-        if (col0 >= p.K_out) break;  // uniform across the warp
+#pragma unroll
+      for (int i = 0; i < kChunksPerWarp; ++i) {
+        const int c = (cgroup + kGroups * i) * 32, col0 = n0 + c;
+        if (c >= p.BN || col0 >= p.K_out) break;  // uniform across the warp
         uint32_t r[32];
         tmem_ld32(taddr + (uint32_t)c, r);
         tmem_ld_wait();
@@ -395,7 +476,8 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const int ncols = min(32, p.K_out - col0);
           if (p.ep.out_dt == DT_S32) {
             int32_t* out = (int32_t*)p.y + row * p.K_out + col0;
-            for (int j = 0; j < ncols; ++j) out[j] = (int32_t)r[j];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) if (j < ncols) out[j] = (int32_t)r[j];
           } else {
             float v[32];
             if (p.acc_int) {
@@ -405,18 +487,20 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
             }
-            epilogue_chunk(p, v, row, col0, ncols);
+            epilogue_chunk(p, v, row, col0, ncols, pre[i], pre_ok[i]);
           }
         }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      if (tcount == 0 && threadIdx.x == 64) TS(5);
     }
   }
   // ------------------------------------------------------------------ teardown ----
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) TS(6);
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols) : "memory");
