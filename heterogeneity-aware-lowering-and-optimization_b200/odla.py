@@ -341,7 +341,10 @@ class Graph:
     def _binary(self, fn, a, b, name):
         h = getattr(self.lib, fn)(a[1], b[1], self._id(name))
         self._line(name, "odla_%s(%s, %s" % (fn, self._n(a), self._n(b)))
-        dims = np.broadcast_shapes(self.shapes[a[0]], self.shapes[b[0]])
+        try:
+            dims = np.broadcast_shapes(self.shapes[a[0]], self.shapes[b[0]])
+        except ValueError:   # the library records the error; keep building like generated code would
+            dims = self.shapes[a[0]]
         return self._reg(name, h, dims, self.dtypes[a[0]])
 
     def Softmax(self, x, axis, name):

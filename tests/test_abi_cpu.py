@@ -1,0 +1,113 @@
+"""The drop-in boundary: libodla_b200.so loads without a GPU, exports every symbol that
+include/odla_b200.h declares, keeps the reference's struct layouts and enum values, and a
+HALO-style model.cc compiles against the headers and links against the library."""
+import os
+import re
+import subprocess
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "odla_b200.h")
+REF_INC = "/root/reference/ODLA/include"
+
+
+def declared_functions():
+    text = re.sub(r"/\*.*?\*/", "", open(HEADER).read(), flags=re.S)
+    return sorted(set(re.findall(r"\b(odla_[A-Za-z0-9_]+)\s*\(", text)) - {"odla_logging_func"})
+
+
+def test_header_declares_the_hot_path_entry_points():
+    names = declared_functions()
+    for must in ["odla_CreateComputation", "odla_CreateArgument", "odla_CreateConstant", "odla_Conv", "odla_Gemm", "odla_BatchNormalization", "odla_Relu",
+                 "odla_MaxPool", "odla_AveragePool", "odla_Softmax", "odla_LayerNorm", "odla_Gelu", "odla_Quantize", "odla_Dequantize", "odla_BindToArgument",
+                 "odla_BindToOutput", "odla_ExecuteComputation", "odla_ReduceMean", "odla_Reshape", "odla_b200_conv_umma"]:
+        assert must in names
+
+
+def test_library_exports_every_declared_symbol(lib):
+    out = subprocess.run(["nm", "-D", "--defined-only", lib.path], capture_output=True, text=True, check=True).stdout
+    exported = set(line.split()[-1] for line in out.splitlines() if " T " in line)
+    missing = [n for n in declared_functions() if n not in exported]
+    assert not missing, "declared in include/odla_b200.h but not exported: %s" % missing
+
+
+def test_library_loads_and_fails_loudly_without_gpu(odla, lib):
+    assert b"odla_b200" in lib.GetVersionString()
+    if lib.b200_DeviceCount() > 0:
+        pytest.skip("a GPU is visible here")
+    g = odla.Graph(lib, "add")
+    a = g.Argument("a", (3,))
+    g.Output(g.Relu(a, "r"))
+    with pytest.raises(RuntimeError):
+        g.run({"a": np.zeros(3, np.float32)})   # ODLA_FAILURE: there is no CPU fallback
+    g.close()
+
+
+ABI_PROBE = r"""
+#include <cstdio>
+#include <cstddef>
+#include <ODLA/odla.h>
+int main() {
+  printf("sizeof_shape=%zu sizeof_type=%zu sizeof_values=%zu sizeof_ids=%zu sizeof_scalar=%zu sizeof_quant=%zu\n", sizeof(odla_value_shape),
+         sizeof(odla_value_type), sizeof(odla_values), sizeof(odla_value_ids), sizeof(odla_scalar_value), sizeof(odla_value_quant_info));
+  printf("off_dims=%zu off_tshape=%zu off_vals=%zu\n", offsetof(odla_value_shape, dims), offsetof(odla_value_type, shape), offsetof(odla_values, values));
+  printf("et=%d %d %d %d %d %d\n", ODLA_INT8, ODLA_UINT8, ODLA_QINT8, ODLA_FLOAT16, ODLA_FLOAT32, ODLA_BOOL);
+  printf("st=%d %d %d %d %d\n", ODLA_SUCCESS, ODLA_INVALID_PARAM, ODLA_UNSUPPORTED_OP, ODLA_TIMEOUT, ODLA_FAILURE);
+  printf("item=%d %d %d %d %d %d %d\n", ODLA_DYNAMIC_BATCH, ODLA_BF16_MODE, ODLA_FP16_MODE, ODLA_PROCESSOR_NUM, ODLA_USE_DATA_TYPE, ODLA_QUANT_TABLE, ODLA_ASYNC_CALLBACK_ARG);
+  printf("lay=%d %d %d %d dev=%d %d info=%d log=%d mode=%d rs=%d %d\n", ODLA_CHANNELS_FIRST, ODLA_CHANNELS_LAST, ODLA_SIO, ODLA_OIS, ODLA_DEVICE_NVIDIA_GPU,
+         ODLA_DEVICE_QUALCOMM_AIC100, ODLA_DEVICE_INFO_SDK_VERSION, ODLA_LOG_LEVEL_TRACE, ODLA_COMPUTE_INFERENCE, ODLA_NEAREST, ODLA_ALIGN_CORNERS);
+  // signatures: assigning to typed function pointers fails to compile if an argument list drifts
+  odla_value (*conv)(odla_value, odla_memory_layout, odla_uint32, odla_value, odla_memory_layout, const odla_uint32*, const odla_uint32*, const odla_uint32*,
+                     const odla_uint32*, odla_value, odla_value_shape, const odla_value_id) = odla_Conv;
+  odla_value (*gemm)(odla_value, odla_bool, odla_value, odla_bool, odla_float32, odla_float32, odla_value, odla_value_shape, const odla_value_id) = odla_Gemm;
+  odla_value (*quant)(odla_value, odla_value, odla_value, odla_int32, odla_element_type, const odla_value_id) = odla_Quantize;
+  odla_status (*exec)(const odla_computation, const odla_context, const odla_compute_mode, odla_device) = odla_ExecuteComputation;
+  odla_value (*pool)(odla_value, odla_memory_layout, const odla_uint32*, const odla_uint32*, const odla_uint32*, const odla_uint32*, odla_value_shape,
+                     const odla_value_id) = odla_MaxPool;
+  odla_value (*rm)(odla_value, odla_size_t, const odla_uint32*, odla_bool, odla_value_shape, const odla_value_id) = odla_ReduceMean;
+  printf("%d\n", conv && gemm && quant && exec && pool && rm);
+  return 0;
+}
+"""
+
+
+def _probe(tmp_path, inc, tag, lib_path):
+    src = tmp_path / ("probe_%s.cc" % tag)
+    src.write_text(ABI_PROBE)
+    exe = tmp_path / ("probe_%s" % tag)
+    d = os.path.dirname(lib_path)
+    subprocess.run(["g++", "-std=c++17", "-I", inc, str(src), "-o", str(exe), "-L", d, "-lodla_b200", "-Wl,-rpath," + d], check=True)
+    return subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout
+
+
+def test_abi_layout_and_enums_match_the_reference_headers(tmp_path, lib):
+    mine = _probe(tmp_path, os.path.join(ROOT, "include"), "mine", lib.path)
+    assert "sizeof_shape=88" in mine and "sizeof_type=96" in mine
+    if not os.path.isdir(REF_INC):
+        pytest.skip("reference headers not mounted here; layout pinned by the constants above")
+    theirs = _probe(tmp_path, REF_INC, "ref", lib.path)
+    assert mine == theirs
+
+
+def test_halo_style_model_cc_compiles_and_links(tmp_path, odla, lib, models):
+    """The emitted mnist_simple.cc includes only <ODLA/odla.h>; it must compile with this
+    repository's headers and with the reference's untouched headers, and link with -lodla_b200."""
+    g = odla.Graph(lib, "mnist_simple")
+    models.mnist.build(g)
+    cc = tmp_path / "mnist_simple.cc"
+    cc.write_text(g.emit_cc())
+    g.write_constants(str(tmp_path / "mnist_simple.bin"), str(tmp_path / "mnist_simple.S"))
+    g.close()
+    main = tmp_path / "main.cc"
+    main.write_text('extern "C" int mnist_simple(const float*, float*);\nint main(){ static float x[64*784], y[640]; return mnist_simple(x, y) == 0 ? 0 : 1; }\n')
+    d = os.path.dirname(lib.path)
+    incs = [os.path.join(ROOT, "include")] + ([REF_INC] if os.path.isdir(REF_INC) else [])
+    for i, inc in enumerate(incs):
+        subprocess.run(["g++", "-std=c++17", "-I", inc, "-c", str(cc), "-o", str(tmp_path / ("model%d.o" % i))], check=True)
+    subprocess.run(["gcc", "-c", str(tmp_path / "mnist_simple.S"), "-o", str(tmp_path / "weights.o")], check=True)
+    subprocess.run(["g++", str(main), str(tmp_path / "model0.o"), str(tmp_path / "weights.o"), "-o", str(tmp_path / "app"), "-L", d, "-lodla_b200",
+                    "-Wl,-rpath," + d], check=True)
+    syms = subprocess.run(["nm", str(tmp_path / "weights.o")], capture_output=True, text=True, check=True).stdout
+    assert " W" in syms and " b" in syms   # one OBJECT symbol per constant, like HALO's .bin

@@ -1,0 +1,156 @@
+"""Host-side logic that needs no GPU: graph recording, getters, property bags, error convention,
+the Python binding, the model emitters and the bench's multi-rank helpers (gloo, world size 2)."""
+import ctypes as C
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_getters_and_ids(odla, lib, models):
+    g = odla.Graph(lib, "mnist_simple")
+    models.mnist.build(g)
+    n = C.c_uint32()
+    assert lib.GetNumOfArgsFromComputation(g.comp, C.byref(n)) == 0 and n.value == 1
+    assert lib.GetNumOfOutputsFromComputation(g.comp, C.byref(n)) == 0 and n.value == 1
+    v = C.c_void_p()
+    assert lib.GetArgFromComputationByIdx(g.comp, 0, C.byref(v)) == 0
+    t = odla.ValueType()
+    assert lib.GetValueType(v, C.byref(t)) == 0
+    assert t.element_type == odla.FLOAT32 and t.shape.size == 2 and list(t.shape.dims[:2]) == [64, 784]
+    name = C.c_char_p()
+    assert lib.GetValueId(v, C.byref(name)) == 0 and name.value == b"x"
+    assert lib.GetOutputFromComputationByIdx(g.comp, 0, C.byref(v)) == 0
+    s = odla.Shape()
+    assert lib.GetRuntimeShape(None, v, C.byref(s)) == 0 and list(s.dims[:2]) == [64, 10]
+    assert lib.GetArgFromComputationByIdx(g.comp, 5, C.byref(v)) == odla.INVALID_PARAM
+    g.close()
+
+
+def test_builder_errors_poison_the_computation(odla, lib):
+    """Generated code never checks builder results (generic_cxx_codegen.cc:775-800 in the
+    reference), so a bad call returns a non-NULL value and the error surfaces at context time."""
+    lib.SetLogLevel(0)
+    try:
+        g = odla.Graph(lib, "bad")
+        x = g.Argument("x", (1, 8, 8, 4))
+        w = g.Constant("w", np.zeros((3, 3, 4, 4), np.float32))
+        y = g.Conv(x, odla.CHANNELS_LAST, 1, w, odla.SIO, (1, 1), (2, 2), (1, 1), (1, 1), None, (1, 8, 8, 4), "y")  # dilation 2: unsupported
+        assert y[1]
+        g.Output(g.Relu(y, "r"))
+        ctx = C.c_void_p()
+        assert lib.CreateContext(C.byref(ctx)) == odla.UNSUPPORTED_OP
+        g.close()
+        g = odla.Graph(lib, "bad2")
+        a, b = g.Argument("a", (2, 3)), g.Argument("b", (4, 5))
+        g.Add(a, b, "s")   # shapes do not broadcast
+        assert lib.CreateContext(C.byref(ctx)) == odla.INVALID_PARAM
+        g.close()
+    finally:
+        lib.SetLogLevel(3)
+
+
+def test_items_and_binding_checks(odla, lib):
+    g = odla.Graph(lib, "items", fp16=True, n_gpus=2, use_graph=False)
+    x = g.Argument("x", (4, 8))
+    y = g.Relu(x, "y")
+    g.Output(y)
+    lib.SetLogLevel(0)
+    try:
+        assert lib.SetComputationItem(g.comp, 999, None) == odla.FAILURE            # unknown key, like odla_dnnl
+        buf = np.zeros((4, 8), np.float32)
+        assert lib.BindToArgumentById(b"nope", buf.ctypes.data, g.context()) == odla.INVALID_PARAM
+        assert lib.BindToOutput(x[1], buf.ctypes.data, g.context()) == odla.INVALID_PARAM   # not an output
+        assert lib.BindToArgument(y[1], buf.ctypes.data, g.context()) == odla.INVALID_PARAM  # not an argument
+        assert lib.BindToOutputById(b"y", buf.ctypes.data, g.context()) == 0
+    finally:
+        lib.SetLogLevel(3)
+    g.close()
+
+
+def test_device_api_every_item_answers(odla, lib):
+    # tests/ODLA/device_test.cc:63-89 in the reference: every odla_GetDeviceInfo item returns SUCCESS
+    dev = C.c_void_p()
+    assert lib.AllocateDevice(None, 0, 0, C.byref(dev)) == 0
+    for item in range(13):
+        sv = odla.ScalarValue()
+        assert lib.GetDeviceInfo(dev, item, C.byref(sv)) == 0, item
+    assert lib.SetCurrentDevice(dev) == 0
+    assert lib.DestroyDevice(dev) == 0
+    assert lib.AllocateDevice(None, 5, 0, C.byref(dev)) != 0   # a Graphcore IPU is not ours
+
+
+def test_resnet50_description(models):
+    rn = models.resnet50
+    convs = rn.conv_list()
+    assert len(convs) == 53
+    by_name = {c[0]: c for c in convs}
+
+    def macs(name, h_in):
+        _, k, cin, cout, s, p = by_name[name]
+        ho = (h_in + 2 * p - k) // s + 1
+        return ho * ho * k * k * cin * cout, ho
+
+    mac, h = macs("conv1", 224)
+    h = (h + 2 - 3) // 2 + 1
+    for si, (blocks, mid, out, stride) in enumerate(rn.STAGES):
+        for b in range(blocks):
+            p = "s%db%d" % (si + 1, b)
+            if b == 0:
+                mac += macs(p + "_sc", h)[0]
+            m1, _ = macs(p + "_c1", h)
+            m2, h2 = macs(p + "_c2", h)
+            m3, _ = macs(p + "_c3", h2)
+            mac += m1 + m2 + m3
+            h = h2
+    mac += 2048 * 1000
+    assert mac == rn.MAC_PER_IMAGE == 4089184256
+    w = rn.weights()
+    assert sum(v.size for k, v in w.items() if k.endswith("_w")) + sum(v.size for k, v in w.items() if k.endswith("_b")) > 25_000_000
+    q = rn.quantize_weights(w)
+    assert q["conv1_w_q"].dtype == np.int8 and q["conv1_w_s"].shape == (64,)
+    assert int(np.abs(q["s2b0_c2_w_q"]).max()) == 127
+
+
+def test_emitted_resnet50_cc_follows_halo_rules(odla, lib, models):
+    rn = models.resnet50
+    w = {k: (v if v.size < 4096 else v) for k, v in rn.weights().items()}
+    g = odla.Graph(lib, "resnet50")
+    rn.build(g, 2, w)
+    text = g.emit_cc()
+    g.close()
+    assert text.count("odla_Conv(") == 53 and "odla_ReduceMean(" in text and "odla_Gemm(" in text
+    assert "nullptr, {.size = 4" in text                      # convolution bias argument is null, the BN offset is a separate Add
+    assert '#include <ODLA/odla.h>' in text and "odla_memory_layout::ODLA_SIO" in text
+    assert "static odla_computation Comp;" in text and "odla_BindToArgumentById" in text
+
+
+def test_two_rank_gloo_timing_helper():
+    """bench.py's max-over-ranks aggregation and per-rank sharding, on CPU with gloo."""
+    code = r'''
+import os, sys
+sys.path.insert(0, %r)
+import torch.distributed as dist
+import bench
+dist.init_process_group("gloo")
+r = dist.get_rank()
+assert bench.max_over_ranks(1.0 + r) == 2.0
+assert bench.sum_over_ranks(3) == 6
+assert bench.rank_seed(10, r) != bench.rank_seed(10, 1 - r)
+dist.barrier()
+dist.destroy_process_group()
+print("rank", r, "ok")
+''' % ROOT
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29533")
+    procs = []
+    for rank in range(2):
+        e = dict(env, RANK=str(rank), WORLD_SIZE="2", LOCAL_RANK=str(rank))
+        procs.append(subprocess.Popen([sys.executable, "-c", code], env=e, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
+    for p in procs:
+        out, err = p.communicate(timeout=120)
+        assert p.returncode == 0, err
+        assert "ok" in out

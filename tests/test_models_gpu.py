@@ -1,0 +1,209 @@
+"""Whole-graph parity on the GPU: the BASELINE configurations at sizes the CPU oracle finishes in
+seconds, the HALO-style model.cc linked against both libraries, multi-GPU sharding, host-side fault
+injection, and size-independent properties at the full batch size."""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_mnist_softmax_regression(odla, gpu_lib, ref, models):
+    x = models.mnist.inputs()
+    outs = []
+    for L, fp16 in ((gpu_lib, False), (ref, False), (gpu_lib, True)):
+        g = odla.Graph(L, "mnist_simple", fp16=fp16)
+        models.mnist.build(g)
+        outs.append(g.run(x)["y"])
+        g.close()
+    assert np.abs(outs[0] - outs[1]).max() < 1e-5
+    assert np.abs(outs[2] - outs[1]).max() < 1e-2 and (outs[2].argmax(1) == outs[1].argmax(1)).mean() >= 0.95
+
+
+@pytest.fixture(scope="module")
+def rn_weights(models):
+    return models.resnet50.weights()
+
+
+@pytest.fixture(scope="module")
+def rn_oracle_fp32(odla, ref, models, rn_weights):
+    """fp32 oracle outputs (soft-max and logits) for 2 images; ~20 s of CPU work, shared by the tests."""
+    rn = models.resnet50
+    x = rn.inputs(2)
+    g = odla.Graph(ref, "resnet50")
+    rn.build(g, 2, rn_weights)
+    prob = g.run(x)["prob"]
+    n = ref.cpuref_GetValueData(g.comp, b"logits", None, 0)
+    logits = np.zeros(n // 4, np.float32)
+    ref.cpuref_GetValueData(g.comp, b"logits", logits.ctypes.data, n)
+    g.close()
+    return x, prob, logits.reshape(2, 1000)
+
+
+def test_resnet50_fp32_matches_oracle(odla, gpu_lib, models, rn_weights, rn_oracle_fp32):
+    x, prob, _ = rn_oracle_fp32
+    g = odla.Graph(gpu_lib, "resnet50")
+    models.resnet50.build(g, 2, rn_weights)
+    got = g.run(x)["prob"]
+    g.close()
+    assert np.abs(got - prob).max() < 1e-4           # the reference's unit-test threshold
+    assert (got.argmax(1) == prob.argmax(1)).all()
+
+
+@pytest.mark.parametrize("mode", ["fp16", "bf16"])
+def test_resnet50_half_precision_within_tolerance(odla, gpu_lib, models, rn_weights, rn_oracle_fp32, mode):
+    x, prob, logits = rn_oracle_fp32
+    g = odla.Graph(gpu_lib, "resnet50", fp16=(mode == "fp16"), bf16=(mode == "bf16"))
+    models.resnet50.build(g, 2, rn_weights)
+    got = g.run(x)["prob"]
+    desc = g.describe()
+    g.close()
+    assert desc.count("conv_umma") >= 52               # everything but (at most) the 3-channel stem runs on the tensor cores
+    assert np.abs(got - prob).max() <= 1e-2            # max-abs 1e-2 against the fp32 reference
+    assert (got.argmax(1) == prob.argmax(1)).all()     # top-1 agreement
+    if mode == "fp16":
+        assert np.abs(got - prob).max() <= 2e-3
+
+
+def test_resnet50_int8_is_bit_exact(odla, gpu_lib, ref, models, rn_weights):
+    """Every requantised int8 tensor that leaves a convolution block, the int8 pooled features and
+    the final probabilities, for 2 images, against the CPU oracle."""
+    rn = models.resnet50
+    scales = rn.calibrate(rn_weights, n_images=8)
+    wq = rn.quantize_weights(rn_weights)
+    taps = ("conv1", "s1b0_sc", "s1b0_c3", "s2b0_c2", "s3b5_c3", "s4b2_c3", "pool")
+    x = rn.inputs(2)
+    outs = []
+    for L in (gpu_lib, ref):
+        g = odla.Graph(L, "resnet50_int8")
+        rn.build_int8(g, 2, rn_weights, wq, scales, extra_outputs=taps)
+        outs.append(g.run(x))
+        if L is gpu_lib:
+            desc = g.describe()
+        g.close()
+    got, want = outs
+    assert desc.count("conv_umma") >= 52 and "gemm_umma" in desc
+    for k in want:
+        if want[k].dtype == np.int8:
+            assert np.array_equal(got[k], want[k]), "%s: %d of %d differ" % (k, int((got[k] != want[k]).sum()), want[k].size)
+    assert int(np.abs(want["s4b2_c3_q"].astype(int)).max()) > 20     # the tensors are not trivially zero
+    assert np.abs(got["prob"] - want["prob"]).max() < 1e-6
+
+
+def test_full_batch_properties_fp16(odla, gpu_lib, models, rn_weights):
+    """At the benchmark batch size (256) the oracle is out of reach; use properties instead: each
+    image's result is independent of its batch neighbours and of its position in the batch, and
+    probabilities sum to one."""
+    rn = models.resnet50
+    B = 256
+    x = rn.inputs(B)["input"]
+    g = odla.Graph(gpu_lib, "resnet50", fp16=True)
+    rn.build(g, B, rn_weights)
+    a = g.run({"input": x})["prob"]
+    perm = np.random.default_rng(0).permutation(B)
+    b = g.run({"input": np.ascontiguousarray(x[perm])})["prob"]
+    g.close()
+    assert np.array_equal(a[perm], b)                      # bitwise: same kernels, same per-row arithmetic
+    np.testing.assert_allclose(a.sum(1), 1.0, atol=1e-3)
+    g = odla.Graph(gpu_lib, "resnet50", fp16=True)
+    rn.build(g, 2, rn_weights)
+    c = g.run({"input": np.ascontiguousarray(x[:2])})["prob"]
+    g.close()
+    assert np.abs(c - a[:2]).max() < 1e-3                  # a different tile decomposition may reorder nothing but the batch rows
+
+
+def test_halo_style_model_runs_against_both_libraries(tmp_path, odla, gpu_lib, ref, models):
+    """mnist_simple.cc (emitted in the shape of HALO's generator) + its constants object + a main(),
+    linked once with -lodla_b200 and once with the oracle platform: same probabilities."""
+    g = odla.Graph(ref, "mnist_simple")
+    models.mnist.build(g)
+    (tmp_path / "model.cc").write_text(g.emit_cc())
+    g.write_constants(str(tmp_path / "model.bin"), str(tmp_path / "model.S"))
+    g.close()
+    x = models.mnist.inputs()["x"]
+    x.tofile(tmp_path / "x.bin")
+    (tmp_path / "main.cc").write_text(r'''
+#include <cstdio>
+extern "C" int mnist_simple(const float*, float*);
+extern "C" int mnist_simple_fini();
+int main(int argc, char** argv) {
+  static float x[64 * 784], y[640];
+  FILE* f = fopen(argv[1], "rb"); if (!f || fread(x, 4, 64 * 784, f) != 64 * 784) return 2; fclose(f);
+  for (int i = 0; i < 2; ++i) if (mnist_simple(x, y) != 0) return 1;     // bind-and-run twice, like a serving loop
+  f = fopen(argv[2], "wb"); fwrite(y, 4, 640, f); fclose(f);
+  return mnist_simple_fini();
+}''')
+    subprocess.run(["g++", "-std=c++17", "-I", os.path.join(ROOT, "include"), "-c", str(tmp_path / "model.cc"), "-o", str(tmp_path / "model.o")], check=True)
+    subprocess.run(["gcc", "-c", str(tmp_path / "model.S"), "-o", str(tmp_path / "weights.o")], check=True)
+    res = {}
+    for tag, path in (("b200", gpu_lib.path), ("cpuref", ref.path)):
+        d, n = os.path.dirname(path), os.path.basename(path)[3:-3]
+        exe = tmp_path / ("app_" + tag)
+        subprocess.run(["g++", str(tmp_path / "main.cc"), str(tmp_path / "model.o"), str(tmp_path / "weights.o"), "-o", str(exe), "-L", d, "-l" + n,
+                        "-Wl,-rpath," + d], check=True)
+        subprocess.run([str(exe), str(tmp_path / "x.bin"), str(tmp_path / (tag + ".out"))], check=True)
+        res[tag] = np.fromfile(tmp_path / (tag + ".out"), np.float32)
+    assert np.abs(res["b200"] - res["cpuref"]).max() < 1e-5
+
+
+def test_device_resident_bindings_and_timing(odla, gpu_lib, models):
+    import torch
+    g = odla.Graph(gpu_lib, "mnist_simple")
+    models.mnist.build(g)
+    x = models.mnist.inputs()["x"]
+    want = g.run({"x": x})["y"]
+    xd = torch.from_numpy(x).cuda()
+    yd = torch.zeros((64, 10), dtype=torch.float32, device="cuda")
+    g.bind_input("x", xd.data_ptr())
+    g.bind_output("y", yd.data_ptr())
+    assert g.execute() == 0
+    assert np.array_equal(yd.cpu().numpy(), want)
+    assert g.device_ms() > 0 and g.launches() >= 2
+    prof = g.profile(2)
+    assert [p["op"] for p in prof] == ["gemm_simt", "softmax"] and all(p["ms"] > 0 for p in prof)
+    g.close()
+
+
+def test_host_side_fault_injection_unwinds_cleanly(odla, gpu_lib, models):
+    """A failing copy or launch (made on the host: the n-th call of a site reports an error without
+    touching the GPU) must surface as an error status, leave the streams idle, and the next execute
+    must succeed with the right answer."""
+    g = odla.Graph(gpu_lib, "mnist_simple")
+    models.mnist.build(g)
+    x = models.mnist.inputs()
+    want = g.run(x)["y"]
+    gpu_lib.SetLogLevel(0)
+    try:
+        for site in ("h2d", "launch", "d2h"):
+            os.environ["ODLA_B200_INJECT"] = site + "@1"
+            with pytest.raises(RuntimeError):
+                g.run(x)
+            del os.environ["ODLA_B200_INJECT"]
+            assert np.array_equal(g.run(x)["y"], want)
+    finally:
+        os.environ.pop("ODLA_B200_INJECT", None)
+        gpu_lib.SetLogLevel(3)
+    g.close()
+
+
+def test_batch_is_sharded_over_every_visible_gpu(odla, gpu_lib, ref, models):
+    """With more than one GPU the batch is split into contiguous shards (uneven when it does not
+    divide, fewer GPUs than requested when the batch is smaller); results equal the oracle's."""
+    n = gpu_lib.b200_DeviceCount()
+    x = models.mnist.inputs(batch=11)
+    gr = odla.Graph(ref, "m")
+    models.mnist.build(gr, batch=11)
+    want = gr.run(x)["y"]
+    gr.close()
+    for want_gpus in sorted({1, min(2, n), n, n + 3}):
+        g = odla.Graph(gpu_lib, "m", n_gpus=want_gpus)
+        models.mnist.build(g, batch=11)
+        got = g.run(x)["y"]
+        desc = g.describe()
+        g.close()
+        assert np.abs(got - want).max() < 1e-5
+        assert desc.count("gpu ") == min(want_gpus, n, 11)
