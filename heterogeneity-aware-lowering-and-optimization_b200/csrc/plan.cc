@@ -320,6 +320,7 @@ void Builder::try_fuse(V root) {
   while (channel_last) {
     if (cur->is_output || users_[cur] != 1) break;
     V nxt = consumers_[cur][0];
+    if (fused_into_.count(nxt)) break;  // already folded into another root's epilogue
     if (nxt->kind == OP_BINARY && nxt->ia[0] == BIN_ADD) {
       V other = nxt->in[0] == cur ? nxt->in[1] : nxt->in[0];
       if (other == cur) break;
@@ -327,7 +328,9 @@ void Builder::try_fuse(V root) {
       bool per_channel = other->kind == OP_CONST && numel(os) == K && os.dims[os.size - 1] == K;
       bool same_shape = numel(other->type.shape) == numel(cur->type.shape) && other->kind != OP_CONST;
       if (per_channel && !f->add_const && !f->res && f->act == ACT_NONE) f->add_const = other;
-      else if (same_shape && !f->res && other->index < nxt->index) {
+      // the residual must exist before this root launches: when two convolutions feed one Add
+      // (projection shortcut), the later one takes the Add and reads the earlier one's result
+      else if (same_shape && !f->res && other->index < root->index) {
         if (is_per_tensor_dq(other)) { f->res = other->in[0]; f->res_scale = other->in[1]; }
         else f->res = other;
         if (f->act != ACT_NONE) f->act_first = true;
@@ -900,6 +903,7 @@ bool graph_shardable(_odla_computation* c, int64_t* batch_out) {
   if (c->args.empty()) return false;
   int64_t B = c->args[0]->type.shape.size ? c->args[0]->type.shape.dims[0] : 1;
   *batch_out = B;
+  if (B <= 0) return false;  // an empty batch cannot be split
   for (V a : c->args) if (a->type.shape.size == 0 || a->type.shape.dims[0] != B) return false;
   std::map<V, bool> cb;
   for (auto& n : c->nodes) {
