@@ -330,7 +330,7 @@ void Builder::try_fuse(V root) {
       if (per_channel && !f->add_const && !f->res && f->act == ACT_NONE) f->add_const = other;
       // the residual must exist before this root launches: when two convolutions feed one Add
       // (projection shortcut), the later one takes the Add and reads the earlier one's result
-      else if (same_shape && !f->res && other->index < root->index) {
+      else if (same_shape && !f->res && (is_per_tensor_dq(other) ? other->in[0] : other)->index < root->index) {
         if (is_per_tensor_dq(other)) { f->res = other->in[0]; f->res_scale = other->in[1]; }
         else f->res = other;
         if (f->act != ACT_NONE) f->act_first = true;
