@@ -158,6 +158,7 @@ _OPTIONAL = {
     "odla_b200_GetProfile": (C.c_int, [_V, C.POINTER(ProfileEntry), C.c_int]),
     "odla_b200_DescribePlan": (C.c_int, [_V, C.c_char_p, C.c_int]),
     "odla_b200_conv_umma": (C.c_int, [C.POINTER(ConvDesc), _V, _V, _V, _V, _V, _V, _V]),
+    "odla_b200_reduce_mean_noalloc": (C.c_int, [_V, _V, C.c_int, C.POINTER(C.c_longlong), C.c_int, C.POINTER(C.c_int), C.c_int, _V]),
     "odla_cpuref_UsesReference": (C.c_int, []),
     "odla_cpuref_Threads": (C.c_int, []),
     "odla_cpuref_GetAccumulators": (C.c_longlong, [_V, C.c_char_p, _V, C.c_longlong]),

@@ -392,6 +392,32 @@ int odla_b200_conv_umma(const odla_b200_conv_desc* desc, const void* x, const vo
                         const float* mul, const float* add, const void* residual, void* y,
                         void* stream);
 
+/* odla_b200_reduce_mean_noalloc -- this entry point has no counterpart in the reference.
+ *
+ * Mean over `n_axes` axes of a dense tensor in device memory, reduced one axis after the other in
+ * the order given (the arithmetic of odla_ReduceMean), without allocating anything: no cudaMalloc,
+ * no cudaFree, no allocating library call.  It is for callers that cannot allocate while they run --
+ * a runtime that gave all device memory to its own pool at start-up, or a serving loop that must
+ * stay clear of the allocator's lock and its device-wide synchronisation.
+ *
+ *   x, y    device pointers on the current device; x holds prod(dims) elements, y the reduced tensor
+ *   dtype   0 = fp32, 1 = fp16, 2 = bf16 (input and output)
+ *   dims    extents, rank <= 10; axes: the axes to reduce, each in [0, rank)
+ *   stream  a cudaStream_t passed as void* (NULL = default stream); the kernels are only enqueued
+ *
+ * Intermediates between passes live in a fixed 8 MiB array inside the library image (two halves of
+ * 1 Mi floats); every GPU that loads the library holds it until the process exits.  A call whose
+ * intermediate after any pass but the last exceeds 1 Mi floats is refused with -1 and a message;
+ * the global pool of a [N,7,7,2048] tensor fits up to N = 73.
+ * The first call on a device looks up the array's device address (driver work): make that call
+ * before any stream capture begins.  All calls share the array and it keeps what the last call left
+ * there (nothing in it needs clearing: each pass overwrites what the next one reads), so two calls
+ * whose kernels may overlap on the GPU -- different streams without an ordering between them --
+ * race on it; order them.
+ * Returns 0, -1 (bad argument or too large) or -2 (CUDA error). */
+int odla_b200_reduce_mean_noalloc(const void* x, void* y, int dtype, const long long* dims, int rank,
+                                  const int* axes, int n_axes, void* stream);
+
 #ifdef __cplusplus
 } /* extern "C" */
 #endif
