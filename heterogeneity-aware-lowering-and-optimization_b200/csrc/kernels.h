@@ -134,6 +134,9 @@ struct MoveGeom {
   int64_t in_offset, out_offset;
 };
 int move(const MoveGeom& g, int esz, const void* x, void* y, cudaStream_t stream);
+// out[pixel][0..Cp) = in[pixel][0..C) followed by zeros; Cp*esz must be 32 (one thread writes one pixel as
+// two 16-byte stores).  Gives few-channel inputs (an RGB image) rows that TMA can address.
+int pad_channels(int esz, const void* x, void* y, int64_t pixels, int C, int Cp, cudaStream_t stream);
 int resize_nearest(int esz, const void* x, void* y, int N, int H, int W, int C, int P, int Q, bool nhwc,
                    cudaStream_t stream);
 // out[o, k, :] = in[o, idx[k], :]; idx int32 or int64.

@@ -413,6 +413,20 @@ __global__ void move_kernel(MoveGeom g, const T* __restrict__ x, T* __restrict__
   }
 }
 template <typename T>
+__global__ void pad_channels_kernel(const T* __restrict__ x, uint4* __restrict__ y, int64_t pixels, int C) {
+  constexpr int CP = 32 / (int)sizeof(T);
+  for (int64_t p = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; p < pixels; p += (int64_t)gridDim.x * blockDim.x) {
+    uint4 out[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+    T* o = (T*)out;
+    const T* in = x + p * C;
+#pragma unroll
+    for (int c = 0; c < CP; ++c)
+      if (c < C) o[c] = in[c];
+    y[2 * p] = out[0];
+    y[2 * p + 1] = out[1];
+  }
+}
+template <typename T>
 __global__ void resize_nearest_kernel(const T* __restrict__ x, T* __restrict__ y, int N, int H, int W, int C, int P, int Q, int nhwc) {
   int64_t total = (int64_t)N * P * Q * C;
   for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
@@ -439,9 +453,6 @@ __global__ void gather_kernel(const T* __restrict__ x, const void* idx, int idx_
     y[e] = x[(o * axis_dim + id) * inner + i];
   }
 }
-
-template <template <typename> class K, typename... Args>
-int dispatch_esz(int esz, int grid, int threads, cudaStream_t s, Args... args);
 
 }  // namespace
 
@@ -577,6 +588,15 @@ int move(const MoveGeom& g, int esz, const void* x, void* y, cudaStream_t s) {
     case 8: move_kernel<uint64_t><<<grid, 256, 0, s>>>(g, (const uint64_t*)x, (uint64_t*)y, total); break;
     default: return -1;
   }
+  return check_launch();
+}
+int pad_channels(int esz, const void* x, void* y, int64_t pixels, int C, int Cp, cudaStream_t s) {
+  if (pixels <= 0) return 0;
+  if (Cp * esz != 32 || C > Cp || (uintptr_t)y % 16 != 0) return -1;
+  int grid = grid_for(pixels, 256);
+  if (esz == 1) pad_channels_kernel<uint8_t><<<grid, 256, 0, s>>>((const uint8_t*)x, (uint4*)y, pixels, C);
+  else if (esz == 2) pad_channels_kernel<uint16_t><<<grid, 256, 0, s>>>((const uint16_t*)x, (uint4*)y, pixels, C);
+  else return -1;
   return check_launch();
 }
 int resize_nearest(int esz, const void* x, void* y, int N, int H, int W, int C, int P, int Q, bool nhwc, cudaStream_t s) {

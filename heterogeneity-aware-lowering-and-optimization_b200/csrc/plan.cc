@@ -502,20 +502,50 @@ odla_status Builder::emit_fused(const Item& it) {
     double flops = 2.0 * g.N * g.P * g.Q * (double)K * g.R * g.S * cg;
     double bytes = tensor_bytes(f.x) + tensor_bytes(f.out) + (double)numel(ws) * storage_size(in_dt) + (f.res ? tensor_bytes(f.res) : 0);
     UmmaConv uc{g.N, g.H, g.W, g.C, g.K, g.R, g.S, g.P, g.Q, g.stride_h, g.stride_w, g.pad_t, g.pad_l, in_dt};
+    // A few-channel input (the RGB stem) has pixels TMA cannot address (rows must be 16-byte
+    // multiples of at least 32 bytes): copy it once into a channel-padded scratch tensor (32 bytes
+    // per pixel, zeros in the tail, zero filter taps to match) and run the tensor-core kernel on that.
+    int Cp = g.C;
+    const void* x_umma = x;
+    void* padded = nullptr;
+    if (allow_umma && nhwc && groups == 1 && (in_dt == DT_F16 || in_dt == DT_BF16 || in_dt == DT_S8) && !umma_conv_supported(uc) &&
+        g.C * storage_size(in_dt) < 32) {
+      UmmaConv up = uc;
+      up.C = 32 / storage_size(in_dt);
+      if (umma_conv_supported(up)) {
+        Cp = up.C;
+        size_t pbytes = (size_t)g.N * g.H * g.W * 32;
+        if (inject_fault("alloc") || cudaMalloc(&padded, pbytes ? pbytes : 32) != cudaSuccess) return fail(ODLA_MEM_ERROR, "scratch allocation failed");
+        p_->extra_allocs.push_back(padded);
+        x_umma = padded;
+        uc = up;
+      }
+    }
     if (allow_umma && nhwc && groups == 1 && umma_conv_supported(uc)) {
       // filters HWIO -> [K][R*S*C] so that each output channel's taps are contiguous (K-major B operand)
       auto wf = const_as_f32(f.w);
-      std::vector<float> w2(wf.size());
-      int64_t rsc = (int64_t)g.R * g.S * g.C;
-      for (int64_t t = 0; t < rsc; ++t)
-        for (int64_t k = 0; k < K; ++k) w2[(size_t)(k * rsc + t)] = wf[(size_t)(t * K + k)];
+      int64_t rs = (int64_t)g.R * g.S;
+      std::vector<float> w2((size_t)(K * rs * Cp), 0.f);
+      for (int64_t t = 0; t < rs; ++t)
+        for (int64_t c = 0; c < g.C; ++c)
+          for (int64_t k = 0; k < K; ++k) w2[(size_t)((k * rs + t) * Cp + c)] = wf[(size_t)((t * g.C + c) * K + k)];
       auto wb = f32_to_storage(w2, in_dt);
       void* wd = upload(wb.data(), wb.size());
       if (!wd) return err_status_;
-      UmmaLaunch* ul = umma_conv_prepare(uc, x, wd, y, ep, p_->status, sms);
+      UmmaLaunch* ul = umma_conv_prepare(uc, x_umma, wd, y, ep, p_->status, sms);
       if (!ul) return fail(ODLA_FAILURE, "'" + root->name + "': tensor-map encoding failed");
       p_->umma.push_back(ul);
-      add_launch("conv_umma", f.out, flops, bytes, [ul](cudaStream_t s) { return umma_conv_run(ul, s); });
+      if (padded) {
+        int esz = storage_size(in_dt), C0 = g.C;
+        int64_t pixels = (int64_t)g.N * g.H * g.W;
+        add_launch("conv_umma", f.out, flops, bytes + 2.0 * pixels * 32, [=](cudaStream_t s) {
+          int rc = pad_channels(esz, x, padded, pixels, C0, Cp, s);
+          return rc ? rc : umma_conv_run(ul, s);
+        });
+        p_->launches.back().n_kernels = 2;
+      } else {
+        add_launch("conv_umma", f.out, flops, bytes, [ul](cudaStream_t s) { return umma_conv_run(ul, s); });
+      }
       return ODLA_SUCCESS;
     }
     const void* wd = const_dev(f.w, in_dt);
