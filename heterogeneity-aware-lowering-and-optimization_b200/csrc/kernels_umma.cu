@@ -47,6 +47,8 @@ struct UmmaParams {
   int kb_bytes;        // bytes of K per stage: 128, 64 or 32 (= swizzle span)
   int chunks_per_tap;  // ceil(C / kbe)
   int num_kb;          // R*S*chunks_per_tap
+  int bps;             // operand boxes (k-blocks) per pipeline stage
+  int num_it;          // ceil(num_kb / bps): stage fills per tile
   int BN, stages, m_tiles, n_tiles, total_tiles;
   uint32_t idesc;      // tcgen05 instruction descriptor
   uint32_t desc_hi;    // upper 32 bits of the shared-memory matrix descriptors
@@ -334,7 +336,7 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (threadIdx.x == 0) TS(7);
   // operand stages start on a 1024-byte boundary (the 128-byte swizzle repeats every 1024 bytes)
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  const int a_bytes = BM * p.kb_bytes, b_bytes = p.BN * p.kb_bytes, stage_bytes = a_bytes + b_bytes;
+  const int stage_bytes = p.bps * (BM + p.BN) * p.kb_bytes;
   uint8_t* ctrl = smem + (size_t)p.stages * stage_bytes;
   uint64_t* full_bar = (uint64_t*)ctrl;            // [stages]
   uint64_t* empty_bar = full_bar + 16;             // [stages]
@@ -361,10 +363,14 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const uint32_t tmem_base = *tmem_slot;
   if (threadIdx.x == 0) TS(0);
 
+  const uint32_t a_box = (uint32_t)(BM * p.kb_bytes), b_box = (uint32_t)(p.BN * p.kb_bytes);
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer ----
+    // One lane runs this loop; it is kept free of divisions (filter tap, channel chunk, stage and
+    // phase are running counters) because its instruction rate bounds the rate of k-blocks.
     if (elect_one()) {
-      uint32_t it = 0;
+      int s = 0;
+      uint32_t ph = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
         const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * p.BN;
@@ -377,57 +383,73 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           w0 = oq * p.stride_w - p.pad_l;
           h0 = op * p.stride_h - p.pad_t;
         }
-        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
-          const int s = it % p.stages;
-          const uint32_t ph = (it / p.stages) & 1;
-          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
-          const int tap = kb / p.chunks_per_tap, c0 = (kb - tap * p.chunks_per_tap) * p.kbe;
+        int tap = 0, fr = 0, fs = 0, c0 = 0, left = p.num_kb;
+        for (int it = 0; it < p.num_it; ++it) {
+          if (!mbar_wait(empty_bar + s, ph ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
+          const int nb = left < p.bps ? left : p.bps;
+          left -= nb;
           uint8_t* sa = smem + (size_t)s * stage_bytes;
-          uint8_t* sb = sa + a_bytes;
-          mbar_expect_tx(&full_bar[s], (uint32_t)stage_bytes);
-          if (p.im2col) {
-            const int fr = tap / p.S, fs = tap - fr * p.S;
-            tma_load_im2col_4d(sa, &tmA, &full_bar[s], c0, w0, h0, img, (uint16_t)fs, (uint16_t)fr);
-          } else {
-            tma_load_2d(sa, &tmA, &full_bar[s], c0, m0);
+          uint8_t* sb = sa + (size_t)p.bps * a_box;
+          uint64_t* fb = full_bar + s;
+          mbar_expect_tx(fb, (uint32_t)nb * (a_box + b_box));
+          for (int j = 0; j < nb; ++j) {
+            if (p.im2col) tma_load_im2col_4d(sa, &tmA, fb, c0, w0, h0, img, (uint16_t)fs, (uint16_t)fr);
+            else tma_load_2d(sa, &tmA, fb, c0, m0);
+            tma_load_3d(sb, &tmB, fb, c0, tap, n0);
+            sa += a_box;
+            sb += b_box;
+            c0 += p.kbe;
+            if (c0 >= p.C) {
+              c0 = 0;
+              ++tap;
+              if (++fs == p.S) { fs = 0; ++fr; }
+            }
           }
-          tma_load_3d(sb, &tmB, &full_bar[s], c0, tap, n0);
-          if (it == 0) TS(1);
+          if (++s == p.stages) { s = 0; ph ^= 1; }
         }
       }
       if (!ok) {
         // give copies already in flight a bounded chance to land before shared memory goes away
-        for (int s = 0; s < p.stages; ++s)
-          for (uint32_t i = 0; i < 4096; ++i)
-            if (mbar_try_wait(&full_bar[s], 0) || mbar_try_wait(&full_bar[s], 1)) break;
+        for (int i = 0; i < p.stages; ++i)
+          for (uint32_t k = 0; k < 4096; ++k)
+            if (mbar_try_wait(&full_bar[i], 0) || mbar_try_wait(&full_bar[i], 1)) break;
       }
     }
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer ----
     if (elect_one()) {
-      uint32_t it = 0, tcount = 0;
+      int s = 0;
+      uint32_t ph = 0, tcount = 0;
       bool ok = true;
+      const uint32_t smem_base = smem_u32(smem);
+      const uint64_t desc_fixed = ((uint64_t)p.desc_hi << 32) | (1ull << 16);
+      const int ksteps = p.kb_bytes >> 5;  // 32 bytes of K per instruction
       for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++tcount) {
         const uint32_t acc = tcount & 1, acc_ph = (tcount >> 1) & 1;
         if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1, abort_flag, p.status, 2)) { ok = false; break; }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * (uint32_t)p.BN;
-        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
-          const int s = it % p.stages;
-          const uint32_t ph = (it / p.stages) & 1;
-          if (!mbar_wait(&full_bar[s], ph, abort_flag, p.status, 3)) { ok = false; break; }
+        int left = p.num_kb;
+        uint32_t accum = 0;
+        for (int it = 0; it < p.num_it; ++it) {
+          if (!mbar_wait(full_bar + s, ph, abort_flag, p.status, 3)) { ok = false; break; }
           tc_fence_after();
-          if (it == 0) TS(2);
-          const uint32_t sa = smem_u32(smem + (size_t)s * stage_bytes), sb = sa + a_bytes;
-          const uint64_t da = ((uint64_t)p.desc_hi << 32) | (uint64_t)((sa & 0x3FFFF) >> 4) | (1ull << 16);
-          const uint64_t db = ((uint64_t)p.desc_hi << 32) | (uint64_t)((sb & 0x3FFFF) >> 4) | (1ull << 16);
-          const int ksteps = p.kb_bytes >> 5;  // 32 bytes of K per instruction
-          for (int k = 0; k < ksteps; ++k) {
-            const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
-            if (p.acc_int) umma_i8(tmem_d, da + 2 * k, db + 2 * k, p.idesc, accum);
-            else umma_f16(tmem_d, da + 2 * k, db + 2 * k, p.idesc, accum);
+          const int nb = left < p.bps ? left : p.bps;
+          left -= nb;
+          uint32_t sa = smem_base + (uint32_t)s * (uint32_t)stage_bytes, sb = sa + (uint32_t)p.bps * a_box;
+          for (int j = 0; j < nb; ++j) {
+            const uint64_t da = desc_fixed | (uint64_t)((sa & 0x3FFFF) >> 4);
+            const uint64_t db = desc_fixed | (uint64_t)((sb & 0x3FFFF) >> 4);
+            for (int k = 0; k < ksteps; ++k) {
+              if (p.acc_int) umma_i8(tmem_d, da + 2 * k, db + 2 * k, p.idesc, accum);
+              else umma_f16(tmem_d, da + 2 * k, db + 2 * k, p.idesc, accum);
+              accum = 1;
+            }
+            sa += a_box;
+            sb += b_box;
           }
-          umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
+          umma_commit(empty_bar + s);  // frees the stage once these MMAs have read it
+          if (++s == p.stages) { s = 0; ph ^= 1; }
         }
         if (ok) umma_commit(&tfull_bar[acc]);  // accumulator complete
         if (tcount == 0) TS(3);
@@ -568,10 +590,20 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
   p.m_tiles = (p.M_total + BM - 1) / BM;
   p.n_tiles = (c.K + p.BN - 1) / p.BN;
   p.total_tiles = p.m_tiles * p.n_tiles;
-  const int stage_bytes = (BM + p.BN) * p.kb_bytes;
+  // Several k-blocks share one pipeline stage (one mbarrier round trip) when they are small: up to
+  // 48 KB per stage, balanced over the tile's k-blocks.
+  const int box_bytes = (BM + p.BN) * p.kb_bytes;
+  int bps_max = (48 * 1024) / box_bytes;
+  if (bps_max < 1) bps_max = 1;
+  if (bps_max > 8) bps_max = 8;
+  const int iters = (p.num_kb + bps_max - 1) / bps_max;
+  p.bps = (p.num_kb + iters - 1) / iters;
+  p.num_it = (p.num_kb + p.bps - 1) / p.bps;
+  const int stage_bytes = p.bps * box_bytes;
   p.stages = (200 * 1024) / stage_bytes;
   if (p.stages > 8) p.stages = 8;
-  if (p.stages > p.num_kb + 1) p.stages = p.num_kb + 1 > 2 ? p.num_kb + 1 : 2;
+  if (p.stages > p.num_it + 1) p.stages = p.num_it + 1;
+  if (p.stages < 2) p.stages = 2;
   p.acc_int = c.in_dt == DT_S8;
   p.tmem_cols = 2 * p.BN;  // 128, 256 or 512: powers of two >= 32
   const uint32_t fmt = c.in_dt == DT_BF16 ? 1u : (c.in_dt == DT_S8 ? 1u : 0u);      // bf16 / signed 8-bit / f16
