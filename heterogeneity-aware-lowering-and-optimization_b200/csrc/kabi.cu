@@ -48,7 +48,7 @@ extern "C" int odla_b200_conv_umma(const odla_b200_conv_desc* d, const void* x, 
   if (cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess) rc = -2;
   umma_conv_destroy(L);
   if (getenv("ODLA_B200_DEBUG_TS")) {
-    unsigned long long ts[12];
+    unsigned long long ts[16];
     cudaMemcpy(ts, (char*)status + 32, sizeof(ts), cudaMemcpyDeviceToHost);
     fprintf(stderr, "ts(ns rel. to kernel entry): sync=%lld tma0=%lld full0=%lld commit=%lld tfull=%lld epi_end=%lld teardown=%lld\n", (long long)(ts[0] - ts[7]),
             (long long)(ts[1] - ts[7]), (long long)(ts[2] - ts[7]), (long long)(ts[3] - ts[7]), (long long)(ts[4] - ts[7]), (long long)(ts[5] - ts[7]), (long long)(ts[6] - ts[7]));

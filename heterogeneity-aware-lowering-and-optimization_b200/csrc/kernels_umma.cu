@@ -13,7 +13,7 @@
 // One persistent CTA per SM walks its tiles (128 pixels x BN channels):
 //   warp 0      producer: waits for a free stage, arms its mbarrier with the byte count, issues TMA
 //   warp 1      allocates tensor memory, issues tcgen05.mma (one lane), commits to mbarriers
-//   warps 2..9  epilogue: tcgen05.ld the fp32 / int32 accumulators (one TMEM lane = one output pixel
+//   warps 2..9  epilogue (warps 10 and 11 feed and drain its shared-memory staging ring): tcgen05.ld the fp32 / int32 accumulators (one TMEM lane = one output pixel
 //               per thread), apply the fused epilogue, store NHWC rows with 16-byte stores
 // Two accumulator buffers in tensor memory let the epilogue of tile i overlap the MMAs of tile i+1.
 //
@@ -23,6 +23,7 @@
 #include <cuda.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "epilogue.cuh"
@@ -36,7 +37,10 @@ constexpr int BM = 128;
 #define UMMA_EPI_WARPS 8
 #endif
 constexpr int kEpilogueWarps = UMMA_EPI_WARPS;
-constexpr int kThreads = 64 + 32 * kEpilogueWarps;
+constexpr int kLoaderWarp = 2 + kEpilogueWarps;   // brings residual boxes into the staging ring
+constexpr int kStorerWarp = 3 + kEpilogueWarps;   // drains finished boxes with TMA stores
+constexpr int kThreads = 32 * (4 + kEpilogueWarps);
+constexpr int kMaxRing = 8;
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 struct UmmaParams {
@@ -53,6 +57,11 @@ struct UmmaParams {
   uint32_t idesc;      // tcgen05 instruction descriptor
   uint32_t desc_hi;    // upper 32 bits of the shared-memory matrix descriptors
   int acc_int;         // accumulators are int32
+  int staged;          // epilogue goes through a shared-memory tile and TMA stores
+  int res_tma;         // the residual tile is brought into that tile by TMA
+  int out_esz;         // bytes per output element
+  int stage_boxes;     // 128-row x 128-byte boxes per output tile
+  int ring_boxes;      // boxes in the staging ring (>= stage_boxes)
   int tmem_cols;
   void* y;
   int* status;
@@ -173,41 +182,64 @@ __device__ __forceinline__ void load_vec32(const float* __restrict__ src, int co
     for (int j = 0; j < 32; ++j) out[j] = __ldg(src + min(col0 + j, kmax));
   }
 }
-__device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, float (&v)[32], int64_t row, int col0, int ncols, const uint4 (&pre)[4], bool use_pre) {
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, const uint4& v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+// Where a thread's 32-channel segment lives in the shared-memory staging tile (128-byte swizzle:
+// 16-byte piece j of row r sits at piece j ^ (r & 7)).  addr == 0 means "not staged".
+struct StagePos {
+  uint32_t row_addr;  // shared address of the 128-byte box row
+  int j0;             // first 16-byte piece of the segment inside the row
+  int rxor;           // r & 7
+};
+__device__ __forceinline__ uint32_t stage_piece(const StagePos& sp, int q) { return sp.row_addr + (uint32_t)(((sp.j0 + q) ^ sp.rxor) << 4); }
+
+// `pre`/`use_pre`: residual pieces already fetched into registers; `res_smem`: the residual tile was
+// brought into the staging tile by TMA; otherwise it is read from global memory here.
+// OUT: the output storage type when known at compile time (DT_F16 / DT_BF16 / DT_S8), or -1 to
+// branch on it at run time.  STAGED: results go to the shared-memory staging tile.  One
+// instantiation per combination keeps the instruction footprint of the epilogue small: with only
+// eight resident warps an epilogue that overflows the instruction cache stalls on every fetch.
+template <int OUT, bool STAGED>
+__device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, float (&v)[32], int64_t row, int col0, int ncols, const uint4 (&pre)[4], bool use_pre,
+                                               const StagePos& sp, bool res_smem_in) {
   const Epilogue& ep = p.ep;
-  const bool full = ncols == 32 && (p.K_out & 15) == 0;
+  constexpr bool staged = STAGED;
+  const bool res_smem = STAGED && res_smem_in;
+  const int out_dt = OUT >= 0 ? OUT : ep.out_dt;
+  const bool cols32 = ncols == 32;
+  const bool full = cols32 && (staged || (p.K_out & 15) == 0);      // per-channel vectors can be read 16 bytes at a time
+  const bool gvec = cols32 && (p.K_out & 15) == 0;                  // the row segment in global memory is 16-byte aligned
   const int kmax = p.K_out - 1;
   const int64_t base = row * p.K_out + col0;
-  // residual first: its latency overlaps the per-channel arithmetic below
   float rv[32];
   const bool has_res = ep.res != nullptr;
   if (has_res) {
-    if (full && ep.res_dt == DT_F16) {
-      const uint4* rp = (const uint4*)((const __half*)ep.res + base);
+    const bool vec = res_smem || use_pre || gvec;
+    if (vec && (ep.res_dt == DT_F16 || ep.res_dt == DT_BF16)) {
+      const uint4* rp = (const uint4*)((const uint16_t*)ep.res + base);
       uint4 u[4];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) u[q] = use_pre ? pre[q] : __ldg(rp + q);
+      for (int q = 0; q < 4; ++q) u[q] = res_smem ? lds128(stage_piece(sp, q)) : (use_pre ? pre[q] : __ldg(rp + q));
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        const __half2* h = (const __half2*)&u[q];
 #pragma unroll
-        for (int t = 0; t < 4; ++t) { float2 f = __half22float2(h[t]); rv[q * 8 + 2 * t] = f.x; rv[q * 8 + 2 * t + 1] = f.y; }
+        for (int t = 0; t < 4; ++t) {
+          float2 f = ep.res_dt == DT_F16 ? __half22float2(((const __half2*)&u[q])[t]) : __bfloat1622float2(((const __nv_bfloat162*)&u[q])[t]);
+          rv[q * 8 + 2 * t] = f.x;
+          rv[q * 8 + 2 * t + 1] = f.y;
+        }
       }
-    } else if (full && ep.res_dt == DT_BF16) {
-      const uint4* rp = (const uint4*)((const __nv_bfloat16*)ep.res + base);
-      uint4 u[4];
-#pragma unroll
-      for (int q = 0; q < 4; ++q) u[q] = use_pre ? pre[q] : __ldg(rp + q);
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const __nv_bfloat162* h = (const __nv_bfloat162*)&u[q];
-#pragma unroll
-        for (int t = 0; t < 4; ++t) { float2 f = __bfloat1622float2(h[t]); rv[q * 8 + 2 * t] = f.x; rv[q * 8 + 2 * t + 1] = f.y; }
-      }
-    } else if (full && ep.res_dt == DT_S8) {
+    } else if (vec && ep.res_dt == DT_S8) {
       const uint4* rp = (const uint4*)((const int8_t*)ep.res + base);
       uint4 u[2];
-      u[0] = use_pre ? pre[0] : __ldg(rp); u[1] = use_pre ? pre[1] : __ldg(rp + 1);
+#pragma unroll
+      for (int q = 0; q < 2; ++q) u[q] = res_smem ? lds128(stage_piece(sp, q)) : (use_pre ? pre[q] : __ldg(rp + q));
 #pragma unroll
       for (int q = 0; q < 2; ++q) {
         const uint32_t* w = (const uint32_t*)&u[q];
@@ -221,7 +253,7 @@ __device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, float (&v)[3
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         float r = 0.f;
-        if (j < ncols) {
+        if (j < ncols && row < p.M_total) {
           r = load_as_float(ep.res, ep.res_dt, base + j);
           if (ep.res_dt == DT_S8) r = __fmul_rn(r, ep.res_scale);
         }
@@ -252,7 +284,7 @@ __device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, float (&v)[3
   if (ep.add_full) {
 #pragma unroll
     for (int j = 0; j < 32; ++j)
-      if (j < ncols) v[j] = __fadd_rn(v[j], __fmul_rn(ep.beta_full, load_as_float(ep.add_full, ep.add_full_dt, base + j)));
+      if (j < ncols && row < p.M_total) v[j] = __fadd_rn(v[j], __fmul_rn(ep.beta_full, load_as_float(ep.add_full, ep.add_full_dt, base + j)));
   }
   if (ep.act != ACT_NONE && ep.act_first) {
 #pragma unroll
@@ -272,11 +304,11 @@ __device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, float (&v)[3
     }
   }
   // ---- store ----
-  if (ep.out_dt == DT_F16 || ep.out_dt == DT_BF16) {
+  if (out_dt == DT_F16 || out_dt == DT_BF16) {
     uint4 u[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      if (ep.out_dt == DT_F16) {
+      if (out_dt == DT_F16) {
         __half2* h = (__half2*)&u[q];
 #pragma unroll
         for (int t = 0; t < 4; ++t) h[t] = __floats2half2_rn(v[q * 8 + 2 * t], v[q * 8 + 2 * t + 1]);
@@ -286,16 +318,21 @@ __device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, float (&v)[3
         for (int t = 0; t < 4; ++t) h[t] = __floats2bfloat162_rn(v[q * 8 + 2 * t], v[q * 8 + 2 * t + 1]);
       }
     }
-    uint16_t* out = (uint16_t*)p.y + base;
-    if (full) {
+    if (staged) {
 #pragma unroll
-      for (int q = 0; q < 4; ++q) ((uint4*)out)[q] = u[q];
-    } else {
-      const uint16_t* e = (const uint16_t*)u;
+      for (int q = 0; q < 4; ++q) sts128(stage_piece(sp, q), u[q]);
+    } else if (row < p.M_total) {
+      uint16_t* out = (uint16_t*)p.y + base;
+      if (gvec) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) if (j < ncols) out[j] = e[j];
+        for (int q = 0; q < 4; ++q) ((uint4*)out)[q] = u[q];
+      } else {
+        const uint16_t* e = (const uint16_t*)u;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) if (j < ncols) out[j] = e[j];
+      }
     }
-  } else if (ep.out_dt == DT_S8) {
+  } else if (out_dt == DT_S8) {
     uint4 u[2];
     uint32_t* w = (uint32_t*)u;
 #pragma unroll
@@ -308,18 +345,23 @@ __device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, float (&v)[3
       }
       w[t] = packed;
     }
-    int8_t* out = (int8_t*)p.y + base;
-    if (full) {
-      ((uint4*)out)[0] = u[0];
-      ((uint4*)out)[1] = u[1];
-    } else {
-      const int8_t* e = (const int8_t*)u;
+    if (staged) {
+      sts128(stage_piece(sp, 0), u[0]);
+      sts128(stage_piece(sp, 1), u[1]);
+    } else if (row < p.M_total) {
+      int8_t* out = (int8_t*)p.y + base;
+      if (gvec) {
+        ((uint4*)out)[0] = u[0];
+        ((uint4*)out)[1] = u[1];
+      } else {
+        const int8_t* e = (const int8_t*)u;
 #pragma unroll
-      for (int j = 0; j < 32; ++j) if (j < ncols) out[j] = e[j];
+        for (int j = 0; j < 32; ++j) if (j < ncols) out[j] = e[j];
+      }
     }
-  } else {  // DT_F32
+  } else if (row < p.M_total) {  // DT_F32
     float* out = (float*)p.y + base;
-    if (full) {
+    if (gvec) {
 #pragma unroll
       for (int q = 0; q < 8; ++q) ((float4*)out)[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
     } else {
@@ -330,25 +372,32 @@ __device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, float (&v)[3
 }
 
 // --------------------------------------------------------------------- kernel ----
+template <int OUT, bool STAGED>
 __global__ void __launch_bounds__(kThreads, 1)
-umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const UmmaParams p) {
+umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmY,
+                 const __grid_constant__ CUtensorMap tmR, const UmmaParams p) {
   extern __shared__ uint8_t smem_raw[];
   if (threadIdx.x == 0) TS(7);
   // operand stages start on a 1024-byte boundary (the 128-byte swizzle repeats every 1024 bytes)
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int stage_bytes = p.bps * (BM + p.BN) * p.kb_bytes;
-  uint8_t* ctrl = smem + (size_t)p.stages * stage_bytes;
+  uint8_t* staging = smem + (size_t)p.stages * stage_bytes;   // 1024-byte aligned: stage sizes are multiples of 2 KiB
+  uint8_t* ctrl = staging + (size_t)p.ring_boxes * 16384;
   uint64_t* full_bar = (uint64_t*)ctrl;            // [stages]
   uint64_t* empty_bar = full_bar + 16;             // [stages]
   uint64_t* tfull_bar = empty_bar + 16;            // [2]
   uint64_t* tempty_bar = tfull_bar + 2;            // [2]
-  uint32_t* tmem_slot = (uint32_t*)(tempty_bar + 2);
+  uint64_t* box_full = tempty_bar + 2;             // [ring] box is armed: free, and its residual (if any) has landed
+  uint64_t* box_done = box_full + kMaxRing;        // [ring] every epilogue warp has written its part
+  uint64_t* box_free = box_done + kMaxRing;        // [ring] the TMA store has finished reading the box
+  uint32_t* tmem_slot = (uint32_t*)(box_free + kMaxRing);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], kEpilogueWarps); }
+    for (int b = 0; b < kMaxRing; ++b) { mbar_init(&box_full[b], 1); mbar_init(&box_done[b], kEpilogueWarps); mbar_init(&box_free[b], 1); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -455,52 +504,92 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (tcount == 0) TS(3);
       }
     }
+  } else if (warp == kLoaderWarp) {
+    // -------------------------------------------- staging ring: arm boxes (residual loads) ----
+    if (STAGED && elect_one()) {
+      const int cols_per_box = 128 / p.out_esz;
+      int slot = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * p.BN;
+        for (int bx = 0; bx < p.stage_boxes; ++bx) {
+          const int x0 = n0 + bx * cols_per_box;
+          if (x0 >= p.K_out) break;
+          if (!mbar_wait(box_free + slot, ph ^ 1, abort_flag, p.status, 5)) { ok = false; break; }
+          if (p.res_tma) {
+            mbar_expect_tx(box_full + slot, 16384u);
+            tma_load_2d(staging + slot * 16384, &tmR, box_full + slot, x0, m0);
+          } else {
+            mbar_arrive(box_full + slot);
+          }
+          if (++slot == p.ring_boxes) { slot = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == kStorerWarp) {
+    // ------------------------------------------------ staging ring: store finished boxes ----
+    if (STAGED && elect_one()) {
+      const int cols_per_box = 128 / p.out_esz;
+      const uint32_t staging_u32 = smem_u32(staging);
+      int slot = 0, prev = -1;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * p.BN;
+        for (int bx = 0; bx < p.stage_boxes; ++bx) {
+          const int x0 = n0 + bx * cols_per_box;
+          if (x0 >= p.K_out) break;
+          if (!mbar_wait(box_done + slot, ph, abort_flag, p.status, 7)) { ok = false; break; }
+          asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"((uint64_t)&tmY),
+                       "r"(staging_u32 + (uint32_t)slot * 16384u), "r"(x0), "r"(m0)
+                       : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          if (prev >= 0) {
+            asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");  // every store but the newest has read its box
+            mbar_arrive(box_free + prev);
+          }
+          prev = slot;
+          if (++slot == p.ring_boxes) { slot = 0; ph ^= 1; }
+        }
+      }
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // stores complete before shared memory is released
+    }
   } else {
     // ---------------------------------------------------------------- epilogue ----
     const int quarter = warp & 3;  // the TMEM lanes this warp may read: 32*quarter .. +31
-    const int cgroup = (warp - 2) >> 2;  // the four warps of a quarter take the 32-column chunks round-robin
+    const int cgroup = (warp - 2) >> 2;  // the warps of a quarter take the 32-column chunks round-robin
     uint32_t tcount = 0;
     bool ok = true;
-    // Residual rows can be fetched before the accumulator is ready: they only depend on the tile.
-    const bool res_vec = p.ep.res && (p.K_out & 15) == 0 && (p.ep.res_dt == DT_F16 || p.ep.res_dt == DT_BF16 || p.ep.res_dt == DT_S8);
-    const int res_q = p.ep.res_dt == DT_S8 ? 2 : 4;       // 16-byte pieces per 32 channels
-    const int res_esz = p.ep.res_dt == DT_S8 ? 1 : 2;
     constexpr int kGroups = kEpilogueWarps / 4;            // warps per TMEM lane quarter
     constexpr int kChunksPerWarp = 8 / kGroups;            // BN <= 256 -> at most 8 chunks of 32 columns
-    for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++tcount) {
-      const uint32_t acc = tcount & 1, acc_ph = (tcount >> 1) & 1;
-      const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * p.BN;
-      const int64_t row = (int64_t)m0 + quarter * 32 + lane;
-      uint4 pre[kChunksPerWarp][4] = {};
-      bool pre_ok[kChunksPerWarp];
-#pragma unroll
-      for (int i = 0; i < kChunksPerWarp; ++i) {
-        const int c = (cgroup + kGroups * i) * 32, col0 = n0 + c;
-        pre_ok[i] = res_vec && c < p.BN && row < p.M_total && col0 + 32 <= p.K_out;
-        if (pre_ok[i]) {
-          const uint4* rp = (const uint4*)((const char*)p.ep.res + (row * p.K_out + col0) * res_esz);
-#pragma unroll
-          for (int q = 0; q < 4; ++q) if (q < res_q) pre[i][q] = __ldg(rp + q);
-        }
-      }
-      if (!mbar_wait(&tfull_bar[acc], acc_ph, abort_flag, p.status, 4)) { ok = false; break; }
-      tc_fence_after();
-      if (tcount == 0 && threadIdx.x == 64) TS(4);
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * (uint32_t)p.BN;
-#pragma unroll
-      for (int i = 0; i < kChunksPerWarp; ++i) {
-        const int c = (cgroup + kGroups * i) * 32, col0 = n0 + c;
-        if (c >= p.BN || col0 >= p.K_out) break;  // uniform across the warp
-        uint32_t r[32];
-        tmem_ld32(taddr + (uint32_t)c, r);
-        tmem_ld_wait();
-        if (row < p.M_total) {
-          const int ncols = min(32, p.K_out - col0);
-          if (p.ep.out_dt == DT_S32) {
-            int32_t* out = (int32_t*)p.y + row * p.K_out + col0;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) if (j < ncols) out[j] = (int32_t)r[j];
-          } else {
+    const int r_in_tile = quarter * 32 + lane;
+    const uint32_t staging_u32 = smem_u32(staging);
+    if (STAGED) {
+      // Per output tile the staging ring supplies stage_boxes boxes of 128 rows x 128 bytes; the
+      // loader warp has already put the residual there, this warp overwrites its part of the box
+      // with the result and the storer warp sends the box out.
+      const int cols_per_box = 128 / p.out_esz, chunks_per_box = cols_per_box >> 5;
+      int slot = 0;
+      uint32_t ph = 0;
+      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++tcount) {
+        const uint32_t acc = tcount & 1, acc_ph = (tcount >> 1) & 1;
+        const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * p.BN;
+        const int64_t row = (int64_t)m0 + r_in_tile;
+        if (!mbar_wait(&tfull_bar[acc], acc_ph, abort_flag, p.status, 4)) { ok = false; break; }
+        tc_fence_after();
+        if (tcount == 0 && threadIdx.x == 64) TS(4);
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * (uint32_t)p.BN;
+        for (int bx = 0; bx < p.stage_boxes && ok; ++bx) {
+          const int x0 = n0 + bx * cols_per_box;
+          if (x0 >= p.K_out) break;
+          if (!mbar_wait(box_full + slot, ph, abort_flag, p.status, 6)) { ok = false; break; }
+#pragma unroll 1
+          for (int ch = cgroup; ch < chunks_per_box; ch += kGroups) {
+            const int c = bx * cols_per_box + ch * 32, col0 = n0 + c;
+            uint32_t r[32];
+            tmem_ld32(taddr + (uint32_t)c, r);
+            tmem_ld_wait();
             float v[32];
             if (p.acc_int) {
 #pragma unroll
@@ -509,14 +598,79 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
             }
-            epilogue_chunk(p, v, row, col0, ncols, pre[i], pre_ok[i]);
+            StagePos sp;
+            sp.row_addr = staging_u32 + (uint32_t)slot * 16384u + (uint32_t)r_in_tile * 128u;
+            sp.j0 = (ch * 32 * p.out_esz) >> 4;
+            sp.rxor = r_in_tile & 7;
+            const uint4 none[4] = {};
+            epilogue_chunk<OUT, true>(p, v, row, col0, max(0, min(32, p.K_out - col0)), none, false, sp, p.res_tma != 0);
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the bulk-copy engine must see these writes
+          __syncwarp();
+          if (lane == 0) mbar_arrive(box_done + slot);
+          if (++slot == p.ring_boxes) { slot = 0; ph ^= 1; }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+        if (tcount == 0 && threadIdx.x == 64) TS(5);
+      }
+    } else {
+      // Direct epilogue: rows go straight to global memory.  Residual rows can be fetched before the
+      // accumulator is ready: they only depend on the tile.
+      const bool res_vec = p.ep.res && (p.K_out & 15) == 0 && (p.ep.res_dt == DT_F16 || p.ep.res_dt == DT_BF16 || p.ep.res_dt == DT_S8);
+      const int res_q = p.ep.res_dt == DT_S8 ? 2 : 4;       // 16-byte pieces per 32 channels
+      const int res_esz = p.ep.res_dt == DT_S8 ? 1 : 2;
+      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++tcount) {
+        const uint32_t acc = tcount & 1, acc_ph = (tcount >> 1) & 1;
+        const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * p.BN;
+        const int64_t row = (int64_t)m0 + r_in_tile;
+        uint4 pre[kChunksPerWarp][4] = {};
+        bool pre_ok[kChunksPerWarp] = {};
+#pragma unroll
+        for (int i = 0; i < kChunksPerWarp; ++i) {
+          const int c = (cgroup + kGroups * i) * 32, col0 = n0 + c;
+          pre_ok[i] = res_vec && c < p.BN && row < p.M_total && col0 + 32 <= p.K_out;
+          if (pre_ok[i]) {
+            const uint4* rp = (const uint4*)((const char*)p.ep.res + (row * p.K_out + col0) * res_esz);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) if (q < res_q) pre[i][q] = __ldg(rp + q);
           }
         }
+        if (!mbar_wait(&tfull_bar[acc], acc_ph, abort_flag, p.status, 4)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * (uint32_t)p.BN;
+#pragma unroll
+        for (int i = 0; i < kChunksPerWarp; ++i) {
+          const int c = (cgroup + kGroups * i) * 32, col0 = n0 + c;
+          if (c >= p.BN || col0 >= p.K_out) break;  // uniform across the warp
+          uint32_t r[32];
+          tmem_ld32(taddr + (uint32_t)c, r);
+          tmem_ld_wait();
+          const int ncols = min(32, p.K_out - col0);
+          if (p.ep.out_dt == DT_S32) {
+            if (row < p.M_total) {
+              int32_t* out = (int32_t*)p.y + row * p.K_out + col0;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) if (j < ncols) out[j] = (int32_t)r[j];
+            }
+          } else if (row < p.M_total) {
+            float v[32];
+            if (p.acc_int) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = (float)(int32_t)r[j];
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            }
+            StagePos sp = {0, 0, 0};
+            epilogue_chunk<OUT, false>(p, v, row, col0, ncols, pre[i], pre_ok[i], sp, false);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty_bar[acc]);
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
-      if (tcount == 0 && threadIdx.x == 64) TS(5);
     }
   }
   // ------------------------------------------------------------------ teardown ----
@@ -549,13 +703,14 @@ bool load_driver_entry_points() {
   return true;
 }
 int elem_bytes(int dt) { return dt == DT_S8 ? 1 : 2; }
+int storage_size_of(int dt) { return dt == DT_S8 || dt == DT_U8 ? 1 : (dt == DT_F16 || dt == DT_BF16 ? 2 : (dt == DT_S64 ? 8 : 4)); }
 int pick_kb_bytes(int c_bytes) { return c_bytes > 64 ? 128 : (c_bytes > 32 ? 64 : 32); }
 int pick_bn(int k_out) { return k_out <= 64 ? 64 : (k_out <= 128 ? 128 : 256); }
 
 }  // namespace
 
 struct UmmaLaunch {
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmY, tmR;
   UmmaParams p;
   int grid;
   size_t smem;
@@ -600,7 +755,30 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
   p.bps = (p.num_kb + iters - 1) / iters;
   p.num_it = (p.num_kb + p.bps - 1) / p.bps;
   const int stage_bytes = p.bps * box_bytes;
-  p.stages = (200 * 1024) / stage_bytes;
+  // Staged epilogue: the output tile goes through shared memory (128-byte-swizzled boxes of 128 rows)
+  // and leaves with TMA stores; the residual tile arrives the same way when its element size equals
+  // the output's.  Needs 16-byte-multiple rows in global memory and a 1/2-byte output type.
+  p.out_esz = storage_size_of(ep.out_dt);
+  p.staged = (ep.out_dt == DT_F16 || ep.out_dt == DT_BF16 || ep.out_dt == DT_S8) && ((int64_t)c.K * p.out_esz) % 16 == 0 && !ep.add_full &&
+             ((uintptr_t)y % 16 == 0) && !getenv("ODLA_B200_DIRECT_EPILOGUE");
+  p.stage_boxes = p.staged ? (p.BN * p.out_esz + 127) / 128 : 0;
+  p.res_tma = p.staged && ep.res && storage_size_of(ep.res_dt) == p.out_esz && (ep.res_dt == DT_F16 || ep.res_dt == DT_BF16 || ep.res_dt == DT_S8) &&
+              ((uintptr_t)ep.res % 16 == 0);
+  // Shared memory: pipeline stages first (up to 4, or what one tile needs), then as many staging
+  // boxes as fit (at least one tile's worth, at most 8) so residual loads run ahead of the epilogue
+  // and stores drain behind it; what is left goes back to the pipeline.
+  const int budget = 224 * 1024;
+  int want_stages = p.num_it + 1 < 4 ? p.num_it + 1 : 4;
+  if (want_stages < 2) want_stages = 2;
+  p.ring_boxes = 0;
+  if (p.staged) {
+    p.ring_boxes = (budget - want_stages * stage_bytes) / 16384;
+    if (p.ring_boxes > kMaxRing) p.ring_boxes = kMaxRing;
+    if (p.ring_boxes > 2 * p.stage_boxes) p.ring_boxes = 2 * p.stage_boxes;
+    if (p.ring_boxes < p.stage_boxes) p.ring_boxes = p.stage_boxes;
+    if (p.ring_boxes < 2) p.ring_boxes = 2;  // the store of box i frees box i-1
+  }
+  p.stages = (budget - p.ring_boxes * 16384) / stage_bytes;
   if (p.stages > 8) p.stages = 8;
   if (p.stages > p.num_it + 1) p.stages = p.num_it + 1;
   if (p.stages < 2) p.stages = 2;
@@ -614,7 +792,8 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
   p.desc_hi = sbo | (1u << 14) | (layout << 29);                                    // bits 32-45 SBO, 46-47 version 1, 61-63 layout
   p.y = y; p.status = status; p.ep = ep;
   L->grid = p.total_tiles < sms ? p.total_tiles : sms;
-  L->smem = (size_t)p.stages * stage_bytes + 1024 /*alignment slack*/ + 512 /*barriers*/;
+  L->smem = (size_t)p.stages * stage_bytes + (size_t)p.ring_boxes * 16384 + 1024 /*alignment slack*/ + 1024 /*barriers*/;
+  if (L->smem > 227 * 1024) { delete L; return nullptr; }
 
   const CUtensorMapDataType dt = c.in_dt == DT_S8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : (c.in_dt == DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
   const CUtensorMapSwizzle sw = p.kb_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (p.kb_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
@@ -656,11 +835,30 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   }
   if (r != CUDA_SUCCESS) { fprintf(stderr, "[odla_b200] tensor map (B) encode failed: %d\n", (int)r); delete L; return nullptr; }
+  if (p.staged) {
+    const CUtensorMapDataType odt = p.out_esz == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16;
+    cuuint64_t dims[2] = {(cuuint64_t)c.K, (cuuint64_t)p.M_total};
+    cuuint64_t strides[1] = {(cuuint64_t)c.K * p.out_esz};
+    cuuint32_t box[2] = {(cuuint32_t)(128 / p.out_esz), (cuuint32_t)BM};
+    cuuint32_t estr[2] = {1, 1};
+    r = g_encode_tiled(&L->tmY, odt, 2, y, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS && p.res_tma)
+      r = g_encode_tiled(&L->tmR, odt, 2, (void*)ep.res, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { fprintf(stderr, "[odla_b200] tensor map (output/residual) encode failed: %d\n", (int)r); delete L; return nullptr; }
+  }
+  if (!p.staged) L->tmY = L->tmA;
+  if (!p.res_tma) L->tmR = L->tmA;
   static bool attr_set[16] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 16 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(umma_conv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) { cudaGetLastError(); delete L; return nullptr; }
+    bool ok = cudaFuncSetAttribute(umma_conv_kernel<DT_F16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess &&
+              cudaFuncSetAttribute(umma_conv_kernel<DT_BF16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess &&
+              cudaFuncSetAttribute(umma_conv_kernel<DT_S8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess &&
+              cudaFuncSetAttribute(umma_conv_kernel<-1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess;
+    if (!ok) { cudaGetLastError(); delete L; return nullptr; }
     attr_set[dev] = true;
   }
   return L;
@@ -669,7 +867,11 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
 int umma_conv_run(UmmaLaunch* L, cudaStream_t stream) {
   if (!L) return -1;
   if (L->p.total_tiles <= 0) return 0;
-  umma_conv_kernel<<<L->grid, kThreads, L->smem, stream>>>(L->tmA, L->tmB, L->p);
+  const UmmaParams& p = L->p;
+  if (!p.staged) umma_conv_kernel<-1, false><<<L->grid, kThreads, L->smem, stream>>>(L->tmA, L->tmB, L->tmY, L->tmR, p);
+  else if (p.ep.out_dt == DT_F16) umma_conv_kernel<DT_F16, true><<<L->grid, kThreads, L->smem, stream>>>(L->tmA, L->tmB, L->tmY, L->tmR, p);
+  else if (p.ep.out_dt == DT_BF16) umma_conv_kernel<DT_BF16, true><<<L->grid, kThreads, L->smem, stream>>>(L->tmA, L->tmB, L->tmY, L->tmR, p);
+  else umma_conv_kernel<DT_S8, true><<<L->grid, kThreads, L->smem, stream>>>(L->tmA, L->tmB, L->tmY, L->tmR, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { fprintf(stderr, "[odla_b200] umma_conv launch failed: %s\n", cudaGetErrorString(e)); return -2; }
   return 0;
