@@ -26,6 +26,12 @@ __device__ __forceinline__ int8_t sat_s8(float r) {  // r already rounded to an 
   r = fminf(fmaxf(r, -128.f), 127.f);
   return (int8_t)(int)r;
 }
+// sat(rne(x)) to int8 in one instruction (cvt.rni.sat.s8.f32); the result sits in the low byte.
+__device__ __forceinline__ int rne_sat_s8(float x) {
+  int r;
+  asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return r;
+}
 __device__ __forceinline__ uint8_t sat_u8(float r) {
   r = fminf(fmaxf(r, 0.f), 255.f);
   return (uint8_t)(int)r;
@@ -70,7 +76,7 @@ __device__ __forceinline__ float epilogue_value(const Epilogue& ep, float t, int
     t = __fadd_rn(t, r);
   }
   if (!ep.act_first) t = apply_act(ep.act, t, ep.act_a, ep.act_b);
-  if (ep.out_dt == DT_S8) t = __fdiv_rn(t, ep.out_scale);
+  if (ep.out_dt == DT_S8) t = ep.out_multiply ? __fmul_rn(t, ep.out_inv) : __fdiv_rn(t, ep.out_scale);
   return t;
 }
 

@@ -30,7 +30,7 @@ extern "C" int odla_b200_conv_umma(const odla_b200_conv_desc* d, const void* x, 
   switch (d->out_kind) {
     case 0: ep.out_dt = in_dt == DT_S8 ? DT_F32 : in_dt; break;
     case 1: ep.out_dt = DT_F32; break;
-    case 2: ep.out_dt = DT_S8; ep.out_scale = d->out_scale; break;
+    case 2: ep.out_dt = DT_S8; ep.out_scale = d->out_scale; ep.out_inv = 1.0f / d->out_scale; ep.out_multiply = d->out_multiply != 0; break;
     case 3: if (in_dt != DT_S8) return -1; ep.out_dt = DT_S32; break;
     default: return -1;
   }

@@ -24,8 +24,9 @@ enum { ACT_NONE = 0, ACT_RELU = 1, ACT_LEAKY = 2, ACT_CLAMP = 3, ACT_GELU_ERF = 
 //   if act_first  : t = act(t)
 //   if res        : t = t + (res_dt == DT_S8 ? (float)res * res_scale : (float)res)
 //   if !act_first : t = act(t)
-//   store         : float types round to nearest even; DT_S8 stores sat(rne(t / out_scale));
-//                   DT_S32 stores the raw accumulator (int8 inputs only).
+//   store         : float types round to nearest even; DT_S8 stores sat(rne(t / out_scale)), or
+//                   sat(rne(t * out_inv)) when out_multiply is set (requantisation of a value that
+//                   comes from int32 accumulators); DT_S32 stores the raw accumulator (int8 inputs only).
 struct Epilogue {
   const float* mul = nullptr;
   float alpha = 1.f;
@@ -42,6 +43,8 @@ struct Epilogue {
   float act_a = 0.f, act_b = 0.f;
   int out_dt = DT_F32;
   float out_scale = 1.f;
+  float out_inv = 1.f;   // fl(1 / out_scale)
+  int out_multiply = 0;
 };
 
 // 2-d convolution geometry.  Data is addressed through element strides so NHWC and NCHW share
@@ -120,6 +123,8 @@ int layernorm(int dt, const void* x, void* y, const float* gamma, const float* b
 // q = sat(rne(x / scale[a]) + zp[a]); x = (q - zp[a]) * scale[a]; (outer, adim, inner) split.
 int quantize(int dt_in, const void* x, void* q, const float* scale, const int* zp, int64_t outer, int64_t adim,
              int64_t inner, bool per_axis, bool is_unsigned, cudaStream_t stream);
+// Per-tensor int8 requantisation q = sat(rne(x * inv_scale)).
+int requantize(int dt_in, const void* x, void* q, float inv_scale, int64_t n, cudaStream_t stream);
 int dequantize(int dt_out, const void* q, void* x, const float* scale, const int* zp, int64_t outer,
                int64_t adim, int64_t inner, bool per_axis, bool is_unsigned, cudaStream_t stream);
 

@@ -370,6 +370,10 @@ __global__ void quantize_f32_s8_vec_kernel(const float4* __restrict__ x, uint4* 
     q[i] = out;
   }
 }
+__global__ void requantize_kernel(int dt_in, const void* x, int8_t* q, float inv, int64_t n) {
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < n; e += (int64_t)gridDim.x * blockDim.x)
+    q[e] = (int8_t)rne_sat_s8(__fmul_rn(load_as_float(x, dt_in, e), inv));
+}
 __global__ void dequantize_kernel(int dt_out, const void* q, void* x, const float* scale, const int* zp, int64_t total, int64_t adim,
                                   int64_t inner, int per_axis, int is_unsigned) {
   for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
@@ -558,6 +562,11 @@ int quantize(int dt_in, const void* x, void* q, const float* scale, const int* z
     return check_launch();
   }
   quantize_kernel<<<grid_for(total, 256), 256, 0, s>>>(dt_in, x, q, scale, zp, total, adim, inner, per_axis, is_unsigned);
+  return check_launch();
+}
+int requantize(int dt_in, const void* x, void* q, float inv_scale, int64_t n, cudaStream_t s) {
+  if (n <= 0) return 0;
+  requantize_kernel<<<grid_for(n, 256), 256, 0, s>>>(dt_in, x, (int8_t*)q, inv_scale, n);
   return check_launch();
 }
 int dequantize(int dt_out, const void* q, void* x, const float* scale, const int* zp, int64_t outer, int64_t adim, int64_t inner,

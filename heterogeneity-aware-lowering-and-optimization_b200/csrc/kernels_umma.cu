@@ -246,7 +246,7 @@ __device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, float (&v)[3
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
 #pragma unroll
-          for (int b = 0; b < 4; ++b) rv[q * 16 + t * 4 + b] = __fmul_rn((float)(int)(int8_t)((w[t] >> (8 * b)) & 0xff), ep.res_scale);
+          for (int b = 0; b < 4; ++b) rv[q * 16 + t * 4 + b] = __fmul_rn((float)((int)(w[t] << (24 - 8 * b)) >> 24), ep.res_scale);
         }
       }
     } else {
@@ -340,8 +340,8 @@ __device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, float (&v)[3
       uint32_t packed = 0;
 #pragma unroll
       for (int b = 0; b < 4; ++b) {
-        int qv = sat_s8(rintf(__fdiv_rn(v[t * 4 + b], ep.out_scale)));
-        packed |= (uint32_t)(qv & 0xff) << (8 * b);
+        const float t4 = ep.out_multiply ? __fmul_rn(v[t * 4 + b], ep.out_inv) : __fdiv_rn(v[t * 4 + b], ep.out_scale);
+        packed |= (uint32_t)(rne_sat_s8(t4) & 0xff) << (8 * b);
       }
       w[t] = packed;
     }

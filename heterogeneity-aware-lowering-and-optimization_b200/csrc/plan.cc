@@ -155,6 +155,7 @@ class Builder {
   std::map<V, int> users_;
   std::map<V, std::vector<V>> consumers_;
   std::map<V, bool> carries_batch_;
+  std::map<V, bool> from_acc_;         // computed from int32 accumulators through element-wise ops only
   std::map<V, V> fused_into_;          // node -> root of the chain that swallowed it
   std::map<V, std::unique_ptr<Fused>> fused_;  // by root
   std::map<V, int> dq_unabsorbed_;     // Dequantize node -> number of consumers that need it in memory
@@ -246,6 +247,17 @@ odla_status Builder::analyse() {
   // fusion roots
   for (auto& n : c_->nodes)
     if (n->kind == OP_CONV || n->kind == OP_GEMM) try_fuse(n.get());
+  // Values that come from int32 accumulators: an int8-path Conv/Gemm result and any element-wise
+  // (unary / binary / reshape) function of one.  Quantising such a value is a requantisation and
+  // multiplies by fl(1/s); every other Quantize divides like the reference.
+  for (auto& n : c_->nodes) {
+    V v = n.get();
+    bool t = false;
+    if ((v->kind == OP_CONV || v->kind == OP_GEMM) && fused_.count(v)) t = fused_[v]->int8;
+    else if (v->kind == OP_UNARY || v->kind == OP_BINARY || v->kind == OP_RESHAPE)
+      for (auto i : v->in) if (i && from_acc_[i]) t = true;
+    from_acc_[v] = t;
+  }
   // which Dequantize nodes still need to exist in memory
   for (auto& n : c_->nodes) {
     V v = n.get();
@@ -476,7 +488,11 @@ odla_status Builder::emit_fused(const Item& it) {
   }
   ep.act = f.act; ep.act_a = f.act_a; ep.act_b = f.act_b; ep.act_first = f.act_first;
   ep.out_dt = dt_[f.out];
-  if (f.quant_scale) ep.out_scale = const_as_f32(f.quant_scale)[0];
+  if (f.quant_scale) {
+    ep.out_scale = const_as_f32(f.quant_scale)[0];
+    ep.out_inv = 1.0f / ep.out_scale;
+    ep.out_multiply = f.int8 ? 1 : 0;  // the chain hangs off int32 accumulators exactly when its root is an int8 kernel
+  }
   bool allow_umma = !getenv("ODLA_B200_NO_UMMA");
   int sms = 148;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, p_->device);
@@ -783,7 +799,11 @@ odla_status Builder::emit_plain(const Item& it) {
         for (int i = 0; i < axis; ++i) outer *= os.dims[i];
         for (int i = axis + 1; i < os.size; ++i) inner *= os.dims[i];
       }
-      if (q) {
+      if (q && from_acc_[v->in[0]] && !per_axis && !zp && odt == DT_S8) {
+        float inv = 1.0f / const_as_f32(v->in[1])[0];
+        int64_t n = count(v);
+        add_launch("requantize", v, 0, tensor_bytes(v->in[0]) + out_bytes, [=](cudaStream_t s) { return requantize(xdt, x, y, inv, n, s); });
+      } else if (q) {
         bool uns = odt == DT_U8;
         add_launch("quantize", v, 0, tensor_bytes(v->in[0]) + out_bytes, [=](cudaStream_t s) { return quantize(xdt, x, y, sc, zp, outer, adim, inner, per_axis, uns, s); });
       } else {

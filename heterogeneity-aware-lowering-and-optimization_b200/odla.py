@@ -63,7 +63,7 @@ class ProfileEntry(C.Structure):
 class ConvDesc(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("n", "h", "w", "c", "k", "r", "s", "stride_h", "stride_w", "pad_top",
                                        "pad_left", "p", "q", "dtype", "out_kind", "res_kind", "act")] + \
-               [("alpha", C.c_float), ("res_scale", C.c_float), ("out_scale", C.c_float)]
+               [("alpha", C.c_float), ("res_scale", C.c_float), ("out_scale", C.c_float), ("out_multiply", C.c_int)]
 
 
 def shape(dims):

@@ -381,12 +381,15 @@ int odla_b200_DescribePlan(odla_computation computation, char* buf, int capacity
  *   Epilogue: t = acc * mul[k] (mul may be NULL = 1) + add[k] (may be NULL);
  *   t += residual * res_scale (residual may be NULL); act 0 none, 1 relu, 2 leaky(alpha);
  *   out_kind 0 = same float type as input (fp16/bf16), 1 = fp32, 2 = int8 via
- *   sat(rne(t / out_scale)), 3 = raw int32 accumulators (int8 input only).
+ *   sat(rne(t / out_scale)) -- or sat(rne(t * fl(1/out_scale))) when out_multiply is non-zero,
+ *   the requantisation form the graph path uses after int32 accumulation --, 3 = raw int32
+ *   accumulators (int8 input only).
  *   res_kind is the residual element type: 0 = fp16/bf16 (the input type), 1 = fp32, 2 = int8. */
 typedef struct {
   int n, h, w, c, k, r, s, stride_h, stride_w, pad_top, pad_left, p, q;
   int dtype, out_kind, res_kind, act;
   float alpha, res_scale, out_scale;
+  int out_multiply;
 } odla_b200_conv_desc;
 int odla_b200_conv_umma(const odla_b200_conv_desc* desc, const void* x, const void* w,
                         const float* mul, const float* add, const void* residual, void* y,

@@ -19,7 +19,11 @@
 // odla_Dequantize(int8, per-tensor or per-output-channel scale), both without zero point, is
 // computed exactly in integers and scaled once: out = float(acc_int32) * (s_in * s_w[k]), the
 // product s_in*s_w[k] rounded to fp32 first.  Everything after that (bias add, residual add,
-// relu, odla_Quantize = rne(x / s) saturated) is ordinary node-by-node fp32 arithmetic.
+// relu) is ordinary node-by-node fp32 arithmetic.  A value "comes from accumulators" if it is such a
+// Conv/Gemm result or an element-wise (unary / binary / reshape) function of one; odla_Quantize of
+// such a value (per-tensor scale, no zero point, int8) is a requantisation and multiplies by
+// fl(1/s): q = sat(rne(x * fl(1/s))).  Every other odla_Quantize divides, q = sat(rne(x / s)), as
+// ODLA/platforms/dnnl/odla_dnnl_quantization.cc:77 does.
 #include <dlfcn.h>
 
 #include <algorithm>
@@ -61,6 +65,7 @@ void ora_reduce_mean_axis_f32(float*, const float*, int64_t, int64_t, int64_t);
 void ora_layernorm_f32(float*, const float*, const float*, const float*, int64_t, int64_t, float);
 void ora_quantize_f32(void*, const float*, const float*, const int32_t*, int64_t, int64_t, int64_t,
                       int, int);
+void ora_requantize_f32(int8_t*, const float*, float, int64_t);
 void ora_dequantize_f32(float*, const void*, const float*, const int32_t*, int64_t, int64_t,
                         int64_t, int, int);
 void ora_transpose(void*, const void*, int, const int64_t*, const int64_t*, int);
@@ -188,6 +193,7 @@ struct _odla_value {
   // producer info used by the int8 rule
   odla_value dq_src = nullptr, dq_scale = nullptr; bool dq_zp = false; int dq_axis = -1;
   std::vector<int32_t> acc;        // int32 accumulators of the last int8 Conv/Gemm (for tests)
+  bool from_acc = false;           // computed from int32 accumulators through element-wise ops only
   float* f() { return (float*)buf.data(); }
   int64_t n() const { return numel(api_type.shape); }
   const odla_value_shape& shape() const { return api_type.shape; }
@@ -332,6 +338,7 @@ odla_value odla_Conv(odla_value in, odla_memory_layout il, odla_uint32 group, od
                   ker->dq_src->store == ODLA_INT8 && in->dq_scale->n() == 1 && nhwc && g == 1;
   if (int_path) {
     odla_value xq = in->dq_src, wq = ker->dq_src, sx = in->dq_scale, sw_ = ker->dq_scale;
+    out->from_acc = true;
     g_comp->ops.push_back([=] {
       out->acc.resize((size_t)out->n());
       parallel_for(N * P, [&](int64_t b, int64_t e) {
@@ -378,6 +385,7 @@ odla_value odla_Gemm(odla_value A, odla_bool ta, odla_value B, odla_bool tb, odl
                   B->dq_src->store == ODLA_INT8 && A->dq_scale->n() == 1 && batch == 1;
   if (int_path) {
     odla_value aq = A->dq_src, bq = B->dq_src, sa = A->dq_scale, sb = B->dq_scale;
+    out->from_acc = true;
     g_comp->ops.push_back([=] {
       out->acc.resize((size_t)out->n());
       ora_matmul_s8(out->acc.data(), (int8_t*)aq->buf.data(), (int8_t*)bq->buf.data(), M, N, Kd, ta, tb);
@@ -448,6 +456,7 @@ odla_value odla_BatchNormalization(odla_value in, odla_memory_layout il, odla_va
 
 static odla_value unary(int op, odla_value in, float a, float b, const odla_value_id id) {
   odla_value out = new_value(ODLA_FLOAT32, in->shape(), id);
+  out->from_acc = in->from_acc;
   g_comp->ops.push_back([=] {
     if (op == U_RELU && reflib().ok) reflib().relu(out->f(), in->f(), in->n());
     else ora_unary_f32(op, out->f(), in->f(), in->n(), a, b);
@@ -481,6 +490,7 @@ static odla_value binary(int op, odla_value l, odla_value r, const odla_value_id
     os[i] = std::max(ls[i], rs[i]); osh.dims[i] = os[i];
   }
   odla_value out = new_value(ODLA_FLOAT32, osh, id);
+  out->from_acc = l->from_acc || r->from_acc;
   g_comp->ops.push_back([=] { ora_binary_f32(op, out->f(), l->f(), r->f(), rank, os.data(), ls.data(), rs.data()); });
   return out;
 }
@@ -551,7 +561,9 @@ odla_value odla_Quantize(odla_value in, odla_value scale, odla_value zp, odla_in
   int64_t outer, adim, inner; int per_axis;
   axis_split(in->shape(), axis, scale->n(), &outer, &adim, &inner, &per_axis);
   odla_value out = new_value(tt, in->shape(), id);
+  const bool requant = in->from_acc && !zp && scale->n() == 1 && tt == ODLA_INT8;
   g_comp->ops.push_back([=] {
+    if (requant) { ora_requantize_f32((int8_t*)out->buf.data(), in->f(), 1.0f / scale->f()[0], in->n()); return; }
     std::vector<int32_t> z;
     if (zp) { z.resize((size_t)zp->n()); for (int64_t i = 0; i < zp->n(); ++i) z[i] = zp->store == ODLA_INT8 ? ((int8_t*)zp->buf.data())[i] : zp->store == ODLA_UINT8 ? ((uint8_t*)zp->buf.data())[i] : ((int32_t*)zp->buf.data())[i]; }
     ora_quantize_f32(out->buf.data(), in->f(), scale->f(), zp ? z.data() : nullptr, outer, adim, inner, per_axis, tt == ODLA_UINT8);
@@ -575,6 +587,7 @@ odla_value odla_Dequantize(odla_value in, odla_value scale, odla_value zp, odla_
 odla_value odla_Reshape(odla_value in, odla_value_shape od, const odla_value_id id) {
   odla_value out = new_value(in->api_type.element_type, od, id);
   if (out->n() != in->n()) return fail("Reshape: element count differs");
+  out->from_acc = in->from_acc;
   g_comp->ops.push_back([=] { memcpy(out->buf.data(), in->buf.data(), in->buf.size()); });
   return out;
 }

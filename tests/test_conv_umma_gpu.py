@@ -61,7 +61,8 @@ def test_conv_umma_matches_numpy(odla, gpu_lib, shape, dtype):
     np.testing.assert_allclose(y.cpu().numpy(), want, rtol=0, atol=2e-3)   # fp32 accumulation of exact products
 
 
-def test_conv_umma_int8_requant_epilogue_is_bit_exact(odla, gpu_lib):
+@pytest.mark.parametrize("multiply", [0, 1])
+def test_conv_umma_int8_requant_epilogue_is_bit_exact(odla, gpu_lib, multiply):
     N, H, Cc, K = 3, 14, 128, 96
     rng = np.random.default_rng(9)
     x = rng.integers(-128, 128, (N, H, H, Cc), dtype=np.int8)
@@ -73,14 +74,16 @@ def test_conv_umma_int8_requant_epilogue_is_bit_exact(odla, gpu_lib):
     t = [torch.from_numpy(a).cuda() for a in (x, w, res, mul, add)]
     y = torch.zeros((N, H, H, K), dtype=torch.int8, device="cuda")
     d = odla.ConvDesc(n=N, h=H, w=H, c=Cc, k=K, r=3, s=3, stride_h=1, stride_w=1, pad_top=1, pad_left=1, p=H, q=H, dtype=2, out_kind=2, res_kind=2, act=1,
-                      alpha=0, res_scale=float(rs), out_scale=float(os_))
+                      alpha=0, res_scale=float(rs), out_scale=float(os_), out_multiply=multiply)
     assert gpu_lib.b200_conv_umma(C.byref(d), t[0].data_ptr(), t[1].data_ptr(), t[3].data_ptr(), t[4].data_ptr(), t[2].data_ptr(), y.data_ptr(), None) == 0
     acc = conv_ref(x, w, 3, 3, 1, 1, H, H, np.int64)
     v = acc.astype(np.float32) * mul          # every step rounds to fp32 separately, like the kernel's *_rn intrinsics
     v = v + add
     v = v + res.astype(np.float32) * rs
     v = np.maximum(v, np.float32(0))
-    q = np.clip(np.rint(v / os_), -128, 127).astype(np.int8)
+    # division like the reference's odla_Quantize, or the requantisation form: times fl(1/s)
+    scaled = v * (np.float32(1.0) / os_) if multiply else v / os_
+    q = np.clip(np.rint(scaled), -128, 127).astype(np.int8)
     assert np.array_equal(y.cpu().numpy(), q)
 
 

@@ -183,3 +183,29 @@ def test_layernorm_gelu_avgpool_against_numpy(odla, ref):
     # corner window sees 2x2 valid pixels: the mean excludes the padding
     np.testing.assert_allclose(got[0, 0, 0], x[0, :2, :2].reshape(-1, 3).mean(0), atol=1e-6)
     g.close()
+
+
+def test_requantisation_multiplies_by_the_reciprocal(odla, ref):
+    """Quantize of a value that comes from int32 accumulators is sat(rne(x * fl(1/s))); the same
+    Quantize applied to an ordinary float tensor divides like the reference."""
+    rng = np.random.default_rng(8)
+    xq = rng.integers(-128, 128, (1, 4, 4, 32), dtype=np.int8)
+    wq = rng.integers(-127, 128, (1, 1, 32, 16), dtype=np.int8)
+    sx, sw, sy = np.float32(0.013), np.float32(0.007), np.float32(0.3)
+    g = odla.Graph(ref, "rq")
+    x = g.Argument("x", xq.shape, odla.INT8)
+    f = g.Argument("f", (1, 4, 4, 16), odla.FLOAT32)
+    xd = g.Dequantize(x, g.Constant("sx", np.array([sx])), None, 0, odla.FLOAT32, "xd")
+    wd = g.Dequantize(g.Constant("wq", wq), g.Constant("sw", np.array([sw])), None, 3, odla.FLOAT32, "wd")
+    c = g.Conv(xd, odla.CHANNELS_LAST, 1, wd, odla.SIO, (1, 1), (1, 1), (0, 0), (0, 0), None, (1, 4, 4, 16), "c")
+    S = g.Constant("sy", np.array([sy]))
+    g.Output(g.Quantize(g.Relu(c, "r"), S, None, 0, odla.INT8, "q_acc"))
+    g.Output(g.Quantize(f, S, None, 0, odla.INT8, "q_plain"))
+    g.Output(c)
+    fv = (rng.standard_normal((1, 4, 4, 16)) * 20).astype(np.float32)
+    out = g.run({"x": xq, "f": fv})
+    conv = out["c"]
+    inv = np.float32(1.0) / sy
+    assert np.array_equal(out["q_acc"], np.clip(np.rint(np.maximum(conv, 0) * inv), -128, 127).astype(np.int8))
+    assert np.array_equal(out["q_plain"], np.clip(np.rint(fv / sy), -128, 127).astype(np.int8))
+    g.close()
