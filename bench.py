@@ -199,6 +199,7 @@ def run_b200(args, rank, world, local_rank):
     if lib.b200_DeviceCount() < 1:
         raise RuntimeError("bench.py needs a CUDA device: libodla_b200 has no CPU fallback")
     w = rn.weights()
+    BATCH = args.batch
     g = odla.Graph(lib, "resnet50", fp16=True, n_gpus=1)
     rn.build(g, BATCH, w, input_type=odla.FLOAT16)
     x_host = torch.from_numpy(rn.inputs(BATCH, seed=rank_seed(10 + BATCH, rank), dtype=np.float16)["input"]).pin_memory()
@@ -270,6 +271,36 @@ def run_b200(args, rank, world, local_rank):
     families = {k: {"launches": v["launches"], "ms": round(v["ms"], 4)} for k, v in sorted(fam.items(), key=lambda kv: -kv[1]["ms"])}
     g.close()
 
+    # Secondary measurement: the same network in int8 quantise/dequantise form (BASELINE config 3),
+    # device-resident fp32 input, same timing method.  int8 tensor peak is taken as 2x the measured bf16 figure.
+    int8 = None
+    if not args.no_int8:
+        scales = rn.calibrate(w, n_images=8)
+        wq = rn.quantize_weights(w)
+        g8 = odla.Graph(lib, "resnet50_int8", n_gpus=1)
+        rn.build_int8(g8, BATCH, w, wq, scales)
+        x8 = x_host.float().cuda()
+        g8.bind_input("input", x8.data_ptr())
+        g8.bind_output("prob", y_dev.data_ptr())
+
+        def step8():
+            flush.zero_()
+            torch.cuda.synchronize()
+            if g8.execute() != 0:
+                raise RuntimeError("int8 execute failed")
+            return g8.device_ms()
+        for _ in range(args.warmup):
+            step8()
+        barrier()
+        ms8 = max_over_ranks(sum(step8() for _ in range(args.steps)))
+        prof8 = g8.profile(runs=2)
+        tc8 = [q for q in prof8 if q["op"].endswith("_umma")]
+        tc8_ms, tc8_ops = sum(q["ms"] for q in tc8), sum(q["flops"] for q in tc8)
+        int8 = {"value": total_images / (ms8 / 1e3), "unit": UNIT, "ms_per_step": ms8 / args.steps, "dtype": "s8 (int32 accumulate)",
+                "roofline": {"bound": "tensor", "achieved": tc8_ops / (tc8_ms * 1e-3) / 1e12 if tc8_ms else 0.0, "peak": 2 * peak, "unit": "TOP/s",
+                             "frac": (tc8_ops / (tc8_ms * 1e-3) / 1e12) / (2 * peak) if tc8_ms else None, "peak_source": "2 x " + peak_kind + " bf16 sustained (no int8 measurement available)"}}
+        g8.close()
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline_leg(pkg, rn, w)
@@ -278,12 +309,12 @@ def run_b200(args, rank, world, local_rank):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": dev_ms / args.steps, "wall_ms_per_step": wall_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f16", "data": "synthetic",
-            "config": {"workload": "resnet50_v1.5_nhwc_fp16_b256", "batch_per_gpu": BATCH, "global_batch": BATCH * world, "input": "NHWC fp16 N(0,1)",
+            "config": {"workload": "resnet50_v1.5_nhwc_fp16_b%d" % BATCH, "batch_per_gpu": BATCH, "global_batch": BATCH * world, "input": "NHWC fp16 N(0,1)",
                        "weights": "He-normal, folded BN, random init", "l2": "256 MiB buffer written between steps", "parallelism": "dp%d" % world,
                        "timing": "CUDA events on the library's stream around each odla_ExecuteComputation, summed over the steps, max over ranks"},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps},
             "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "kernel_families_ms_per_step": families,
-            "cpu_baseline": cpu, "check": {"top1_of_first_image": top1}}))
+            "int8": int8, "cpu_baseline": cpu, "check": {"top1_of_first_image": top1}}))
 
 
 def main():
@@ -293,6 +324,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-int8", action="store_true", help="skip the secondary int8 measurement")
+    ap.add_argument("--batch", type=int, default=BATCH, help="images per GPU per step (256 = the benchmark configuration; smaller values are for profiling)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else max(args.warmup, 1)
     rank, world, local_rank = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
