@@ -142,6 +142,11 @@ int move(const MoveGeom& g, int esz, const void* x, void* y, cudaStream_t stream
 // out[pixel][0..Cp) = in[pixel][0..C) followed by zeros; Cp*esz must be 32 (one thread writes one pixel as
 // two 16-byte stores).  Gives few-channel inputs (an RGB image) rows that TMA can address.
 int pad_channels(int esz, const void* x, void* y, int64_t pixels, int C, int Cp, cudaStream_t stream);
+// Stride-2 stem helper: y[n][h][q][8*4] gathers, for every output column q, the eight input pixels
+// 2q-4 .. 2q+3 (C <= 4 channels each, zero outside the image or beyond C) so that a (R x S) stride-2
+// convolution over few channels becomes an (R x 1) convolution over 32 channels with unit column
+// stride.  esz is 1 or 2 bytes; one thread writes 16 bytes.
+int stem_widen(int esz, const void* x, void* y, int N, int H, int W, int C, int Q, cudaStream_t stream);
 int resize_nearest(int esz, const void* x, void* y, int N, int H, int W, int C, int P, int Q, bool nhwc,
                    cudaStream_t stream);
 // out[o, k, :] = in[o, idx[k], :]; idx int32 or int64.

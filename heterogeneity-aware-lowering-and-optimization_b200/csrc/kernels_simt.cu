@@ -431,6 +431,26 @@ __global__ void pad_channels_kernel(const T* __restrict__ x, uint4* __restrict__
   }
 }
 template <typename T>
+__global__ void stem_widen_kernel(const T* __restrict__ x, uint4* __restrict__ y, int N, int H, int W, int C, int Q) {
+  constexpr int PER = 16 / (int)sizeof(T);       // elements per 16-byte piece
+  constexpr int PIECES = 32 / PER;                // pieces per widened pixel (32 elements)
+  const int64_t total = (int64_t)N * H * Q * PIECES;
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    const int piece = (int)(e % PIECES);
+    const int64_t wp = e / PIECES;               // (n*H + h)*Q + q
+    const int q = (int)(wp % Q);
+    const int64_t nh = wp / Q;
+    uint4 out = make_uint4(0, 0, 0, 0);
+    T* o = (T*)&out;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int el = piece * PER + i, pix = 2 * q - 4 + (el >> 2), c = el & 3;
+      if (pix >= 0 && pix < W && c < C) o[i] = x[(nh * W + pix) * C + c];
+    }
+    y[e] = out;
+  }
+}
+template <typename T>
 __global__ void resize_nearest_kernel(const T* __restrict__ x, T* __restrict__ y, int N, int H, int W, int C, int P, int Q, int nhwc) {
   int64_t total = (int64_t)N * P * Q * C;
   for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
@@ -605,6 +625,16 @@ int pad_channels(int esz, const void* x, void* y, int64_t pixels, int C, int Cp,
   int grid = grid_for(pixels, 256);
   if (esz == 1) pad_channels_kernel<uint8_t><<<grid, 256, 0, s>>>((const uint8_t*)x, (uint4*)y, pixels, C);
   else if (esz == 2) pad_channels_kernel<uint16_t><<<grid, 256, 0, s>>>((const uint16_t*)x, (uint4*)y, pixels, C);
+  else return -1;
+  return check_launch();
+}
+int stem_widen(int esz, const void* x, void* y, int N, int H, int W, int C, int Q, cudaStream_t s) {
+  int64_t total = (int64_t)N * H * Q * (32 * esz / 16);
+  if (total <= 0) return 0;
+  if (C > 4 || (uintptr_t)y % 16 != 0) return -1;
+  int grid = grid_for(total, 256);
+  if (esz == 1) stem_widen_kernel<uint8_t><<<grid, 256, 0, s>>>((const uint8_t*)x, (uint4*)y, N, H, W, C, Q);
+  else if (esz == 2) stem_widen_kernel<uint16_t><<<grid, 256, 0, s>>>((const uint16_t*)x, (uint4*)y, N, H, W, C, Q);
   else return -1;
   return check_launch();
 }

@@ -524,8 +524,24 @@ odla_status Builder::emit_fused(const Item& it) {
     int Cp = g.C;
     const void* x_umma = x;
     void* padded = nullptr;
-    if (allow_umma && nhwc && groups == 1 && (in_dt == DT_F16 || in_dt == DT_BF16 || in_dt == DT_S8) && !umma_conv_supported(uc) &&
-        g.C * storage_size(in_dt) < 32) {
+    bool widened = false;   // stride-2 stem rewritten as an (R x 1) convolution over 32-channel widened pixels
+    const bool small_c = allow_umma && nhwc && groups == 1 && (in_dt == DT_F16 || in_dt == DT_BF16 || in_dt == DT_S8) && !umma_conv_supported(uc) &&
+                         g.C * storage_size(in_dt) < 32;
+    if (small_c && g.C <= 4 && g.stride_w == 2 && g.pad_l <= 4 && g.S - g.pad_l <= 4 && !getenv("ODLA_B200_NO_WIDEN")) {
+      // Output column q reads input pixels 2q-pad_l .. 2q-pad_l+S-1, all inside 2q-4 .. 2q+3: gather those
+      // eight pixels (x 4 channels) once per (row, q) and the column taps collapse into the channel axis.
+      UmmaConv uw = uc;
+      uw.W = g.Q; uw.C = 32; uw.S = 1; uw.stride_w = 1; uw.pad_l = 0;
+      if (umma_conv_supported(uw)) {
+        size_t pbytes = (size_t)g.N * g.H * g.Q * 32 * storage_size(in_dt);
+        if (inject_fault("alloc") || cudaMalloc(&padded, pbytes ? pbytes : 32) != cudaSuccess) return fail(ODLA_MEM_ERROR, "scratch allocation failed");
+        p_->extra_allocs.push_back(padded);
+        x_umma = padded;
+        uc = uw;
+        widened = true;
+      }
+    }
+    if (small_c && !widened) {
       UmmaConv up = uc;
       up.C = 32 / storage_size(in_dt);
       if (umma_conv_supported(up)) {
@@ -541,10 +557,22 @@ odla_status Builder::emit_fused(const Item& it) {
       // filters HWIO -> [K][R*S*C] so that each output channel's taps are contiguous (K-major B operand)
       auto wf = const_as_f32(f.w);
       int64_t rs = (int64_t)g.R * g.S;
-      std::vector<float> w2((size_t)(K * rs * Cp), 0.f);
-      for (int64_t t = 0; t < rs; ++t)
-        for (int64_t c = 0; c < g.C; ++c)
-          for (int64_t k = 0; k < K; ++k) w2[(size_t)((k * rs + t) * Cp + c)] = wf[(size_t)((t * g.C + c) * K + k)];
+      std::vector<float> w2;
+      if (widened) {
+        // [K][R][32]: element el of a widened pixel is input pixel 2q-4+el/4, channel el%4, i.e. filter column el/4-4+pad_l
+        w2.assign((size_t)(K * g.R * 32), 0.f);
+        for (int64_t r = 0; r < g.R; ++r)
+          for (int el = 0; el < 32; ++el) {
+            int sc = el / 4 - 4 + g.pad_l, c = el % 4;
+            if (sc < 0 || sc >= g.S || c >= g.C) continue;
+            for (int64_t k = 0; k < K; ++k) w2[(size_t)((k * g.R + r) * 32 + el)] = wf[(size_t)(((r * g.S + sc) * g.C + c) * K + k)];
+          }
+      } else {
+        w2.assign((size_t)(K * rs * Cp), 0.f);
+        for (int64_t t = 0; t < rs; ++t)
+          for (int64_t c = 0; c < g.C; ++c)
+            for (int64_t k = 0; k < K; ++k) w2[(size_t)((k * rs + t) * Cp + c)] = wf[(size_t)((t * g.C + c) * K + k)];
+      }
       auto wb = f32_to_storage(w2, in_dt);
       void* wd = upload(wb.data(), wb.size());
       if (!wd) return err_status_;
@@ -554,8 +582,11 @@ odla_status Builder::emit_fused(const Item& it) {
       if (padded) {
         int esz = storage_size(in_dt), C0 = g.C;
         int64_t pixels = (int64_t)g.N * g.H * g.W;
-        add_launch("conv_umma", f.out, flops, bytes + 2.0 * pixels * 32, [=](cudaStream_t s) {
-          int rc = pad_channels(esz, x, padded, pixels, C0, Cp, s);
+        ConvGeom gg = g;
+        bool wide = widened;
+        double scratch_bytes = wide ? 2.0 * g.N * g.H * g.Q * 32 * esz : 2.0 * pixels * 32;
+        add_launch("conv_umma", f.out, flops, bytes + scratch_bytes, [=](cudaStream_t s) {
+          int rc = wide ? stem_widen(esz, x, padded, gg.N, gg.H, gg.W, C0, gg.Q, s) : pad_channels(esz, x, padded, pixels, C0, Cp, s);
           return rc ? rc : umma_conv_run(ul, s);
         });
         p_->launches.back().n_kernels = 2;
