@@ -1,4 +1,4 @@
 """Model descriptions that follow the emission rules of HALO's generic C++ code generator
 (Conv with a null bias followed by a per-channel Add, residual Add then Relu, ReduceMean for the
 global pool, Gemm for every matmul) and drive any ODLA platform library through ``odla.Graph``."""
-from . import mnist, resnet50  # noqa: F401
+from . import bert, mnist, resnet50, yolov3  # noqa: F401

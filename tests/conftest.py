@@ -30,6 +30,8 @@ def models():
     class M:
         mnist = importlib.import_module(PKG + ".halo_models.mnist")
         resnet50 = importlib.import_module(PKG + ".halo_models.resnet50")
+        yolov3 = importlib.import_module(PKG + ".halo_models.yolov3")
+        bert = importlib.import_module(PKG + ".halo_models.bert")
     return M
 
 

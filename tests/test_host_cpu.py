@@ -116,6 +116,37 @@ def test_resnet50_description(models):
     assert int(np.abs(q["s2b0_c2_w_q"]).max()) == 127
 
 
+def test_yolov3_and_bert_descriptions(models):
+    yo, be = models.yolov3, models.bert
+    specs = yo.conv_specs()
+    assert len(specs) == 75 and sum(1 for s in specs if s[5]) == 3
+    # MAC count at 416x416: walk the same structure the builder walks
+    it = iter(specs)
+    mac, h = 0, 416
+
+    def conv(h_in):
+        nonlocal mac
+        _, k, cin, cout, s, _ = next(it)
+        ho = (h_in + 2 * (k // 2) - k) // s + 1
+        mac += ho * ho * k * k * cin * cout
+        return ho
+
+    for ch, k, s, nres in yo.BACKBONE:
+        h = conv(h)
+        for _ in range(nres):
+            conv(h); conv(h)
+    for width, route in ((512, None), (256, 512), (128, 256)):
+        if route:
+            conv(h)
+            h *= 2
+        for _ in range(7):
+            conv(h)
+    assert mac == yo.MAC_PER_IMAGE_416 == 32932037632
+    c = be.BASE
+    S, H, F, L = c["seq"], c["hidden"], c["ffn"], c["layers"]
+    assert L * (3 * S * H * H + 2 * S * S * H + S * H * H + 2 * S * H * F) == be.MAC_PER_SEQUENCE_BASE == 11173625856
+
+
 def test_emitted_resnet50_cc_follows_halo_rules(odla, lib, models):
     rn = models.resnet50
     w = {k: (v if v.size < 4096 else v) for k, v in rn.weights().items()}

@@ -116,6 +116,54 @@ def test_full_batch_properties_fp16(odla, gpu_lib, models, rn_weights):
     assert np.abs(c - a[:2]).max() < 1e-3                  # a different tile decomposition may reorder nothing but the batch rows
 
 
+def _run_pair(odla, gpu_lib, ref, build, inputs, **gpu_mode):
+    outs = []
+    for L in (gpu_lib, ref):
+        g = odla.Graph(L, "m", **(gpu_mode if L is gpu_lib else {}))
+        build(g)
+        outs.append(g.run(inputs))
+        desc = g.describe() if L is gpu_lib else None
+        if L is gpu_lib:
+            d = desc
+        g.close()
+    return outs[0], outs[1], d
+
+
+@pytest.mark.parametrize("mode", ["fp32", "fp16"])
+def test_yolov3_heads_match_oracle(odla, gpu_lib, ref, models, mode):
+    """Darknet-53 + three heads (75 convolutions, LeakyRelu epilogues, residual adds after the
+    activation, nearest upsample, channel concat), 96x96 input so the oracle finishes in seconds."""
+    yo = models.yolov3
+    w = yo.weights()
+    x = yo.inputs(2, size=96)
+    got, want, desc = _run_pair(odla, gpu_lib, ref, lambda g: yo.build(g, 2, w, size=96), x, fp16=(mode == "fp16"))
+    assert [v.shape for v in want.values()] == [(2, 3, 3, 255), (2, 6, 6, 255), (2, 12, 12, 255)]
+    if mode == "fp16":
+        assert desc.count("conv_umma") == 75 and "resize" in desc and "concat" in desc
+        assert desc.count("binary") == 0        # every residual Add was folded into a convolution epilogue
+    for k in want:
+        scale = float(np.abs(want[k]).max())
+        err = float(np.abs(got[k] - want[k]).max())
+        assert err <= (1e-4 if mode == "fp32" else 2e-2) * max(scale, 1.0), (k, err, scale)
+
+
+@pytest.mark.parametrize("mode,cfg", [("fp32", dict(vocab=500, hidden=64, heads=4, ffn=256, layers=2, seq=16)),
+                                      ("fp16", dict(vocab=500, hidden=64, heads=4, ffn=256, layers=2, seq=16)),
+                                      ("fp16", dict(vocab=30522, hidden=768, heads=12, ffn=3072, layers=1, seq=128))])
+def test_bert_encoder_matches_oracle(odla, gpu_lib, ref, models, mode, cfg):
+    """Embedding gather, LayerNorm, Q/K/V/out/FFN Gemms with bias (+GELU) epilogues, head split/merge
+    transposes, batched score and context Gemms, soft-max; a small configuration in fp32 and fp16
+    and one full-width BERT-base layer in fp16."""
+    be = models.bert
+    w = be.weights(cfg)
+    x = be.inputs(cfg, 2)
+    got, want, desc = _run_pair(odla, gpu_lib, ref, lambda g: be.build(g, 2, cfg, w), x, fp16=(mode == "fp16"))
+    err = float(np.abs(got["encoder_out"] - want["encoder_out"]).max())
+    assert err <= (2e-4 if mode == "fp32" else 3e-2), err
+    if mode == "fp16":
+        assert desc.count("gemm_umma") == 6 * cfg["layers"] and "layernorm" in desc and "gather" in desc
+
+
 def test_halo_style_model_runs_against_both_libraries(tmp_path, odla, gpu_lib, ref, models):
     """mnist_simple.cc (emitted in the shape of HALO's generator) + its constants object + a main(),
     linked once with -lodla_b200 and once with the oracle platform: same probabilities."""
