@@ -410,6 +410,10 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Programmatic dependent launch: everything above overlapped the previous kernel's tail; from here on
+  // this kernel reads what that kernel wrote.  The next kernel may start its own prologue now.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (threadIdx.x == 0) TS(0);
 
   const uint32_t a_box = (uint32_t)(BM * p.kb_bytes), b_box = (uint32_t)(p.BN * p.kb_bytes);
@@ -587,6 +591,7 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll 1
           for (int ch = cgroup; ch < chunks_per_box; ch += kGroups) {
             const int c = bx * cols_per_box + ch * 32, col0 = n0 + c;
+            if (c >= p.BN) break;  // a box may be wider than the tile (int8 boxes hold 128 channels)
             uint32_t r[32];
             tmem_ld32(taddr + (uint32_t)c, r);
             tmem_ld_wait();
@@ -868,10 +873,23 @@ int umma_conv_run(UmmaLaunch* L, cudaStream_t stream) {
   if (!L) return -1;
   if (L->p.total_tiles <= 0) return 0;
   const UmmaParams& p = L->p;
-  if (!p.staged) umma_conv_kernel<-1, false><<<L->grid, kThreads, L->smem, stream>>>(L->tmA, L->tmB, L->tmY, L->tmR, p);
-  else if (p.ep.out_dt == DT_F16) umma_conv_kernel<DT_F16, true><<<L->grid, kThreads, L->smem, stream>>>(L->tmA, L->tmB, L->tmY, L->tmR, p);
-  else if (p.ep.out_dt == DT_BF16) umma_conv_kernel<DT_BF16, true><<<L->grid, kThreads, L->smem, stream>>>(L->tmA, L->tmB, L->tmY, L->tmR, p);
-  else umma_conv_kernel<DT_S8, true><<<L->grid, kThreads, L->smem, stream>>>(L->tmA, L->tmB, L->tmY, L->tmR, p);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)L->grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = L->smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  static const bool pdl = !getenv("ODLA_B200_NO_PDL");
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  cudaError_t le;
+  if (!p.staged) le = cudaLaunchKernelEx(&cfg, umma_conv_kernel<-1, false>, L->tmA, L->tmB, L->tmY, L->tmR, p);
+  else if (p.ep.out_dt == DT_F16) le = cudaLaunchKernelEx(&cfg, umma_conv_kernel<DT_F16, true>, L->tmA, L->tmB, L->tmY, L->tmR, p);
+  else if (p.ep.out_dt == DT_BF16) le = cudaLaunchKernelEx(&cfg, umma_conv_kernel<DT_BF16, true>, L->tmA, L->tmB, L->tmY, L->tmR, p);
+  else le = cudaLaunchKernelEx(&cfg, umma_conv_kernel<DT_S8, true>, L->tmA, L->tmB, L->tmY, L->tmR, p);
+  if (le != cudaSuccess) { fprintf(stderr, "[odla_b200] umma_conv launch failed: %s\n", cudaGetErrorString(le)); cudaGetLastError(); return -2; }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { fprintf(stderr, "[odla_b200] umma_conv launch failed: %s\n", cudaGetErrorString(e)); return -2; }
   return 0;
