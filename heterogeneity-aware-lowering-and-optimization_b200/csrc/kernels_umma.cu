@@ -206,8 +206,10 @@ __device__ __forceinline__ uint32_t stage_piece(const StagePos& sp, int q) { ret
 // instantiation per combination keeps the instruction footprint of the epilogue small: with only
 // eight resident warps an epilogue that overflows the instruction cache stalls on every fetch.
 template <int OUT, bool STAGED>
+// pmul / padd: per-channel multiplier and addend vectors already fetched by the caller (bit 0 / bit 1
+// of pre_vec), so their load latency overlaps the tensor-memory read.
 __device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, float (&v)[32], int64_t row, int col0, int ncols, const uint4 (&pre)[4], bool use_pre,
-                                               const StagePos& sp, bool res_smem_in) {
+                                               const StagePos& sp, bool res_smem_in, const float (&pmul)[32], const float (&padd)[32], int pre_vec) {
   const Epilogue& ep = p.ep;
   constexpr bool staged = STAGED;
   const bool res_smem = STAGED && res_smem_in;
@@ -246,7 +248,7 @@ __device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, float (&v)[3
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
 #pragma unroll
-          for (int b = 0; b < 4; ++b) rv[q * 16 + t * 4 + b] = __fmul_rn((float)((int)(w[t] << (24 - 8 * b)) >> 24), ep.res_scale);
+          for (int b = 0; b < 4; ++b) rv[q * 16 + t * 4 + b] = __fmul_rn((float)(signed char)(w[t] >> (8 * b)), ep.res_scale);
         }
       }
     } else {
@@ -263,23 +265,38 @@ __device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, float (&v)[3
   }
   float cv[32];
   if (ep.mul) {
-    load_vec32(ep.mul, col0, kmax, full, cv);
+    if (pre_vec & 1) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(v[j], cv[j]);
+      for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(v[j], pmul[j]);
+    } else {
+      load_vec32(ep.mul, col0, kmax, full, cv);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(v[j], cv[j]);
+    }
   }
   if (ep.alpha != 1.f) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(v[j], ep.alpha);
   }
   if (ep.add1) {
-    load_vec32(ep.add1, col0, kmax, full, cv);
+    if ((pre_vec & 2) && !ep.add2) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], cv[j]);
+      for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], padd[j]);
+    } else {
+      load_vec32(ep.add1, col0, kmax, full, cv);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], cv[j]);
+    }
   }
   if (ep.add2) {
-    load_vec32(ep.add2, col0, kmax, full, cv);
+    if (pre_vec & 2) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], cv[j]);
+      for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], padd[j]);
+    } else {
+      load_vec32(ep.add2, col0, kmax, full, cv);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], cv[j]);
+    }
   }
   if (ep.add_full) {
 #pragma unroll
@@ -337,13 +354,14 @@ __device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, float (&v)[3
     uint32_t* w = (uint32_t*)u;
 #pragma unroll
     for (int t = 0; t < 8; ++t) {
-      uint32_t packed = 0;
+      uint32_t qb[4];
 #pragma unroll
       for (int b = 0; b < 4; ++b) {
         const float t4 = ep.out_multiply ? __fmul_rn(v[t * 4 + b], ep.out_inv) : __fdiv_rn(v[t * 4 + b], ep.out_scale);
-        packed |= (uint32_t)(rne_sat_s8(t4) & 0xff) << (8 * b);
+        qb[b] = (uint32_t)rne_sat_s8(t4);
       }
-      w[t] = packed;
+      // low bytes of the four results -> one word (three byte permutes)
+      w[t] = __byte_perm(__byte_perm(qb[0], qb[1], 0x0040), __byte_perm(qb[2], qb[3], 0x0040), 0x5410);
     }
     if (staged) {
       sts128(stage_piece(sp, 0), u[0]);
@@ -608,7 +626,10 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             sp.j0 = (ch * 32 * p.out_esz) >> 4;
             sp.rxor = r_in_tile & 7;
             const uint4 none[4] = {};
-            epilogue_chunk<OUT, true>(p, v, row, col0, max(0, min(32, p.K_out - col0)), none, false, sp, p.res_tma != 0);
+            const float none32[32] = {};
+            // (Fetching the residual pieces and per-channel vectors before tcgen05.wait::ld was tried and
+            // measured slower: the extra live registers cost more than the hidden latency.)
+            epilogue_chunk<OUT, true>(p, v, row, col0, max(0, min(32, p.K_out - col0)), none, false, sp, p.res_tma != 0, none32, none32, 0);
           }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the bulk-copy engine must see these writes
           __syncwarp();
@@ -669,7 +690,8 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
             }
             StagePos sp = {0, 0, 0};
-            epilogue_chunk<OUT, false>(p, v, row, col0, ncols, pre[i], pre_ok[i], sp, false);
+            const float none32[32] = {};
+            epilogue_chunk<OUT, false>(p, v, row, col0, ncols, pre[i], pre_ok[i], sp, false, none32, none32, 0);
           }
         }
         tc_fence_before();
