@@ -395,6 +395,9 @@ odla_status odla_ExecuteComputation(const odla_computation c, const odla_context
   if (!c || !ctx) return ODLA_INVALID_PARAM;
   if (mode == ODLA_COMPUTE_TRAINING) return ODLA_UNSUPPORTED_OP;
   if (!c->first_error.empty()) { B2_ERR("computation has a build error: %s", c->first_error.c_str()); return c->error_status; }
+  // Contexts of one computation may be driven from different threads; they share the computation's
+  // per-GPU arenas and streams, so executions are serialised here.
+  std::lock_guard<std::mutex> lock(c->exec_mutex);
   odla_status s = ensure_planned(c);
   if (s != ODLA_SUCCESS) return s;
   return execute(c, ctx);

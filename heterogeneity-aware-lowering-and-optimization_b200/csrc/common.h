@@ -9,6 +9,7 @@
 #include <functional>
 #include <map>
 #include <memory>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -146,6 +147,7 @@ struct _odla_computation {
   bool planned = false;
   bool shardable = true;           // dim 0 of every argument/output is an independent batch
   std::vector<b200::Replica> replicas;
+  std::mutex exec_mutex;           // executions of one computation share its arenas: one at a time
   ~_odla_computation();
 };
 
