@@ -13,7 +13,7 @@
 // One persistent CTA per SM walks its tiles (128 pixels x BN channels):
 //   warp 0      producer: waits for a free stage, arms its mbarrier with the byte count, issues TMA
 //   warp 1      allocates tensor memory, issues tcgen05.mma (one lane), commits to mbarriers
-//   warps 2..9  epilogue (warps 10 and 11 feed and drain its shared-memory staging ring): tcgen05.ld the fp32 / int32 accumulators (one TMEM lane = one output pixel
+//   next 8 or 16 warps: epilogue (two more warps feed and drain its shared-memory staging ring): tcgen05.ld the fp32 / int32 accumulators (one TMEM lane = one output pixel
 //               per thread), apply the fused epilogue, store NHWC rows with 16-byte stores
 // Two accumulator buffers in tensor memory let the epilogue of tile i overlap the MMAs of tile i+1.
 //
@@ -33,13 +33,17 @@ namespace b200 {
 namespace {
 
 constexpr int BM = 128;
-#ifndef UMMA_EPI_WARPS
-#define UMMA_EPI_WARPS 8
-#endif
-constexpr int kEpilogueWarps = UMMA_EPI_WARPS;
-constexpr int kLoaderWarp = 2 + kEpilogueWarps;   // brings residual boxes into the staging ring
-constexpr int kStorerWarp = 3 + kEpilogueWarps;   // drains finished boxes with TMA stores
-constexpr int kThreads = 32 * (4 + kEpilogueWarps);
+// Epilogue organisation.  Staged kernels (results leave through the shared-memory ring) run 16 epilogue
+// warps on 16-column chunks: four warps per scheduler hide the latency of each other's tensor-memory
+// and shared-memory reads, and 16 columns keep a thread under 96 registers.  The direct kernel (fp32 /
+// int32 outputs, rows stored straight to global memory) keeps 8 warps on 32-column chunks.
+template <bool STAGED> struct EpiCfg {
+  static constexpr int kWarps = STAGED ? 16 : 8;     // epilogue warps (a multiple of 4: one per TMEM lane quarter)
+  static constexpr int kChunk = STAGED ? 16 : 32;    // accumulator columns per tcgen05.ld
+  static constexpr int kLoaderWarp = 2 + kWarps;      // brings residual boxes into the staging ring
+  static constexpr int kStorerWarp = 3 + kWarps;      // drains finished boxes with TMA stores
+  static constexpr int kThreads = 32 * (4 + kWarps);
+};
 constexpr int kMaxRing = 8;
 constexpr uint32_t kSpinLimit = 1u << 22;
 
@@ -147,6 +151,18 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+template <int CW> __device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t* r) {
+  if (CW == 32) tmem_ld32(taddr, r); else tmem_ld16(taddr, r);
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -167,19 +183,19 @@ __device__ __forceinline__ unsigned long long gtime() { unsigned long long t; as
 #define TS(i) do {} while (0)
 #endif
 // ------------------------------------------------------------------- epilogue ----
-// One thread owns one output pixel (row) and 32 consecutive channels held in v[] (registers: every
-// index below is a compile-time constant after unrolling).  `full` says all 32 columns exist and
-// the row segment is 16-byte aligned, which allows 16-byte loads and stores.
-__device__ __forceinline__ void load_vec32(const float* __restrict__ src, int col0, int kmax, bool full, float (&out)[32]) {
+// One thread owns one output pixel (row) and CW consecutive channels held in v[] (registers: every
+// index below is a compile-time constant after unrolling).
+template <int CW>
+__device__ __forceinline__ void load_vec(const float* __restrict__ src, int col0, int kmax, bool full, float (&out)[CW]) {
   if (full) {
 #pragma unroll
-    for (int q = 0; q < 8; ++q) {
+    for (int q = 0; q < CW / 4; ++q) {
       float4 f = __ldg((const float4*)(src + col0) + q);
       out[4 * q] = f.x; out[4 * q + 1] = f.y; out[4 * q + 2] = f.z; out[4 * q + 3] = f.w;
     }
   } else {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) out[j] = __ldg(src + min(col0 + j, kmax));
+    for (int j = 0; j < CW; ++j) out[j] = __ldg(src + min(col0 + j, kmax));
   }
 }
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
@@ -190,8 +206,8 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
 __device__ __forceinline__ void sts128(uint32_t addr, const uint4& v) {
   asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
-// Where a thread's 32-channel segment lives in the shared-memory staging tile (128-byte swizzle:
-// 16-byte piece j of row r sits at piece j ^ (r & 7)).  addr == 0 means "not staged".
+// Where a thread's channel segment lives in the shared-memory staging box (128-byte swizzle:
+// 16-byte piece j of row r sits at piece j ^ (r & 7)).
 struct StagePos {
   uint32_t row_addr;  // shared address of the 128-byte box row
   int j0;             // first 16-byte piece of the segment inside the row
@@ -199,37 +215,35 @@ struct StagePos {
 };
 __device__ __forceinline__ uint32_t stage_piece(const StagePos& sp, int q) { return sp.row_addr + (uint32_t)(((sp.j0 + q) ^ sp.rxor) << 4); }
 
-// `pre`/`use_pre`: residual pieces already fetched into registers; `res_smem`: the residual tile was
-// brought into the staging tile by TMA; otherwise it is read from global memory here.
 // OUT: the output storage type when known at compile time (DT_F16 / DT_BF16 / DT_S8), or -1 to
-// branch on it at run time.  STAGED: results go to the shared-memory staging tile.  One
-// instantiation per combination keeps the instruction footprint of the epilogue small: with only
-// eight resident warps an epilogue that overflows the instruction cache stalls on every fetch.
-template <int OUT, bool STAGED>
-// pmul / padd: per-channel multiplier and addend vectors already fetched by the caller (bit 0 / bit 1
-// of pre_vec), so their load latency overlaps the tensor-memory read.
-__device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, float (&v)[32], int64_t row, int col0, int ncols, const uint4 (&pre)[4], bool use_pre,
-                                               const StagePos& sp, bool res_smem_in, const float (&pmul)[32], const float (&padd)[32], int pre_vec) {
+// branch on it at run time.  STAGED: results go to the shared-memory staging box and the residual
+// (res_smem) is read from it.  `pre`/`use_pre`: residual pieces already fetched into registers (direct
+// epilogue).  One instantiation per combination keeps the instruction footprint of the epilogue small:
+// with few resident warps an epilogue that overflows the instruction cache stalls on every fetch.
+template <int OUT, bool STAGED, int CW>
+__device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, float (&v)[CW], int64_t row, int col0, int ncols, const uint4 (&pre)[4], bool use_pre,
+                                               const StagePos& sp, bool res_smem_in) {
   const Epilogue& ep = p.ep;
   constexpr bool staged = STAGED;
   const bool res_smem = STAGED && res_smem_in;
   const int out_dt = OUT >= 0 ? OUT : ep.out_dt;
-  const bool cols32 = ncols == 32;
-  const bool full = cols32 && (staged || (p.K_out & 15) == 0);      // per-channel vectors can be read 16 bytes at a time
-  const bool gvec = cols32 && (p.K_out & 15) == 0;                  // the row segment in global memory is 16-byte aligned
+  const bool colsall = ncols == CW;
+  const bool full = colsall && (staged || (p.K_out & 15) == 0);      // per-channel vectors can be read 16 bytes at a time
+  const bool gvec = colsall && (p.K_out & 15) == 0;                  // the row segment in global memory is 16-byte aligned
   const int kmax = p.K_out - 1;
   const int64_t base = row * p.K_out + col0;
-  float rv[32];
+  float rv[CW];
   const bool has_res = ep.res != nullptr;
   if (has_res) {
     const bool vec = res_smem || use_pre || gvec;
     if (vec && (ep.res_dt == DT_F16 || ep.res_dt == DT_BF16)) {
+      constexpr int NQ = CW / 8;
       const uint4* rp = (const uint4*)((const uint16_t*)ep.res + base);
-      uint4 u[4];
+      uint4 u[NQ];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) u[q] = res_smem ? lds128(stage_piece(sp, q)) : (use_pre ? pre[q] : __ldg(rp + q));
+      for (int q = 0; q < NQ; ++q) u[q] = res_smem ? lds128(stage_piece(sp, q)) : (use_pre ? pre[q] : __ldg(rp + q));
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
+      for (int q = 0; q < NQ; ++q) {
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
           float2 f = ep.res_dt == DT_F16 ? __half22float2(((const __half2*)&u[q])[t]) : __bfloat1622float2(((const __nv_bfloat162*)&u[q])[t]);
@@ -238,12 +252,13 @@ __device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, float (&v)[3
         }
       }
     } else if (vec && ep.res_dt == DT_S8) {
+      constexpr int NQ = CW / 16;
       const uint4* rp = (const uint4*)((const int8_t*)ep.res + base);
-      uint4 u[2];
+      uint4 u[NQ];
 #pragma unroll
-      for (int q = 0; q < 2; ++q) u[q] = res_smem ? lds128(stage_piece(sp, q)) : (use_pre ? pre[q] : __ldg(rp + q));
+      for (int q = 0; q < NQ; ++q) u[q] = res_smem ? lds128(stage_piece(sp, q)) : (use_pre ? pre[q] : __ldg(rp + q));
 #pragma unroll
-      for (int q = 0; q < 2; ++q) {
+      for (int q = 0; q < NQ; ++q) {
         const uint32_t* w = (const uint32_t*)&u[q];
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
@@ -253,7 +268,7 @@ __device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, float (&v)[3
       }
     } else {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
+      for (int j = 0; j < CW; ++j) {
         float r = 0.f;
         if (j < ncols && row < p.M_total) {
           r = load_as_float(ep.res, ep.res_dt, base + j);
@@ -263,68 +278,54 @@ __device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, float (&v)[3
       }
     }
   }
-  float cv[32];
+  float cv[CW];
   if (ep.mul) {
-    if (pre_vec & 1) {
+    load_vec<CW>(ep.mul, col0, kmax, full, cv);
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(v[j], pmul[j]);
-    } else {
-      load_vec32(ep.mul, col0, kmax, full, cv);
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(v[j], cv[j]);
-    }
+    for (int j = 0; j < CW; ++j) v[j] = __fmul_rn(v[j], cv[j]);
   }
   if (ep.alpha != 1.f) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(v[j], ep.alpha);
+    for (int j = 0; j < CW; ++j) v[j] = __fmul_rn(v[j], ep.alpha);
   }
   if (ep.add1) {
-    if ((pre_vec & 2) && !ep.add2) {
+    load_vec<CW>(ep.add1, col0, kmax, full, cv);
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], padd[j]);
-    } else {
-      load_vec32(ep.add1, col0, kmax, full, cv);
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], cv[j]);
-    }
+    for (int j = 0; j < CW; ++j) v[j] = __fadd_rn(v[j], cv[j]);
   }
   if (ep.add2) {
-    if (pre_vec & 2) {
+    load_vec<CW>(ep.add2, col0, kmax, full, cv);
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], padd[j]);
-    } else {
-      load_vec32(ep.add2, col0, kmax, full, cv);
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], cv[j]);
-    }
+    for (int j = 0; j < CW; ++j) v[j] = __fadd_rn(v[j], cv[j]);
   }
   if (ep.add_full) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j)
+    for (int j = 0; j < CW; ++j)
       if (j < ncols && row < p.M_total) v[j] = __fadd_rn(v[j], __fmul_rn(ep.beta_full, load_as_float(ep.add_full, ep.add_full_dt, base + j)));
   }
   if (ep.act != ACT_NONE && ep.act_first) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = apply_act(ep.act, v[j], ep.act_a, ep.act_b);
+    for (int j = 0; j < CW; ++j) v[j] = apply_act(ep.act, v[j], ep.act_a, ep.act_b);
   }
   if (has_res) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], rv[j]);
+    for (int j = 0; j < CW; ++j) v[j] = __fadd_rn(v[j], rv[j]);
   }
   if (ep.act != ACT_NONE && !ep.act_first) {
     if (ep.act == ACT_RELU) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+      for (int j = 0; j < CW; ++j) v[j] = fmaxf(v[j], 0.f);
     } else {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = apply_act(ep.act, v[j], ep.act_a, ep.act_b);
+      for (int j = 0; j < CW; ++j) v[j] = apply_act(ep.act, v[j], ep.act_a, ep.act_b);
     }
   }
   // ---- store ----
   if (out_dt == DT_F16 || out_dt == DT_BF16) {
-    uint4 u[4];
+    constexpr int NQ = CW / 8;
+    uint4 u[NQ];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
+    for (int q = 0; q < NQ; ++q) {
       if (out_dt == DT_F16) {
         __half2* h = (__half2*)&u[q];
 #pragma unroll
@@ -337,23 +338,24 @@ __device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, float (&v)[3
     }
     if (staged) {
 #pragma unroll
-      for (int q = 0; q < 4; ++q) sts128(stage_piece(sp, q), u[q]);
+      for (int q = 0; q < NQ; ++q) sts128(stage_piece(sp, q), u[q]);
     } else if (row < p.M_total) {
       uint16_t* out = (uint16_t*)p.y + base;
       if (gvec) {
 #pragma unroll
-        for (int q = 0; q < 4; ++q) ((uint4*)out)[q] = u[q];
+        for (int q = 0; q < NQ; ++q) ((uint4*)out)[q] = u[q];
       } else {
         const uint16_t* e = (const uint16_t*)u;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) if (j < ncols) out[j] = e[j];
+        for (int j = 0; j < CW; ++j) if (j < ncols) out[j] = e[j];
       }
     }
   } else if (out_dt == DT_S8) {
-    uint4 u[2];
+    constexpr int NQ = CW / 16;
+    uint4 u[NQ];
     uint32_t* w = (uint32_t*)u;
 #pragma unroll
-    for (int t = 0; t < 8; ++t) {
+    for (int t = 0; t < CW / 4; ++t) {
       uint32_t qb[4];
 #pragma unroll
       for (int b = 0; b < 4; ++b) {
@@ -364,36 +366,38 @@ __device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, float (&v)[3
       w[t] = __byte_perm(__byte_perm(qb[0], qb[1], 0x0040), __byte_perm(qb[2], qb[3], 0x0040), 0x5410);
     }
     if (staged) {
-      sts128(stage_piece(sp, 0), u[0]);
-      sts128(stage_piece(sp, 1), u[1]);
+#pragma unroll
+      for (int q = 0; q < NQ; ++q) sts128(stage_piece(sp, q), u[q]);
     } else if (row < p.M_total) {
       int8_t* out = (int8_t*)p.y + base;
       if (gvec) {
-        ((uint4*)out)[0] = u[0];
-        ((uint4*)out)[1] = u[1];
+#pragma unroll
+        for (int q = 0; q < NQ; ++q) ((uint4*)out)[q] = u[q];
       } else {
         const int8_t* e = (const int8_t*)u;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) if (j < ncols) out[j] = e[j];
+        for (int j = 0; j < CW; ++j) if (j < ncols) out[j] = e[j];
       }
     }
   } else if (row < p.M_total) {  // DT_F32
     float* out = (float*)p.y + base;
     if (gvec) {
 #pragma unroll
-      for (int q = 0; q < 8; ++q) ((float4*)out)[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+      for (int q = 0; q < CW / 4; ++q) ((float4*)out)[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
     } else {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) if (j < ncols) out[j] = v[j];
+      for (int j = 0; j < CW; ++j) if (j < ncols) out[j] = v[j];
     }
   }
 }
 
 // --------------------------------------------------------------------- kernel ----
 template <int OUT, bool STAGED>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(EpiCfg<STAGED>::kThreads, 1)
 umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmY,
                  const __grid_constant__ CUtensorMap tmR, const UmmaParams p) {
+  constexpr int kEpilogueWarps = EpiCfg<STAGED>::kWarps, kLoaderWarp = EpiCfg<STAGED>::kLoaderWarp, kStorerWarp = EpiCfg<STAGED>::kStorerWarp;
+  constexpr int CW = EpiCfg<STAGED>::kChunk;
   extern __shared__ uint8_t smem_raw[];
   if (threadIdx.x == 0) TS(7);
   // operand stages start on a 1024-byte boundary (the 128-byte swizzle repeats every 1024 bytes)
@@ -591,7 +595,7 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       // Per output tile the staging ring supplies stage_boxes boxes of 128 rows x 128 bytes; the
       // loader warp has already put the residual there, this warp overwrites its part of the box
       // with the result and the storer warp sends the box out.
-      const int cols_per_box = 128 / p.out_esz, chunks_per_box = cols_per_box >> 5;
+      const int cols_per_box = 128 / p.out_esz, chunks_per_box = cols_per_box / CW;
       int slot = 0;
       uint32_t ph = 0;
       for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++tcount) {
@@ -608,28 +612,27 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (!mbar_wait(box_full + slot, ph, abort_flag, p.status, 6)) { ok = false; break; }
 #pragma unroll 1
           for (int ch = cgroup; ch < chunks_per_box; ch += kGroups) {
-            const int c = bx * cols_per_box + ch * 32, col0 = n0 + c;
+            const int c = bx * cols_per_box + ch * CW, col0 = n0 + c;
             if (c >= p.BN) break;  // a box may be wider than the tile (int8 boxes hold 128 channels)
-            uint32_t r[32];
-            tmem_ld32(taddr + (uint32_t)c, r);
+            uint32_t r[CW];
+            tmem_ld<CW>(taddr + (uint32_t)c, r);
             tmem_ld_wait();
-            float v[32];
+            float v[CW];
             if (p.acc_int) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = (float)(int32_t)r[j];
+              for (int j = 0; j < CW; ++j) v[j] = (float)(int32_t)r[j];
             } else {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+              for (int j = 0; j < CW; ++j) v[j] = __uint_as_float(r[j]);
             }
             StagePos sp;
             sp.row_addr = staging_u32 + (uint32_t)slot * 16384u + (uint32_t)r_in_tile * 128u;
-            sp.j0 = (ch * 32 * p.out_esz) >> 4;
+            sp.j0 = (ch * CW * p.out_esz) >> 4;
             sp.rxor = r_in_tile & 7;
             const uint4 none[4] = {};
-            const float none32[32] = {};
             // (Fetching the residual pieces and per-channel vectors before tcgen05.wait::ld was tried and
             // measured slower: the extra live registers cost more than the hidden latency.)
-            epilogue_chunk<OUT, true>(p, v, row, col0, max(0, min(32, p.K_out - col0)), none, false, sp, p.res_tma != 0, none32, none32, 0);
+            epilogue_chunk<OUT, true, CW>(p, v, row, col0, max(0, min(CW, p.K_out - col0)), none, false, sp, p.res_tma != 0);
           }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the bulk-copy engine must see these writes
           __syncwarp();
@@ -690,8 +693,7 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
             }
             StagePos sp = {0, 0, 0};
-            const float none32[32] = {};
-            epilogue_chunk<OUT, false>(p, v, row, col0, ncols, pre[i], pre_ok[i], sp, false, none32, none32, 0);
+            epilogue_chunk<OUT, false, 32>(p, v, row, col0, ncols, pre[i], pre_ok[i], sp, false);
           }
         }
         tc_fence_before();
@@ -897,7 +899,7 @@ int umma_conv_run(UmmaLaunch* L, cudaStream_t stream) {
   const UmmaParams& p = L->p;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)L->grid);
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(p.staged ? EpiCfg<true>::kThreads : EpiCfg<false>::kThreads);
   cfg.dynamicSmemBytes = L->smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
