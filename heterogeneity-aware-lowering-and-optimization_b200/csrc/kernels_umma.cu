@@ -45,7 +45,7 @@ template <bool STAGED> struct EpiCfg {
   static constexpr int kThreads = 32 * (4 + kWarps);
 };
 constexpr int kMaxRing = 8;
-constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr uint32_t kSpinLimit = 1u << 20;  // attempts of up to 4 us each before a wait gives up
 
 struct UmmaParams {
   int M_total, K_out, C, R, S, P, Q;
@@ -94,11 +94,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Same, but the thread may stay suspended in hardware for up to `ns` nanoseconds before the attempt
+// reports failure (it resumes at once when the phase completes).  Long suspensions keep waiting warps
+// from spending issue slots on polling while the epilogue warps of the same scheduler have work.
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait.  Returns false when the limit expired or another role already aborted.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023) == 1023 && *abort_flag) return false;
+    if (mbar_try_wait_suspend(bar, parity, 4000u)) return true;
+    if ((i & 63) == 63 && *abort_flag) return false;
   }
   *abort_flag = 1;
   if (status) { atomicCAS(status, 0, code); status[1] = (int)blockIdx.x; }
