@@ -77,6 +77,13 @@ int gemm_simt(const GemmGeom& g, int in_dt, const void* A, const void* B, void* 
 struct UmmaConv {
   int N, H, W, C, K, R, S, P, Q, stride_h, stride_w, pad_t, pad_l;
   int in_dt;  // DT_F16, DT_BF16 or DT_S8
+  // Optional byte strides of the W and H dimensions of x (0 = dense NHWC).  A W stride smaller than C*elemsize
+  // describes overlapping pixels: each position reads C contiguous elements starting x_w_stride bytes after
+  // the previous one (the widened-pixel stem without a materialised copy).
+  long long x_w_stride = 0, x_h_stride = 0, x_n_stride = 0;
+  // Batched GEMM (attention): w holds `w_batches` matrices [K][C] back to back and output rows
+  // [b*rows_per_batch, (b+1)*rows_per_batch) use matrix b.  rows_per_batch must be a multiple of 128.
+  int w_batches = 0, rows_per_batch = 0;
 };
 // True when the tensor-core kernel can run this problem.
 bool umma_conv_supported(const UmmaConv& p);
@@ -147,6 +154,9 @@ int pad_channels(int esz, const void* x, void* y, int64_t pixels, int C, int Cp,
 // convolution over few channels becomes an (R x 1) convolution over 32 channels with unit column
 // stride.  esz is 1 or 2 bytes; one thread writes 16 bytes.
 int stem_widen(int esz, const void* x, void* y, int N, int H, int W, int C, int Q, cudaStream_t stream);
+// y[n][h][4 + w][4] = x[n][h][w][0..C) (zeros elsewhere): a 4-channel image with 4 pixels of zero padding on the
+// left and right of every row, from which overlapping 8-pixel windows can be read at 16-byte steps.
+int stem_pad4(int esz, const void* x, void* y, int N, int H, int W, int C, cudaStream_t stream);
 int resize_nearest(int esz, const void* x, void* y, int N, int H, int W, int C, int P, int Q, bool nhwc,
                    cudaStream_t stream);
 // out[o, k, :] = in[o, idx[k], :]; idx int32 or int64.

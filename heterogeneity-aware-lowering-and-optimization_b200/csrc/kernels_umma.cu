@@ -61,6 +61,7 @@ struct UmmaParams {
   uint32_t idesc;      // tcgen05 instruction descriptor
   uint32_t desc_hi;    // upper 32 bits of the shared-memory matrix descriptors
   int acc_int;         // accumulators are int32
+  int rows_per_batch;  // batched GEMM: output rows per B matrix (0 = one shared B)
   int staged;          // epilogue goes through a shared-memory tile and TMA stores
   int res_tma;         // the residual tile is brought into that tile by TMA
   int out_esz;         // bytes per output element
@@ -474,6 +475,7 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           h0 = op * p.stride_h - p.pad_t;
         }
         int tap = 0, fr = 0, fs = 0, c0 = 0, left = p.num_kb;
+        const int bidx = p.rows_per_batch ? m0 / p.rows_per_batch : 0;
         for (int it = 0; it < p.num_it; ++it) {
           if (!mbar_wait(empty_bar + s, ph ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
           const int nb = left < p.bps ? left : p.bps;
@@ -485,7 +487,8 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           for (int j = 0; j < nb; ++j) {
             if (p.im2col) tma_load_im2col_4d(sa, &tmA, fb, c0, w0, h0, img, (uint16_t)fs, (uint16_t)fr);
             else tma_load_2d(sa, &tmA, fb, c0, m0);
-            tma_load_3d(sb, &tmB, fb, c0, tap, n0);
+            if (p.rows_per_batch) tma_load_3d(sb, &tmB, fb, c0, n0, bidx);
+            else tma_load_3d(sb, &tmB, fb, c0, tap, n0);
             sa += a_box;
             sb += b_box;
             c0 += p.kbe;
@@ -770,6 +773,7 @@ bool umma_conv_supported(const UmmaConv& c) {
   if (c.pad_t > 127 || c.pad_l > 127 || c.R > 128 || c.S > 128) return false;  // im2col corners are 8-bit
   if ((int64_t)c.N * c.P * c.Q >= (1ll << 31)) return false;
   if (c.H < 1 || c.W < 1 || c.P < 1 || c.Q < 1) return false;
+  if (c.w_batches > 0 && (c.R != 1 || c.S != 1 || c.rows_per_batch <= 0 || c.rows_per_batch % 128 != 0)) return false;
   return true;
 }
 
@@ -827,6 +831,7 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
   if (p.stages > p.num_it + 1) p.stages = p.num_it + 1;
   if (p.stages < 2) p.stages = 2;
   p.acc_int = c.in_dt == DT_S8;
+  p.rows_per_batch = c.w_batches > 0 ? c.rows_per_batch : 0;
   p.tmem_cols = 2 * p.BN;  // 128, 256 or 512: powers of two >= 32
   const uint32_t fmt = c.in_dt == DT_BF16 ? 1u : (c.in_dt == DT_S8 ? 1u : 0u);      // bf16 / signed 8-bit / f16
   const uint32_t cfmt = p.acc_int ? 2u : 1u;                                        // s32 / f32 accumulators
@@ -845,6 +850,7 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
   if (p.im2col) {
     cuuint64_t dims[4] = {(cuuint64_t)c.C, (cuuint64_t)c.W, (cuuint64_t)c.H, (cuuint64_t)c.N};
     cuuint64_t strides[3] = {(cuuint64_t)c.C * es, (cuuint64_t)c.W * c.C * es, (cuuint64_t)c.H * c.W * c.C * es};
+    if (c.x_w_stride) { strides[0] = (cuuint64_t)c.x_w_stride; strides[1] = (cuuint64_t)c.x_h_stride; strides[2] = (cuuint64_t)c.x_n_stride; }
     // The box of filter-window origins: from -pad to the last origin that still yields an output.
     int lower[2] = {-c.pad_l, -c.pad_t};
     // The last origin is (Q-1)*stride - pad; the upper corner is that position relative to W-1 (H-1).
@@ -859,7 +865,8 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
       // (cute/atom/copy_traits_sm90_im2col.hpp), and so does this library.
       int drv = 0;
       cudaDriverGetVersion(&drv);
-      if (drv <= 13010 && (int64_t)c.N * c.H * c.W * c.C * es < 131072) ((uint64_t*)&L->tmA)[1] &= ~(1ull << 21);
+      const int64_t span = c.x_w_stride ? (int64_t)c.N * c.x_n_stride : (int64_t)c.N * c.H * c.W * c.C * es;
+      if (drv <= 13010 && span < 131072) ((uint64_t*)&L->tmA)[1] &= ~(1ull << 21);
     }
   } else {
     cuuint64_t dims[2] = {(cuuint64_t)c.C, (cuuint64_t)p.M_total};
@@ -869,11 +876,20 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
     r = g_encode_tiled(&L->tmA, dt, 2, (void*)x, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   }
-  if (r != CUDA_SUCCESS) { fprintf(stderr, "[odla_b200] tensor map (A) encode failed: %d\n", (int)r); delete L; return nullptr; }
+  if (r != CUDA_SUCCESS) {
+    if (!c.x_w_stride) fprintf(stderr, "[odla_b200] tensor map (A) encode failed: %d\n", (int)r);  // overlapping strides are an optional fast path
+    delete L;
+    return nullptr;
+  }
   {
     cuuint64_t dims[3] = {(cuuint64_t)c.C, (cuuint64_t)(c.R * c.S), (cuuint64_t)c.K};
     cuuint64_t strides[2] = {(cuuint64_t)c.C * es, (cuuint64_t)c.R * c.S * c.C * es};
     cuuint32_t box[3] = {(cuuint32_t)p.kbe, 1, (cuuint32_t)p.BN};
+    if (c.w_batches > 0) {  // [batches][K][C]: the box spans BN rows of one matrix
+      dims[1] = (cuuint64_t)c.K; dims[2] = (cuuint64_t)c.w_batches;
+      strides[1] = (cuuint64_t)c.K * c.C * es;
+      box[1] = (cuuint32_t)p.BN; box[2] = 1;
+    }
     cuuint32_t estr[3] = {1, 1, 1};
     r = g_encode_tiled(&L->tmB, dt, 3, (void*)w, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);

@@ -134,6 +134,8 @@ struct Fused {
   V res_scale = nullptr;    // Dequantize scale when the residual is int8
   int act = ACT_NONE; float act_a = 0, act_b = 0; bool act_first = false;
   V quant_scale = nullptr;  // absorbed Quantize
+  float scalar_mul = 1.f;   // a following Mul by a scalar constant, folded into alpha
+  bool has_scalar_mul = false;
 };
 
 struct Item {               // one launch-list entry before emission
@@ -347,6 +349,12 @@ void Builder::try_fuse(V root) {
         else f->res = other;
         if (f->act != ACT_NONE) f->act_first = true;
       } else break;
+    } else if (nxt->kind == OP_BINARY && nxt->ia[0] == BIN_MUL && !f->int8 && !f->add_const && !f->res && f->act == ACT_NONE && !f->has_scalar_mul &&
+               !root->in[2] && (nxt->in[0] == cur ? nxt->in[1] : nxt->in[0])->kind == OP_CONST &&
+               numel((nxt->in[0] == cur ? nxt->in[1] : nxt->in[0])->type.shape) == 1 && (nxt->in[0] == cur ? nxt->in[1] : nxt->in[0]) != cur) {
+      // Gemm / Conv without bias followed by a multiplication by a scalar constant (the 1/sqrt(d) of attention)
+      f->scalar_mul = const_as_f32(nxt->in[0] == cur ? nxt->in[1] : nxt->in[0])[0];
+      f->has_scalar_mul = true;
     } else if (nxt->kind == OP_UNARY && f->act == ACT_NONE &&
                (nxt->ia[0] == UN_RELU || nxt->ia[0] == UN_LEAKY || nxt->ia[0] == UN_CLAMP || nxt->ia[0] == UN_GELU_ERF || nxt->ia[0] == UN_GELU_TANH)) {
       f->act = nxt->ia[0] == UN_RELU ? ACT_RELU : nxt->ia[0] == UN_LEAKY ? ACT_LEAKY : nxt->ia[0] == UN_CLAMP ? ACT_CLAMP
@@ -493,6 +501,7 @@ odla_status Builder::emit_fused(const Item& it) {
     ep.out_inv = 1.0f / ep.out_scale;
     ep.out_multiply = f.int8 ? 1 : 0;  // the chain hangs off int32 accumulators exactly when its root is an int8 kernel
   }
+  if (f.has_scalar_mul) ep.alpha = f.scalar_mul;
   bool allow_umma = !getenv("ODLA_B200_NO_UMMA");
   int sms = 148;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, p_->device);
@@ -524,6 +533,7 @@ odla_status Builder::emit_fused(const Item& it) {
     int Cp = g.C;
     const void* x_umma = x;
     void* padded = nullptr;
+    bool overlap = false;   // ... read through overlapping tensor-map strides instead of a materialised copy
     bool widened = false;   // stride-2 stem rewritten as an (R x 1) convolution over 32-channel widened pixels
     const bool small_c = allow_umma && nhwc && groups == 1 && (in_dt == DT_F16 || in_dt == DT_BF16 || in_dt == DT_S8) && !umma_conv_supported(uc) &&
                          g.C * storage_size(in_dt) < 32;
@@ -533,12 +543,43 @@ odla_status Builder::emit_fused(const Item& it) {
       UmmaConv uw = uc;
       uw.W = g.Q; uw.C = 32; uw.S = 1; uw.stride_w = 1; uw.pad_l = 0;
       if (umma_conv_supported(uw)) {
-        size_t pbytes = (size_t)g.N * g.H * g.Q * 32 * storage_size(in_dt);
-        if (inject_fault("alloc") || cudaMalloc(&padded, pbytes ? pbytes : 32) != cudaSuccess) return fail(ODLA_MEM_ERROR, "scratch allocation failed");
-        p_->extra_allocs.push_back(padded);
-        x_umma = padded;
-        uc = uw;
-        widened = true;
+        const int esz0 = storage_size(in_dt);
+        // First choice: no widened copy at all.  Pad the image to 4 channels with 4 zero pixels on each side of
+        // every row; the widened pixel of column q is then the 32 contiguous elements that start 16*esz... bytes
+        // (two pixels) after the one of column q-1, which a tensor map with a W stride smaller than the pixel
+        // size describes directly.  If the driver refuses such a map, fall back to the materialised copy.
+        if (esz0 == 2 && !getenv("ODLA_B200_NO_OVERLAP")) {
+          UmmaConv uo = uw;
+          uo.x_w_stride = 2 * 4 * esz0;                       // two 4-channel pixels
+          uo.x_h_stride = (long long)(g.W + 8) * 4 * esz0;
+          uo.x_n_stride = uo.x_h_stride * g.H;
+          void* pad4 = nullptr;
+          size_t pb = (size_t)uo.x_n_stride * g.N + 256;
+          if (!inject_fault("alloc") && cudaMalloc(&pad4, pb) == cudaSuccess) {
+            Epilogue probe_ep;
+            probe_ep.out_dt = DT_F32;
+            UmmaLaunch* probe = umma_conv_prepare(uo, pad4, pad4, pad4, probe_ep, p_->status, sms);
+            if (probe) {
+              umma_conv_destroy(probe);
+              p_->extra_allocs.push_back(pad4);
+              padded = pad4;
+              x_umma = padded;
+              uc = uo;
+              widened = true;
+              overlap = true;
+            } else {
+              cudaFree(pad4);
+            }
+          } else cudaGetLastError();
+        }
+        if (!widened) {
+          size_t pbytes = (size_t)g.N * g.H * g.Q * 32 * esz0;
+          if (inject_fault("alloc") || cudaMalloc(&padded, pbytes ? pbytes : 32) != cudaSuccess) return fail(ODLA_MEM_ERROR, "scratch allocation failed");
+          p_->extra_allocs.push_back(padded);
+          x_umma = padded;
+          uc = uw;
+          widened = true;
+        }
       }
     }
     if (small_c && !widened) {
@@ -583,10 +624,11 @@ odla_status Builder::emit_fused(const Item& it) {
         int esz = storage_size(in_dt), C0 = g.C;
         int64_t pixels = (int64_t)g.N * g.H * g.W;
         ConvGeom gg = g;
-        bool wide = widened;
-        double scratch_bytes = wide ? 2.0 * g.N * g.H * g.Q * 32 * esz : 2.0 * pixels * 32;
+        bool wide = widened, ov = overlap;
+        double scratch_bytes = ov ? 2.0 * g.N * g.H * (g.W + 8) * 4 * esz : wide ? 2.0 * g.N * g.H * g.Q * 32 * esz : 2.0 * pixels * 32;
         add_launch("conv_umma", f.out, flops, bytes + scratch_bytes, [=](cudaStream_t s) {
-          int rc = wide ? stem_widen(esz, x, padded, gg.N, gg.H, gg.W, C0, gg.Q, s) : pad_channels(esz, x, padded, pixels, C0, Cp, s);
+          int rc = ov ? stem_pad4(esz, x, padded, gg.N, gg.H, gg.W, C0, s)
+                      : wide ? stem_widen(esz, x, padded, gg.N, gg.H, gg.W, C0, gg.Q, s) : pad_channels(esz, x, padded, pixels, C0, Cp, s);
           return rc ? rc : umma_conv_run(ul, s);
         });
         p_->launches.back().n_kernels = 2;
@@ -626,7 +668,7 @@ odla_status Builder::emit_fused(const Item& it) {
   if ((tb ? bc : br) != Kd) return fail(ODLA_INVALID_PARAM, "'" + root->name + "': Gemm inner dimensions differ");
   if (bbatch != batch && bbatch != 1) return fail(ODLA_INVALID_PARAM, "'" + root->name + "': Gemm batch dimensions differ");
   if (count(root) != batch * M * N) return fail(ODLA_INVALID_PARAM, "'" + root->name + "': Gemm output_dims do not match the operands");
-  ep.alpha = alpha;
+  ep.alpha = alpha * f.scalar_mul;
   if (C && beta != 0.f) {
     int64_t cn = C->kind == OP_CONST ? numel(C->type.shape) : count(C);
     if (C->kind == OP_CONST && (cn == 1 || cn == N)) {
@@ -657,6 +699,37 @@ odla_status Builder::emit_fused(const Item& it) {
       if (!ul) return fail(ODLA_FAILURE, "'" + root->name + "': tensor-map encoding failed");
       p_->umma.push_back(ul);
       add_launch("gemm_umma", f.out, flops, bytes, [ul](cudaStream_t s) { return umma_conv_run(ul, s); });
+      return ODLA_SUCCESS;
+    }
+  }
+  // Batched product of two run-time tensors (attention scores and context): one tensor-core launch whose B
+  // operand changes with the batch.  B must be K-major; a [batch, K, N] operand is transposed into scratch first.
+  if (allow_umma && !ta && f.w->kind != OP_CONST && bbatch == batch && batch > 1 && M % 128 == 0 && (in_dt == DT_F16 || in_dt == DT_BF16) &&
+      dt_[resolve(f.w)] == in_dt && batch * M < (1ll << 31)) {
+    UmmaConv uc{1, 1, (int)(batch * M), (int)Kd, (int)N, 1, 1, 1, (int)(batch * M), 1, 1, 0, 0, in_dt};
+    uc.w_batches = (int)batch;
+    uc.rows_per_batch = (int)M;
+    if (umma_conv_supported(uc)) {
+      const void* bsrc = dev_ptr(f.w);
+      void* bt = nullptr;
+      MoveGeom mg{};
+      if (!tb) {
+        if (cudaMalloc(&bt, (size_t)(batch * N * Kd * storage_size(in_dt))) != cudaSuccess) return fail(ODLA_MEM_ERROR, "scratch allocation failed");
+        p_->extra_allocs.push_back(bt);
+        mg.rank = 3;
+        mg.oshape[0] = batch; mg.oshape[1] = N; mg.oshape[2] = Kd;
+        mg.istride[0] = Kd * N; mg.istride[1] = 1; mg.istride[2] = N;
+        mg.ostride[0] = N * Kd; mg.ostride[1] = Kd; mg.ostride[2] = 1;
+      }
+      UmmaLaunch* ul = umma_conv_prepare(uc, x, bt ? bt : bsrc, y, ep, p_->status, sms);
+      if (!ul) return fail(ODLA_FAILURE, "'" + root->name + "': tensor-map encoding failed");
+      p_->umma.push_back(ul);
+      int esz = storage_size(in_dt);
+      add_launch("gemm_umma", f.out, flops, bytes, [=](cudaStream_t s) {
+        if (bt) { int rc = move(mg, esz, bsrc, bt, s); if (rc) return rc; }
+        return umma_conv_run(ul, s);
+      });
+      p_->launches.back().n_kernels = bt ? 2 : 1;
       return ODLA_SUCCESS;
     }
   }
