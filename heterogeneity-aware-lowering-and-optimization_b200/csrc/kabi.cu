@@ -38,8 +38,8 @@ extern "C" int odla_b200_conv_umma(const odla_b200_conv_desc* d, const void* x, 
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   int* status = nullptr;
-  if (cudaMalloc((void**)&status, 256) != cudaSuccess) return -2;
-  cudaMemsetAsync(status, 0, 256, (cudaStream_t)stream);
+  if (cudaMalloc((void**)&status, 1024) != cudaSuccess) return -2;
+  cudaMemsetAsync(status, 0, 1024, (cudaStream_t)stream);
   UmmaLaunch* L = umma_conv_prepare(c, x, w, y, ep, status, sms);
   if (!L) { cudaFree(status); return -2; }
   int rc = umma_conv_run(L, (cudaStream_t)stream);
@@ -48,10 +48,16 @@ extern "C" int odla_b200_conv_umma(const odla_b200_conv_desc* d, const void* x, 
   if (cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess) rc = -2;
   umma_conv_destroy(L);
   if (getenv("ODLA_B200_DEBUG_TS")) {
-    unsigned long long ts[16];
+    // only meaningful in a build with UMMA_DEBUG_TS: block 0's timeline (ns) and the cycles it spent in each wait
+    unsigned long long ts[124];
     cudaMemcpy(ts, (char*)status + 32, sizeof(ts), cudaMemcpyDeviceToHost);
-    fprintf(stderr, "ts(ns rel. to kernel entry): sync=%lld tma0=%lld full0=%lld commit=%lld tfull=%lld epi_end=%lld teardown=%lld\n", (long long)(ts[0] - ts[7]),
-            (long long)(ts[1] - ts[7]), (long long)(ts[2] - ts[7]), (long long)(ts[3] - ts[7]), (long long)(ts[4] - ts[7]), (long long)(ts[5] - ts[7]), (long long)(ts[6] - ts[7]));
+    fprintf(stderr, "ts(ns rel. to kernel entry): sync=%lld tfull0=%lld epi0_end=%lld teardown=%lld | cycles %lld\n", (long long)(ts[0] - ts[7]),
+            (long long)(ts[4] - ts[7]), (long long)(ts[5] - ts[7]), (long long)(ts[6] - ts[7]), (long long)(ts[16 + 6] - ts[16 + 7]));
+    static const char* site[8] = {"", "producer<-empty", "mma<-tempty", "mma<-full", "epi<-tfull", "loader<-box_free", "epi<-box_full", "storer<-box_done"};
+    for (int code = 1; code < 8; ++code) {
+      const unsigned long long* c4 = ts + 28 + code * 4;  // ts[] starts at status + 32 bytes = 4 words
+      fprintf(stderr, "  wait %-18s %10llu %10llu %10llu %10llu\n", site[code], c4[0], c4[1], c4[2], c4[3]);
+    }
   }
   if (rc == 0 && host_status[0] != 0) {
     fprintf(stderr, "[odla_b200] odla_b200_conv_umma: bounded wait expired (code %d, block %d)\n", host_status[0], host_status[1]);

@@ -154,8 +154,9 @@ int pad_channels(int esz, const void* x, void* y, int64_t pixels, int C, int Cp,
 // convolution over few channels becomes an (R x 1) convolution over 32 channels with unit column
 // stride.  esz is 1 or 2 bytes; one thread writes 16 bytes.
 int stem_widen(int esz, const void* x, void* y, int N, int H, int W, int C, int Q, cudaStream_t stream);
-// y[n][h][4 + w][4] = x[n][h][w][0..C) (zeros elsewhere): a 4-channel image with 4 pixels of zero padding on the
-// left and right of every row, from which overlapping 8-pixel windows can be read at 16-byte steps.
+// y[n][h][4 + w][cp] = x[n][h][w][0..C) (zeros elsewhere), cp = 8 / esz channels so that a pixel is 8 bytes: an image
+// with 4 pixels of zero padding on the left and right of every row, from which overlapping 8-pixel windows (64 bytes)
+// can be read at 16-byte steps.
 int stem_pad4(int esz, const void* x, void* y, int N, int H, int W, int C, cudaStream_t stream);
 int resize_nearest(int esz, const void* x, void* y, int N, int H, int W, int C, int P, int Q, bool nhwc,
                    cudaStream_t stream);

@@ -450,21 +450,24 @@ __global__ void stem_widen_kernel(const T* __restrict__ x, uint4* __restrict__ y
     y[e] = out;
   }
 }
-template <typename T>
+// Pads every pixel to 8 bytes (CP = 4 two-byte or 8 one-byte channels) and every image row with 4 zero pixels on each side.
+template <typename T, int CP>
 __global__ void stem_pad4_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int W, int C) {
+  static_assert(sizeof(T) * CP == 8, "a padded pixel is 8 bytes");
   const int Wp = W + 8;
   const int64_t total = rows * Wp;
   for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
     const int wp = (int)(e % Wp);
     const int64_t row = e / Wp;
     const int w = wp - 4;
-    T px[4] = {0, 0, 0, 0};
+    __align__(8) T px[CP];
+#pragma unroll
+    for (int c = 0; c < CP; ++c) px[c] = 0;
     if (w >= 0 && w < W) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) if (c < C) px[c] = x[(row * W + w) * C + c];
+      for (int c = 0; c < CP; ++c) if (c < C) px[c] = x[(row * W + w) * C + c];
     }
-    if (sizeof(T) == 2) *(uint2*)(y + e * 4) = *(const uint2*)px;
-    else *(uint32_t*)(y + e * 4) = *(const uint32_t*)px;
+    *(uint2*)(y + e * CP) = *(const uint2*)px;
   }
 }
 template <typename T>
@@ -660,8 +663,8 @@ int stem_pad4(int esz, const void* x, void* y, int N, int H, int W, int C, cudaS
   if (total <= 0) return 0;
   if (C > 4) return -1;
   int grid = grid_for(total, 256);
-  if (esz == 1) stem_pad4_kernel<uint8_t><<<grid, 256, 0, s>>>((const uint8_t*)x, (uint8_t*)y, rows, W, C);
-  else if (esz == 2) stem_pad4_kernel<uint16_t><<<grid, 256, 0, s>>>((const uint16_t*)x, (uint16_t*)y, rows, W, C);
+  if (esz == 1) stem_pad4_kernel<uint8_t, 8><<<grid, 256, 0, s>>>((const uint8_t*)x, (uint8_t*)y, rows, W, C);
+  else if (esz == 2) stem_pad4_kernel<uint16_t, 4><<<grid, 256, 0, s>>>((const uint16_t*)x, (uint16_t*)y, rows, W, C);
   else return -1;
   return check_launch();
 }

@@ -67,6 +67,9 @@ struct UmmaParams {
   int out_esz;         // bytes per output element
   int stage_boxes;     // 128-row x 128-byte boxes per output tile
   int ring_boxes;      // boxes in the staging ring (>= stage_boxes)
+  int box_arrivals;    // epilogue warps that write into one box
+  int epi_interleave;  // groups take every fourth chunk instead of a contiguous run
+  int epi_mode;        // kernel variant: 0 direct, 1 staged, 2 staged with the general activation / division
   int tmem_cols;
   void* y;
   int* status;
@@ -110,7 +113,22 @@ __device__ __forceinline__ bool mbar_try_wait_suspend(uint64_t* bar, uint32_t pa
   return ok != 0;
 }
 // Bounded wait.  Returns false when the limit expired or another role already aborted.
+__device__ __forceinline__ bool mbar_wait_impl(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code);
+// Debug builds add up, per wait site (and per epilogue group), the cycles block 0 spent waiting.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+#ifdef UMMA_DEBUG_TS
+  const long long t0 = clock64();
+  const bool ok = mbar_wait_impl(bar, parity, abort_flag, status, code);
+  const int warp = threadIdx.x >> 5;
+  const bool epi = code == 4 || code == 6;
+  if (blockIdx.x == 0 && status && (!epi || ((threadIdx.x & 31) == 0 && ((warp - 2) & 3) == 0)))
+    atomicAdd((unsigned long long*)status + 32 + code * 4 + (epi ? (warp - 2) >> 2 : 0), (unsigned long long)(clock64() - t0));
+  return ok;
+#else
+  return mbar_wait_impl(bar, parity, abort_flag, status, code);
+#endif
+}
+__device__ __forceinline__ bool mbar_wait_impl(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
   if (mbar_try_wait(bar, parity)) return true;
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait_suspend(bar, parity, 4000u)) return true;
@@ -180,6 +198,16 @@ template <int CW> __device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32
   if (CW == 32) tmem_ld32(taddr, r); else tmem_ld16(taddr, r);
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// The same wait, naming the registers of the load it completes so that no read of them can be scheduled above it.
+template <int N> __device__ __forceinline__ void tmem_ld_wait_regs(uint32_t (&r)[N]);
+template <> __device__ __forceinline__ void tmem_ld_wait_regs<16>(uint32_t (&r)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]),
+                 "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+               :
+               : "memory");
+}
+template <> __device__ __forceinline__ void tmem_ld_wait_regs<32>(uint32_t (&r)[32]) { tmem_ld_wait(); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ bool elect_one() {
@@ -194,7 +222,7 @@ __device__ __forceinline__ bool elect_one() {
 
 __device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
 #ifdef UMMA_DEBUG_TS
-#define TS(i) do { if (blockIdx.x == 0 && p.status) ((unsigned long long*)p.status)[4 + (i)] = gtime(); } while (0)
+#define TS(i) do { if (blockIdx.x == 0 && p.status) { ((unsigned long long*)p.status)[4 + (i)] = gtime(); ((unsigned long long*)p.status)[20 + (i)] = (unsigned long long)clock64(); } } while (0)
 #else
 #define TS(i) do {} while (0)
 #endif
@@ -407,11 +435,110 @@ __device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, float (&v)[C
   }
 }
 
+// The staged epilogue's chunk: 16 consecutive channels of one output row, residual read from and result
+// written to the row's place in the staging box.  Only what a staged launch can need is here (the launcher
+// sends everything else to the direct epilogue), so the loop around it stays small.
+template <int OUT, bool ANYACT>
+__device__ __forceinline__ void epilogue_chunk_staged(const UmmaParams& p, float (&v)[16], int col0, const StagePos& sp) {
+  const Epilogue& ep = p.ep;
+  const bool full = col0 + 16 <= p.K_out;  // the last chunk of a row may be cut short: its vectors are read with clamped indices
+  const int kmax = p.K_out - 1;
+  float cv[16];
+  if (ep.mul) {
+    load_vec<16>(ep.mul, col0, kmax, full, cv);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = __fmul_rn(v[j], cv[j]);
+  }
+  if (ep.alpha != 1.f) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = __fmul_rn(v[j], ep.alpha);
+  }
+  if (ep.add1) {
+    load_vec<16>(ep.add1, col0, kmax, full, cv);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = __fadd_rn(v[j], cv[j]);
+  }
+  if (ep.add2) {
+    load_vec<16>(ep.add2, col0, kmax, full, cv);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = __fadd_rn(v[j], cv[j]);
+  }
+  if (ANYACT && ep.act_first) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = apply_act(ep.act, v[j], ep.act_a, ep.act_b);
+  }
+  if (p.res_tma) {
+    if (OUT == DT_S8) {
+      const uint4 u = lds128(stage_piece(sp, 0));
+      const uint32_t* w = (const uint32_t*)&u;
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+#pragma unroll
+        for (int b = 0; b < 4; ++b) v[t * 4 + b] = __fadd_rn(v[t * 4 + b], __fmul_rn((float)(signed char)(w[t] >> (8 * b)), ep.res_scale));
+      }
+    } else {
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const uint4 u = lds128(stage_piece(sp, q));
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float2 f = OUT == DT_F16 ? __half22float2(((const __half2*)&u)[t]) : __bfloat1622float2(((const __nv_bfloat162*)&u)[t]);
+          v[q * 8 + 2 * t] = __fadd_rn(v[q * 8 + 2 * t], f.x);
+          v[q * 8 + 2 * t + 1] = __fadd_rn(v[q * 8 + 2 * t + 1], f.y);
+        }
+      }
+    }
+  }
+  if (ANYACT) {
+    if (!ep.act_first) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] = apply_act(ep.act, v[j], ep.act_a, ep.act_b);
+    }
+  } else if (ep.act == ACT_RELU) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = fmaxf(v[j], 0.f);
+  }
+  if (OUT == DT_S8) {
+    uint4 u;
+    uint32_t* w = (uint32_t*)&u;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      uint32_t qb[4];
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const float t4 = (!ANYACT || ep.out_multiply) ? __fmul_rn(v[t * 4 + b], ep.out_inv) : __fdiv_rn(v[t * 4 + b], ep.out_scale);
+        qb[b] = (uint32_t)rne_sat_s8(t4);
+      }
+      w[t] = __byte_perm(__byte_perm(qb[0], qb[1], 0x0040), __byte_perm(qb[2], qb[3], 0x0040), 0x5410);
+    }
+    sts128(stage_piece(sp, 0), u);
+  } else {
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      uint4 u;
+      if (OUT == DT_F16) {
+        __half2* h = (__half2*)&u;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) h[t] = __floats2half2_rn(v[q * 8 + 2 * t], v[q * 8 + 2 * t + 1]);
+      } else {
+        __nv_bfloat162* h = (__nv_bfloat162*)&u;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) h[t] = __floats2bfloat162_rn(v[q * 8 + 2 * t], v[q * 8 + 2 * t + 1]);
+      }
+      sts128(stage_piece(sp, q), u);
+    }
+  }
+}
+
 // --------------------------------------------------------------------- kernel ----
-template <int OUT, bool STAGED>
-__global__ void __launch_bounds__(EpiCfg<STAGED>::kThreads, 1)
+// MODE 0: direct epilogue (any output type, rows written straight to global memory).
+// MODE 1: staged epilogue, activation none / ReLU after the residual, int8 requantisation by multiplication.
+// MODE 2: staged epilogue with every activation, activation before the residual and division requantisation.
+template <int OUT, int MODE>
+__global__ void __launch_bounds__(EpiCfg<MODE != 0>::kThreads, 1)
 umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmY,
                  const __grid_constant__ CUtensorMap tmR, const UmmaParams p) {
+  constexpr bool STAGED = MODE != 0;
   constexpr int kEpilogueWarps = EpiCfg<STAGED>::kWarps, kLoaderWarp = EpiCfg<STAGED>::kLoaderWarp, kStorerWarp = EpiCfg<STAGED>::kStorerWarp;
   constexpr int CW = EpiCfg<STAGED>::kChunk;
   extern __shared__ uint8_t smem_raw[];
@@ -426,7 +553,7 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* tfull_bar = empty_bar + 16;            // [2]
   uint64_t* tempty_bar = tfull_bar + 2;            // [2]
   uint64_t* box_full = tempty_bar + 2;             // [ring] box is armed: free, and its residual (if any) has landed
-  uint64_t* box_done = box_full + kMaxRing;        // [ring] every epilogue warp has written its part
+  uint64_t* box_done = box_full + kMaxRing;        // [ring] every epilogue warp that owns part of the box has written it
   uint64_t* box_free = box_done + kMaxRing;        // [ring] the TMA store has finished reading the box
   uint32_t* tmem_slot = (uint32_t*)(box_free + kMaxRing);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
@@ -435,7 +562,7 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], kEpilogueWarps); }
-    for (int b = 0; b < kMaxRing; ++b) { mbar_init(&box_full[b], 1); mbar_init(&box_done[b], kEpilogueWarps); mbar_init(&box_free[b], 1); }
+    for (int b = 0; b < kMaxRing; ++b) { mbar_init(&box_full[b], 1); mbar_init(&box_done[b], (uint32_t)p.box_arrivals); mbar_init(&box_free[b], 1); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -609,52 +736,57 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     constexpr int kChunksPerWarp = 8 / kGroups;            // BN <= 256 -> at most 8 chunks of 32 columns
     const int r_in_tile = quarter * 32 + lane;
     const uint32_t staging_u32 = smem_u32(staging);
-    if (STAGED) {
+    if constexpr (STAGED) {
       // Per output tile the staging ring supplies stage_boxes boxes of 128 rows x 128 bytes; the
       // loader warp has already put the residual there, this warp overwrites its part of the box
       // with the result and the storer warp sends the box out.
       const int cols_per_box = 128 / p.out_esz, chunks_per_box = cols_per_box / CW;
+      // Which 16-column chunks of a tile the four warps of a group (one per lane quarter) take: either a
+      // contiguous run, so that a group fills and hands over a box (or its share of one) on its own while the
+      // other groups work on other boxes, or every fourth chunk, so that all groups finish box after box together.
+      const int n_chunks = p.BN / CW, per_group = n_chunks / kGroups;  // per group: 1, 2 or 4 chunks
+      const int ch_lo = cgroup * per_group, ch_hi = ch_lo + per_group;
       int slot = 0;
       uint32_t ph = 0;
       for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++tcount) {
         const uint32_t acc = tcount & 1, acc_ph = (tcount >> 1) & 1;
-        const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * p.BN;
-        const int64_t row = (int64_t)m0 + r_in_tile;
+        const int n0 = (tile / p.m_tiles) * p.BN;
         if (!mbar_wait(&tfull_bar[acc], acc_ph, abort_flag, p.status, 4)) { ok = false; break; }
         tc_fence_after();
         if (tcount == 0 && threadIdx.x == 64) TS(4);
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * (uint32_t)p.BN;
         for (int bx = 0; bx < p.stage_boxes && ok; ++bx) {
-          const int x0 = n0 + bx * cols_per_box;
-          if (x0 >= p.K_out) break;
-          if (!mbar_wait(box_full + slot, ph, abort_flag, p.status, 6)) { ok = false; break; }
-#pragma unroll 1
-          for (int ch = cgroup; ch < chunks_per_box; ch += kGroups) {
-            const int c = bx * cols_per_box + ch * CW, col0 = n0 + c;
-            if (c >= p.BN) break;  // a box may be wider than the tile (int8 boxes hold 128 channels)
-            uint32_t r[CW];
-            tmem_ld<CW>(taddr + (uint32_t)c, r);
-            tmem_ld_wait();
-            float v[CW];
-            if (p.acc_int) {
-#pragma unroll
-              for (int j = 0; j < CW; ++j) v[j] = (float)(int32_t)r[j];
-            } else {
-#pragma unroll
-              for (int j = 0; j < CW; ++j) v[j] = __uint_as_float(r[j]);
-            }
+          if (n0 + bx * cols_per_box >= p.K_out) break;
+          int first, last, step;
+          if (p.epi_interleave) { first = bx * chunks_per_box + cgroup; last = min((bx + 1) * chunks_per_box, n_chunks); step = kGroups; }
+          else { first = max(ch_lo, bx * chunks_per_box); last = min(ch_hi, (bx + 1) * chunks_per_box); step = 1; }
+          if (first < last) {
+            if (!mbar_wait(box_full + slot, ph, abort_flag, p.status, 6)) { ok = false; break; }
             StagePos sp;
             sp.row_addr = staging_u32 + (uint32_t)slot * 16384u + (uint32_t)r_in_tile * 128u;
-            sp.j0 = (ch * CW * p.out_esz) >> 4;
             sp.rxor = r_in_tile & 7;
-            const uint4 none[4] = {};
-            // (Fetching the residual pieces and per-channel vectors before tcgen05.wait::ld was tried and
-            // measured slower: the extra live registers cost more than the hidden latency.)
-            epilogue_chunk<OUT, true, CW>(p, v, row, col0, max(0, min(CW, p.K_out - col0)), none, false, sp, p.res_tma != 0);
+#pragma unroll 1
+            for (int ch = first; ch < last; ch += step) {
+              const int col0 = n0 + ch * CW;
+              if (col0 >= p.K_out) break;  // columns past K_out inside a chunk are computed and then clipped by the store
+              uint32_t r[CW];
+              tmem_ld<CW>(taddr + (uint32_t)(ch * CW), r);
+              tmem_ld_wait_regs<CW>(r);
+              float v[CW];
+              if (p.acc_int) {
+#pragma unroll
+                for (int j = 0; j < CW; ++j) v[j] = (float)(int32_t)r[j];
+              } else {
+#pragma unroll
+                for (int j = 0; j < CW; ++j) v[j] = __uint_as_float(r[j]);
+              }
+              sp.j0 = ((ch - bx * chunks_per_box) * CW * p.out_esz) >> 4;
+              epilogue_chunk_staged<OUT, MODE == 2>(p, v, col0, sp);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the bulk-copy engine must see these writes
+            __syncwarp();
+            if (lane == 0) mbar_arrive(box_done + slot);
           }
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the bulk-copy engine must see these writes
-          __syncwarp();
-          if (lane == 0) mbar_arrive(box_done + slot);
           if (++slot == p.ring_boxes) { slot = 0; ph ^= 1; }
         }
         tc_fence_before();
@@ -807,11 +939,14 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
   // and leaves with TMA stores; the residual tile arrives the same way when its element size equals
   // the output's.  Needs 16-byte-multiple rows in global memory and a 1/2-byte output type.
   p.out_esz = storage_size_of(ep.out_dt);
-  p.staged = (ep.out_dt == DT_F16 || ep.out_dt == DT_BF16 || ep.out_dt == DT_S8) && ((int64_t)c.K * p.out_esz) % 16 == 0 && !ep.add_full &&
+  // The residual of a staged launch always comes through the staging box, so it must have the output's type.
+  const bool res_ok = !ep.res || (ep.res_dt == ep.out_dt && (uintptr_t)ep.res % 16 == 0);
+  p.staged = (ep.out_dt == DT_F16 || ep.out_dt == DT_BF16 || ep.out_dt == DT_S8) && ((int64_t)c.K * p.out_esz) % 16 == 0 && !ep.add_full && res_ok &&
              ((uintptr_t)y % 16 == 0) && !getenv("ODLA_B200_DIRECT_EPILOGUE");
   p.stage_boxes = p.staged ? (p.BN * p.out_esz + 127) / 128 : 0;
-  p.res_tma = p.staged && ep.res && storage_size_of(ep.res_dt) == p.out_esz && (ep.res_dt == DT_F16 || ep.res_dt == DT_BF16 || ep.res_dt == DT_S8) &&
-              ((uintptr_t)ep.res % 16 == 0);
+  p.res_tma = p.staged && ep.res;
+  const bool plain_act = !ep.act_first && (ep.act == ACT_NONE || ep.act == ACT_RELU) && (ep.out_dt != DT_S8 || ep.out_multiply);
+  p.epi_mode = !p.staged ? 0 : (plain_act ? 1 : 2);
   // Shared memory: pipeline stages first (up to 4, or what one tile needs), then as many staging
   // boxes as fit (at least one tile's worth, at most 8) so residual loads run ahead of the epilogue
   // and stores drain behind it; what is left goes back to the pipeline.
@@ -825,6 +960,17 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
     if (p.ring_boxes > 2 * p.stage_boxes) p.ring_boxes = 2 * p.stage_boxes;
     if (p.ring_boxes < p.stage_boxes) p.ring_boxes = p.stage_boxes;
     if (p.ring_boxes < 2) p.ring_boxes = 2;  // the store of box i frees box i-1
+  }
+  {
+    // 16 epilogue warps = 4 groups; a group owns BN/64 consecutive 16-column chunks, a box holds 128/out_esz/16
+    const int per_group = p.BN / 64, per_box = 128 / p.out_esz / 16;
+    const int groups_per_box = per_box / per_group < 4 ? per_box / per_group : 4;
+    p.box_arrivals = 4 * (groups_per_box < 1 ? 1 : groups_per_box);
+    // Contiguous runs let the groups work on different boxes at once, which pays when boxes need no residual and
+    // the CTA has many tiles to stream through; otherwise finishing box after box gets the first store out sooner.
+    p.epi_interleave = ep.res != nullptr || p.total_tiles < 16 * sms;
+    if (getenv("ODLA_B200_EPI_INTERLEAVE")) p.epi_interleave = atoi(getenv("ODLA_B200_EPI_INTERLEAVE"));
+    if (p.epi_interleave) p.box_arrivals = 16;
   }
   p.stages = (budget - p.ring_boxes * 16384) / stage_bytes;
   if (p.stages > 8) p.stages = 8;
@@ -914,10 +1060,9 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 16 && !attr_set[dev]) {
-    bool ok = cudaFuncSetAttribute(umma_conv_kernel<DT_F16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess &&
-              cudaFuncSetAttribute(umma_conv_kernel<DT_BF16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess &&
-              cudaFuncSetAttribute(umma_conv_kernel<DT_S8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess &&
-              cudaFuncSetAttribute(umma_conv_kernel<-1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess;
+#define B2_SMEM(O, M) (cudaFuncSetAttribute(umma_conv_kernel<O, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess)
+    bool ok = B2_SMEM(DT_F16, 1) && B2_SMEM(DT_BF16, 1) && B2_SMEM(DT_S8, 1) && B2_SMEM(DT_F16, 2) && B2_SMEM(DT_BF16, 2) && B2_SMEM(DT_S8, 2) && B2_SMEM(-1, 0);
+#undef B2_SMEM
     if (!ok) { cudaGetLastError(); delete L; return nullptr; }
     attr_set[dev] = true;
   }
@@ -940,10 +1085,11 @@ int umma_conv_run(UmmaLaunch* L, cudaStream_t stream) {
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
   cudaError_t le;
-  if (!p.staged) le = cudaLaunchKernelEx(&cfg, umma_conv_kernel<-1, false>, L->tmA, L->tmB, L->tmY, L->tmR, p);
-  else if (p.ep.out_dt == DT_F16) le = cudaLaunchKernelEx(&cfg, umma_conv_kernel<DT_F16, true>, L->tmA, L->tmB, L->tmY, L->tmR, p);
-  else if (p.ep.out_dt == DT_BF16) le = cudaLaunchKernelEx(&cfg, umma_conv_kernel<DT_BF16, true>, L->tmA, L->tmB, L->tmY, L->tmR, p);
-  else le = cudaLaunchKernelEx(&cfg, umma_conv_kernel<DT_S8, true>, L->tmA, L->tmB, L->tmY, L->tmR, p);
+#define B2_LAUNCH(O, M) le = cudaLaunchKernelEx(&cfg, umma_conv_kernel<O, M>, L->tmA, L->tmB, L->tmY, L->tmR, p)
+  if (p.epi_mode == 0) B2_LAUNCH(-1, 0);
+  else if (p.epi_mode == 1) { if (p.ep.out_dt == DT_F16) B2_LAUNCH(DT_F16, 1); else if (p.ep.out_dt == DT_BF16) B2_LAUNCH(DT_BF16, 1); else B2_LAUNCH(DT_S8, 1); }
+  else { if (p.ep.out_dt == DT_F16) B2_LAUNCH(DT_F16, 2); else if (p.ep.out_dt == DT_BF16) B2_LAUNCH(DT_BF16, 2); else B2_LAUNCH(DT_S8, 2); }
+#undef B2_LAUNCH
   if (le != cudaSuccess) { fprintf(stderr, "[odla_b200] umma_conv launch failed: %s\n", cudaGetErrorString(le)); cudaGetLastError(); return -2; }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { fprintf(stderr, "[odla_b200] umma_conv launch failed: %s\n", cudaGetErrorString(e)); return -2; }

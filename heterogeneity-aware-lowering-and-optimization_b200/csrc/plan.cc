@@ -534,7 +534,8 @@ odla_status Builder::emit_fused(const Item& it) {
     const void* x_umma = x;
     void* padded = nullptr;
     bool overlap = false;   // ... read through overlapping tensor-map strides instead of a materialised copy
-    bool widened = false;   // stride-2 stem rewritten as an (R x 1) convolution over 32-channel widened pixels
+    bool widened = false;   // stride-2 stem rewritten as an (R x 1) convolution over widened pixels (8 input pixels each)
+    int wide_c = 32, wide_cp = 4;  // channels of a widened pixel / of each input pixel inside it
     const bool small_c = allow_umma && nhwc && groups == 1 && (in_dt == DT_F16 || in_dt == DT_BF16 || in_dt == DT_S8) && !umma_conv_supported(uc) &&
                          g.C * storage_size(in_dt) < 32;
     if (small_c && g.C <= 4 && g.stride_w == 2 && g.pad_l <= 4 && g.S - g.pad_l <= 4 && !getenv("ODLA_B200_NO_WIDEN")) {
@@ -544,18 +545,19 @@ odla_status Builder::emit_fused(const Item& it) {
       uw.W = g.Q; uw.C = 32; uw.S = 1; uw.stride_w = 1; uw.pad_l = 0;
       if (umma_conv_supported(uw)) {
         const int esz0 = storage_size(in_dt);
-        // First choice: no widened copy at all.  Pad the image to 4 channels with 4 zero pixels on each side of
-        // every row; the widened pixel of column q is then the 32 contiguous elements that start 16*esz... bytes
-        // (two pixels) after the one of column q-1, which a tensor map with a W stride smaller than the pixel
-        // size describes directly.  If the driver refuses such a map, fall back to the materialised copy.
-        if (esz0 == 2 && !getenv("ODLA_B200_NO_OVERLAP")) {
+        // First choice: no widened copy at all.  Pad every pixel to 8 bytes (4 two-byte or 8 one-byte channels) and
+        // every row with 4 zero pixels on each side; the widened pixel of column q is then the 64 contiguous bytes
+        // that start 16 bytes (two pixels) after the one of column q-1, which a tensor map with a W stride smaller
+        // than the pixel size describes directly.  If the driver refuses such a map, fall back to the materialised copy.
+        if (!getenv("ODLA_B200_NO_OVERLAP")) {
           UmmaConv uo = uw;
-          uo.x_w_stride = 2 * 4 * esz0;                       // two 4-channel pixels
-          uo.x_h_stride = (long long)(g.W + 8) * 4 * esz0;
+          uo.C = 64 / esz0;
+          uo.x_w_stride = 16;
+          uo.x_h_stride = (long long)(g.W + 8) * 8;
           uo.x_n_stride = uo.x_h_stride * g.H;
           void* pad4 = nullptr;
           size_t pb = (size_t)uo.x_n_stride * g.N + 256;
-          if (!inject_fault("alloc") && cudaMalloc(&pad4, pb) == cudaSuccess) {
+          if (umma_conv_supported(uo) && !inject_fault("alloc") && cudaMalloc(&pad4, pb) == cudaSuccess) {
             Epilogue probe_ep;
             probe_ep.out_dt = DT_F32;
             UmmaLaunch* probe = umma_conv_prepare(uo, pad4, pad4, pad4, probe_ep, p_->status, sms);
@@ -567,6 +569,8 @@ odla_status Builder::emit_fused(const Item& it) {
               uc = uo;
               widened = true;
               overlap = true;
+              wide_c = uo.C;
+              wide_cp = 8 / esz0;
             } else {
               cudaFree(pad4);
             }
@@ -600,13 +604,13 @@ odla_status Builder::emit_fused(const Item& it) {
       int64_t rs = (int64_t)g.R * g.S;
       std::vector<float> w2;
       if (widened) {
-        // [K][R][32]: element el of a widened pixel is input pixel 2q-4+el/4, channel el%4, i.e. filter column el/4-4+pad_l
-        w2.assign((size_t)(K * g.R * 32), 0.f);
+        // [K][R][wide_c]: element el of a widened pixel is input pixel 2q-4+el/cp, channel el%cp, i.e. filter column el/cp-4+pad_l
+        w2.assign((size_t)(K * g.R * wide_c), 0.f);
         for (int64_t r = 0; r < g.R; ++r)
-          for (int el = 0; el < 32; ++el) {
-            int sc = el / 4 - 4 + g.pad_l, c = el % 4;
+          for (int el = 0; el < wide_c; ++el) {
+            int sc = el / wide_cp - 4 + g.pad_l, c = el % wide_cp;
             if (sc < 0 || sc >= g.S || c >= g.C) continue;
-            for (int64_t k = 0; k < K; ++k) w2[(size_t)((k * g.R + r) * 32 + el)] = wf[(size_t)(((r * g.S + sc) * g.C + c) * K + k)];
+            for (int64_t k = 0; k < K; ++k) w2[(size_t)((k * g.R + r) * wide_c + el)] = wf[(size_t)(((r * g.S + sc) * g.C + c) * K + k)];
           }
       } else {
         w2.assign((size_t)(K * rs * Cp), 0.f);
@@ -625,7 +629,7 @@ odla_status Builder::emit_fused(const Item& it) {
         int64_t pixels = (int64_t)g.N * g.H * g.W;
         ConvGeom gg = g;
         bool wide = widened, ov = overlap;
-        double scratch_bytes = ov ? 2.0 * g.N * g.H * (g.W + 8) * 4 * esz : wide ? 2.0 * g.N * g.H * g.Q * 32 * esz : 2.0 * pixels * 32;
+        double scratch_bytes = ov ? 2.0 * g.N * g.H * (g.W + 8) * 8 : wide ? 2.0 * g.N * g.H * g.Q * 32 * esz : 2.0 * pixels * 32;
         add_launch("conv_umma", f.out, flops, bytes + scratch_bytes, [=](cudaStream_t s) {
           int rc = ov ? stem_pad4(esz, x, padded, gg.N, gg.H, gg.W, C0, s)
                       : wide ? stem_widen(esz, x, padded, gg.N, gg.H, gg.W, C0, gg.Q, s) : pad_channels(esz, x, padded, pixels, C0, Cp, s);
