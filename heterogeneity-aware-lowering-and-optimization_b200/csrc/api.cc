@@ -285,7 +285,17 @@ odla_status odla_SetComputationItem(odla_computation c, odla_item_type type, odl
     case ODLA_AGGREGATE_OPS: c->use_graph = value ? *(bool*)value : true; break;
     case ODLA_QUANT_TABLE_SIZE: c->quant_table.resize(value ? (size_t)*(int*)value : 0); break;
     case ODLA_QUANT_TABLE:
-      if (value && !c->quant_table.empty()) memcpy(c->quant_table.data(), value, sizeof(odla_value_quant_info) * c->quant_table.size());
+      // `value` is the first of ODLA_QUANT_TABLE_SIZE records; the value ids are copied so the table need not outlive the call
+      if (value && !c->quant_table.empty()) {
+        memcpy(c->quant_table.data(), value, sizeof(odla_value_quant_info) * c->quant_table.size());
+        for (auto& rec : c->quant_table) {
+          if (!rec.value_id) continue;
+          c->quant_names.emplace_back((const char*)rec.value_id);
+          rec.value_id = (odla_value_id)c->quant_names.back().c_str();
+        }
+        if (c->quant_applied) B2_WARN("ODLA_QUANT_TABLE set after the computation was planned: ignored");
+        c->planned = false;
+      }
       break;
     case ODLA_DYNAMIC_BATCH: case ODLA_MIN_BATCH_SIZE: case ODLA_MAX_BATCH_SIZE: case ODLA_OPT_BATCH_SIZE:
     case ODLA_USE_SIM_MODE: case ODLA_BATCHES_PER_STEP: case ODLA_LOAD_ENGINE_MODE: case ODLA_ENABLE_ENGINE_CACHE:

@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <deque>
 #include <functional>
 #include <map>
 #include <memory>
@@ -143,6 +144,9 @@ struct _odla_computation {
   bool use_graph = true;           // ODLA_AGGREGATE_OPS / ODLA_B200_GRAPH
   int first_device = 0;
   std::vector<odla_value_quant_info> quant_table;
+  std::deque<std::string> quant_names;   // owns the value ids the table's records point to
+  bool quant_applied = false;      // the table has been folded into the graph (quant_table.cc)
+  std::vector<std::unique_ptr<std::vector<uint8_t>>> owned_consts;  // data of constants the library synthesised
   // built lazily at first context / execute
   bool planned = false;
   bool shardable = true;           // dim 0 of every argument/output is an independent batch
@@ -165,6 +169,8 @@ struct _odla_device {
 };
 
 namespace b200 {
+// Rewrites the graph according to comp->quant_table (once).  Defined in quant_table.cc.
+odla_status apply_quant_table(_odla_computation* comp);
 // Builds replicas and plans for `comp` (idempotent).  Defined in plan.cc.
 odla_status ensure_planned(_odla_computation* comp);
 odla_status execute(_odla_computation* comp, _odla_context* ctx);

@@ -1104,6 +1104,7 @@ odla_status ensure_planned(_odla_computation* c) {
     B2_ERR("no CUDA device is visible: libodla_b200 has no CPU fallback");
     return ODLA_FAILURE;
   }
+  if (odla_status qs = apply_quant_table(c)) return qs;
   for (auto& r : c->replicas) {
     cudaSetDevice(r.device);
     r.plan.reset();

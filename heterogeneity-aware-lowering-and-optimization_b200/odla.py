@@ -21,6 +21,7 @@ INT8, INT16, INT32, INT64, UINT8, UINT16, UINT32, UINT64 = range(8)
 FLOAT16, BFLOAT16, FLOAT32, FLOAT64, BOOL = 16, 17, 18, 19, 20
 # odla_item_type
 ITEM_BF16_MODE, ITEM_FP16_MODE, ITEM_PROCESSOR_NUM, ITEM_USE_DATA_TYPE, ITEM_AGGREGATE_OPS = 13, 14, 16, 18, 23
+ITEM_QUANT_TABLE, ITEM_QUANT_TABLE_SIZE = 21, 22
 # odla_memory_layout
 CHANNELS_FIRST, CHANNELS_LAST, SIO, SOI, OIS, IOS = range(6)
 # odla_status
@@ -53,6 +54,11 @@ class ScalarValue(C.Structure):
                     ("f32", C.c_float), ("f64", C.c_double), ("s", C.c_char_p)]
     _anonymous_ = ("u",)
     _fields_ = [("data_type", C.c_int), ("u", _U)]
+
+
+class QuantInfo(C.Structure):
+    """odla_value_quant_info (ODLA/include/ODLA/ops/odla_ops_quantization.h:33-41 in the reference)."""
+    _fields_ = [("value_id", C.c_char_p), ("ch_idx", C.c_int), ("scale", C.c_float), ("offset", C.c_float), ("min", C.c_float), ("max", C.c_float)]
 
 
 class ProfileEntry(C.Structure):
@@ -232,6 +238,30 @@ class Graph:
         self._check(self.lib.SetComputationItem(self.comp, key, C.cast(C.byref(cval), _V)), "odla_SetComputationItem")
         var = "item_%d" % len(self.cc_items)
         self.cc_items.append("  %s %s = %s;\n  odla_SetComputationItem(comp, %s, (odla_item_value)&%s);" % (ctype, var, ctext, key_name, var))
+
+    def set_quant_table(self, records):
+        """Hands a quantisation table to the computation (ODLA_QUANT_TABLE_SIZE, then ODLA_QUANT_TABLE).
+        `records` = [(value_id, ch_idx, scale, offset, min, max), ...] laid out as utils/halo_pgq.py:309-327
+        of the reference writes them: one record per value with ch_idx = -channels, then one per channel."""
+        arr = (QuantInfo * len(records))()
+        for i, (vid, ch, sc, off, mn, mx) in enumerate(records):
+            arr[i] = QuantInfo(self._id(vid), int(ch), float(sc), float(off), float(mn), float(mx))
+        n = C.c_int(len(records))
+        self._keep += [arr, n]
+        self._check(self.lib.SetComputationItem(self.comp, ITEM_QUANT_TABLE_SIZE, C.cast(C.byref(n), _V)), "odla_SetComputationItem")
+        self._check(self.lib.SetComputationItem(self.comp, ITEM_QUANT_TABLE, C.cast(arr, _V)), "odla_SetComputationItem")
+        self.quant_records = list(records)
+        # generated code declares the table the way lib/target/generic_cpp/generic_cxx_codegen.cc:110-116 does
+        self.cc_items.append("  odla_SetComputationItem(comp, ODLA_QUANT_TABLE_SIZE, (odla_item_value)&quant_infos_size);\n"
+                             "  odla_SetComputationItem(comp, ODLA_QUANT_TABLE, (odla_item_value)quant_infos);")
+
+    def emit_quant_table_c(self):
+        """The C file utils/halo_pgq.py:309-333 of the reference writes next to the model."""
+        fmt = '  {.value_id = (const odla_value_id) "%s", .ch_idx = %d, .scale = %r, .offset = %r, .min = %r, .max = %r},'
+        lines = ["#include <ODLA/odla.h>", "const odla_value_quant_info quant_infos[] = {"]
+        lines += [fmt % (v, ch, float(sc), float(off), float(mn), float(mx)) for (v, ch, sc, off, mn, mx) in self.quant_records]
+        lines += ["};", "const int quant_infos_size = %d;" % len(self.quant_records), ""]
+        return "\n".join(lines)
 
     def _id(self, name):
         b = name.encode()
@@ -488,6 +518,8 @@ class Graph:
         sig_out = ", ".join("%s out_%s[%d]" % (_CTYPE[self.dtypes[n]], _cname(n), int(np.prod(self.shapes[n]))) for n in self.out_names)
         out = ["// HALO-style ODLA model (shape of the generic C++ code generator's output)", "#include <ODLA/odla.h>", ""]
         out += self.cc_consts
+        if getattr(self, "quant_records", None):
+            out += ['extern "C" {', "extern const odla_value_quant_info quant_infos[];", "extern const int quant_infos_size;", "}", ""]
         out += ['extern "C" {', "int %s(%s, %s);" % (fn, sig_in, sig_out), "int %s_init();" % fn, "int %s_fini();" % fn,
                 "int %s_helper(odla_computation comp);" % fn, "};", "static odla_computation Comp;",
                 "int %s_helper(odla_computation comp) {" % fn]

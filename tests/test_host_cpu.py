@@ -160,6 +160,22 @@ def test_emitted_resnet50_cc_follows_halo_rules(odla, lib, models):
     assert "static odla_computation Comp;" in text and "odla_BindToArgumentById" in text
 
 
+def test_quant_table_item_and_emission(odla, lib):
+    """ODLA_QUANT_TABLE_SIZE / ODLA_QUANT_TABLE are accepted (the ids are copied, the caller's table may go away)
+    and the emitted model declares the table the way the reference's code generator does."""
+    g = odla.Graph(lib, "qt")
+    x = g.Argument("x", (2, 8, 8, 32))
+    w = g.Constant("w", np.ones((1, 1, 32, 32), np.float32))
+    g.Output(g.Conv(x, odla.CHANNELS_LAST, 1, w, odla.SIO, (1, 1), (1, 1), (0, 0), (0, 0), None, (2, 8, 8, 32), "c"))
+    recs = [("x", -1, 0.0, 0.0, -2.0, 2.0), ("w_", -2, 0.0, 0.0, -1.0, 1.0), ("w_", 0, 0.0, 0.0, -1.0, 0.5), ("w_", 1, 0.0, 0.0, -0.5, 1.0)]
+    g.set_quant_table(recs)
+    cc, tbl = g.emit_cc(), g.emit_quant_table_c()
+    g.close()
+    assert "extern const odla_value_quant_info quant_infos[];" in cc and "extern const int quant_infos_size;" in cc
+    assert cc.index("ODLA_QUANT_TABLE_SIZE") < cc.index("ODLA_QUANT_TABLE, ")      # the size is set before the records
+    assert tbl.count(".value_id") == 4 and "const int quant_infos_size = 4;" in tbl and '"w_", .ch_idx = -2' in tbl
+
+
 def test_two_rank_gloo_timing_helper():
     """bench.py's max-over-ranks aggregation and per-rank sharding, on CPU with gloo."""
     code = r'''

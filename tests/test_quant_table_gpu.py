@@ -1,0 +1,151 @@
+"""Quantisation-table ingestion (ODLA_QUANT_TABLE / ODLA_QUANT_TABLE_SIZE): a float graph plus a table of
+value ranges must run exactly like the hand-written Quantize/Dequantize graph with the same scales."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _scale(mn, mx):
+    a = np.float32(max(abs(np.float32(mn)), abs(np.float32(mx))))
+    return np.float32(a / np.float32(127.0)) if a > 0 else np.float32(1.0)
+
+
+def _small_net(odla, g, w, ranges=None, transpose_fc=False):
+    """conv3x3+bias+relu -> conv1x1+bias + residual -> relu -> mean -> Gemm(+bias).  With `ranges` the
+    Quantize/Dequantize nodes are written out by hand, the way the table rewrite is documented to place them."""
+    NHWC, SIO, F32, I8 = odla.CHANNELS_LAST, odla.SIO, odla.FLOAT32, odla.INT8
+    B, H, C0, C1 = 4, 16, 32, 64
+
+    def q_act(x, name):
+        if ranges is None:
+            return x
+        s = g.Constant(name + "_s", np.array([_scale(*ranges[name])], np.float32))
+        return g.Dequantize(g.Quantize(x, s, None, 0, I8, name + "_q"), s, None, 0, F32, name + "_dq")
+
+    def q_w(name, axis, k_first=False):
+        a = w[name]
+        if ranges is None:
+            return g.Constant(name, a)
+        m = a.reshape(a.shape[0], -1) if k_first else a.reshape(-1, a.shape[-1]).T          # [K, rest]
+        s = np.array([_scale(r.min(initial=0.0), r.max(initial=0.0)) for r in m], np.float32)
+        sb = s.reshape((-1,) + (1,) * (a.ndim - 1)) if k_first else s
+        aq = np.clip(np.rint(a / sb), -127, 127).astype(np.int8)
+        return g.Dequantize(g.Constant(name + "_q", aq), g.Constant(name + "_qs", s), None, axis, F32, name + "_dq")
+
+    x = g.Argument("x", (B, H, H, C0), F32)
+    y = g.Conv(q_act(x, "x"), NHWC, 1, q_w("w1", 3), SIO, (1, 1), (1, 1), (1, 1), (1, 1), None, (B, H, H, C1), "c1")
+    y = g.Relu(g.Add(y, g.Constant("b1", w["b1"]), "c1_b"), "r1")
+    z = g.Conv(q_act(y, "r1"), NHWC, 1, q_w("w2", 3), SIO, (1, 1), (1, 1), (0, 0), (0, 0), None, (B, H, H, C1), "c2")
+    z = g.Relu(g.Add(g.Add(z, g.Constant("b2", w["b2"]), "c2_b"), y, "c2_res"), "r2")
+    p = g.Reshape(g.ReduceMean(z, (1, 2), True, (B, 1, 1, C1), "gap"), (B, C1), "flat")
+    if transpose_fc:
+        out = g.Gemm(q_act(p, "flat"), False, q_w("wfc_t", 0, k_first=True), True, 1.0, 1.0, g.Constant("bfc", w["bfc"]), (B, 10), "fc")
+    else:
+        out = g.Gemm(q_act(p, "flat"), False, q_w("wfc", 1), False, 1.0, 1.0, g.Constant("bfc", w["bfc"]), (B, 10), "fc")
+    g.Output(z)
+    g.Output(out)
+    return g
+
+
+def _weights():
+    rng = np.random.default_rng(5)
+    w = {"w1": rng.standard_normal((3, 3, 32, 64)).astype(np.float32) * 0.06, "b1": rng.standard_normal(64).astype(np.float32) * 0.1,
+         "w2": rng.standard_normal((1, 1, 64, 64)).astype(np.float32) * 0.12, "b2": rng.standard_normal(64).astype(np.float32) * 0.1,
+         "wfc": rng.standard_normal((64, 10)).astype(np.float32) * 0.1, "bfc": rng.standard_normal(10).astype(np.float32) * 0.1}
+    w["wfc_t"] = np.ascontiguousarray(w["wfc"].T)
+    return w, rng.standard_normal((4, 16, 16, 32)).astype(np.float32)
+
+
+@pytest.mark.parametrize("transpose_fc", [False, True])
+def test_table_equals_handwritten_qdq_graph(odla, gpu_lib, ref, transpose_fc):
+    w, x = _weights()
+    ranges = {"x": (-3.1, 2.7), "r1": (0.0, 4.5), "flat": (0.0, 1.9)}     # one range deliberately asymmetric
+    # the table: one tensor record per activation (ch_idx = -channels), as the reference's profiler script writes it
+    records = [(k, -1, 0.0, 0.0, mn, mx) for k, (mn, mx) in ranges.items()]
+    g = _small_net(odla, odla.Graph(gpu_lib, "qt"), w, transpose_fc=transpose_fc)
+    g.set_quant_table(records)
+    got = g.run({"x": x})
+    desc = g.describe()
+    g.close()
+    # the operands were absorbed: both convolutions and the Gemm run on the int8 tensor-core kernel
+    assert desc.count("conv_umma") == 2 and "quantize" in desc
+    h = _small_net(odla, odla.Graph(ref, "qt_ref"), w, ranges=ranges, transpose_fc=transpose_fc)
+    want = h.run({"x": x})
+    h.close()
+    f = _small_net(odla, odla.Graph(ref, "qt_f32"), w, transpose_fc=transpose_fc)
+    flt = f.run({"x": x})
+    f.close()
+    for k in ("r2", "fc"):
+        assert np.array_equal(got[k], want[k]), (k, float(np.abs(got[k] - want[k]).max()))
+        # and int8 really happened: the result differs from the float graph, by quantisation noise only
+        d = float(np.abs(got[k] - flt[k]).max())
+        assert 0 < d < 1.0, (k, d)
+
+
+def test_table_with_per_channel_weight_records_and_direct_scale(odla, gpu_lib, ref):
+    """Weight ranges given per channel in the table override the constant's own ranges; a record with
+    min = max = 0 and a positive scale supplies the scale directly."""
+    w, x = _weights()
+    rng = np.random.default_rng(11)
+    NHWC, SIO, F32, I8 = odla.CHANNELS_LAST, odla.SIO, odla.FLOAT32, odla.INT8
+    sx = np.float32(0.031)
+    ch_rng = [(-float(a), float(a) * 0.5) for a in (np.abs(w["w1"]).reshape(-1, 64).max(0) * rng.uniform(0.6, 1.0, 64))]
+    # a constant's value id is its symbol plus "_" (include/halo/lib/target/generic_cxx/generic_cxx_codegen.h:292-314 in the reference)
+    records = [("x", -1, float(sx), 0.0, 0.0, 0.0), ("w1_", -64, 0.0, 0.0, -1.0, 1.0)] + [("w1_", c, 0.0, 0.0, mn, mx) for c, (mn, mx) in enumerate(ch_rng)]
+
+    def net(g, table):
+        xa = g.Argument("x", (4, 16, 16, 32), F32)
+        if table:
+            xin, win = xa, g.Constant("w1", w["w1"])
+        else:
+            s = g.Constant("x_s", np.array([sx], np.float32))
+            xin = g.Dequantize(g.Quantize(xa, s, None, 0, I8, "x_q"), s, None, 0, F32, "x_dq")
+            sw = np.array([_scale(mn, mx) for mn, mx in ch_rng], np.float32)
+            wq = np.clip(np.rint(w["w1"] / sw), -127, 127).astype(np.int8)     # out-of-range weights saturate
+            win = g.Dequantize(g.Constant("w1_q", wq), g.Constant("w1_s", sw), None, 3, F32, "w1_dq")
+        y = g.Conv(xin, NHWC, 1, win, SIO, (1, 1), (1, 1), (1, 1), (1, 1), None, (4, 16, 16, 64), "c1")
+        g.Output(g.Relu(g.Add(y, g.Constant("b1", w["b1"]), "c1_b"), "r1"))
+        return g
+
+    g = net(odla.Graph(gpu_lib, "qt2"), True)
+    g.set_quant_table(records)
+    got = g.run({"x": x})["r1"]
+    g.close()
+    h = net(odla.Graph(ref, "qt2_ref"), False)
+    want = h.run({"x": x})["r1"]
+    h.close()
+    assert np.array_equal(got, want), float(np.abs(got - want).max())
+
+
+def test_resnet50_float_graph_with_table_runs_int8(odla, gpu_lib, models):
+    """The fp32 ResNet-50 graph plus a table made from the calibration ranges: every convolution and the
+    FC layer run in int8, and the classifier still agrees with the float run."""
+    rn = models.resnet50
+    w = rn.weights()
+    scales = rn.calibrate(w, n_images=8)
+    x = rn.inputs(8)
+    g = odla.Graph(gpu_lib, "resnet50", fp16=True)
+    rn.build(g, 8, w)
+    ref_prob = g.run(x)["prob"]
+    g.close()
+    records = []
+    for name, s in scales.items():
+        if name.endswith("_sc"):
+            continue                     # projection shortcuts feed only the residual additions
+        # the stem's range also holds for the max-pool output, which is what the first block reads
+        vid = {"input": "input", "pool": "flatten", "conv1": "pool1"}.get(name, name + "_relu")
+        a = float(s) * 127.0
+        records.append((vid, -1, 0.0, 0.0, -a, a))
+    g = odla.Graph(gpu_lib, "resnet50_qt", fp16=True)
+    rn.build(g, 8, w)
+    g.set_quant_table(records)
+    prob = g.run(x)["prob"]
+    desc = g.describe()
+    g.close()
+    assert desc.count("_qt_q") + desc.count("quantize") >= 16          # activations are quantised ...
+    assert np.abs(prob - ref_prob).max() < 0.1                            # ... and the result stays close to the float run
+    assert (prob.argmax(1) == ref_prob.argmax(1)).mean() >= 0.75
+    cc = g.emit_cc()
+    assert "extern const odla_value_quant_info quant_infos[];" in cc and "ODLA_QUANT_TABLE_SIZE" in cc
+    assert "quant_infos_size = %d" % len(records) in g.emit_quant_table_c()
