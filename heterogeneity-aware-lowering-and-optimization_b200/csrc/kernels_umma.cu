@@ -69,6 +69,8 @@ struct UmmaParams {
   int ring_boxes;      // boxes in the staging ring (>= stage_boxes)
   int box_arrivals;    // epilogue warps that write into one box
   int epi_interleave;  // groups take every fourth chunk instead of a contiguous run
+  int pair;            // 1: two CTAs of a cluster share each 256-row tile (tcgen05 cta_group::2), each loading half of B
+  int bn_load;         // rows of B this CTA brings into shared memory per k-block (BN, or BN/2 in pair mode)
   int epi_mode;        // kernel variant: 0 direct, 1 staged, 2 staged with the general activation / division
   int tmem_cols;
   void* y;
@@ -172,6 +174,63 @@ __device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t da, uint64_t d
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// ---- CTA-pair (cta_group::2) forms.  Both CTAs of the pair issue their own loads; the byte counts land on
+// the barrier of the pair's first CTA (`bar_cluster` is that barrier's shared::cluster address), whose MMA lane
+// issues for both and signals barriers in both with a multicast commit.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
+               "l"((uint64_t)map), "r"(bar_cluster), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_u32(dst)),
+               "l"((uint64_t)map), "r"(bar_cluster), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+__device__ __forceinline__ void tma_load_im2col_4d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster, int c, int w, int h, int n,
+                                                        uint16_t off_w, uint16_t off_h) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.im2col.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};" ::"r"(
+          smem_u32(dst)),
+      "l"((uint64_t)map), "r"(bar_cluster), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_i8_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrives on the barrier at this offset in both CTAs of the pair once the MMAs issued so far have completed
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(smem_u32(bar)), "h"((uint16_t)3)
+               : "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
   asm volatile(
@@ -534,18 +593,20 @@ __device__ __forceinline__ void epilogue_chunk_staged(const UmmaParams& p, float
 // MODE 0: direct epilogue (any output type, rows written straight to global memory).
 // MODE 1: staged epilogue, activation none / ReLU after the residual, int8 requantisation by multiplication.
 // MODE 2: staged epilogue with every activation, activation before the residual and division requantisation.
-template <int OUT, int MODE>
+// PAIR: CTA-pair variant (its cta_group::2 instructions make the kernel launchable only as clusters of two).
+template <int OUT, int MODE, bool PAIR>
 __global__ void __launch_bounds__(EpiCfg<MODE != 0>::kThreads, 1)
 umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmY,
                  const __grid_constant__ CUtensorMap tmR, const UmmaParams p) {
   constexpr bool STAGED = MODE != 0;
+  constexpr int kPair = PAIR ? 1 : 0;
   constexpr int kEpilogueWarps = EpiCfg<STAGED>::kWarps, kLoaderWarp = EpiCfg<STAGED>::kLoaderWarp, kStorerWarp = EpiCfg<STAGED>::kStorerWarp;
   constexpr int CW = EpiCfg<STAGED>::kChunk;
   extern __shared__ uint8_t smem_raw[];
   if (threadIdx.x == 0) TS(7);
   // operand stages start on a 1024-byte boundary (the 128-byte swizzle repeats every 1024 bytes)
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  const int stage_bytes = p.bps * (BM + p.BN) * p.kb_bytes;
+  const int stage_bytes = p.bps * (BM + p.bn_load) * p.kb_bytes;
   uint8_t* staging = smem + (size_t)p.stages * stage_bytes;   // 1024-byte aligned: stage sizes are multiples of 2 KiB
   uint8_t* ctrl = staging + (size_t)p.ring_boxes * 16384;
   uint64_t* full_bar = (uint64_t*)ctrl;            // [stages]
@@ -561,15 +622,22 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], kEpilogueWarps); }
+    // in pair mode the epilogue warps of both CTAs release an accumulator on the first CTA's barrier
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], (uint32_t)(kEpilogueWarps << kPair)); }
     for (int b = 0; b < kMaxRing; ++b) { mbar_init(&box_full[b], 1); mbar_init(&box_done[b], (uint32_t)p.box_arrivals); mbar_init(&box_free[b], 1); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
+  if constexpr (PAIR) cluster_sync_all();  // the peer's barriers exist before anything of this CTA can reach them
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)p.tmem_cols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if constexpr (PAIR) {  // the same warp of both CTAs allocates the same columns in both tensor memories
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)p.tmem_cols) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)p.tmem_cols) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -581,7 +649,11 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (threadIdx.x == 0) TS(0);
 
-  const uint32_t a_box = (uint32_t)(BM * p.kb_bytes), b_box = (uint32_t)(p.BN * p.kb_bytes);
+  const uint32_t a_box = (uint32_t)(BM * p.kb_bytes), b_box = (uint32_t)(p.bn_load * p.kb_bytes);
+  // Tile walk: a unit (a CTA, or a CTA pair) takes every `tile_step`-th tile; in pair mode a tile is 256 rows and
+  // this CTA owns the half given by its rank in the cluster.
+  const int rank = PAIR ? (int)cluster_ctarank() : 0;
+  const int tile_first = (int)(blockIdx.x >> kPair), tile_step = (int)(gridDim.x >> kPair);
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer ----
     // One lane runs this loop; it is kept free of divisions (filter tap, channel chunk, stage and
@@ -590,8 +662,8 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * p.BN;
+      for (int tile = tile_first; tile < p.total_tiles && ok; tile += tile_step) {
+        const int m0 = (((tile % p.m_tiles) << kPair) + rank) * BM, n0 = (tile / p.m_tiles) * p.BN;
         int w0 = 0, h0 = 0, img = 0;
         if (p.im2col) {
           const int pq = p.P * p.Q;
@@ -610,6 +682,28 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint8_t* sa = smem + (size_t)s * stage_bytes;
           uint8_t* sb = sa + (size_t)p.bps * a_box;
           uint64_t* fb = full_bar + s;
+          if constexpr (PAIR) {
+            // the first CTA's barrier counts the bytes of both CTAs; only it is armed
+            if (rank == 0) mbar_expect_tx(fb, 2u * (uint32_t)nb * (a_box + b_box));
+            const uint32_t fbc = map_to_cta(smem_u32(fb), 0);
+            const int nb0 = n0 + rank * p.bn_load;
+            for (int j = 0; j < nb; ++j) {
+              if (p.im2col) tma_load_im2col_4d_pair(sa, &tmA, fbc, c0, w0, h0, img, (uint16_t)fs, (uint16_t)fr);
+              else tma_load_2d_pair(sa, &tmA, fbc, c0, m0);
+              if (p.rows_per_batch) tma_load_3d_pair(sb, &tmB, fbc, c0, nb0, bidx);
+              else tma_load_3d_pair(sb, &tmB, fbc, c0, tap, nb0);
+              sa += a_box;
+              sb += b_box;
+              c0 += p.kbe;
+              if (c0 >= p.C) {
+                c0 = 0;
+                ++tap;
+                if (++fs == p.S) { fs = 0; ++fr; }
+              }
+            }
+            if (++s == p.stages) { s = 0; ph ^= 1; }
+            continue;
+          }
           mbar_expect_tx(fb, (uint32_t)nb * (a_box + b_box));
           for (int j = 0; j < nb; ++j) {
             if (p.im2col) tma_load_im2col_4d(sa, &tmA, fb, c0, w0, h0, img, (uint16_t)fs, (uint16_t)fr);
@@ -637,14 +731,14 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer ----
-    if (elect_one()) {
+    if (rank == 0 && elect_one()) {  // in pair mode the first CTA's lane issues for both
       int s = 0;
       uint32_t ph = 0, tcount = 0;
       bool ok = true;
       const uint32_t smem_base = smem_u32(smem);
       const uint64_t desc_fixed = ((uint64_t)p.desc_hi << 32) | (1ull << 16);
       const int ksteps = p.kb_bytes >> 5;  // 32 bytes of K per instruction
-      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++tcount) {
+      for (int tile = tile_first; tile < p.total_tiles && ok; tile += tile_step, ++tcount) {
         const uint32_t acc = tcount & 1, acc_ph = (tcount >> 1) & 1;
         if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1, abort_flag, p.status, 2)) { ok = false; break; }
         tc_fence_after();
@@ -661,17 +755,22 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const uint64_t da = desc_fixed | (uint64_t)((sa & 0x3FFFF) >> 4);
             const uint64_t db = desc_fixed | (uint64_t)((sb & 0x3FFFF) >> 4);
             for (int k = 0; k < ksteps; ++k) {
-              if (p.acc_int) umma_i8(tmem_d, da + 2 * k, db + 2 * k, p.idesc, accum);
-              else umma_f16(tmem_d, da + 2 * k, db + 2 * k, p.idesc, accum);
+              if constexpr (PAIR) {
+                if (p.acc_int) umma_i8_pair(tmem_d, da + 2 * k, db + 2 * k, p.idesc, accum);
+                else umma_f16_pair(tmem_d, da + 2 * k, db + 2 * k, p.idesc, accum);
+              } else {
+                if (p.acc_int) umma_i8(tmem_d, da + 2 * k, db + 2 * k, p.idesc, accum);
+                else umma_f16(tmem_d, da + 2 * k, db + 2 * k, p.idesc, accum);
+              }
               accum = 1;
             }
             sa += a_box;
             sb += b_box;
           }
-          umma_commit(empty_bar + s);  // frees the stage once these MMAs have read it
+          if constexpr (PAIR) umma_commit_pair(empty_bar + s); else umma_commit(empty_bar + s);  // frees the stage once these MMAs have read it
           if (++s == p.stages) { s = 0; ph ^= 1; }
         }
-        if (ok) umma_commit(&tfull_bar[acc]);  // accumulator complete
+        if (ok) { if constexpr (PAIR) umma_commit_pair(&tfull_bar[acc]); else umma_commit(&tfull_bar[acc]); }  // accumulator complete
         if (tcount == 0) TS(3);
       }
     }
@@ -682,8 +781,8 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int slot = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * p.BN;
+      for (int tile = tile_first; tile < p.total_tiles && ok; tile += tile_step) {
+        const int m0 = (((tile % p.m_tiles) << kPair) + rank) * BM, n0 = (tile / p.m_tiles) * p.BN;
         for (int bx = 0; bx < p.stage_boxes; ++bx) {
           const int x0 = n0 + bx * cols_per_box;
           if (x0 >= p.K_out) break;
@@ -706,8 +805,8 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int slot = 0, prev = -1;
       uint32_t ph = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * p.BN;
+      for (int tile = tile_first; tile < p.total_tiles && ok; tile += tile_step) {
+        const int m0 = (((tile % p.m_tiles) << kPair) + rank) * BM, n0 = (tile / p.m_tiles) * p.BN;
         for (int bx = 0; bx < p.stage_boxes; ++bx) {
           const int x0 = n0 + bx * cols_per_box;
           if (x0 >= p.K_out) break;
@@ -748,7 +847,7 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int ch_lo = cgroup * per_group, ch_hi = ch_lo + per_group;
       int slot = 0;
       uint32_t ph = 0;
-      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++tcount) {
+      for (int tile = tile_first; tile < p.total_tiles && ok; tile += tile_step, ++tcount) {
         const uint32_t acc = tcount & 1, acc_ph = (tcount >> 1) & 1;
         const int n0 = (tile / p.m_tiles) * p.BN;
         if (!mbar_wait(&tfull_bar[acc], acc_ph, abort_flag, p.status, 4)) { ok = false; break; }
@@ -791,7 +890,7 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+        if (lane == 0) { if (PAIR && rank) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0)); else mbar_arrive(&tempty_bar[acc]); }
         if (tcount == 0 && threadIdx.x == 64) TS(5);
       }
     } else {
@@ -800,9 +899,9 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const bool res_vec = p.ep.res && (p.K_out & 15) == 0 && (p.ep.res_dt == DT_F16 || p.ep.res_dt == DT_BF16 || p.ep.res_dt == DT_S8);
       const int res_q = p.ep.res_dt == DT_S8 ? 2 : 4;       // 16-byte pieces per 32 channels
       const int res_esz = p.ep.res_dt == DT_S8 ? 1 : 2;
-      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++tcount) {
+      for (int tile = tile_first; tile < p.total_tiles && ok; tile += tile_step, ++tcount) {
         const uint32_t acc = tcount & 1, acc_ph = (tcount >> 1) & 1;
-        const int m0 = (tile % p.m_tiles) * BM, n0 = (tile / p.m_tiles) * p.BN;
+        const int m0 = (((tile % p.m_tiles) << kPair) + rank) * BM, n0 = (tile / p.m_tiles) * p.BN;
         const int64_t row = (int64_t)m0 + r_in_tile;
         uint4 pre[kChunksPerWarp][4] = {};
         bool pre_ok[kChunksPerWarp] = {};
@@ -848,7 +947,7 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+        if (lane == 0) { if (PAIR && rank) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0)); else mbar_arrive(&tempty_bar[acc]); }
       }
     }
   }
@@ -856,9 +955,11 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0) TS(6);
+  if constexpr (PAIR) cluster_sync_all();  // neither CTA leaves (or frees tensor memory) while the other may still signal it
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols) : "memory");
+    if constexpr (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols) : "memory");
   }
 }
 
@@ -925,9 +1026,26 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
   p.m_tiles = (p.M_total + BM - 1) / BM;
   p.n_tiles = (c.K + p.BN - 1) / p.BN;
   p.total_tiles = p.m_tiles * p.n_tiles;
+  // CTA pairs (tcgen05 cta_group::2): a pair computes 256 rows x BN columns and each CTA loads only half of the
+  // filter tile.  That pays where operand traffic into shared memory is the limit -- two-byte operands and a long
+  // reduction (measured: 16 or more k-blocks) -- and costs where the epilogue is, because the pair's CTAs then wait
+  // for each other's accumulators.  Needs whole 256-row tiles and an even grid.
+  {
+    // (the thresholds can be moved through the environment, which the tests use to run every shape on pairs)
+    const int pair_min_bn = getenv("ODLA_B200_PAIR_MIN_BN") ? atoi(getenv("ODLA_B200_PAIR_MIN_BN")) : 128;
+    const int pair_min_kb = getenv("ODLA_B200_PAIR_MIN_KB") ? atoi(getenv("ODLA_B200_PAIR_MIN_KB")) : 16;
+    const bool pair_s8 = getenv("ODLA_B200_PAIR_S8") != nullptr;
+    p.pair = ((c.in_dt != DT_S8 || pair_s8) && p.BN >= pair_min_bn && p.num_kb >= pair_min_kb && p.M_total % (2 * BM) == 0 && sms >= 2 &&
+              c.w_batches == 0) ? 1 : 0;
+    p.bn_load = p.pair ? p.BN / 2 : p.BN;
+    if (p.pair) {
+      p.m_tiles = p.M_total / (2 * BM);
+      p.total_tiles = p.m_tiles * p.n_tiles;
+    }
+  }
   // Several k-blocks share one pipeline stage (one mbarrier round trip) when they are small: up to
   // 48 KB per stage, balanced over the tile's k-blocks.
-  const int box_bytes = (BM + p.BN) * p.kb_bytes;
+  const int box_bytes = (BM + p.bn_load) * p.kb_bytes;
   int bps_max = (48 * 1024) / box_bytes;
   if (bps_max < 1) bps_max = 1;
   if (bps_max > 8) bps_max = 8;
@@ -968,7 +1086,7 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
     p.box_arrivals = 4 * (groups_per_box < 1 ? 1 : groups_per_box);
     // Contiguous runs let the groups work on different boxes at once, which pays when boxes need no residual and
     // the CTA has many tiles to stream through; otherwise finishing box after box gets the first store out sooner.
-    p.epi_interleave = ep.res != nullptr || p.total_tiles < 16 * sms;
+    p.epi_interleave = ep.res != nullptr || (p.total_tiles << p.pair) < 16 * sms;
     if (getenv("ODLA_B200_EPI_INTERLEAVE")) p.epi_interleave = atoi(getenv("ODLA_B200_EPI_INTERLEAVE"));
     if (p.epi_interleave) p.box_arrivals = 16;
   }
@@ -981,12 +1099,12 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
   p.tmem_cols = 2 * p.BN;  // 128, 256 or 512: powers of two >= 32
   const uint32_t fmt = c.in_dt == DT_BF16 ? 1u : (c.in_dt == DT_S8 ? 1u : 0u);      // bf16 / signed 8-bit / f16
   const uint32_t cfmt = p.acc_int ? 2u : 1u;                                        // s32 / f32 accumulators
-  p.idesc = (cfmt << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(p.BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+  p.idesc = (cfmt << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(p.BN >> 3) << 17) | ((uint32_t)((BM << p.pair) >> 4) << 24);
   const uint32_t layout = p.kb_bytes == 128 ? 2u : (p.kb_bytes == 64 ? 4u : 6u);    // swizzle mode of the operand tiles
   const uint32_t sbo = (uint32_t)(8 * p.kb_bytes) >> 4;                             // 8-row group pitch, 16-byte units
   p.desc_hi = sbo | (1u << 14) | (layout << 29);                                    // bits 32-45 SBO, 46-47 version 1, 61-63 layout
   p.y = y; p.status = status; p.ep = ep;
-  L->grid = p.total_tiles < sms ? p.total_tiles : sms;
+  L->grid = p.pair ? (2 * p.total_tiles < (sms & ~1) ? 2 * p.total_tiles : (sms & ~1)) : (p.total_tiles < sms ? p.total_tiles : sms);
   L->smem = (size_t)p.stages * stage_bytes + (size_t)p.ring_boxes * 16384 + 1024 /*alignment slack*/ + 1024 /*barriers*/;
   if (L->smem > 227 * 1024) { delete L; return nullptr; }
 
@@ -1030,7 +1148,7 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
   {
     cuuint64_t dims[3] = {(cuuint64_t)c.C, (cuuint64_t)(c.R * c.S), (cuuint64_t)c.K};
     cuuint64_t strides[2] = {(cuuint64_t)c.C * es, (cuuint64_t)c.R * c.S * c.C * es};
-    cuuint32_t box[3] = {(cuuint32_t)p.kbe, 1, (cuuint32_t)p.BN};
+    cuuint32_t box[3] = {(cuuint32_t)p.kbe, 1, (cuuint32_t)p.bn_load};
     if (c.w_batches > 0) {  // [batches][K][C]: the box spans BN rows of one matrix
       dims[1] = (cuuint64_t)c.K; dims[2] = (cuuint64_t)c.w_batches;
       strides[1] = (cuuint64_t)c.K * c.C * es;
@@ -1060,7 +1178,9 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 16 && !attr_set[dev]) {
-#define B2_SMEM(O, M) (cudaFuncSetAttribute(umma_conv_kernel<O, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess)
+#define B2_SMEM(O, M)                                                                                                              \
+  (cudaFuncSetAttribute(umma_conv_kernel<O, M, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess && \
+   cudaFuncSetAttribute(umma_conv_kernel<O, M, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess)
     bool ok = B2_SMEM(DT_F16, 1) && B2_SMEM(DT_BF16, 1) && B2_SMEM(DT_S8, 1) && B2_SMEM(DT_F16, 2) && B2_SMEM(DT_BF16, 2) && B2_SMEM(DT_S8, 2) && B2_SMEM(-1, 0);
 #undef B2_SMEM
     if (!ok) { cudaGetLastError(); delete L; return nullptr; }
@@ -1078,14 +1198,27 @@ int umma_conv_run(UmmaLaunch* L, cudaStream_t stream) {
   cfg.blockDim = dim3(p.staged ? EpiCfg<true>::kThreads : EpiCfg<false>::kThreads);
   cfg.dynamicSmemBytes = L->smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
   static const bool pdl = !getenv("ODLA_B200_NO_PDL");
+  int na = 0;
+  if (pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (p.pair) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 2;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
+  cfg.numAttrs = na;
   cudaError_t le;
-#define B2_LAUNCH(O, M) le = cudaLaunchKernelEx(&cfg, umma_conv_kernel<O, M>, L->tmA, L->tmB, L->tmY, L->tmR, p)
+#define B2_LAUNCH(O, M)                                                                                   \
+  le = p.pair ? cudaLaunchKernelEx(&cfg, umma_conv_kernel<O, M, true>, L->tmA, L->tmB, L->tmY, L->tmR, p) \
+              : cudaLaunchKernelEx(&cfg, umma_conv_kernel<O, M, false>, L->tmA, L->tmB, L->tmY, L->tmR, p)
   if (p.epi_mode == 0) B2_LAUNCH(-1, 0);
   else if (p.epi_mode == 1) { if (p.ep.out_dt == DT_F16) B2_LAUNCH(DT_F16, 1); else if (p.ep.out_dt == DT_BF16) B2_LAUNCH(DT_BF16, 1); else B2_LAUNCH(DT_S8, 1); }
   else { if (p.ep.out_dt == DT_F16) B2_LAUNCH(DT_F16, 2); else if (p.ep.out_dt == DT_BF16) B2_LAUNCH(DT_BF16, 2); else B2_LAUNCH(DT_S8, 2); }

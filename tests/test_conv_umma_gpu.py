@@ -28,7 +28,25 @@ SHAPES = [  # N, H, W, C, K, R, stride, pad
     (2, 14, 14, 64, 64, 3, 1, 1), (1, 7, 7, 512, 512, 3, 1, 1), (3, 28, 28, 128, 128, 3, 2, 1), (2, 56, 56, 64, 256, 1, 1, 0),
     (2, 28, 28, 256, 512, 1, 2, 0), (1, 9, 11, 32, 40, 3, 1, 1), (2, 5, 5, 16, 8, 3, 1, 1), (1, 13, 13, 24, 255, 1, 1, 0),
     (1, 1, 300, 72, 10, 1, 1, 0), (5, 7, 7, 160, 96, 3, 2, 1), (1, 17, 17, 64, 64, 5, 1, 2), (4, 8, 8, 200, 130, 1, 1, 0),
+    # whole 256-row tiles with more than 128 output channels: the CTA-pair (cta_group::2) path, one and several tiles per pair,
+    # and a last column tile whose second half lies entirely past K
+    (4, 16, 16, 128, 512, 3, 1, 1), (2, 16, 8, 64, 256, 1, 1, 0), (8, 16, 16, 96, 384, 3, 2, 1), (64, 16, 16, 64, 256, 1, 1, 0),
+    (4, 8, 8, 64, 64, 3, 1, 1), (16, 8, 8, 256, 128, 1, 1, 0),
 ]
+
+
+@pytest.fixture
+def every_layer_on_pairs(monkeypatch):
+    """Lowers the CTA-pair thresholds so that every shape with whole 256-row tiles takes the cta_group::2 kernel."""
+    monkeypatch.setenv("ODLA_B200_PAIR_MIN_BN", "64")
+    monkeypatch.setenv("ODLA_B200_PAIR_MIN_KB", "1")
+    monkeypatch.setenv("ODLA_B200_PAIR_S8", "1")
+
+
+@pytest.mark.parametrize("shape", [s for s in SHAPES if (s[0] * ((s[1] + 2 * s[7] - s[5]) // s[6] + 1) * ((s[2] + 2 * s[7] - s[5]) // s[6] + 1)) % 256 == 0])
+@pytest.mark.parametrize("dtype", ["f16", "s8"])
+def test_conv_umma_on_cta_pairs(odla, gpu_lib, shape, dtype, every_layer_on_pairs):
+    test_conv_umma_matches_numpy(odla, gpu_lib, shape, dtype)
 
 
 @pytest.mark.parametrize("shape", SHAPES)
@@ -61,9 +79,10 @@ def test_conv_umma_matches_numpy(odla, gpu_lib, shape, dtype):
     np.testing.assert_allclose(y.cpu().numpy(), want, rtol=0, atol=2e-3)   # fp32 accumulation of exact products
 
 
+@pytest.mark.parametrize("dims", [(3, 14, 128, 96), (4, 16, 128, 256)])   # the second has whole 256-row tiles: CTA pairs
 @pytest.mark.parametrize("multiply", [0, 1])
-def test_conv_umma_int8_requant_epilogue_is_bit_exact(odla, gpu_lib, multiply):
-    N, H, Cc, K = 3, 14, 128, 96
+def test_conv_umma_int8_requant_epilogue_is_bit_exact(odla, gpu_lib, multiply, dims, every_layer_on_pairs):
+    N, H, Cc, K = dims
     rng = np.random.default_rng(9)
     x = rng.integers(-128, 128, (N, H, H, Cc), dtype=np.int8)
     w = rng.integers(-127, 128, (K, 9 * Cc), dtype=np.int8)
