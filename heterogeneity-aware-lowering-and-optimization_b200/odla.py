@@ -481,11 +481,18 @@ class Graph:
     def launches(self):
         return int(self.lib.b200_LastExecuteLaunches(self.context()))
 
-    def describe(self):
+    def describe(self, first_gpu_only=False):
+        """The launch list of every replica ("gpu <d> rows [a,b) ..." header, then one line per launch), or of the
+        first replica only -- the lists are identical up to the batch shard."""
         need = self.lib.b200_DescribePlan(self.comp, None, 0)
         buf = C.create_string_buffer(max(need, 1))
         self.lib.b200_DescribePlan(self.comp, buf, need)
-        return buf.value.decode()
+        text = buf.value.decode()
+        if first_gpu_only:
+            second = text.find("\ngpu ", 1)
+            if second >= 0:
+                text = text[:second + 1]
+        return text
 
     def profile(self, runs=1):
         ctx = self.context()

@@ -46,7 +46,7 @@ def check_block(odla, lib, ref, mode, batch, hw, cin, cout, k=3, stride=1, seed=
         ins = build_block(odla, g, "int8" if mode == "int8" else "fp", batch, hw, cin, cout, k, stride, seed, act)
         outs.append(g.run(ins)["y"])
         if L is lib:
-            desc = g.describe()
+            desc = g.describe(first_gpu_only=True)
         g.close()
     if expect_op is not None:
         assert expect_op in desc, "expected a %s launch, plan was:\n%s" % (expect_op, desc)

@@ -60,7 +60,7 @@ def test_resnet50_half_precision_within_tolerance(odla, gpu_lib, models, rn_weig
     g = odla.Graph(gpu_lib, "resnet50", fp16=(mode == "fp16"), bf16=(mode == "bf16"))
     models.resnet50.build(g, 2, rn_weights)
     got = g.run(x)["prob"]
-    desc = g.describe()
+    desc = g.describe(first_gpu_only=True)
     g.close()
     assert desc.count("conv_umma") >= 52               # everything but (at most) the 3-channel stem runs on the tensor cores
     assert np.abs(got - prob).max() <= 1e-2            # max-abs 1e-2 against the fp32 reference
@@ -83,7 +83,7 @@ def test_resnet50_int8_is_bit_exact(odla, gpu_lib, ref, models, rn_weights):
         rn.build_int8(g, 2, rn_weights, wq, scales, extra_outputs=taps)
         outs.append(g.run(x))
         if L is gpu_lib:
-            desc = g.describe()
+            desc = g.describe(first_gpu_only=True)
         g.close()
     got, want = outs
     assert desc.count("conv_umma") >= 52 and "gemm_umma" in desc
@@ -122,7 +122,7 @@ def _run_pair(odla, gpu_lib, ref, build, inputs, **gpu_mode):
         g = odla.Graph(L, "m", **(gpu_mode if L is gpu_lib else {}))
         build(g)
         outs.append(g.run(inputs))
-        desc = g.describe() if L is gpu_lib else None
+        desc = g.describe(first_gpu_only=True) if L is gpu_lib else None
         if L is gpu_lib:
             d = desc
         g.close()

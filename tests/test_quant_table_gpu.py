@@ -66,7 +66,7 @@ def test_table_equals_handwritten_qdq_graph(odla, gpu_lib, ref, transpose_fc):
     g = _small_net(odla, odla.Graph(gpu_lib, "qt"), w, transpose_fc=transpose_fc)
     g.set_quant_table(records)
     got = g.run({"x": x})
-    desc = g.describe()
+    desc = g.describe(first_gpu_only=True)
     g.close()
     # the operands were absorbed: both convolutions and the Gemm run on the int8 tensor-core kernel
     assert desc.count("conv_umma") == 2 and "quantize" in desc
@@ -141,7 +141,7 @@ def test_resnet50_float_graph_with_table_runs_int8(odla, gpu_lib, models):
     rn.build(g, 8, w)
     g.set_quant_table(records)
     prob = g.run(x)["prob"]
-    desc = g.describe()
+    desc = g.describe(first_gpu_only=True)
     g.close()
     assert desc.count("_qt_q") + desc.count("quantize") >= 16          # activations are quantised ...
     assert np.abs(prob - ref_prob).max() < 0.1                            # ... and the result stays close to the float run
