@@ -143,6 +143,7 @@ struct _odla_computation {
   int n_gpus = 0;                  // ODLA_PROCESSOR_NUM; 0 = all visible
   bool use_graph = true;           // ODLA_AGGREGATE_OPS / ODLA_B200_GRAPH
   int first_device = 0;
+  int sub_batches = 0;             // ODLA_BATCHES_PER_STEP: replicas per GPU; 0 = environment / 1
   std::vector<odla_value_quant_info> quant_table;
   std::deque<std::string> quant_names;   // owns the value ids the table's records point to
   bool quant_applied = false;      // the table has been folded into the graph (quant_table.cc)

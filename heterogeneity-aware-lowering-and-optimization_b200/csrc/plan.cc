@@ -1119,11 +1119,18 @@ odla_status ensure_planned(_odla_computation* c) {
   int want = c->n_gpus > 0 ? c->n_gpus : visible;
   int G = c->shardable ? (int)std::min<int64_t>(std::min(want, visible), std::max<int64_t>(B, 1)) : 1;
   if (G < 1) G = 1;
+  // Sub-batches: S replicas per GPU, each with its own stream, so that one sub-batch's host-to-device copy runs
+  // under another's kernels (the call stays synchronous).  Pays when inputs are bound as host pointers.
+  int S = c->sub_batches > 0 ? c->sub_batches : (getenv("ODLA_B200_SUBBATCHES") ? atoi(getenv("ODLA_B200_SUBBATCHES")) : 1);
+  if (!c->shardable || S < 1) S = 1;
+  while (S > 1 && (int64_t)G * S > B) --S;
+  const int devices = G;
+  G *= S;
   c->replicas.resize((size_t)G);
   int64_t start = 0;
   for (int i = 0; i < G; ++i) {
     Replica& r = c->replicas[i];
-    r.device = (c->first_device + i) % visible;
+    r.device = (c->first_device + i / S) % visible;
     r.shard_batch = c->shardable ? B / G + (i < B % G ? 1 : 0) : B;
     r.shard_start = start;
     start += r.shard_batch;
@@ -1143,9 +1150,10 @@ odla_status ensure_planned(_odla_computation* c) {
             (long long)(r.shard_start + r.shard_batch), r.plan->launches.size(), r.plan->arena_bytes / 1048576.0, r.plan->const_bytes / 1048576.0);
   }
   // peer access between every pair, for device-resident outputs gathered over NVLink
+  (void)devices;
   for (int i = 0; i < G; ++i)
     for (int j = 0; j < G; ++j) {
-      if (i == j) continue;
+      if (i == j || c->replicas[i].device == c->replicas[j].device) continue;
       int can = 0;
       cudaDeviceCanAccessPeer(&can, c->replicas[i].device, c->replicas[j].device);
       if (can) { cudaSetDevice(c->replicas[i].device); cudaError_t e = cudaDeviceEnablePeerAccess(c->replicas[j].device, 0); if (e != cudaSuccess) cudaGetLastError(); }

@@ -22,6 +22,7 @@ FLOAT16, BFLOAT16, FLOAT32, FLOAT64, BOOL = 16, 17, 18, 19, 20
 # odla_item_type
 ITEM_BF16_MODE, ITEM_FP16_MODE, ITEM_PROCESSOR_NUM, ITEM_USE_DATA_TYPE, ITEM_AGGREGATE_OPS = 13, 14, 16, 18, 23
 ITEM_QUANT_TABLE, ITEM_QUANT_TABLE_SIZE = 21, 22
+ITEM_BATCHES_PER_STEP = 17
 # odla_memory_layout
 CHANNELS_FIRST, CHANNELS_LAST, SIO, SOI, OIS, IOS = range(6)
 # odla_status
@@ -208,7 +209,7 @@ def _cname(name):
 class Graph:
     """One ODLA computation under construction.  Methods are named after the ODLA builders."""
 
-    def __init__(self, lib, name="model", fp16=False, bf16=False, n_gpus=None, use_graph=None):
+    def __init__(self, lib, name="model", fp16=False, bf16=False, n_gpus=None, use_graph=None, sub_batches=None):
         self.lib, self.name = lib, name
         self._keep = []            # numpy constants and name strings must outlive the computation
         self.shapes, self.dtypes = {}, {}
@@ -226,6 +227,8 @@ class Graph:
             self._item(ITEM_PROCESSOR_NUM, C.c_int(n_gpus), "ODLA_PROCESSOR_NUM", "int", str(n_gpus))
         if use_graph is not None:
             self._item(ITEM_AGGREGATE_OPS, C.c_bool(use_graph), "ODLA_AGGREGATE_OPS", "bool", "true" if use_graph else "false")
+        if sub_batches is not None:
+            self._item(ITEM_BATCHES_PER_STEP, C.c_int(sub_batches), "ODLA_BATCHES_PER_STEP", "int", str(sub_batches))
 
     # ---- helpers ----
     @staticmethod

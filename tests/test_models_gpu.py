@@ -259,3 +259,21 @@ def test_batch_is_sharded_over_every_visible_gpu(odla, gpu_lib, ref, models):
         g.close()
         assert np.abs(got - want).max() < 1e-5
         assert desc.count("gpu ") == min(want_gpus, n, 11)
+
+
+def test_sub_batches_pipeline_one_gpu(odla, gpu_lib, models, rn_weights):
+    """ODLA_BATCHES_PER_STEP = S gives every GPU S replicas (own stream and arena) so that copies of one
+    sub-batch overlap kernels of another; an image's result does not depend on how the batch was cut."""
+    rn = models.resnet50
+    x = rn.inputs(6)
+    outs, descs = [], []
+    for s in (1, 2, 4, 16):
+        g = odla.Graph(gpu_lib, "resnet50", fp16=True, n_gpus=1, sub_batches=s)
+        rn.build(g, 6, rn_weights)
+        outs.append(g.run(x)["prob"])
+        descs.append(g.describe())
+        g.close()
+    assert [d.count("gpu ") for d in descs] == [1, 2, 4, 6]        # never more sub-batches than images
+    assert "rows [0,3)" in descs[1] and "rows [3,6)" in descs[1] and "rows [4,5)" in descs[2]
+    for o in outs[1:]:
+        assert np.array_equal(o, outs[0])
