@@ -32,6 +32,8 @@ SHAPES = [  # N, H, W, C, K, R, stride, pad
     # and a last column tile whose second half lies entirely past K
     (4, 16, 16, 128, 512, 3, 1, 1), (2, 16, 8, 64, 256, 1, 1, 0), (8, 16, 16, 96, 384, 3, 2, 1), (64, 16, 16, 64, 256, 1, 1, 0),
     (4, 8, 8, 64, 64, 3, 1, 1), (16, 8, 8, 256, 128, 1, 1, 0),
+    # a few whole output rows fill a tile: rectangular tiles fed by tiled 4-d loads (stride 1 and 2, 3x3 and strided 1x1, 108..128 rows)
+    (2, 56, 56, 64, 64, 3, 1, 1), (2, 28, 28, 128, 128, 3, 1, 1), (2, 56, 56, 64, 128, 3, 2, 1), (2, 56, 56, 256, 512, 1, 2, 0), (2, 36, 36, 64, 64, 3, 1, 1),
 ]
 
 
