@@ -332,6 +332,104 @@ def run_b200(args, rank, world, local_rank):
             "int8": int8, "cpu_baseline": cpu, "check": {"top1_of_first_image": top1}}))
 
 
+
+def run_secondary(args, rank, world, local_rank):
+    """The other BASELINE configurations (YOLOv3-416, BERT-base S=128) through the same path and timing
+    method as the ResNet-50 line: fp16 storage, device-resident `value`, host-bound `e2e`, tensor-core roofline."""
+    import torch
+    pkg = importlib.import_module(PKG)
+    odla = pkg.odla
+    os.environ["ODLA_B200_DEVICE"] = str(local_rank)
+    os.environ["ODLA_B200_NUM_GPUS"] = "1"
+    torch.cuda.set_device(local_rank)
+    lib = pkg.load()
+    if lib.b200_DeviceCount() < 1:
+        raise RuntimeError("bench.py needs a CUDA device: libodla_b200 has no CPU fallback")
+    if args.workload == "yolov3":
+        m = importlib.import_module(PKG + ".halo_models.yolov3")
+        batch = args.batch if args.batch != BATCH else 16
+        w = m.weights()
+        x_np = m.inputs(batch)
+        build = lambda g: m.build(g, batch, w)
+        unit, metric, mac, name = "img/s", "yolov3_416_inference_throughput", m.MAC_PER_IMAGE_416, "yolov3_416_nhwc_fp16_b%d" % batch
+    else:
+        m = importlib.import_module(PKG + ".halo_models.bert")
+        batch = args.batch if args.batch != BATCH else 64
+        w = m.weights(m.BASE)
+        x_np = m.inputs(m.BASE, batch)
+        build = lambda g: m.build(g, batch, m.BASE, w)
+        unit, metric, mac, name = "seq/s", "bert_base_s128_encoder_throughput", m.MAC_PER_SEQUENCE_BASE, "bert_base_s128_fp16_b%d" % batch
+    g = odla.Graph(lib, args.workload, fp16=True, n_gpus=1)
+    build(g)
+    g.context()
+    g_host = odla.Graph(lib, args.workload + "_host", fp16=True, n_gpus=1, sub_batches=args.sub_batches)
+    build(g_host)
+    g_host.context()
+    x_host = {k: torch.from_numpy(v).pin_memory() for k, v in x_np.items()}
+    x_dev = {k: v.cuda() for k, v in x_host.items()}
+    np_dt = {odla.FLOAT32: torch.float32, odla.FLOAT16: torch.float16, odla.INT32: torch.int32, odla.INT8: torch.int8}
+    y_host = {n: torch.empty(g.shapes[n], dtype=np_dt[g.dtypes[n]]).pin_memory() for n in g.out_names}
+    y_dev = {n: torch.empty(g.shapes[n], dtype=np_dt[g.dtypes[n]], device="cuda") for n in g.out_names}
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    h2d = sum(v.numel() * v.element_size() for v in x_host.values())
+    d2h = sum(v.numel() * v.element_size() for v in y_host.values())
+
+    def timed(gg, xs, ys, sampler=None):
+        for k, v in xs.items():
+            gg.bind_input(k, v.data_ptr())
+        for k, v in ys.items():
+            gg.bind_output(k, v.data_ptr())
+
+        def step():
+            flush.zero_()
+            torch.cuda.synchronize()
+            if gg.execute() != 0:
+                raise RuntimeError("odla_ExecuteComputation failed")
+            return gg.device_ms()
+        for _ in range(args.warmup):
+            step()
+        barrier()
+        if sampler:
+            sampler.start()
+        ms = sum(step() for _ in range(args.steps))
+        barrier()
+        return max_over_ranks(ms)
+
+    sampler = ClockSampler(local_rank)
+    dev_ms = timed(g, x_dev, y_dev, sampler)
+    clocks = sampler.summary()
+    launches = g.launches() * args.steps
+    e2e_ms = timed(g_host, x_host, y_host)
+    total = sum_over_ranks(batch * args.steps)
+    prof = g.profile(runs=2)
+    tc = [q for q in prof if q["op"].endswith("_umma")]
+    tc_ms, tc_flops = sum(q["ms"] for q in tc), sum(q["flops"] for q in tc)
+    all_ms = sum(q["ms"] for q in prof)
+    peaks, peak_kind = measured_peaks()
+    peak = float(peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops")))
+    achieved = tc_flops / (tc_ms * 1e-3) / 1e12 if tc_ms else 0.0
+    fam = {}
+    for q in prof:
+        f = fam.setdefault(q["op"], {"launches": 0, "ms": 0.0})
+        f["launches"] += 1
+        f["ms"] = round(f["ms"] + q["ms"], 4)
+    if rank == 0:
+        print(json.dumps({
+            "metric": metric, "value": total / (dev_ms / 1e3), "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": name, "batch_per_gpu": batch, "l2": "256 MiB buffer written between steps", "parallelism": "dp%d" % world,
+                       "work_per_unit_gflop": 2 * mac / 1e9},
+            "e2e": {"value": total / (e2e_ms / 1e3), "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps,
+                    "sub_batches": args.sub_batches},
+            "gpu_launches": launches, "clocks": clocks,
+            "roofline": {"bound": "tensor", "kernel": "umma_conv_kernel (%d launches per step)" % len(tc), "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                         "frac": achieved / peak if peak else None, "peak_source": peak_kind + " bf16 sustained", "share_of_step": tc_ms / max(all_ms, 1e-9),
+                         "traffic": None},
+            "kernel_families_ms_per_step": dict(sorted(fam.items(), key=lambda kv: -kv[1]["ms"])),
+            "cpu_baseline": None}))
+    g.close()
+    g_host.close()
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -340,6 +438,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-int8", action="store_true", help="skip the secondary int8 measurement")
+    ap.add_argument("--workload", default="resnet50", choices=["resnet50", "yolov3", "bert"],
+                    help="resnet50 is the benchmark line; yolov3 (B=16) and bert (B=64) are the secondary BASELINE configurations")
     ap.add_argument("--sub-batches", type=int, default=2, help="ODLA_BATCHES_PER_STEP of the end-to-end (host-bound) leg; 1 = off")
     ap.add_argument("--batch", type=int, default=BATCH, help="images per GPU per step (256 = the benchmark configuration; smaller values are for profiling)")
     args = ap.parse_args()
@@ -354,7 +454,10 @@ def main():
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     try:
-        run_b200(args, rank, world, local_rank)
+        if args.workload == "resnet50":
+            run_b200(args, rank, world, local_rank)
+        else:
+            run_secondary(args, rank, world, local_rank)
     finally:
         d = _dist()
         if d is not None:

@@ -301,6 +301,127 @@ __global__ void softmax_rows_kernel(int dt, const void* x, void* y, int64_t rows
     }
   }
 }
+// Two-byte rows of at most 8*32*NP elements, one warp per row: every lane keeps its 16-byte pieces (8 elements each)
+// in registers, so a row is read once and written once.  T is __half or __nv_bfloat16.
+template <typename T> __device__ __forceinline__ float2 pair_to_float2(uint32_t u);
+template <> __device__ __forceinline__ float2 pair_to_float2<__half>(uint32_t u) { return __half22float2(*(const __half2*)&u); }
+template <> __device__ __forceinline__ float2 pair_to_float2<__nv_bfloat16>(uint32_t u) { return __bfloat1622float2(*(const __nv_bfloat162*)&u); }
+template <typename T> __device__ __forceinline__ uint32_t float2_to_pair(float a, float b);
+template <> __device__ __forceinline__ uint32_t float2_to_pair<__half>(float a, float b) { __half2 h = __floats2half2_rn(a, b); return *(uint32_t*)&h; }
+template <> __device__ __forceinline__ uint32_t float2_to_pair<__nv_bfloat16>(float a, float b) { __nv_bfloat162 h = __floats2bfloat162_rn(a, b); return *(uint32_t*)&h; }
+template <typename T, int NP>
+__device__ __forceinline__ void load_row_pieces(const uint4* row, int pieces, int lane, float (&v)[NP][8], bool (&have)[NP]) {
+#pragma unroll
+  for (int i = 0; i < NP; ++i) {
+    const int pc = lane + 32 * i;
+    have[i] = pc < pieces;
+    if (have[i]) {
+      const uint4 u = row[pc];
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int t = 0; t < 4; ++t) { float2 f = pair_to_float2<T>(w[t]); v[i][2 * t] = f.x; v[i][2 * t + 1] = f.y; }
+    }
+  }
+}
+template <typename T, int NP>
+__global__ void softmax_rows_vec_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, int64_t rows, int pieces, int log_form) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t row = warp; row < rows; row += nwarps) {
+    float v[NP][8];
+    bool have[NP];
+    load_row_pieces<T, NP>(x + row * pieces, pieces, lane, v, have);
+    float mx = -3.402823466e+38f;
+#pragma unroll
+    for (int i = 0; i < NP; ++i)
+      if (have[i]) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) mx = fmaxf(mx, v[i][j]);
+      }
+    mx = warp_max(mx);
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < NP; ++i)
+      if (have[i]) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { v[i][j] -= mx; sum += expf(v[i][j]); }
+      }
+    sum = warp_sum(sum);
+    const float lsum = logf(sum);
+#pragma unroll
+    for (int i = 0; i < NP; ++i)
+      if (have[i]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float a = log_form ? v[i][2 * t] - lsum : __fdiv_rn(expf(v[i][2 * t]), sum);
+          const float b = log_form ? v[i][2 * t + 1] - lsum : __fdiv_rn(expf(v[i][2 * t + 1]), sum);
+          w[t] = float2_to_pair<T>(a, b);
+        }
+        y[row * pieces + lane + 32 * i] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+  }
+}
+template <typename T, int NP>
+__global__ void layernorm_rows_vec_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, const float* __restrict__ gamma, const float* __restrict__ beta,
+                                          int64_t rows, int pieces, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const float dim = (float)(pieces * 8);
+  for (int64_t row = warp; row < rows; row += nwarps) {
+    float v[NP][8];
+    bool have[NP];
+    load_row_pieces<T, NP>(x + row * pieces, pieces, lane, v, have);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < NP; ++i)
+      if (have[i]) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s += v[i][j];
+      }
+    const float mean = warp_sum(s) / dim;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < NP; ++i)
+      if (have[i]) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { v[i][j] -= mean; q += v[i][j] * v[i][j]; }
+      }
+    const float inv = 1.0f / sqrtf(warp_sum(q) / dim + eps);
+#pragma unroll
+    for (int i = 0; i < NP; ++i)
+      if (have[i]) {
+        const int d0 = (lane + 32 * i) * 8;
+        uint32_t w[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          float a = v[i][2 * t] * inv, b = v[i][2 * t + 1] * inv;
+          if (gamma) { a *= gamma[d0 + 2 * t]; b *= gamma[d0 + 2 * t + 1]; }
+          if (beta) { a += beta[d0 + 2 * t]; b += beta[d0 + 2 * t + 1]; }
+          w[t] = float2_to_pair<T>(a, b);
+        }
+        y[row * pieces + lane + 32 * i] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+  }
+}
+template <typename T>
+bool launch_rows_vec(bool is_softmax, const void* x, void* y, const float* gamma, const float* beta, int64_t rows, int64_t dim, float eps, int log_form,
+                     cudaStream_t s) {
+  if (dim % 8 != 0 || dim > 8 * 32 * 8 || (uintptr_t)x % 16 != 0 || (uintptr_t)y % 16 != 0) return false;
+  const int pieces = (int)(dim / 8), np = (pieces + 31) / 32;
+  const int grid = grid_for(rows * 32, 256);
+#define B2_ROWS(NP)                                                                                                                      \
+  do {                                                                                                                                   \
+    if (is_softmax) softmax_rows_vec_kernel<T, NP><<<grid, 256, 0, s>>>((const uint4*)x, (uint4*)y, rows, pieces, log_form);             \
+    else layernorm_rows_vec_kernel<T, NP><<<grid, 256, 0, s>>>((const uint4*)x, (uint4*)y, gamma, beta, rows, pieces, eps);              \
+  } while (0)
+  if (np <= 1) B2_ROWS(1);
+  else if (np <= 2) B2_ROWS(2);
+  else if (np <= 4) B2_ROWS(4);
+  else B2_ROWS(8);
+#undef B2_ROWS
+  return true;
+}
 // Strided axis: one thread per (outer, inner) pair.
 __global__ void softmax_strided_kernel(int dt, const void* x, void* y, int64_t outer, int64_t dim, int64_t inner, int log_form) {
   int64_t total = outer * inner;
@@ -579,6 +700,8 @@ int channel_affine(int dt, const void* x, void* y, const float* a, const float* 
 }
 int softmax(int dt, const void* x, void* y, int64_t outer, int64_t dim, int64_t inner, bool log_form, cudaStream_t s) {
   if (outer * dim * inner <= 0) return 0;
+  if (inner == 1 && dt == DT_F16 && launch_rows_vec<__half>(true, x, y, nullptr, nullptr, outer, dim, 0.f, log_form, s)) return check_launch();
+  if (inner == 1 && dt == DT_BF16 && launch_rows_vec<__nv_bfloat16>(true, x, y, nullptr, nullptr, outer, dim, 0.f, log_form, s)) return check_launch();
   if (inner == 1) softmax_rows_kernel<<<grid_for(outer * 32, 256), 256, 0, s>>>(dt, x, y, outer, dim, log_form);
   else softmax_strided_kernel<<<grid_for(outer * inner, 128), 128, 0, s>>>(dt, x, y, outer, dim, inner, log_form);
   return check_launch();
@@ -590,6 +713,8 @@ int reduce_mean_axis(int dt_in, int dt_out, const void* x, void* y, int64_t befo
 }
 int layernorm(int dt, const void* x, void* y, const float* gamma, const float* beta, int64_t rows, int64_t dim, float eps, cudaStream_t s) {
   if (rows * dim <= 0) return 0;
+  if (dt == DT_F16 && launch_rows_vec<__half>(false, x, y, gamma, beta, rows, dim, eps, 0, s)) return check_launch();
+  if (dt == DT_BF16 && launch_rows_vec<__nv_bfloat16>(false, x, y, gamma, beta, rows, dim, eps, 0, s)) return check_launch();
   layernorm_kernel<<<grid_for(rows * 32, 256), 256, 0, s>>>(dt, x, y, gamma, beta, rows, dim, eps);
   return check_launch();
 }
@@ -625,12 +750,30 @@ int convert(int dt_in, int dt_out, const void* x, void* y, int64_t n, cudaStream
   convert_kernel<<<grid_for(n, 256), 256, 0, s>>>(dt_in, dt_out, x, y, n);
   return check_launch();
 }
-int move(const MoveGeom& g, int esz, const void* x, void* y, cudaStream_t s) {
+int move(const MoveGeom& g0, int esz, const void* x, void* y, cudaStream_t s) {
+  MoveGeom g = g0;
+  // When the innermost axis is contiguous on both sides (a head split / merge, a concat along an outer axis), move
+  // the widest power-of-two unit up to 16 bytes that divides every stride, offset and the innermost extent.
+  if (g.rank >= 1 && g.istride[g.rank - 1] == 1 && g.ostride[g.rank - 1] == 1) {
+    for (int unit = 16; unit > esz; unit /= 2) {
+      const int v = unit / esz;
+      bool ok = unit % esz == 0 && g.oshape[g.rank - 1] % v == 0 && g.in_offset % v == 0 && g.out_offset % v == 0 &&
+                (uintptr_t)x % unit == 0 && (uintptr_t)y % unit == 0;
+      for (int d = 0; d + 1 < g.rank && ok; ++d) ok = g.istride[d] % v == 0 && g.ostride[d] % v == 0;
+      if (!ok) continue;
+      g.oshape[g.rank - 1] /= v;
+      for (int d = 0; d + 1 < g.rank; ++d) { g.istride[d] /= v; g.ostride[d] /= v; }
+      g.in_offset /= v; g.out_offset /= v;
+      esz = unit;
+      break;
+    }
+  }
   int64_t total = 1;
   for (int d = 0; d < g.rank; ++d) total *= g.oshape[d];
   if (total <= 0) return 0;
   int grid = grid_for(total, 256);
   switch (esz) {
+    case 16: move_kernel<uint4><<<grid, 256, 0, s>>>(g, (const uint4*)x, (uint4*)y, total); break;
     case 1: move_kernel<uint8_t><<<grid, 256, 0, s>>>(g, (const uint8_t*)x, (uint8_t*)y, total); break;
     case 2: move_kernel<uint16_t><<<grid, 256, 0, s>>>(g, (const uint16_t*)x, (uint16_t*)y, total); break;
     case 4: move_kernel<uint32_t><<<grid, 256, 0, s>>>(g, (const uint32_t*)x, (uint32_t*)y, total); break;
