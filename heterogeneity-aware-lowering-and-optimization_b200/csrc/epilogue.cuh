@@ -62,6 +62,35 @@ __device__ __forceinline__ float apply_act(int act, float t, float a, float b) {
   return t;
 }
 
+// The same activation over N register-resident values with the dispatch outside the loop, so that the N
+// evaluations (an erf or tanh each, for GELU) are independent instruction streams the scheduler can interleave.
+template <int N>
+__device__ __forceinline__ void apply_act_all(int act, float (&v)[N], float a, float b) {
+  switch (act) {
+    case ACT_RELU:
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = apply_act(ACT_RELU, v[j], a, b);
+      break;
+    case ACT_LEAKY:
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = apply_act(ACT_LEAKY, v[j], a, b);
+      break;
+    case ACT_CLAMP:
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = apply_act(ACT_CLAMP, v[j], a, b);
+      break;
+    case ACT_GELU_ERF:
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = apply_act(ACT_GELU_ERF, v[j], a, b);
+      break;
+    case ACT_GELU_TANH:
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[j] = apply_act(ACT_GELU_TANH, v[j], a, b);
+      break;
+    default: break;
+  }
+}
+
 // Steps that depend only on the column (output channel), applied to t = (float)acc.
 __device__ __forceinline__ float epilogue_value(const Epilogue& ep, float t, int64_t row, int col, int64_t ld) {
   if (ep.mul) t = __fmul_rn(t, ep.mul[col]);

@@ -752,6 +752,23 @@ int convert(int dt_in, int dt_out, const void* x, void* y, int64_t n, cudaStream
 }
 int move(const MoveGeom& g0, int esz, const void* x, void* y, cudaStream_t s) {
   MoveGeom g = g0;
+  // Canonical form first: axes of extent 1 dropped, neighbours that are contiguous on both sides merged.
+  {
+    int r = 0;
+    for (int d = 0; d < g.rank; ++d) {
+      if (g.oshape[d] == 1 && g.rank > 1) continue;
+      if (r > 0 && g.istride[r - 1] == g.istride[d] * g.oshape[d] && g.ostride[r - 1] == g.ostride[d] * g.oshape[d]) {
+        g.oshape[r - 1] *= g.oshape[d];
+        g.istride[r - 1] = g.istride[d];
+        g.ostride[r - 1] = g.ostride[d];
+        continue;
+      }
+      g.oshape[r] = g.oshape[d]; g.istride[r] = g.istride[d]; g.ostride[r] = g.ostride[d];
+      ++r;
+    }
+    if (r == 0) { g.oshape[0] = 1; g.istride[0] = 1; g.ostride[0] = 1; r = 1; }
+    g.rank = r;
+  }
   // When the innermost axis is contiguous on both sides (a head split / merge, a concat along an outer axis), move
   // the widest power-of-two unit up to 16 bytes that divides every stride, offset and the innermost extent.
   if (g.rank >= 1 && g.istride[g.rank - 1] == 1 && g.ostride[g.rank - 1] == 1) {

@@ -522,10 +522,7 @@ __device__ __forceinline__ void epilogue_chunk_staged(const UmmaParams& p, float
 #pragma unroll
     for (int j = 0; j < 16; ++j) v[j] = __fadd_rn(v[j], cv[j]);
   }
-  if (ANYACT && ep.act_first) {
-#pragma unroll
-    for (int j = 0; j < 16; ++j) v[j] = apply_act(ep.act, v[j], ep.act_a, ep.act_b);
-  }
+  if (ANYACT && ep.act_first) apply_act_all<16>(ep.act, v, ep.act_a, ep.act_b);
   if (p.res_tma) {
     if (OUT == DT_S8) {
       const uint4 u = lds128(stage_piece(sp, 0));
@@ -549,10 +546,7 @@ __device__ __forceinline__ void epilogue_chunk_staged(const UmmaParams& p, float
     }
   }
   if (ANYACT) {
-    if (!ep.act_first) {
-#pragma unroll
-      for (int j = 0; j < 16; ++j) v[j] = apply_act(ep.act, v[j], ep.act_a, ep.act_b);
-    }
+    if (!ep.act_first) apply_act_all<16>(ep.act, v, ep.act_a, ep.act_b);
   } else if (ep.act == ACT_RELU) {
 #pragma unroll
     for (int j = 0; j < 16; ++j) v[j] = fmaxf(v[j], 0.f);
