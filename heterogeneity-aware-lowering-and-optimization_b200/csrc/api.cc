@@ -148,14 +148,8 @@ static bool any_null(std::initializer_list<odla_value> vs) {
 using namespace b200;
 
 _odla_computation::~_odla_computation() {
-  for (auto& r : replicas) {
-    cudaSetDevice(r.device);
-    r.plan.reset();
-    if (r.host_status) cudaFreeHost(r.host_status);
-    if (r.ev_begin) cudaEventDestroy(r.ev_begin);
-    if (r.ev_end) cudaEventDestroy(r.ev_end);
-    if (r.stream) cudaStreamDestroy(r.stream);
-  }
+  b200::destroy_replicas(replicas);
+  for (auto& kv : batch_replicas) b200::destroy_replicas(kv.second);
 }
 
 extern "C" {
@@ -324,10 +318,29 @@ odla_status odla_CreateContext(odla_context* context) {
   (*context)->comp = g_comp;
   return ODLA_SUCCESS;
 }
-odla_status odla_DestroyContext(odla_context context) { delete context; return ODLA_SUCCESS; }
-odla_status odla_SetContextItem(odla_context context, odla_item_type type, odla_item_value) {
+odla_status odla_DestroyContext(odla_context context) {
+  if (context && context->worker.joinable()) context->worker.join();  // an asynchronous execute still owns the bindings
+  delete context;
+  return ODLA_SUCCESS;
+}
+// ODLA_RUN_BATCH_SIZE: `value` points to an int, as for the TensorRT platform (ODLA/platforms/tensorrt/odla_tensorrt.cc:284-301).
+// ODLA_ASYNC_CALLBACK_FUNC / _ARG: `value` is the function pointer / the argument itself, as for the PopART
+// platform (ODLA/platforms/odla_popart/odla_compute.cc:85-100); the callback is int (*)(void* arg, odla_status).
+odla_status odla_SetContextItem(odla_context context, odla_item_type type, odla_item_value value) {
   if (!context) return ODLA_INVALID_PARAM;
-  if (type == ODLA_RUN_BATCH_SIZE || type == ODLA_ASYNC_CALLBACK_FUNC || type == ODLA_ASYNC_CALLBACK_ARG) return ODLA_SUCCESS;
+  if (context->worker.joinable()) context->worker.join();
+  switch (type) {
+    case ODLA_RUN_BATCH_SIZE: {
+      if (!value) return ODLA_INVALID_PARAM;
+      int bs = *(int*)value;
+      if (bs < 0) return ODLA_FAILURE;
+      context->run_batch = bs;
+      return ODLA_SUCCESS;
+    }
+    case ODLA_ASYNC_CALLBACK_FUNC: context->async_fn = (int (*)(void*, odla_status))value; return ODLA_SUCCESS;
+    case ODLA_ASYNC_CALLBACK_ARG: context->async_arg = (void*)value; return ODLA_SUCCESS;
+    default: break;
+  }
   B2_ERR("unsupported context item %d", (int)type);
   return ODLA_FAILURE;
 }
@@ -352,9 +365,13 @@ odla_status odla_GetOutputFromComputationByIdx(const odla_computation c, const o
   return ODLA_SUCCESS;
 }
 odla_status odla_SetValueShapeInfo(odla_value, odla_item_type, odla_value_shape) { return ODLA_SUCCESS; }
-odla_status odla_GetRuntimeShape(odla_context, odla_value value, odla_value_shape* shape) {
+odla_status odla_GetRuntimeShape(odla_context context, odla_value value, odla_value_shape* shape) {
   if (!value || !shape) return ODLA_INVALID_PARAM;
   *shape = value->type.shape;
+  // with ODLA_RUN_BATCH_SIZE set, dim 0 of a batched value follows it
+  if (context && context->run_batch > 0 && context->comp && context->comp->planned && context->comp->shardable && shape->size > 0 &&
+      context->comp->graph_batch > 0 && shape->dims[0] % context->comp->graph_batch == 0 && value->kind != OP_CONST)
+    shape->dims[0] = shape->dims[0] / context->comp->graph_batch * context->run_batch;
   return ODLA_SUCCESS;
 }
 odla_status odla_GetValueType(const odla_value value, odla_value_type* type) {
@@ -405,16 +422,49 @@ odla_status odla_BindToOutputById(const odla_value_id id, odla_void* data, odla_
   if (it == ctx->comp->by_name.end()) { B2_ERR("odla_BindToOutputById: unknown value '%s'", (const char*)id); return ODLA_INVALID_PARAM; }
   return odla_BindToOutput(it->second, data, ctx);
 }
-odla_status odla_ExecuteComputation(const odla_computation c, const odla_context ctx, const odla_compute_mode mode, odla_device) {
-  if (!c || !ctx) return ODLA_INVALID_PARAM;
-  if (mode == ODLA_COMPUTE_TRAINING) return ODLA_UNSUPPORTED_OP;
-  if (!c->first_error.empty()) { B2_ERR("computation has a build error: %s", c->first_error.c_str()); return c->error_status; }
+static odla_status execute_locked(odla_computation c, odla_context ctx) {
   // Contexts of one computation may be driven from different threads; they share the computation's
   // per-GPU arenas and streams, so executions are serialised here.
   std::lock_guard<std::mutex> lock(c->exec_mutex);
   odla_status s = ensure_planned(c);
   if (s != ODLA_SUCCESS) return s;
   return execute(c, ctx);
+}
+// Returns once the work is handed to a worker thread; when it has finished (outputs written) the context's
+// callback, if set, is called with its argument and the status -- the shape of the PopART platform's asynchronous
+// execute (ODLA/platforms/odla_popart/odla_compute.cc:262-291).  Bindings must not change until then; the next
+// execute / item / destroy call on the context waits for it, and odla_b200_WaitContext returns its status.
+odla_status odla_AsyncExecuteComputation(const odla_computation c, const odla_context ctx, const odla_compute_mode mode, odla_device) {
+  if (!c || !ctx) return ODLA_INVALID_PARAM;
+  if (mode == ODLA_COMPUTE_TRAINING) return ODLA_UNSUPPORTED_OP;
+  if (!c->first_error.empty()) { B2_ERR("computation has a build error: %s", c->first_error.c_str()); return c->error_status; }
+  if (ctx->worker.joinable()) ctx->worker.join();
+  for (auto a : c->args)
+    if (!ctx->in.count(a)) { B2_ERR("argument '%s' is not bound", a->name.c_str()); return ODLA_INVALID_PARAM; }
+  ctx->async_status = ODLA_SUCCESS;
+  try {
+    ctx->worker = std::thread([c, ctx]() {
+      odla_status s = execute_locked(c, ctx);
+      ctx->async_status = s;
+      if (ctx->async_fn) ctx->async_fn(ctx->async_arg, s);
+    });
+  } catch (...) {
+    B2_ERR("could not start a worker thread");
+    return ODLA_FAILURE;
+  }
+  return ODLA_SUCCESS;
+}
+odla_status odla_b200_WaitContext(odla_context ctx) {
+  if (!ctx) return ODLA_INVALID_PARAM;
+  if (ctx->worker.joinable()) ctx->worker.join();
+  return ctx->async_status;
+}
+odla_status odla_ExecuteComputation(const odla_computation c, const odla_context ctx, const odla_compute_mode mode, odla_device) {
+  if (!c || !ctx) return ODLA_INVALID_PARAM;
+  if (mode == ODLA_COMPUTE_TRAINING) return ODLA_UNSUPPORTED_OP;
+  if (ctx->worker.joinable()) ctx->worker.join();
+  if (!c->first_error.empty()) { B2_ERR("computation has a build error: %s", c->first_error.c_str()); return c->error_status; }
+  return execute_locked(c, ctx);
 }
 // The executable is the planned computation itself; these two exist so callers written against
 // the TensorRT platform's compile/launch pair (ODLA/platforms/tensorrt/odla_tensorrt.cc:561-701)

@@ -12,6 +12,7 @@
 #include <memory>
 #include <mutex>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "../../include/odla_b200.h"
@@ -152,6 +153,8 @@ struct _odla_computation {
   bool planned = false;
   bool shardable = true;           // dim 0 of every argument/output is an independent batch
   std::vector<b200::Replica> replicas;
+  int64_t graph_batch = 1;         // dim 0 of the recorded graph
+  std::map<int64_t, std::vector<b200::Replica>> batch_replicas;  // plans for other run batch sizes (ODLA_RUN_BATCH_SIZE)
   std::mutex exec_mutex;           // executions of one computation share its arenas: one at a time
   ~_odla_computation();
 };
@@ -163,6 +166,12 @@ struct _odla_context {
   float last_ms = -1.f;
   long long last_launches = 0;
   bool profiling = false;
+  int64_t run_batch = 0;           // ODLA_RUN_BATCH_SIZE; 0 = the recorded batch
+  // odla_AsyncExecuteComputation: one worker at a time per context
+  std::thread worker;
+  int (*async_fn)(void*, odla_status) = nullptr;
+  void* async_arg = nullptr;
+  odla_status async_status = ODLA_SUCCESS;
 };
 
 struct _odla_device {
@@ -175,6 +184,7 @@ odla_status apply_quant_table(_odla_computation* comp);
 // Builds replicas and plans for `comp` (idempotent).  Defined in plan.cc.
 odla_status ensure_planned(_odla_computation* comp);
 odla_status execute(_odla_computation* comp, _odla_context* ctx);
+void destroy_replicas(std::vector<Replica>& reps);
 int visible_devices();
 extern thread_local int g_current_device;  // set by odla_SetCurrentDevice, -1 = unset
 }  // namespace b200

@@ -1097,15 +1097,8 @@ bool graph_shardable(_odla_computation* c, int64_t* batch_out) {
 
 }  // namespace
 
-odla_status ensure_planned(_odla_computation* c) {
-  if (c->planned) return ODLA_SUCCESS;
-  int visible = visible_devices();
-  if (visible <= 0) {
-    B2_ERR("no CUDA device is visible: libodla_b200 has no CPU fallback");
-    return ODLA_FAILURE;
-  }
-  if (odla_status qs = apply_quant_table(c)) return qs;
-  for (auto& r : c->replicas) {
+void destroy_replicas(std::vector<Replica>& reps) {
+  for (auto& r : reps) {
     cudaSetDevice(r.device);
     r.plan.reset();
     if (r.host_status) cudaFreeHost(r.host_status);
@@ -1113,25 +1106,27 @@ odla_status ensure_planned(_odla_computation* c) {
     if (r.ev_end) cudaEventDestroy(r.ev_end);
     if (r.stream) cudaStreamDestroy(r.stream);
   }
-  c->replicas.clear();
-  int64_t B = 1;
-  c->shardable = graph_shardable(c, &B);
+  reps.clear();
+}
+
+// Builds the replicas (streams, arenas, constant pools, launch lists) that run `run_batch` rows of a graph
+// recorded with `B` rows in dim 0.
+static odla_status build_replicas(_odla_computation* c, int visible, int64_t B, int64_t run_batch, std::vector<Replica>& reps) {
   int want = c->n_gpus > 0 ? c->n_gpus : visible;
-  int G = c->shardable ? (int)std::min<int64_t>(std::min(want, visible), std::max<int64_t>(B, 1)) : 1;
+  int G = c->shardable ? (int)std::min<int64_t>(std::min(want, visible), std::max<int64_t>(run_batch, 1)) : 1;
   if (G < 1) G = 1;
   // Sub-batches: S replicas per GPU, each with its own stream, so that one sub-batch's host-to-device copy runs
   // under another's kernels (the call stays synchronous).  Pays when inputs are bound as host pointers.
   int S = c->sub_batches > 0 ? c->sub_batches : (getenv("ODLA_B200_SUBBATCHES") ? atoi(getenv("ODLA_B200_SUBBATCHES")) : 1);
   if (!c->shardable || S < 1) S = 1;
-  while (S > 1 && (int64_t)G * S > B) --S;
-  const int devices = G;
+  while (S > 1 && (int64_t)G * S > run_batch) --S;
   G *= S;
-  c->replicas.resize((size_t)G);
+  reps.resize((size_t)G);
   int64_t start = 0;
   for (int i = 0; i < G; ++i) {
-    Replica& r = c->replicas[i];
+    Replica& r = reps[i];
     r.device = (c->first_device + i / S) % visible;
-    r.shard_batch = c->shardable ? B / G + (i < B % G ? 1 : 0) : B;
+    r.shard_batch = c->shardable ? run_batch / G + (i < run_batch % G ? 1 : 0) : B;
     r.shard_start = start;
     start += r.shard_batch;
     B2_CUDA("setdevice", cudaSetDevice(r.device), ODLA_FAILURE);
@@ -1145,20 +1140,57 @@ odla_status ensure_planned(_odla_computation* c) {
     r.plan->batch = r.shard_batch;
     Builder b(c, r.plan.get(), c->shardable ? B : r.shard_batch, r.shard_batch, r.shard_start);
     odla_status s = b.run();
-    if (s != ODLA_SUCCESS) { c->replicas.clear(); return s; }
+    if (s != ODLA_SUCCESS) { destroy_replicas(reps); return s; }
     B2_INFO("GPU %d: rows [%lld,%lld), %zu launches, arena %.1f MiB, constants %.1f MiB", r.device, (long long)r.shard_start,
             (long long)(r.shard_start + r.shard_batch), r.plan->launches.size(), r.plan->arena_bytes / 1048576.0, r.plan->const_bytes / 1048576.0);
   }
   // peer access between every pair, for device-resident outputs gathered over NVLink
-  (void)devices;
   for (int i = 0; i < G; ++i)
     for (int j = 0; j < G; ++j) {
-      if (i == j || c->replicas[i].device == c->replicas[j].device) continue;
+      if (i == j || reps[i].device == reps[j].device) continue;
       int can = 0;
-      cudaDeviceCanAccessPeer(&can, c->replicas[i].device, c->replicas[j].device);
-      if (can) { cudaSetDevice(c->replicas[i].device); cudaError_t e = cudaDeviceEnablePeerAccess(c->replicas[j].device, 0); if (e != cudaSuccess) cudaGetLastError(); }
+      cudaDeviceCanAccessPeer(&can, reps[i].device, reps[j].device);
+      if (can) { cudaSetDevice(reps[i].device); cudaError_t e = cudaDeviceEnablePeerAccess(reps[j].device, 0); if (e != cudaSuccess) cudaGetLastError(); }
     }
+  return ODLA_SUCCESS;
+}
+
+odla_status ensure_planned(_odla_computation* c) {
+  if (c->planned) return ODLA_SUCCESS;
+  int visible = visible_devices();
+  if (visible <= 0) {
+    B2_ERR("no CUDA device is visible: libodla_b200 has no CPU fallback");
+    return ODLA_FAILURE;
+  }
+  if (odla_status qs = apply_quant_table(c)) return qs;
+  destroy_replicas(c->replicas);
+  for (auto& kv : c->batch_replicas) destroy_replicas(kv.second);
+  c->batch_replicas.clear();
+  int64_t B = 1;
+  c->shardable = graph_shardable(c, &B);
+  c->graph_batch = B;
+  odla_status s = build_replicas(c, visible, B, B, c->replicas);
+  if (s != ODLA_SUCCESS) return s;
   c->planned = true;
+  return ODLA_SUCCESS;
+}
+
+// The replicas that run `run_batch` rows (ODLA_RUN_BATCH_SIZE); plans for other batch sizes than the recorded one
+// are built on first use and kept.
+odla_status replicas_for_batch(_odla_computation* c, int64_t run_batch, std::vector<Replica>** out) {
+  odla_status s = ensure_planned(c);
+  if (s != ODLA_SUCCESS) return s;
+  if (run_batch <= 0 || run_batch == c->graph_batch) { *out = &c->replicas; return ODLA_SUCCESS; }
+  if (!c->shardable) { B2_ERR("ODLA_RUN_BATCH_SIZE needs a graph whose dim 0 is an independent batch"); return ODLA_UNSUPPORTED_OP; }
+  if (run_batch > c->graph_batch) { B2_ERR("ODLA_RUN_BATCH_SIZE %lld exceeds the recorded batch %lld", (long long)run_batch, (long long)c->graph_batch); return ODLA_INVALID_PARAM; }
+  auto it = c->batch_replicas.find(run_batch);
+  if (it == c->batch_replicas.end()) {
+    std::vector<Replica> reps;
+    s = build_replicas(c, visible_devices(), c->graph_batch, run_batch, reps);
+    if (s != ODLA_SUCCESS) return s;
+    it = c->batch_replicas.emplace(run_batch, std::move(reps)).first;
+  }
+  *out = &it->second;
   return ODLA_SUCCESS;
 }
 
@@ -1222,9 +1254,12 @@ odla_status execute(_odla_computation* c, _odla_context* ctx) {
   odla_status result = ODLA_SUCCESS;
   long long launched = 0;
   size_t enq = 0;
+  std::vector<Replica>* reps_p = nullptr;
+  if (odla_status rs = replicas_for_batch(c, ctx->run_batch, &reps_p)) return rs;
+  std::vector<Replica>& reps = *reps_p;
   // enqueue everything on every GPU, then wait; on a failure stop enqueuing and drain what started
-  for (; enq < c->replicas.size() && result == ODLA_SUCCESS; ++enq) {
-    Replica& r = c->replicas[enq];
+  for (; enq < reps.size() && result == ODLA_SUCCESS; ++enq) {
+    Replica& r = reps[enq];
     Plan& p = *r.plan;
     auto fail_here = [&](odla_status s, const char* what) { B2_ERR("GPU %d: %s failed", r.device, what); result = s; };
     if (cudaSetDevice(r.device) != cudaSuccess) { fail_here(ODLA_FAILURE, "cudaSetDevice"); break; }
@@ -1262,9 +1297,9 @@ odla_status execute(_odla_computation* c, _odla_context* ctx) {
   }
   if (result != ODLA_SUCCESS) cudaGetLastError();
   float worst = 0.f;
-  size_t started = std::min(enq + (result == ODLA_SUCCESS ? 0 : 1), c->replicas.size());
+  size_t started = std::min(enq + (result == ODLA_SUCCESS ? 0 : 1), reps.size());
   for (size_t i = 0; i < started; ++i) {
-    Replica& r = c->replicas[i];
+    Replica& r = reps[i];
     cudaSetDevice(r.device);
     cudaError_t e = cudaStreamSynchronize(r.stream);
     if (e != cudaSuccess) { B2_ERR("GPU %d: stream synchronise failed: %s", r.device, cudaGetErrorString(e)); if (result == ODLA_SUCCESS) result = ODLA_FAILURE; continue; }

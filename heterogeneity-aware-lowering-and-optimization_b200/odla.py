@@ -23,6 +23,8 @@ FLOAT16, BFLOAT16, FLOAT32, FLOAT64, BOOL = 16, 17, 18, 19, 20
 ITEM_BF16_MODE, ITEM_FP16_MODE, ITEM_PROCESSOR_NUM, ITEM_USE_DATA_TYPE, ITEM_AGGREGATE_OPS = 13, 14, 16, 18, 23
 ITEM_QUANT_TABLE, ITEM_QUANT_TABLE_SIZE = 21, 22
 ITEM_BATCHES_PER_STEP = 17
+ITEM_RUN_BATCH_SIZE, ITEM_ASYNC_CALLBACK_FUNC, ITEM_ASYNC_CALLBACK_ARG = 4, 26, 27
+ASYNC_CALLBACK = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int)   # int (*)(void* arg, odla_status)
 # odla_memory_layout
 CHANNELS_FIRST, CHANNELS_LAST, SIO, SOI, OIS, IOS = range(6)
 # odla_status
@@ -106,6 +108,7 @@ _SIGNATURES = {
     "odla_CreateContext": (C.c_int, [C.POINTER(_V)]),
     "odla_DestroyContext": (C.c_int, [_V]),
     "odla_ExecuteComputation": (C.c_int, [_V, _V, C.c_int, _V]),
+    "odla_SetContextItem": (C.c_int, [_V, C.c_int, _V]),
     "odla_GetNumOfArgsFromComputation": (C.c_int, [_V, C.POINTER(C.c_uint32)]),
     "odla_GetArgFromComputationByIdx": (C.c_int, [_V, C.c_uint32, C.POINTER(_V)]),
     "odla_GetNumOfOutputsFromComputation": (C.c_int, [_V, C.POINTER(C.c_uint32)]),
@@ -158,6 +161,8 @@ _OPTIONAL = {
     "odla_SetLogLevel": (C.c_int, [C.c_int]),
     "odla_AllocateHostMemory": (C.c_int, [C.POINTER(_V), C.c_size_t]),
     "odla_FreeHostMemory": (C.c_int, [_V]),
+    "odla_AsyncExecuteComputation": (C.c_int, [_V, _V, C.c_int, _V]),
+    "odla_b200_WaitContext": (C.c_int, [_V]),
     "odla_b200_DeviceCount": (C.c_int, []),
     "odla_b200_LastExecuteDeviceMs": (C.c_float, [_V]),
     "odla_b200_LastExecuteLaunches": (C.c_longlong, [_V]),
@@ -212,7 +217,7 @@ class Graph:
     def __init__(self, lib, name="model", fp16=False, bf16=False, n_gpus=None, use_graph=None, sub_batches=None):
         self.lib, self.name = lib, name
         self._keep = []            # numpy constants and name strings must outlive the computation
-        self.shapes, self.dtypes = {}, {}
+        self.shapes, self.dtypes, self._handles = {}, {}, {}
         self.cc_consts, self.cc_body, self.cc_items = [], [], []
         self.const_arrays = {}
         self.arg_names, self.out_names = [], []
@@ -271,9 +276,14 @@ class Graph:
         self._keep.append(b)
         return b
 
+    def value_handle(self, name):
+        """The odla_value behind a value id."""
+        return self._handles[name]
+
     def _reg(self, name, handle, dims, et):
         if not handle:
             raise RuntimeError("builder for '%s' returned NULL" % name)
+        self._handles[name] = handle
         self.shapes[name] = tuple(int(d) for d in dims)
         self.dtypes[name] = et
         return (name, handle)
@@ -461,6 +471,22 @@ class Graph:
 
     def execute(self):
         return self.lib.ExecuteComputation(self.comp, self.context(), 1, None)
+
+    def set_run_batch(self, n):
+        """ODLA_RUN_BATCH_SIZE: run only the first n rows of the recorded batch (bound buffers hold n rows)."""
+        v = C.c_int(n)
+        return self.lib.SetContextItem(self.context(), ITEM_RUN_BATCH_SIZE, C.cast(C.byref(v), _V))
+
+    def execute_async(self, callback=None, arg=None):
+        """odla_AsyncExecuteComputation; `callback(arg, status)` runs on the library's worker thread when the outputs are written."""
+        if callback is not None:
+            self._async_cb = ASYNC_CALLBACK(callback)
+            self._check(self.lib.SetContextItem(self.context(), ITEM_ASYNC_CALLBACK_FUNC, C.cast(self._async_cb, _V)), "odla_SetContextItem")
+            self._check(self.lib.SetContextItem(self.context(), ITEM_ASYNC_CALLBACK_ARG, C.c_void_p(arg)), "odla_SetContextItem")
+        return self.lib.AsyncExecuteComputation(self.comp, self.context(), 1, None)
+
+    def wait(self):
+        return self.lib.b200_WaitContext(self.context())
 
     def run(self, inputs):
         """inputs: dict name -> numpy array.  Returns dict output name -> numpy array."""

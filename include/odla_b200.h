@@ -197,6 +197,13 @@ odla_status odla_CreateComputation(odla_computation* computation);
 odla_status odla_DestroyComputation(odla_computation computation);
 odla_status odla_SetComputationItem(odla_computation computation, odla_item_type type,
                                     odla_item_value value);
+/* ODLA/include/ODLA/odla_compute.h:184-186.  Hands the execute to a worker thread and returns; the context's
+ * ODLA_ASYNC_CALLBACK_FUNC (int (*)(void* arg, odla_status)), if set, is called with ODLA_ASYNC_CALLBACK_ARG when
+ * the outputs are written.  Bindings must stay as they are until then. */
+odla_status odla_AsyncExecuteComputation(const odla_computation computation, const odla_context context,
+                                         const odla_compute_mode mode, odla_device device);
+/* Extension (no counterpart in the reference): waits for the context's asynchronous execute and returns its status. */
+odla_status odla_b200_WaitContext(odla_context context);
 odla_status odla_CompileComputation(const odla_computation computation, const odla_device device,
                                     odla_executable* executable);
 odla_status odla_LaunchExecutable(odla_executable executable, odla_context context);

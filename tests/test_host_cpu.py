@@ -201,3 +201,31 @@ print("rank", r, "ok")
         out, err = p.communicate(timeout=120)
         assert p.returncode == 0, err
         assert "ok" in out
+
+
+def test_async_execute_reports_failure_through_the_callback_without_a_gpu(odla, lib):
+    """odla_AsyncExecuteComputation returns at once; the status reaches the caller through the callback and
+    odla_b200_WaitContext.  On a box without a CUDA device that status is a failure (there is no CPU fallback)."""
+    if lib.b200_DeviceCount() > 0:
+        pytest.skip("needs a box without a GPU")
+    g = odla.Graph(lib, "async")
+    x = g.Argument("x", (4, 8))
+    g.Output(g.Relu(x, "y"))
+    a, b = np.ones((4, 8), np.float32), np.zeros((4, 8), np.float32)
+    lib.SetLogLevel(0)
+    try:
+        g.bind_input("x", a.ctypes.data)
+        g.bind_output("y", b.ctypes.data)
+        seen = []
+        assert g.set_run_batch(2) == 0 and g.set_run_batch(-1) == odla.FAILURE
+        assert g.execute_async(lambda arg, status: seen.append((arg, status)) or 0, 1234) == 0
+        assert g.wait() != 0
+        assert seen == [(1234, g.wait())]
+        # an unbound argument is refused before any thread starts
+        h = odla.Graph(lib, "async2")
+        h.Output(h.Relu(h.Argument("x", (4, 8)), "y"))
+        assert h.execute_async() == odla.INVALID_PARAM
+        h.close()
+    finally:
+        lib.SetLogLevel(3)
+    g.close()

@@ -277,3 +277,42 @@ def test_sub_batches_pipeline_one_gpu(odla, gpu_lib, models, rn_weights):
     assert "rows [0,3)" in descs[1] and "rows [3,6)" in descs[1] and "rows [4,5)" in descs[2]
     for o in outs[1:]:
         assert np.array_equal(o, outs[0])
+
+
+def test_run_batch_size_and_async_execute(odla, gpu_lib, ref, models):
+    """ODLA_RUN_BATCH_SIZE runs the first n rows of the recorded batch through a plan of its own (kept for the
+    next call); odla_AsyncExecuteComputation returns before the outputs are written and calls back when they are."""
+    import threading
+    x = models.mnist.inputs(batch=64)["x"]
+    gr = odla.Graph(ref, "m")
+    models.mnist.build(gr, batch=64)
+    want = gr.run({"x": x})["y"]
+    gr.close()
+    g = odla.Graph(gpu_lib, "m")
+    models.mnist.build(g, batch=64)
+    for n in (10, 64, 1, 10):
+        xin, out = np.ascontiguousarray(x[:n]), np.full((n, 10), -1.0, np.float32)
+        g.bind_input("x", xin.ctypes.data)
+        g.bind_output("y", out.ctypes.data)
+        assert g.set_run_batch(n) == 0
+        assert g.execute() == 0
+        assert np.abs(out - want[:n]).max() < 1e-5
+        shp = odla.Shape()
+        gpu_lib.GetRuntimeShape(g.context(), g.value_handle("y"), C.byref(shp))
+        assert list(shp.dims[:2]) == [n, 10]
+    gpu_lib.SetLogLevel(0)
+    assert g.set_run_batch(65) == 0 and g.execute() == odla.INVALID_PARAM      # more rows than were recorded
+    gpu_lib.SetLogLevel(3)
+    # asynchronous execute with a callback
+    assert g.set_run_batch(0) == 0
+    out = np.full((64, 10), -1.0, np.float32)
+    g.bind_input("x", x.ctypes.data)
+    g.bind_output("y", out.ctypes.data)
+    done, seen = threading.Event(), []
+    assert g.execute_async(lambda arg, status: (seen.append((arg, status)), done.set(), 0)[2], 77) == 0
+    assert done.wait(30) and seen == [(77, 0)]
+    assert g.wait() == 0 and np.abs(out - want).max() < 1e-5
+    # without a callback: the next call on the context waits
+    out[:] = -1
+    assert g.execute_async() == 0 and g.wait() == 0 and np.abs(out - want).max() < 1e-5
+    g.close()
