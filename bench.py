@@ -278,8 +278,8 @@ def run_b200(args, rank, world, local_rank):
                 "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak if peak else None, "peak_source": peak_kind + " bf16 sustained",
                 "avg_launch_ms": tc_ms / max(tc_launches, 1), "share_of_step": tc_ms / max(sum(f["ms"] for f in fam.values()), 1e-9),
                 # dram__bytes_read.sum + dram__bytes_write.sum of this kernel, average per launch: one ncu capture of all 54
-                # launches at B=128 (5.49 GB; activations already exceed the 126 MB L2 there), scaled by 2 to B=256.
-                "traffic": 2.0334e8 * (BATCH / 256.0), "traffic_unit": "bytes per launch (54 launches per step)",
+                # launches at B=128 (5.321 GB; activations already exceed the 126 MB L2 there), scaled by 2 to B=256.
+                "traffic": 1.9707e8 * (BATCH / 256.0), "traffic_unit": "bytes per launch (54 launches per step)",
                 "algorithmic_bytes_per_launch": sum(f["bytes"] for f in tc) / max(tc_launches, 1),
                 "hbm_view": {"achieved_gbs": sum(f["bytes"] for f in tc) / (tc_ms * 1e-3) / 1e9 if tc_ms > 0 else 0.0, "peak_gbs": float(peaks.get("hbm_gbs", 0))}}
     families = {k: {"launches": v["launches"], "ms": round(v["ms"], 4)} for k, v in sorted(fam.items(), key=lambda kv: -kv[1]["ms"])}
