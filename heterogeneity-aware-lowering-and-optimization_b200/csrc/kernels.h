@@ -84,9 +84,15 @@ struct UmmaConv {
   // Batched GEMM (attention): w holds `w_batches` matrices [K][C] back to back and output rows
   // [b*rows_per_batch, (b+1)*rows_per_batch) use matrix b.  rows_per_batch must be a multiple of 128.
   int w_batches = 0, rows_per_batch = 0;
+  // Permuted store (attention head split / merge folded into the GEMM): the output rows are (b, s) [mode 1] or
+  // (b, h, s) [mode 2] with s < store_S, the columns are head h x store_D [mode 1] or store_D [mode 2], and element
+  // (b, h, s, d) goes to y[b][h][s][d] (mode 1: [B,S,NH*D] -> [B,NH,S,D]) or y[b][s][h][d] (mode 2: [B,NH,S,D] -> [B,S,NH,D]).
+  int store_mode = 0, store_S = 0, store_NH = 0, store_D = 0;
 };
 // True when the tensor-core kernel can run this problem.
 bool umma_conv_supported(const UmmaConv& p);
+// Whether a launch with p.store_mode != 0 can store through the permuted tensor map (staged epilogue, one head = one box).
+bool umma_store_perm_ok(const UmmaConv& p, const Epilogue& ep, const void* y);
 // Opaque prepared launch (tensor maps live in it).  Create once at plan time.
 struct UmmaLaunch;
 UmmaLaunch* umma_conv_prepare(const UmmaConv& p, const void* x, const void* w, void* y, const Epilogue& ep,
@@ -154,10 +160,10 @@ int pad_channels(int esz, const void* x, void* y, int64_t pixels, int C, int Cp,
 // convolution over few channels becomes an (R x 1) convolution over 32 channels with unit column
 // stride.  esz is 1 or 2 bytes; one thread writes 16 bytes.
 int stem_widen(int esz, const void* x, void* y, int N, int H, int W, int C, int Q, cudaStream_t stream);
-// y[n][h][4 + w][cp] = x[n][h][w][0..C) (zeros elsewhere), cp = 8 / esz channels so that a pixel is 8 bytes: an image
-// with 4 pixels of zero padding on the left and right of every row, from which overlapping 8-pixel windows (64 bytes)
-// can be read at 16-byte steps.
-int stem_pad4(int esz, const void* x, void* y, int N, int H, int W, int C, cudaStream_t stream);
+// y[n][h][lp + w][cp] = x[n][h][w][0..C) (zeros elsewhere), cp = pixel_bytes / esz channels (pixel_bytes 8 or 16), rows of
+// Wp pixels: an image with zero columns on both sides from which overlapping windows of 64 bytes can be read at
+// 16-byte steps (every pixel at 16-byte pixels, every second one at 8-byte pixels).
+int stem_pad(int esz, const void* x, void* y, int N, int H, int W, int C, int pixel_bytes, int lp, int Wp, cudaStream_t stream);
 int resize_nearest(int esz, const void* x, void* y, int N, int H, int W, int C, int P, int Q, bool nhwc,
                    cudaStream_t stream);
 // out[o, k, :] = in[o, idx[k], :]; idx int32 or int64.

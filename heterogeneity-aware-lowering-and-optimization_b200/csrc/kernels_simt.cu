@@ -571,24 +571,25 @@ __global__ void stem_widen_kernel(const T* __restrict__ x, uint4* __restrict__ y
     y[e] = out;
   }
 }
-// Pads every pixel to 8 bytes (CP = 4 two-byte or 8 one-byte channels) and every image row with 4 zero pixels on each side.
+// Pads every pixel to CP channels (8 or 16 bytes) and every image row with `lp` zero pixels on the left and zeros up
+// to Wp pixels on the right.
 template <typename T, int CP>
-__global__ void stem_pad4_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int W, int C) {
-  static_assert(sizeof(T) * CP == 8, "a padded pixel is 8 bytes");
-  const int Wp = W + 8;
+__global__ void stem_pad_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int W, int C, int lp, int Wp) {
+  static_assert(sizeof(T) * CP == 8 || sizeof(T) * CP == 16, "a padded pixel is 8 or 16 bytes");
   const int64_t total = rows * Wp;
   for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
     const int wp = (int)(e % Wp);
     const int64_t row = e / Wp;
-    const int w = wp - 4;
-    __align__(8) T px[CP];
+    const int w = wp - lp;
+    __align__(16) T px[CP];
 #pragma unroll
     for (int c = 0; c < CP; ++c) px[c] = 0;
     if (w >= 0 && w < W) {
 #pragma unroll
       for (int c = 0; c < CP; ++c) if (c < C) px[c] = x[(row * W + w) * C + c];
     }
-    *(uint2*)(y + e * CP) = *(const uint2*)px;
+    if (sizeof(T) * CP == 8) *(uint2*)(y + e * CP) = *(const uint2*)px;
+    else *(uint4*)(y + e * CP) = *(const uint4*)px;
   }
 }
 template <typename T>
@@ -718,12 +719,39 @@ int layernorm(int dt, const void* x, void* y, const float* gamma, const float* b
   layernorm_kernel<<<grid_for(rows * 32, 256), 256, 0, s>>>(dt, x, y, gamma, beta, rows, dim, eps);
   return check_launch();
 }
+// Per-tensor two-byte float -> int8, 16 elements per thread (two 16-byte loads, one 16-byte store).
+template <typename T>
+__global__ void quantize_h_s8_vec_kernel(const uint4* __restrict__ x, uint4* __restrict__ q, const float* scale, int64_t n16) {
+  const float s = scale[0];
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n16; i += (int64_t)gridDim.x * blockDim.x) {
+    uint4 out;
+    uint32_t* o = (uint32_t*)&out;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint4 u = x[i * 2 + h];
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        const float2 f0 = pair_to_float2<T>(w[2 * t]), f1 = pair_to_float2<T>(w[2 * t + 1]);
+        const int a = sat_s8(rintf(__fdiv_rn(f0.x, s))), b = sat_s8(rintf(__fdiv_rn(f0.y, s)));
+        const int c = sat_s8(rintf(__fdiv_rn(f1.x, s))), d = sat_s8(rintf(__fdiv_rn(f1.y, s)));
+        o[2 * h + t] = (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) | ((uint32_t)(d & 0xff) << 24);
+      }
+    }
+    q[i] = out;
+  }
+}
 int quantize(int dt_in, const void* x, void* q, const float* scale, const int* zp, int64_t outer, int64_t adim, int64_t inner,
              bool per_axis, bool is_unsigned, cudaStream_t s) {
   int64_t total = outer * adim * inner;
   if (total <= 0) return 0;
   if (dt_in == DT_F32 && !per_axis && !zp && !is_unsigned && total % 16 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)q % 16 == 0) {
     quantize_f32_s8_vec_kernel<<<grid_for(total / 16, 256), 256, 0, s>>>((const float4*)x, (uint4*)q, scale, total / 16);
+    return check_launch();
+  }
+  if ((dt_in == DT_F16 || dt_in == DT_BF16) && !per_axis && !zp && !is_unsigned && total % 16 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)q % 16 == 0) {
+    if (dt_in == DT_F16) quantize_h_s8_vec_kernel<__half><<<grid_for(total / 16, 256), 256, 0, s>>>((const uint4*)x, (uint4*)q, scale, total / 16);
+    else quantize_h_s8_vec_kernel<__nv_bfloat16><<<grid_for(total / 16, 256), 256, 0, s>>>((const uint4*)x, (uint4*)q, scale, total / 16);
     return check_launch();
   }
   quantize_kernel<<<grid_for(total, 256), 256, 0, s>>>(dt_in, x, q, scale, zp, total, adim, inner, per_axis, is_unsigned);
@@ -818,13 +846,16 @@ int stem_widen(int esz, const void* x, void* y, int N, int H, int W, int C, int 
   else return -1;
   return check_launch();
 }
-int stem_pad4(int esz, const void* x, void* y, int N, int H, int W, int C, cudaStream_t s) {
-  int64_t rows = (int64_t)N * H, total = rows * (W + 8);
+int stem_pad(int esz, const void* x, void* y, int N, int H, int W, int C, int pixel_bytes, int lp, int Wp, cudaStream_t s) {
+  int64_t rows = (int64_t)N * H, total = rows * Wp;
   if (total <= 0) return 0;
-  if (C > 4) return -1;
+  const int cp = pixel_bytes / esz;
+  if (C > cp || (uintptr_t)y % 16 != 0) return -1;
   int grid = grid_for(total, 256);
-  if (esz == 1) stem_pad4_kernel<uint8_t, 8><<<grid, 256, 0, s>>>((const uint8_t*)x, (uint8_t*)y, rows, W, C);
-  else if (esz == 2) stem_pad4_kernel<uint16_t, 4><<<grid, 256, 0, s>>>((const uint16_t*)x, (uint16_t*)y, rows, W, C);
+  if (esz == 1 && cp == 8) stem_pad_kernel<uint8_t, 8><<<grid, 256, 0, s>>>((const uint8_t*)x, (uint8_t*)y, rows, W, C, lp, Wp);
+  else if (esz == 1 && cp == 16) stem_pad_kernel<uint8_t, 16><<<grid, 256, 0, s>>>((const uint8_t*)x, (uint8_t*)y, rows, W, C, lp, Wp);
+  else if (esz == 2 && cp == 4) stem_pad_kernel<uint16_t, 4><<<grid, 256, 0, s>>>((const uint16_t*)x, (uint16_t*)y, rows, W, C, lp, Wp);
+  else if (esz == 2 && cp == 8) stem_pad_kernel<uint16_t, 8><<<grid, 256, 0, s>>>((const uint16_t*)x, (uint16_t*)y, rows, W, C, lp, Wp);
   else return -1;
   return check_launch();
 }

@@ -71,6 +71,7 @@ struct UmmaParams {
   int epi_interleave;  // groups take every fourth chunk instead of a contiguous run
   int pair;            // 1: two CTAs of a cluster share each 256-row tile (tcgen05 cta_group::2), each loading half of B
   int bn_load;         // rows of B this CTA brings into shared memory per k-block (BN, or BN/2 in pair mode)
+  int store_mode, store_S, store_NH;  // permuted store through a 4-d map (see UmmaConv)
   int epi_mode;        // kernel variant: 0 direct, 1 staged, 2 staged with the general activation / division
   int tmem_cols;
   void* y;
@@ -805,9 +806,20 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const int x0 = n0 + bx * cols_per_box;
           if (x0 >= p.K_out) break;
           if (!mbar_wait(box_done + slot, ph, abort_flag, p.status, 7)) { ok = false; break; }
-          asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"((uint64_t)&tmY),
-                       "r"(staging_u32 + (uint32_t)slot * 16384u), "r"(x0), "r"(m0)
-                       : "memory");
+          if (p.store_mode == 0) {
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"((uint64_t)&tmY),
+                         "r"(staging_u32 + (uint32_t)slot * 16384u), "r"(x0), "r"(m0)
+                         : "memory");
+          } else {
+            // the 128 rows of the box are one run of sequence positions of one batch element; its columns one head
+            const int g = m0 / p.store_S, s0 = m0 - g * p.store_S;
+            int c1, c2, c3;
+            if (p.store_mode == 1) { c1 = s0; c2 = x0 / cols_per_box; c3 = g; }                                   // [B][NH][S][D]
+            else { const int b = g / p.store_NH; c1 = g - b * p.store_NH; c2 = s0; c3 = b; }                      // [B][S][NH][D]
+            asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"((uint64_t)&tmY),
+                         "r"(staging_u32 + (uint32_t)slot * 16384u), "r"(0), "r"(c1), "r"(c2), "r"(c3)
+                         : "memory");
+          }
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           if (prev >= 0) {
             asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");  // every store but the newest has read its box
@@ -1004,6 +1016,17 @@ bool umma_conv_supported(const UmmaConv& c) {
   return true;
 }
 
+bool umma_store_perm_ok(const UmmaConv& c, const Epilogue& ep, const void* y) {
+  if (c.store_mode != 1 && c.store_mode != 2) return false;
+  const int oes = storage_size_of(ep.out_dt);
+  if (!(ep.out_dt == DT_F16 || ep.out_dt == DT_BF16 || ep.out_dt == DT_S8) || c.store_D * oes != 128) return false;  // one head = one 128-byte box
+  if (ep.res || ep.add_full || (uintptr_t)y % 16 != 0 || getenv("ODLA_B200_DIRECT_EPILOGUE")) return false;
+  if (c.store_S <= 0 || c.store_S % 128 != 0 || c.store_NH <= 0 || c.R != 1 || c.S != 1) return false;
+  const long long M = (long long)c.N * c.P * c.Q;
+  if (c.store_mode == 1) return M % c.store_S == 0 && c.K == c.store_NH * c.store_D;
+  return M % ((long long)c.store_S * c.store_NH) == 0 && c.K == c.store_D;
+}
+
 UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, void* y, const Epilogue& ep, int* status, int sms) {
   if (!umma_conv_supported(c) || !load_driver_entry_points()) return nullptr;
   auto* L = new UmmaLaunch();
@@ -1089,6 +1112,8 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
   if (p.stages > p.num_it + 1) p.stages = p.num_it + 1;
   if (p.stages < 2) p.stages = 2;
   p.acc_int = c.in_dt == DT_S8;
+  p.store_mode = c.store_mode; p.store_S = c.store_S; p.store_NH = c.store_NH;
+  if (p.store_mode && (!p.staged || !umma_store_perm_ok(c, ep, y))) { delete L; return nullptr; }
   p.rows_per_batch = c.w_batches > 0 ? c.rows_per_batch : 0;
   p.tmem_cols = 2 * p.BN;  // 128, 256 or 512: powers of two >= 32
   const uint32_t fmt = c.in_dt == DT_BF16 ? 1u : (c.in_dt == DT_S8 ? 1u : 0u);      // bf16 / signed 8-bit / f16
@@ -1159,6 +1184,16 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
     cuuint64_t strides[1] = {(cuuint64_t)c.K * p.out_esz};
     cuuint32_t box[2] = {(cuuint32_t)(128 / p.out_esz), (cuuint32_t)BM};
     cuuint32_t estr[2] = {1, 1};
+    if (p.store_mode) {
+      const cuuint64_t D = (cuuint64_t)c.store_D, S = (cuuint64_t)c.store_S, NH = (cuuint64_t)c.store_NH;
+      const cuuint64_t Bn = (cuuint64_t)p.M_total / (S * (p.store_mode == 1 ? 1 : NH));
+      cuuint64_t d4[4] = {D, p.store_mode == 1 ? S : NH, p.store_mode == 1 ? NH : S, Bn};
+      cuuint64_t s4[3] = {D * p.out_esz, d4[1] * D * p.out_esz, d4[1] * d4[2] * D * p.out_esz};
+      cuuint32_t b4[4] = {(cuuint32_t)D, p.store_mode == 1 ? (cuuint32_t)BM : 1u, p.store_mode == 1 ? 1u : (cuuint32_t)BM, 1};
+      cuuint32_t e4[4] = {1, 1, 1, 1};
+      r = g_encode_tiled(&L->tmY, odt, 4, y, d4, s4, b4, e4, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else
     r = g_encode_tiled(&L->tmY, odt, 2, y, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r == CUDA_SUCCESS && p.res_tma)

@@ -135,6 +135,10 @@ struct Fused {
   int act = ACT_NONE; float act_a = 0, act_b = 0; bool act_first = false;
   V quant_scale = nullptr;  // absorbed Quantize
   float scalar_mul = 1.f;   // a following Mul by a scalar constant, folded into alpha
+  // attention head split ([B*S, NH*D] -> Reshape -> Transpose(0,2,1,3) = [B,NH,S,D], mode 1) or merge ([B,NH,S,D] ->
+  // Transpose(0,2,1,3) = [B,S,NH,D], mode 2) folded into the Gemm's store
+  int perm_mode = 0;
+  int64_t perm_S = 0, perm_NH = 0, perm_D = 0;
   bool has_scalar_mul = false;
 };
 
@@ -370,6 +374,28 @@ void Builder::try_fuse(V root) {
     fused_into_[nxt] = root;
     cur = nxt;
   }
+  // A Gemm whose only consumer is the head split / merge of attention stores straight into the permuted tensor.
+  if (root->kind == OP_GEMM && channel_last && !f->quant_scale && !f->res && !cur->is_output && users_[cur] == 1 && !getenv("ODLA_B200_NO_PERM_STORE")) {
+    auto is_head_swap = [](V t) {
+      return t->kind == OP_TRANSPOSE && t->ia.size() == 4 && t->ia[0] == 0 && t->ia[1] == 2 && t->ia[2] == 1 && t->ia[3] == 3;
+    };
+    V nxt = consumers_[cur][0];
+    const auto& cs = cur->type.shape;
+    if (nxt->kind == OP_RESHAPE && cs.size == 2 && nxt->type.shape.size == 4 && !nxt->is_output && users_[nxt] == 1 && !fused_into_.count(nxt)) {
+      V t = consumers_[nxt][0];
+      const auto& rs = nxt->type.shape;  // [B, S, NH, D]
+      if (is_head_swap(t) && !fused_into_.count(t) && rs.dims[0] * rs.dims[1] == cs.dims[0] && rs.dims[2] * rs.dims[3] == cs.dims[1]) {
+        f->perm_mode = 1; f->perm_S = rs.dims[1]; f->perm_NH = rs.dims[2]; f->perm_D = rs.dims[3];
+        fused_into_[nxt] = root;
+        fused_into_[t] = root;
+        cur = t;
+      }
+    } else if (is_head_swap(nxt) && cs.size == 4 && !fused_into_.count(nxt)) {  // [B, NH, S, D]
+      f->perm_mode = 2; f->perm_NH = cs.dims[1]; f->perm_S = cs.dims[2]; f->perm_D = cs.dims[3];
+      fused_into_[nxt] = root;
+      cur = nxt;
+    }
+  }
   f->out = cur;
   fused_[root] = std::move(f);
 }
@@ -538,51 +564,63 @@ odla_status Builder::emit_fused(const Item& it) {
     int wide_c = 32, wide_cp = 4;  // channels of a widened pixel / of each input pixel inside it
     const bool small_c = allow_umma && nhwc && groups == 1 && (in_dt == DT_F16 || in_dt == DT_BF16 || in_dt == DT_S8) && !umma_conv_supported(uc) &&
                          g.C * storage_size(in_dt) < 32;
-    if (small_c && g.C <= 4 && g.stride_w == 2 && g.pad_l <= 4 && g.S - g.pad_l <= 4 && !getenv("ODLA_B200_NO_WIDEN")) {
-      // Output column q reads input pixels 2q-pad_l .. 2q-pad_l+S-1, all inside 2q-4 .. 2q+3: gather those
-      // eight pixels (x 4 channels) once per (row, q) and the column taps collapse into the channel axis.
+    // Widened pixels: output column q reads the S input pixels from q*stride_w - pad_l on.  With pixels padded to
+    // 16 / stride_w bytes those taps lie inside one 64-byte window that starts 16 bytes after the window of column
+    // q-1, so the column taps collapse into the channel axis: an (R x S) convolution over few channels becomes an
+    // (R x 1) convolution over 64-byte "widened pixels" with unit column stride.
+    int wide_pb = 8, wide_lp = 4, wide_Wp = 0;   // pixel bytes, zero pixels on the left, padded row length (overlapping form)
+    if (small_c && (g.stride_w == 1 || g.stride_w == 2) && g.S <= 4 * g.stride_w && g.C * storage_size(in_dt) <= 16 / g.stride_w &&
+        !getenv("ODLA_B200_NO_WIDEN")) {
+      const int esz0 = storage_size(in_dt);
       UmmaConv uw = uc;
-      uw.W = g.Q; uw.C = 32; uw.S = 1; uw.stride_w = 1; uw.pad_l = 0;
-      if (umma_conv_supported(uw)) {
-        const int esz0 = storage_size(in_dt);
-        // First choice: no widened copy at all.  Pad every pixel to 8 bytes (4 two-byte or 8 one-byte channels) and
-        // every row with 4 zero pixels on each side; the widened pixel of column q is then the 64 contiguous bytes
-        // that start 16 bytes (two pixels) after the one of column q-1, which a tensor map with a W stride smaller
-        // than the pixel size describes directly.  If the driver refuses such a map, fall back to the materialised copy.
-        if (!getenv("ODLA_B200_NO_OVERLAP")) {
-          UmmaConv uo = uw;
-          uo.C = 64 / esz0;
-          uo.x_w_stride = 16;
-          uo.x_h_stride = (long long)(g.W + 8) * 8;
-          uo.x_n_stride = uo.x_h_stride * g.H;
-          void* pad4 = nullptr;
-          size_t pb = (size_t)uo.x_n_stride * g.N + 256;
-          if (umma_conv_supported(uo) && !inject_fault("alloc") && cudaMalloc(&pad4, pb) == cudaSuccess) {
-            Epilogue probe_ep;
-            probe_ep.out_dt = DT_F32;
-            UmmaLaunch* probe = umma_conv_prepare(uo, pad4, pad4, pad4, probe_ep, p_->status, sms);
-            if (probe) {
-              umma_conv_destroy(probe);
-              p_->extra_allocs.push_back(pad4);
-              padded = pad4;
-              x_umma = padded;
-              uc = uo;
-              widened = true;
-              overlap = true;
-              wide_c = uo.C;
-              wide_cp = 8 / esz0;
-            } else {
-              cudaFree(pad4);
-            }
-          } else cudaGetLastError();
-        }
-        if (!widened) {
+      uw.W = g.Q; uw.C = 64 / esz0; uw.S = 1; uw.stride_w = 1; uw.pad_l = 0;
+      // First choice: no widened copy at all.  A pre-pass pads every pixel to 16 / stride_w bytes and every row with
+      // pad_l zero pixels on the left (and enough on the right); the widened pixel of column q is then the 64
+      // contiguous bytes that start 16 bytes after the one of column q-1, which a tensor map with a W stride smaller
+      // than the pixel size describes directly.  If the driver refuses such a map, a stride-2 stem falls back to a
+      // materialised widened copy, others to plain channel padding.
+      if (umma_conv_supported(uw) && !getenv("ODLA_B200_NO_OVERLAP")) {
+        const int pb = 16 / g.stride_w, wp = 64 / pb;
+        int Wp = std::max(g.pad_l + g.W, (g.Q - 1) * g.stride_w + wp);
+        Wp = (Wp + 1) & ~1;  // rows are 16-byte multiples also with 8-byte pixels
+        UmmaConv uo = uw;
+        uo.x_w_stride = 16;
+        uo.x_h_stride = (long long)Wp * pb;
+        uo.x_n_stride = uo.x_h_stride * g.H;
+        void* padbuf = nullptr;
+        size_t pbytes = (size_t)uo.x_n_stride * g.N + 256;
+        if (!inject_fault("alloc") && cudaMalloc(&padbuf, pbytes) == cudaSuccess) {
+          Epilogue probe_ep;
+          probe_ep.out_dt = DT_F32;
+          UmmaLaunch* probe = umma_conv_prepare(uo, padbuf, padbuf, padbuf, probe_ep, p_->status, sms);
+          if (probe) {
+            umma_conv_destroy(probe);
+            p_->extra_allocs.push_back(padbuf);
+            padded = padbuf;
+            x_umma = padded;
+            uc = uo;
+            widened = true;
+            overlap = true;
+            wide_c = uo.C;
+            wide_pb = pb; wide_cp = pb / esz0; wide_lp = g.pad_l; wide_Wp = Wp;
+          } else {
+            cudaFree(padbuf);
+          }
+        } else cudaGetLastError();
+      }
+      // Second choice (stride 2, at most 4 channels, taps within 2q-4 .. 2q+3): gather the eight pixels x 4 channels
+      // of every output column into a materialised 32-channel tensor.
+      if (!widened && g.stride_w == 2 && g.C <= 4 && g.pad_l <= 4 && g.S - g.pad_l <= 4) {
+        UmmaConv um = uw;
+        um.C = 32;
+        if (umma_conv_supported(um)) {
           size_t pbytes = (size_t)g.N * g.H * g.Q * 32 * esz0;
           if (inject_fault("alloc") || cudaMalloc(&padded, pbytes ? pbytes : 32) != cudaSuccess) return fail(ODLA_MEM_ERROR, "scratch allocation failed");
           p_->extra_allocs.push_back(padded);
           x_umma = padded;
-          uc = uw;
+          uc = um;
           widened = true;
+          wide_c = 32; wide_cp = 4; wide_lp = 4;
         }
       }
     }
@@ -604,11 +642,12 @@ odla_status Builder::emit_fused(const Item& it) {
       int64_t rs = (int64_t)g.R * g.S;
       std::vector<float> w2;
       if (widened) {
-        // [K][R][wide_c]: element el of a widened pixel is input pixel 2q-4+el/cp, channel el%cp, i.e. filter column el/cp-4+pad_l
+        // [K][R][wide_c]: element el of a widened pixel is window pixel el / cp, channel el % cp; the window starts wide_lp
+        // pixels left of column q*stride_w, the taps pad_l pixels left of it: filter column = el / cp - wide_lp + pad_l
         w2.assign((size_t)(K * g.R * wide_c), 0.f);
         for (int64_t r = 0; r < g.R; ++r)
           for (int el = 0; el < wide_c; ++el) {
-            int sc = el / wide_cp - 4 + g.pad_l, c = el % wide_cp;
+            int sc = el / wide_cp - wide_lp + g.pad_l, c = el % wide_cp;
             if (sc < 0 || sc >= g.S || c >= g.C) continue;
             for (int64_t k = 0; k < K; ++k) w2[(size_t)((k * g.R + r) * wide_c + el)] = wf[(size_t)(((r * g.S + sc) * g.C + c) * K + k)];
           }
@@ -629,9 +668,10 @@ odla_status Builder::emit_fused(const Item& it) {
         int64_t pixels = (int64_t)g.N * g.H * g.W;
         ConvGeom gg = g;
         bool wide = widened, ov = overlap;
-        double scratch_bytes = ov ? 2.0 * g.N * g.H * (g.W + 8) * 8 : wide ? 2.0 * g.N * g.H * g.Q * 32 * esz : 2.0 * pixels * 32;
+        const int pbb = wide_pb, lpp = wide_lp, Wpp = wide_Wp;
+        double scratch_bytes = ov ? 2.0 * g.N * g.H * (double)Wpp * pbb : wide ? 2.0 * g.N * g.H * g.Q * 32 * esz : 2.0 * pixels * 32;
         add_launch("conv_umma", f.out, flops, bytes + scratch_bytes, [=](cudaStream_t s) {
-          int rc = ov ? stem_pad4(esz, x, padded, gg.N, gg.H, gg.W, C0, s)
+          int rc = ov ? stem_pad(esz, x, padded, gg.N, gg.H, gg.W, C0, pbb, lpp, Wpp, s)
                       : wide ? stem_widen(esz, x, padded, gg.N, gg.H, gg.W, C0, gg.Q, s) : pad_channels(esz, x, padded, pixels, C0, Cp, s);
           return rc ? rc : umma_conv_run(ul, s);
         });
@@ -688,9 +728,49 @@ odla_status Builder::emit_fused(const Item& it) {
   }
   double flops = 2.0 * batch * M * N * Kd;
   double bytes = tensor_bytes(f.x) + tensor_bytes(f.out) + (double)(br * bc * bbatch) * storage_size(in_dt);
+  // Head split / merge folded into the store.  When the tensor-core kernel cannot store through the permuted map
+  // (fp32 graphs, a sequence that does not fill 128-row boxes, ...) the product goes to scratch and is moved.
+  void* y_final = y;
+  MoveGeom perm_move{};
+  bool perm_via_move = false;
+  auto set_store = [&](UmmaConv& u) { u.store_mode = f.perm_mode; u.store_S = (int)f.perm_S; u.store_NH = (int)f.perm_NH; u.store_D = (int)f.perm_D; };
+  if (f.perm_mode) {
+    bool direct = false;
+    if (allow_umma && !ta) {
+      UmmaConv probe{1, 1, (int)(batch * M), (int)Kd, (int)N, 1, 1, 1, (int)(batch * M), 1, 1, 0, 0, in_dt};
+      if (f.w->kind != OP_CONST) { probe.w_batches = (int)batch; probe.rows_per_batch = (int)M; }
+      set_store(probe);
+      const bool shape_ok = f.w->kind == OP_CONST ? bbatch == 1
+                                                  : (bbatch == batch && batch > 1 && M % 128 == 0 && (in_dt == DT_F16 || in_dt == DT_BF16) && dt_[resolve(f.w)] == in_dt);
+      direct = shape_ok && batch * M < (1ll << 31) && umma_conv_supported(probe) && umma_store_perm_ok(probe, ep, y);
+    }
+    if (!direct) {
+      void* tmp = nullptr;
+      if (cudaMalloc(&tmp, (size_t)std::max<int64_t>(count(root) * storage_size(dt_[f.out]), 16)) != cudaSuccess) return fail(ODLA_MEM_ERROR, "scratch allocation failed");
+      p_->extra_allocs.push_back(tmp);
+      y = tmp;
+      perm_via_move = true;
+      // scratch is [B][X][Y][D] row-major (X, Y = S, NH for a split; NH, S for a merge); the result swaps X and Y
+      const int64_t X = f.perm_mode == 1 ? f.perm_S : f.perm_NH, Yd = f.perm_mode == 1 ? f.perm_NH : f.perm_S, D = f.perm_D;
+      const int64_t Bn = count(root) / (X * Yd * D);
+      perm_move.rank = 4;
+      perm_move.oshape[0] = Bn; perm_move.oshape[1] = Yd; perm_move.oshape[2] = X; perm_move.oshape[3] = D;
+      perm_move.istride[0] = X * Yd * D; perm_move.istride[1] = D; perm_move.istride[2] = Yd * D; perm_move.istride[3] = 1;
+      perm_move.ostride[0] = X * Yd * D; perm_move.ostride[1] = X * D; perm_move.ostride[2] = D; perm_move.ostride[3] = 1;
+    }
+  }
+  const bool store_direct = f.perm_mode && !perm_via_move;
+  const int out_esz = storage_size(dt_[f.out]);
+  // wraps a launch so that the scratch result is moved into place afterwards
+  auto with_move = [&](std::function<int(cudaStream_t)> fn) -> std::function<int(cudaStream_t)> {
+    if (!perm_via_move) return fn;
+    const void* src = y;
+    return [=](cudaStream_t s) { int rc = fn(s); return rc ? rc : move(perm_move, out_esz, src, y_final, s); };
+  };
   if (allow_umma && !ta && f.w->kind == OP_CONST && bbatch == 1) {
     int64_t Mt = batch * M;
     UmmaConv uc{1, 1, (int)Mt, (int)Kd, (int)N, 1, 1, 1, (int)Mt, 1, 1, 0, 0, in_dt};
+    if (store_direct) set_store(uc);
     if (Mt < (1ll << 31) && umma_conv_supported(uc)) {
       auto wf = const_as_f32(f.w);
       std::vector<float> w2;
@@ -702,7 +782,8 @@ odla_status Builder::emit_fused(const Item& it) {
       UmmaLaunch* ul = umma_conv_prepare(uc, x, wd, y, ep, p_->status, sms);
       if (!ul) return fail(ODLA_FAILURE, "'" + root->name + "': tensor-map encoding failed");
       p_->umma.push_back(ul);
-      add_launch("gemm_umma", f.out, flops, bytes, [ul](cudaStream_t s) { return umma_conv_run(ul, s); });
+      add_launch("gemm_umma", f.out, flops, bytes, with_move([ul](cudaStream_t s) { return umma_conv_run(ul, s); }));
+      if (perm_via_move) p_->launches.back().n_kernels = 2;
       return ODLA_SUCCESS;
     }
   }
@@ -713,6 +794,7 @@ odla_status Builder::emit_fused(const Item& it) {
     UmmaConv uc{1, 1, (int)(batch * M), (int)Kd, (int)N, 1, 1, 1, (int)(batch * M), 1, 1, 0, 0, in_dt};
     uc.w_batches = (int)batch;
     uc.rows_per_batch = (int)M;
+    if (store_direct) set_store(uc);
     if (umma_conv_supported(uc)) {
       const void* bsrc = dev_ptr(f.w);
       void* bt = nullptr;
@@ -729,11 +811,11 @@ odla_status Builder::emit_fused(const Item& it) {
       if (!ul) return fail(ODLA_FAILURE, "'" + root->name + "': tensor-map encoding failed");
       p_->umma.push_back(ul);
       int esz = storage_size(in_dt);
-      add_launch("gemm_umma", f.out, flops, bytes, [=](cudaStream_t s) {
+      add_launch("gemm_umma", f.out, flops, bytes, with_move([=](cudaStream_t s) {
         if (bt) { int rc = move(mg, esz, bsrc, bt, s); if (rc) return rc; }
         return umma_conv_run(ul, s);
-      });
-      p_->launches.back().n_kernels = bt ? 2 : 1;
+      }));
+      p_->launches.back().n_kernels = (bt ? 2 : 1) + (perm_via_move ? 1 : 0);
       return ODLA_SUCCESS;
     }
   }
@@ -748,7 +830,8 @@ odla_status Builder::emit_fused(const Item& it) {
     bp = dev_ptr(f.w);
   }
   if (!bp) return err_status_;
-  add_launch("gemm_simt", f.out, flops, bytes, [=](cudaStream_t s) { return gemm_simt(g, in_dt, x, bp, y, ep, s); });
+  add_launch("gemm_simt", f.out, flops, bytes, with_move([=](cudaStream_t s) { return gemm_simt(g, in_dt, x, bp, y, ep, s); }));
+  if (perm_via_move) p_->launches.back().n_kernels = 2;
   return ODLA_SUCCESS;
 }
 
