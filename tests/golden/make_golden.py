@@ -1,6 +1,6 @@
 """Generates tests/golden/ref_kernels.npz from the reference's own CPU kernels.
 
-Run in a checkout that has the reference mounted (default /root/reference):
+Run on a machine that has the reference tree (oracle/Makefile's REFERENCE variable points to it):
     make -C oracle ref && python tests/golden/make_golden.py
 It calls the _sn_rt_* functions of oracle/_ref/libhalo_rt_generic.so (compiled from the reference's
 runtime/generic/*.cc) on small seeded inputs and stores inputs and outputs, so the oracle
