@@ -88,6 +88,9 @@ struct UmmaConv {
   // (b, h, s) [mode 2] with s < store_S, the columns are head h x store_D [mode 1] or store_D [mode 2], and element
   // (b, h, s, d) goes to y[b][h][s][d] (mode 1: [B,S,NH*D] -> [B,NH,S,D]) or y[b][s][h][d] (mode 2: [B,NH,S,D] -> [B,S,NH,D]).
   int store_mode = 0, store_S = 0, store_NH = 0, store_D = 0;
+  // Row pitch of y in elements when it is wider than K (0 = K): lets an output with rows that are not 16-byte
+  // multiples use the TMA-store epilogue; columns K .. y_pitch-1 receive unspecified values.
+  int y_pitch = 0;
 };
 // True when the tensor-core kernel can run this problem.
 bool umma_conv_supported(const UmmaConv& p);
@@ -143,6 +146,8 @@ int dequantize(int dt_out, const void* q, void* x, const float* scale, const int
 
 // Type conversion between storage types (float<->float, int<->float with saturation to int8).
 int convert(int dt_in, int dt_out, const void* x, void* y, int64_t n, cudaStream_t stream);
+// y[r][0..K) = x[r][0..K) for rows of pitch Kp (>= K) in x and K in y, with the same type conversion.
+int convert_rows(int dt_in, int dt_out, const void* x, void* y, int64_t rows, int64_t K, int64_t Kp, cudaStream_t stream);
 
 // Generic gather-style movement: out[e] = in[src(e)] with src given by per-dimension strides and
 // an element offset (covers transpose, slice, concat parts, broadcast).  esz in bytes.

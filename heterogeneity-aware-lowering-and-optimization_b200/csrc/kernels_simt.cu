@@ -778,6 +778,18 @@ int convert(int dt_in, int dt_out, const void* x, void* y, int64_t n, cudaStream
   convert_kernel<<<grid_for(n, 256), 256, 0, s>>>(dt_in, dt_out, x, y, n);
   return check_launch();
 }
+__global__ void convert_rows_kernel(int dt_in, int dt_out, const void* x, void* y, int64_t rows, int64_t K, int64_t Kp) {
+  const int64_t total = rows * K;
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = e / K, k = e - r * K;
+    store_from_float(y, dt_out, e, load_as_float(x, dt_in, r * Kp + k));
+  }
+}
+int convert_rows(int dt_in, int dt_out, const void* x, void* y, int64_t rows, int64_t K, int64_t Kp, cudaStream_t s) {
+  if (rows * K <= 0) return 0;
+  convert_rows_kernel<<<grid_for(rows * K, 256), 256, 0, s>>>(dt_in, dt_out, x, y, rows, K, Kp);
+  return check_launch();
+}
 int move(const MoveGeom& g0, int esz, const void* x, void* y, cudaStream_t s) {
   MoveGeom g = g0;
   // Canonical form first: axes of extent 1 dropped, neighbours that are contiguous on both sides merged.

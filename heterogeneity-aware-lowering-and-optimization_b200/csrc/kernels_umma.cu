@@ -1076,7 +1076,9 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
   p.out_esz = storage_size_of(ep.out_dt);
   // The residual of a staged launch always comes through the staging box, so it must have the output's type.
   const bool res_ok = !ep.res || (ep.res_dt == ep.out_dt && (uintptr_t)ep.res % 16 == 0);
-  p.staged = (ep.out_dt == DT_F16 || ep.out_dt == DT_BF16 || ep.out_dt == DT_S8) && ((int64_t)c.K * p.out_esz) % 16 == 0 && !ep.add_full && res_ok &&
+  const int64_t y_cols = c.y_pitch > 0 ? c.y_pitch : c.K;  // row pitch of y in elements
+  p.staged = (ep.out_dt == DT_F16 || ep.out_dt == DT_BF16 || ep.out_dt == DT_S8) && (y_cols * p.out_esz) % 16 == 0 && !ep.add_full && res_ok &&
+             (c.y_pitch == 0 || (c.y_pitch >= c.K && !ep.res && c.store_mode == 0)) &&
              ((uintptr_t)y % 16 == 0) && !getenv("ODLA_B200_DIRECT_EPILOGUE");
   p.stage_boxes = p.staged ? (p.BN * p.out_esz + 127) / 128 : 0;
   p.res_tma = p.staged && ep.res;
@@ -1114,6 +1116,7 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
   p.acc_int = c.in_dt == DT_S8;
   p.store_mode = c.store_mode; p.store_S = c.store_S; p.store_NH = c.store_NH;
   if (p.store_mode && (!p.staged || !umma_store_perm_ok(c, ep, y))) { delete L; return nullptr; }
+  if (c.y_pitch > 0 && !p.staged) { delete L; return nullptr; }  // the direct epilogue writes rows of K elements
   p.rows_per_batch = c.w_batches > 0 ? c.rows_per_batch : 0;
   p.tmem_cols = 2 * p.BN;  // 128, 256 or 512: powers of two >= 32
   const uint32_t fmt = c.in_dt == DT_BF16 ? 1u : (c.in_dt == DT_S8 ? 1u : 0u);      // bf16 / signed 8-bit / f16
@@ -1180,8 +1183,8 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
   if (r != CUDA_SUCCESS) { fprintf(stderr, "[odla_b200] tensor map (B) encode failed: %d\n", (int)r); delete L; return nullptr; }
   if (p.staged) {
     const CUtensorMapDataType odt = p.out_esz == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16;
-    cuuint64_t dims[2] = {(cuuint64_t)c.K, (cuuint64_t)p.M_total};
-    cuuint64_t strides[1] = {(cuuint64_t)c.K * p.out_esz};
+    cuuint64_t dims[2] = {(cuuint64_t)y_cols, (cuuint64_t)p.M_total};
+    cuuint64_t strides[1] = {(cuuint64_t)y_cols * p.out_esz};
     cuuint32_t box[2] = {(cuuint32_t)(128 / p.out_esz), (cuuint32_t)BM};
     cuuint32_t estr[2] = {1, 1};
     if (p.store_mode) {

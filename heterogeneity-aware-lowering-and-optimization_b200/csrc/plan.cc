@@ -167,6 +167,7 @@ class Builder {
   std::map<V, int> dq_unabsorbed_;     // Dequantize node -> number of consumers that need it in memory
   std::map<V, V> alias_;               // reshape output -> source
   std::map<V, int> dt_;                // storage type of materialised values
+  std::map<V, int64_t> pitch_;          // internal row pitch (elements) of an output whose rows TMA could not store otherwise
   std::vector<Item> items_;
   std::map<std::pair<V, int>, void*> const_cache_;
   std::string err_;
@@ -443,7 +444,31 @@ odla_status Builder::place() {
   std::map<V, int> last;
   for (size_t i = 0; i < items_.size(); ++i)
     for (V r : items_[i].reads) last[resolve(r)] = (int)i;
-  auto bytes_of = [&](V v) { return count(v) * storage_size(dt_[v]); };
+  // A channels-last convolution that ends the graph with an odd channel count (YOLO's 255-channel heads) has rows
+  // that are not 16-byte multiples, which would push it off the TMA-store epilogue.  When only the output conversion
+  // reads it, its internal rows are padded to the next multiple of 8 channels and the conversion drops the padding.
+  for (auto& it : items_) {
+    V v = it.out;
+    if (!it.fused || it.fused->root->kind != OP_CONV || !it.fused->root->ia[0] || !v->is_output || users_[v] != 0 || alias_.count(v)) continue;
+    if (!(dt_[v] == DT_F16 || dt_[v] == DT_BF16) || api_dt(v->type.element_type) == dt_[v] || getenv("ODLA_B200_NO_PITCH")) continue;
+    // only where the tensor-core kernel with the staged epilogue is certain to run
+    if (getenv("ODLA_B200_NO_UMMA") || getenv("ODLA_B200_DIRECT_EPILOGUE") || it.fused->root->ia[1] != 1 || it.fused->res) continue;
+    {
+      const auto& xs = it.fused->root->in[0]->type.shape;
+      const int64_t cin_bytes = xs.dims[xs.size - 1] * 2;
+      if (cin_bytes % 16 != 0 || cin_bytes < 32) continue;
+    }
+    const auto& sh = v->type.shape;
+    const int64_t K = sh.dims[sh.size - 1];
+    bool aliased = false;
+    for (auto& kv : alias_) if (resolve(kv.first) == v) aliased = true;
+    if ((K * 2) % 16 != 0 && !aliased) pitch_[v] = (K + 7) / 8 * 8;
+  }
+  auto bytes_of = [&](V v) {
+    auto pi = pitch_.find(v);
+    if (pi != pitch_.end()) { const auto& sh = v->type.shape; return count(v) / sh.dims[sh.size - 1] * pi->second * storage_size(dt_[v]); }
+    return count(v) * storage_size(dt_[v]);
+  };
   for (V a : c_->args) {
     Slot s; s.dt = dt_[a]; s.bytes = bytes_of(a); s.offset = arena.alloc(s.bytes);
     p_->slots[a] = s;
@@ -660,6 +685,7 @@ odla_status Builder::emit_fused(const Item& it) {
       auto wb = f32_to_storage(w2, in_dt);
       void* wd = upload(wb.data(), wb.size());
       if (!wd) return err_status_;
+      if (pitch_.count(f.out)) uc.y_pitch = (int)pitch_[f.out];
       UmmaLaunch* ul = umma_conv_prepare(uc, x_umma, wd, y, ep, p_->status, sms);
       if (!ul) return fail(ODLA_FAILURE, "'" + root->name + "': tensor-map encoding failed");
       p_->umma.push_back(ul);
@@ -1122,6 +1148,12 @@ odla_status Builder::emit() {
     int sdt = dt_[r], ddt = api_dt(io.v->type.element_type);
     int64_t n = count(io.v);
     Launch l; l.op = "convert_out"; l.name = io.v->name; l.bytes = (double)io.api_bytes + (double)n * storage_size(sdt);
+    auto pi = pitch_.find(r);
+    if (pi != pitch_.end()) {
+      const auto& sh = r->type.shape;
+      const int64_t K = sh.dims[sh.size - 1], Kp = pi->second, rows = n / K;
+      l.fn = [=](cudaStream_t s) { return convert_rows(sdt, ddt, src, dst, rows, K, Kp, s); };
+    } else
     l.fn = [=](cudaStream_t s) { return convert(sdt, ddt, src, dst, n, s); };
     p_->launches.push_back(std::move(l));
   }
