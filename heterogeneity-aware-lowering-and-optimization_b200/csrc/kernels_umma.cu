@@ -13,9 +13,15 @@
 // One persistent CTA per SM walks its tiles (128 pixels x BN channels):
 //   warp 0      producer: waits for a free stage, arms its mbarrier with the byte count, issues TMA
 //   warp 1      allocates tensor memory, issues tcgen05.mma (one lane), commits to mbarriers
-//   next 8 or 16 warps: epilogue (two more warps feed and drain its shared-memory staging ring): tcgen05.ld the fp32 / int32 accumulators (one TMEM lane = one output pixel
-//               per thread), apply the fused epilogue, store NHWC rows with 16-byte stores
+//   16 warps    staged epilogue: tcgen05.ld the fp32 / int32 accumulators (one TMEM lane = one output pixel per
+//               thread), apply the fused epilogue, write 16-byte pieces into a ring of 128-row x 128-byte boxes
+//   2 warps     feed the ring (TMA loads of residual boxes) and drain it (TMA stores, plain or through a 4-d map
+//               of a head-permuted tensor)
+//   (the direct variant, for fp32 / int32 outputs, runs 8 epilogue warps that store rows straight to global memory)
 // Two accumulator buffers in tensor memory let the epilogue of tile i overlap the MMAs of tile i+1.
+//
+// The CTA-pair variant (clusters of two, tcgen05 cta_group::2) computes 256-row tiles across two SMs: each CTA
+// loads its own rows of A and half of the filter tile, the first CTA issues the MMAs for both.
 //
 // Every mbarrier wait is bounded: when the limit expires the waiter records a code in the
 // plan's status word, raises a CTA-wide abort flag, and every role falls through to the common
