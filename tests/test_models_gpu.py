@@ -275,7 +275,8 @@ def test_sub_batches_pipeline_one_gpu(odla, gpu_lib, models, rn_weights):
         descs.append(g.describe())
         g.close()
     assert [d.count("gpu ") for d in descs] == [1, 2, 4, 6]        # never more sub-batches than images
-    assert "rows [0,3)" in descs[1] and "rows [3,6)" in descs[1] and "rows [4,5)" in descs[2]
+    # inputs are the larger transfer here, so the sub-batches grow (1 : 3 : 9 ...): the exposed first copy is short
+    assert "rows [0,1)" in descs[1] and "rows [1,6)" in descs[1] and "rows [0,1)" in descs[2] and "rows [3,6)" in descs[2]
     for o in outs[1:]:
         assert np.array_equal(o, outs[0])
 
