@@ -501,6 +501,12 @@ __device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, float (&v)[C
   }
 }
 
+// Two fp32 additions in one instruction (add.rn.f32x2, sm_100): same rounding as two __fadd_rn.
+__device__ __forceinline__ void fadd2_rn(float& a0, float& a1, float b0, float b1) {
+  asm("{\n\t.reg .b64 x, y;\n\tmov.b64 x, {%0, %1};\n\tmov.b64 y, {%2, %3};\n\tadd.rn.f32x2 x, x, y;\n\tmov.b64 {%0, %1}, x;\n\t}"
+      : "+f"(a0), "+f"(a1)
+      : "f"(b0), "f"(b1));
+}
 // The staged epilogue's chunk: 16 consecutive channels of one output row, residual read from and result
 // written to the row's place in the staging box.  Only what a staged launch can need is here (the launcher
 // sends everything else to the direct epilogue), so the loop around it stays small.
@@ -522,12 +528,12 @@ __device__ __forceinline__ void epilogue_chunk_staged(const UmmaParams& p, float
   if (ep.add1) {
     load_vec<16>(ep.add1, col0, kmax, full, cv);
 #pragma unroll
-    for (int j = 0; j < 16; ++j) v[j] = __fadd_rn(v[j], cv[j]);
+    for (int j = 0; j < 16; j += 2) fadd2_rn(v[j], v[j + 1], cv[j], cv[j + 1]);
   }
   if (ep.add2) {
     load_vec<16>(ep.add2, col0, kmax, full, cv);
 #pragma unroll
-    for (int j = 0; j < 16; ++j) v[j] = __fadd_rn(v[j], cv[j]);
+    for (int j = 0; j < 16; j += 2) fadd2_rn(v[j], v[j + 1], cv[j], cv[j + 1]);
   }
   if (ANYACT && ep.act_first) apply_act_all<16>(ep.act, v, ep.act_a, ep.act_b);
   if (p.res_tma) {
@@ -546,18 +552,19 @@ __device__ __forceinline__ void epilogue_chunk_staged(const UmmaParams& p, float
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
           const float2 f = OUT == DT_F16 ? __half22float2(((const __half2*)&u)[t]) : __bfloat1622float2(((const __nv_bfloat162*)&u)[t]);
-          v[q * 8 + 2 * t] = __fadd_rn(v[q * 8 + 2 * t], f.x);
-          v[q * 8 + 2 * t + 1] = __fadd_rn(v[q * 8 + 2 * t + 1], f.y);
+          fadd2_rn(v[q * 8 + 2 * t], v[q * 8 + 2 * t + 1], f.x, f.y);
         }
       }
     }
   }
   if (ANYACT) {
     if (!ep.act_first) apply_act_all<16>(ep.act, v, ep.act_a, ep.act_b);
-  } else if (ep.act == ACT_RELU) {
+  } else if (ep.act == ACT_RELU && OUT == DT_S8) {
 #pragma unroll
     for (int j = 0; j < 16; ++j) v[j] = fmaxf(v[j], 0.f);
   }
+  // (two-byte outputs take their ReLU after packing, two values per instruction: rounding is monotonic and keeps the sign)
+  const bool relu_packed = !ANYACT && ep.act == ACT_RELU && OUT != DT_S8;
   if (OUT == DT_S8) {
     uint4 u;
     uint32_t* w = (uint32_t*)&u;
@@ -579,11 +586,17 @@ __device__ __forceinline__ void epilogue_chunk_staged(const UmmaParams& p, float
       if (OUT == DT_F16) {
         __half2* h = (__half2*)&u;
 #pragma unroll
-        for (int t = 0; t < 4; ++t) h[t] = __floats2half2_rn(v[q * 8 + 2 * t], v[q * 8 + 2 * t + 1]);
+        for (int t = 0; t < 4; ++t) {
+          h[t] = __floats2half2_rn(v[q * 8 + 2 * t], v[q * 8 + 2 * t + 1]);
+          if (relu_packed) h[t] = __hmax2(h[t], __float2half2_rn(0.f));
+        }
       } else {
         __nv_bfloat162* h = (__nv_bfloat162*)&u;
 #pragma unroll
-        for (int t = 0; t < 4; ++t) h[t] = __floats2bfloat162_rn(v[q * 8 + 2 * t], v[q * 8 + 2 * t + 1]);
+        for (int t = 0; t < 4; ++t) {
+          h[t] = __floats2bfloat162_rn(v[q * 8 + 2 * t], v[q * 8 + 2 * t + 1]);
+          if (relu_packed) h[t] = __hmax2(h[t], __float2bfloat162_rn(0.f));
+        }
       }
       sts128(stage_piece(sp, q), u);
     }
