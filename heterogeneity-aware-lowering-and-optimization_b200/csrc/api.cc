@@ -11,6 +11,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <set>
 #include <mutex>
 
 #include "common.h"
@@ -250,7 +251,19 @@ odla_status odla_CreateComputation(odla_computation* computation) {
   return ODLA_SUCCESS;
 }
 odla_status odla_DestroyComputation(odla_computation computation) {
+  if (!computation) return ODLA_SUCCESS;
   if (g_comp == computation) g_comp = nullptr;
+  // Callers may destroy the computation before its contexts, even right after an asynchronous execute
+  // (ODLA/platforms/odla_popart/test/odla_compute_test.cc:302-309): wait for that work and detach the contexts.
+  std::set<odla_context> ctxs;
+  {
+    std::lock_guard<std::mutex> lock(computation->ctx_mutex);
+    ctxs.swap(computation->contexts);
+  }
+  for (odla_context ctx : ctxs) {
+    if (ctx->worker.joinable()) ctx->worker.join();
+    ctx->comp = nullptr;
+  }
   delete computation;
   return ODLA_SUCCESS;
 }
@@ -316,10 +329,19 @@ odla_status odla_CreateContext(odla_context* context) {
   }
   *context = new _odla_context();
   (*context)->comp = g_comp;
+  {
+    std::lock_guard<std::mutex> lock(g_comp->ctx_mutex);
+    g_comp->contexts.insert(*context);
+  }
   return ODLA_SUCCESS;
 }
 odla_status odla_DestroyContext(odla_context context) {
-  if (context && context->worker.joinable()) context->worker.join();  // an asynchronous execute still owns the bindings
+  if (!context) return ODLA_SUCCESS;
+  if (context->worker.joinable()) context->worker.join();  // an asynchronous execute still owns the bindings
+  if (context->comp) {
+    std::lock_guard<std::mutex> lock(context->comp->ctx_mutex);
+    context->comp->contexts.erase(context);
+  }
   delete context;
   return ODLA_SUCCESS;
 }

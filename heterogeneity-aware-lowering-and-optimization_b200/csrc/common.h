@@ -11,6 +11,7 @@
 #include <map>
 #include <memory>
 #include <mutex>
+#include <set>
 #include <string>
 #include <thread>
 #include <vector>
@@ -133,6 +134,7 @@ struct Replica {
 
 }  // namespace b200
 
+struct _odla_context;
 struct _odla_computation {
   std::vector<std::unique_ptr<_odla_value>> nodes;
   std::vector<odla_value> args, outs;
@@ -156,6 +158,8 @@ struct _odla_computation {
   int64_t graph_batch = 1;         // dim 0 of the recorded graph
   std::map<int64_t, std::vector<b200::Replica>> batch_replicas;  // plans for other run batch sizes (ODLA_RUN_BATCH_SIZE)
   std::mutex exec_mutex;           // executions of one computation share its arenas: one at a time
+  std::mutex ctx_mutex;            // guards `contexts`
+  std::set<_odla_context*> contexts;  // live contexts created for this computation
   ~_odla_computation();
 };
 

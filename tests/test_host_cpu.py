@@ -225,7 +225,13 @@ def test_async_execute_reports_failure_through_the_callback_without_a_gpu(odla, 
         h = odla.Graph(lib, "async2")
         h.Output(h.Relu(h.Argument("x", (4, 8)), "y"))
         assert h.execute_async() == odla.INVALID_PARAM
-        h.close()
+        # destroying the computation before its context is allowed; the context is detached
+        ctx = h.context()
+        assert lib.DestroyComputation(h.comp) == 0
+        buf = np.zeros((4, 8), np.float32)
+        assert lib.BindToArgumentById(b"x", buf.ctypes.data, ctx) == odla.INVALID_PARAM
+        assert lib.DestroyContext(ctx) == 0
+        h.comp, h.ctx = odla._V(), None
     finally:
         lib.SetLogLevel(3)
     g.close()
