@@ -593,7 +593,7 @@ odla_status Builder::emit_fused(const Item& it) {
     // 16 / stride_w bytes those taps lie inside one 64-byte window that starts 16 bytes after the window of column
     // q-1, so the column taps collapse into the channel axis: an (R x S) convolution over few channels becomes an
     // (R x 1) convolution over 64-byte "widened pixels" with unit column stride.
-    int wide_pb = 8, wide_lp = 4, wide_Wp = 0;   // pixel bytes, zero pixels on the left, padded row length (overlapping form)
+    int wide_pb = 8, wide_lp = 4, wide_Wp = 0, wide_gq = 1;   // pixel bytes, zero pixels on the left, padded row length, columns per group (overlapping form)
     if (small_c && (g.stride_w == 1 || g.stride_w == 2) && g.S <= 4 * g.stride_w && g.C * storage_size(in_dt) <= 16 / g.stride_w &&
         !getenv("ODLA_B200_NO_WIDEN")) {
       const int esz0 = storage_size(in_dt);
@@ -605,16 +605,27 @@ odla_status Builder::emit_fused(const Item& it) {
       // than the pixel size describes directly.  If the driver refuses such a map, a stride-2 stem falls back to a
       // materialised widened copy, others to plain channel padding.
       if (umma_conv_supported(uw) && !getenv("ODLA_B200_NO_OVERLAP")) {
-        const int pb = 16 / g.stride_w, wp = 64 / pb;
-        int Wp = std::max(g.pad_l + g.W, (g.Q - 1) * g.stride_w + wp);
+        const int pb = 16 / g.stride_w;
+        // Column groups: gq neighbouring output columns share one 128-byte window (their taps span
+        // (gq-1)*stride_w + S pixels) and become gq*K "channels" of one output pixel -- the same bytes in memory.
+        // That divides the number of rows the TMA unit has to deliver, which is what bounds a stem, by gq and gives
+        // the tensor pipe gq times wider instructions.
+        int gq = 1;
+        if (!f.res && !getenv("ODLA_B200_NO_COLUMN_GROUPS"))
+          for (int cand = 4; cand >= 2; cand /= 2)
+            if (g.Q % cand == 0 && (int64_t)cand * K <= 256 && (cand - 1) * g.stride_w + g.S <= 128 / pb) { gq = cand; break; }
+        const int win_bytes = gq > 1 ? 128 : 64, wp = win_bytes / pb;
+        int Wp = std::max(g.pad_l + g.W, (g.Q / gq - 1) * gq * g.stride_w + wp);
         Wp = (Wp + 1) & ~1;  // rows are 16-byte multiples also with 8-byte pixels
         UmmaConv uo = uw;
-        uo.x_w_stride = 16;
+        uo.C = win_bytes / esz0;
+        uo.W = g.Q / gq; uo.Q = g.Q / gq; uo.K = (int)(K * gq);
+        uo.x_w_stride = (long long)gq * g.stride_w * pb;
         uo.x_h_stride = (long long)Wp * pb;
         uo.x_n_stride = uo.x_h_stride * g.H;
         void* padbuf = nullptr;
         size_t pbytes = (size_t)uo.x_n_stride * g.N + 256;
-        if (!inject_fault("alloc") && cudaMalloc(&padbuf, pbytes) == cudaSuccess) {
+        if (umma_conv_supported(uo) && !inject_fault("alloc") && cudaMalloc(&padbuf, pbytes) == cudaSuccess) {
           Epilogue probe_ep;
           probe_ep.out_dt = DT_F32;
           UmmaLaunch* probe = umma_conv_prepare(uo, padbuf, padbuf, padbuf, probe_ep, p_->status, sms);
@@ -627,7 +638,14 @@ odla_status Builder::emit_fused(const Item& it) {
             widened = true;
             overlap = true;
             wide_c = uo.C;
-            wide_pb = pb; wide_cp = pb / esz0; wide_lp = g.pad_l; wide_Wp = Wp;
+            wide_pb = pb; wide_cp = pb / esz0; wide_lp = g.pad_l; wide_Wp = Wp; wide_gq = gq;
+            if (gq > 1) {
+              // per-channel vectors repeat for every column of the group
+              auto tile = [&](const std::vector<float>& v) { std::vector<float> t; t.reserve(v.size() * gq); for (int r = 0; r < gq; ++r) t.insert(t.end(), v.begin(), v.end()); return upload_f32(t); };
+              if (ep.mul) { auto sx = const_as_f32(f.x_scale), sw = const_as_f32(f.w_scale); std::vector<float> m((size_t)K); for (int64_t k = 0; k < K; ++k) m[k] = sx[0] * sw[sw.size() == 1 ? 0 : k]; ep.mul = tile(m); }
+              if (ep.add1) ep.add1 = tile(const_as_f32(root->in[2]));
+              if (ep.add2) ep.add2 = tile(const_as_f32(f.add_const));
+            }
           } else {
             cudaFree(padbuf);
           }
@@ -667,15 +685,17 @@ odla_status Builder::emit_fused(const Item& it) {
       int64_t rs = (int64_t)g.R * g.S;
       std::vector<float> w2;
       if (widened) {
-        // [K][R][wide_c]: element el of a widened pixel is window pixel el / cp, channel el % cp; the window starts wide_lp
-        // pixels left of column q*stride_w, the taps pad_l pixels left of it: filter column = el / cp - wide_lp + pad_l
-        w2.assign((size_t)(K * g.R * wide_c), 0.f);
-        for (int64_t r = 0; r < g.R; ++r)
-          for (int el = 0; el < wide_c; ++el) {
-            int sc = el / wide_cp - wide_lp + g.pad_l, c = el % wide_cp;
-            if (sc < 0 || sc >= g.S || c >= g.C) continue;
-            for (int64_t k = 0; k < K; ++k) w2[(size_t)((k * g.R + r) * wide_c + el)] = wf[(size_t)(((r * g.S + sc) * g.C + c) * K + k)];
-          }
+        // [gq*K][R][wide_c]: element el of a window is pixel el / cp, channel el % cp; the window starts wide_lp pixels
+        // left of column (q - q % gq) * stride_w, the taps of the group's column j start pad_l - j*stride_w pixels left
+        // of it: filter column = el / cp - wide_lp + pad_l - j * stride_w
+        w2.assign((size_t)(K * wide_gq * g.R * wide_c), 0.f);
+        for (int j = 0; j < wide_gq; ++j)
+          for (int64_t r = 0; r < g.R; ++r)
+            for (int el = 0; el < wide_c; ++el) {
+              int sc = el / wide_cp - wide_lp + g.pad_l - j * g.stride_w, c = el % wide_cp;
+              if (sc < 0 || sc >= g.S || c >= g.C) continue;
+              for (int64_t k = 0; k < K; ++k) w2[(size_t)(((j * K + k) * g.R + r) * wide_c + el)] = wf[(size_t)(((r * g.S + sc) * g.C + c) * K + k)];
+            }
       } else {
         w2.assign((size_t)(K * rs * Cp), 0.f);
         for (int64_t t = 0; t < rs; ++t)
