@@ -309,12 +309,23 @@ template <> __device__ __forceinline__ float2 pair_to_float2<__nv_bfloat16>(uint
 template <typename T> __device__ __forceinline__ uint32_t float2_to_pair(float a, float b);
 template <> __device__ __forceinline__ uint32_t float2_to_pair<__half>(float a, float b) { __half2 h = __floats2half2_rn(a, b); return *(uint32_t*)&h; }
 template <> __device__ __forceinline__ uint32_t float2_to_pair<__nv_bfloat16>(float a, float b) { __nv_bfloat162 h = __floats2bfloat162_rn(a, b); return *(uint32_t*)&h; }
-template <typename T, int NP>
-__device__ __forceinline__ void load_row_pieces(const uint4* row, int pieces, int lane, float (&v)[NP][8], bool (&have)[NP]) {
+// LPR lanes share a row (32, 16 or 8: short rows put several rows in one warp); lane l of the row holds pieces l, l + LPR, ...
+template <int LPR> __device__ __forceinline__ float group_max(float v) {
+#pragma unroll
+  for (int o = LPR / 2; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+template <int LPR> __device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+  for (int o = LPR / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+template <typename T, int NP, int LPR>
+__device__ __forceinline__ void load_row_pieces(const uint4* row, int pieces, int l, bool row_ok, float (&v)[NP][8], bool (&have)[NP]) {
 #pragma unroll
   for (int i = 0; i < NP; ++i) {
-    const int pc = lane + 32 * i;
-    have[i] = pc < pieces;
+    const int pc = l + LPR * i;
+    have[i] = row_ok && pc < pieces;
     if (have[i]) {
       const uint4 u = row[pc];
       const uint32_t w[4] = {u.x, u.y, u.z, u.w};
@@ -323,14 +334,17 @@ __device__ __forceinline__ void load_row_pieces(const uint4* row, int pieces, in
     }
   }
 }
-template <typename T, int NP>
+template <typename T, int NP, int LPR>
 __global__ void softmax_rows_vec_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, int64_t rows, int pieces, int log_form) {
-  const int lane = threadIdx.x & 31;
+  constexpr int RPW = 32 / LPR;  // rows per warp
+  const int lane = threadIdx.x & 31, l = lane % LPR;
   const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-  for (int64_t row = warp; row < rows; row += nwarps) {
+  for (int64_t row0 = warp * RPW; row0 < rows; row0 += nwarps * RPW) {  // uniform across the warp: every lane reaches the shuffles
+    const int64_t row = row0 + lane / LPR;
+    const bool row_ok = row < rows;
     float v[NP][8];
     bool have[NP];
-    load_row_pieces<T, NP>(x + row * pieces, pieces, lane, v, have);
+    load_row_pieces<T, NP, LPR>(x + row * pieces, pieces, l, row_ok, v, have);
     float mx = -3.402823466e+38f;
 #pragma unroll
     for (int i = 0; i < NP; ++i)
@@ -338,15 +352,16 @@ __global__ void softmax_rows_vec_kernel(const uint4* __restrict__ x, uint4* __re
 #pragma unroll
         for (int j = 0; j < 8; ++j) mx = fmaxf(mx, v[i][j]);
       }
-    mx = warp_max(mx);
+    mx = group_max<LPR>(mx);
     float sum = 0.f;
+    float e[NP][8];
 #pragma unroll
     for (int i = 0; i < NP; ++i)
       if (have[i]) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) { v[i][j] -= mx; sum += expf(v[i][j]); }
+        for (int j = 0; j < 8; ++j) { v[i][j] -= mx; e[i][j] = expf(v[i][j]); sum += e[i][j]; }
       }
-    sum = warp_sum(sum);
+    sum = group_sum<LPR>(sum);
     const float lsum = logf(sum);
 #pragma unroll
     for (int i = 0; i < NP; ++i)
@@ -354,24 +369,28 @@ __global__ void softmax_rows_vec_kernel(const uint4* __restrict__ x, uint4* __re
         uint32_t w[4];
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
-          const float a = log_form ? v[i][2 * t] - lsum : __fdiv_rn(expf(v[i][2 * t]), sum);
-          const float b = log_form ? v[i][2 * t + 1] - lsum : __fdiv_rn(expf(v[i][2 * t + 1]), sum);
+          // e[][] holds exp(x - max) from the summation pass
+          const float a = log_form ? v[i][2 * t] - lsum : __fdiv_rn(e[i][2 * t], sum);
+          const float b = log_form ? v[i][2 * t + 1] - lsum : __fdiv_rn(e[i][2 * t + 1], sum);
           w[t] = float2_to_pair<T>(a, b);
         }
-        y[row * pieces + lane + 32 * i] = make_uint4(w[0], w[1], w[2], w[3]);
+        y[row * pieces + l + LPR * i] = make_uint4(w[0], w[1], w[2], w[3]);
       }
   }
 }
-template <typename T, int NP>
+template <typename T, int NP, int LPR>
 __global__ void layernorm_rows_vec_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, const float* __restrict__ gamma, const float* __restrict__ beta,
                                           int64_t rows, int pieces, float eps) {
-  const int lane = threadIdx.x & 31;
+  constexpr int RPW = 32 / LPR;
+  const int lane = threadIdx.x & 31, l = lane % LPR;
   const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
   const float dim = (float)(pieces * 8);
-  for (int64_t row = warp; row < rows; row += nwarps) {
+  for (int64_t row0 = warp * RPW; row0 < rows; row0 += nwarps * RPW) {
+    const int64_t row = row0 + lane / LPR;
+    const bool row_ok = row < rows;
     float v[NP][8];
     bool have[NP];
-    load_row_pieces<T, NP>(x + row * pieces, pieces, lane, v, have);
+    load_row_pieces<T, NP, LPR>(x + row * pieces, pieces, l, row_ok, v, have);
     float s = 0.f;
 #pragma unroll
     for (int i = 0; i < NP; ++i)
@@ -379,7 +398,7 @@ __global__ void layernorm_rows_vec_kernel(const uint4* __restrict__ x, uint4* __
 #pragma unroll
         for (int j = 0; j < 8; ++j) s += v[i][j];
       }
-    const float mean = warp_sum(s) / dim;
+    const float mean = group_sum<LPR>(s) / dim;
     float q = 0.f;
 #pragma unroll
     for (int i = 0; i < NP; ++i)
@@ -387,38 +406,44 @@ __global__ void layernorm_rows_vec_kernel(const uint4* __restrict__ x, uint4* __
 #pragma unroll
         for (int j = 0; j < 8; ++j) { v[i][j] -= mean; q += v[i][j] * v[i][j]; }
       }
-    const float inv = 1.0f / sqrtf(warp_sum(q) / dim + eps);
+    const float inv = 1.0f / sqrtf(group_sum<LPR>(q) / dim + eps);
 #pragma unroll
     for (int i = 0; i < NP; ++i)
       if (have[i]) {
-        const int d0 = (lane + 32 * i) * 8;
+        const int d0 = (l + LPR * i) * 8;
+        float gm[8], bt[8];
+        if (gamma) { const float4 g0 = *(const float4*)(gamma + d0), g1 = *(const float4*)(gamma + d0 + 4); gm[0] = g0.x; gm[1] = g0.y; gm[2] = g0.z; gm[3] = g0.w; gm[4] = g1.x; gm[5] = g1.y; gm[6] = g1.z; gm[7] = g1.w; }
+        if (beta) { const float4 b0 = *(const float4*)(beta + d0), b1 = *(const float4*)(beta + d0 + 4); bt[0] = b0.x; bt[1] = b0.y; bt[2] = b0.z; bt[3] = b0.w; bt[4] = b1.x; bt[5] = b1.y; bt[6] = b1.z; bt[7] = b1.w; }
         uint32_t w[4];
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
           float a = v[i][2 * t] * inv, b = v[i][2 * t + 1] * inv;
-          if (gamma) { a *= gamma[d0 + 2 * t]; b *= gamma[d0 + 2 * t + 1]; }
-          if (beta) { a += beta[d0 + 2 * t]; b += beta[d0 + 2 * t + 1]; }
+          if (gamma) { a *= gm[2 * t]; b *= gm[2 * t + 1]; }
+          if (beta) { a += bt[2 * t]; b += bt[2 * t + 1]; }
           w[t] = float2_to_pair<T>(a, b);
         }
-        y[row * pieces + lane + 32 * i] = make_uint4(w[0], w[1], w[2], w[3]);
+        y[row * pieces + l + LPR * i] = make_uint4(w[0], w[1], w[2], w[3]);
       }
   }
 }
 template <typename T>
 bool launch_rows_vec(bool is_softmax, const void* x, void* y, const float* gamma, const float* beta, int64_t rows, int64_t dim, float eps, int log_form,
                      cudaStream_t s) {
-  if (dim % 8 != 0 || dim > 8 * 32 * 8 || (uintptr_t)x % 16 != 0 || (uintptr_t)y % 16 != 0) return false;
-  const int pieces = (int)(dim / 8), np = (pieces + 31) / 32;
-  const int grid = grid_for(rows * 32, 256);
-#define B2_ROWS(NP)                                                                                                                      \
-  do {                                                                                                                                   \
-    if (is_softmax) softmax_rows_vec_kernel<T, NP><<<grid, 256, 0, s>>>((const uint4*)x, (uint4*)y, rows, pieces, log_form);             \
-    else layernorm_rows_vec_kernel<T, NP><<<grid, 256, 0, s>>>((const uint4*)x, (uint4*)y, gamma, beta, rows, pieces, eps);              \
+  if (dim % 8 != 0 || dim > 8 * 32 * 8 || (uintptr_t)x % 16 != 0 || (uintptr_t)y % 16 != 0 || (uintptr_t)gamma % 16 != 0 || (uintptr_t)beta % 16 != 0) return false;
+  const int pieces = (int)(dim / 8);
+  const int lpr = pieces <= 8 ? 8 : (pieces <= 16 ? 16 : 32), np = (pieces + lpr - 1) / lpr;
+  const int grid = grid_for(rows * lpr, 256);
+#define B2_ROWS(NP, LPR)                                                                                                                      \
+  do {                                                                                                                                        \
+    if (is_softmax) softmax_rows_vec_kernel<T, NP, LPR><<<grid, 256, 0, s>>>((const uint4*)x, (uint4*)y, rows, pieces, log_form);             \
+    else layernorm_rows_vec_kernel<T, NP, LPR><<<grid, 256, 0, s>>>((const uint4*)x, (uint4*)y, gamma, beta, rows, pieces, eps);              \
   } while (0)
-  if (np <= 1) B2_ROWS(1);
-  else if (np <= 2) B2_ROWS(2);
-  else if (np <= 4) B2_ROWS(4);
-  else B2_ROWS(8);
+  if (lpr == 8) B2_ROWS(1, 8);
+  else if (lpr == 16) B2_ROWS(1, 16);
+  else if (np <= 1) B2_ROWS(1, 32);
+  else if (np <= 2) B2_ROWS(2, 32);
+  else if (np <= 4) B2_ROWS(4, 32);
+  else B2_ROWS(8, 32);
 #undef B2_ROWS
   return true;
 }
