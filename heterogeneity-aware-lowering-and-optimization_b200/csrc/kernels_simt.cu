@@ -815,6 +815,41 @@ int convert_rows(int dt_in, int dt_out, const void* x, void* y, int64_t rows, in
   convert_rows_kernel<<<grid_for(rows * K, 256), 256, 0, s>>>(dt_in, dt_out, x, y, rows, K, Kp);
   return check_launch();
 }
+// out[b][n][k] = in[b][k][n]: the last two axes swapped, through 32 x 32 shared-memory tiles so that both the reads
+// (along n) and the writes (along k) are contiguous.
+template <typename T>
+__global__ void transpose_last2_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t in_off, int64_t out_off, int N, int K, int tiles_n, int tiles_k) {
+  __shared__ T tile[32][33];
+  const int64_t b = blockIdx.x / (tiles_n * tiles_k);
+  const int t = (int)(blockIdx.x % (tiles_n * tiles_k));
+  const int n0 = (t % tiles_n) * 32, k0 = (t / tiles_n) * 32;
+  const T* src = x + in_off + b * (int64_t)N * K;
+  T* dst = y + out_off + b * (int64_t)N * K;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int k = k0 + r, n = n0 + threadIdx.x;
+    if (k < K && n < N) tile[r][threadIdx.x] = src[(int64_t)k * N + n];
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int n = n0 + r, k = k0 + threadIdx.x;
+    if (n < N && k < K) dst[(int64_t)n * K + k] = tile[threadIdx.x][r];
+  }
+}
+template <typename T>
+static bool launch_transpose_last2(const MoveGeom& g, const void* x, void* y, cudaStream_t s) {
+  // canonical rank 2 or 3: out [B][N][K] dense, in strides {N*K, 1, N}
+  const int r = g.rank;
+  if (r != 2 && r != 3) return false;
+  const int64_t N = g.oshape[r - 2], K = g.oshape[r - 1], B = r == 3 ? g.oshape[0] : 1;
+  if (g.ostride[r - 1] != 1 || g.ostride[r - 2] != K || g.istride[r - 2] != 1 || g.istride[r - 1] != N) return false;
+  if (r == 3 && (g.ostride[0] != N * K || g.istride[0] != N * K)) return false;
+  if (N > (1 << 30) || K > (1 << 30)) return false;
+  const int tn = (int)((N + 31) / 32), tk = (int)((K + 31) / 32);
+  const int64_t blocks = B * tn * tk;
+  if (blocks <= 0 || blocks > 0x7fffffffLL) return false;
+  transpose_last2_kernel<T><<<(unsigned)blocks, dim3(32, 8), 0, s>>>((const T*)x, (T*)y, g.in_offset, g.out_offset, (int)N, (int)K, tn, tk);
+  return true;
+}
 int move(const MoveGeom& g0, int esz, const void* x, void* y, cudaStream_t s) {
   MoveGeom g = g0;
   // Canonical form first: axes of extent 1 dropped, neighbours that are contiguous on both sides merged.
@@ -833,6 +868,11 @@ int move(const MoveGeom& g0, int esz, const void* x, void* y, cudaStream_t s) {
     }
     if (r == 0) { g.oshape[0] = 1; g.istride[0] = 1; g.ostride[0] = 1; r = 1; }
     g.rank = r;
+  }
+  if (g.rank >= 2 && g.istride[g.rank - 1] != 1) {
+    bool done = esz == 1 ? launch_transpose_last2<uint8_t>(g, x, y, s) : esz == 2 ? launch_transpose_last2<uint16_t>(g, x, y, s)
+              : esz == 4 ? launch_transpose_last2<uint32_t>(g, x, y, s) : esz == 8 ? launch_transpose_last2<uint64_t>(g, x, y, s) : false;
+    if (done) return check_launch();
   }
   // When the innermost axis is contiguous on both sides (a head split / merge, a concat along an outer axis), move
   // the widest power-of-two unit up to 16 bytes that divides every stride, offset and the innermost extent.

@@ -218,6 +218,31 @@ def test_data_movement_ops(odla, gpu_lib, ref):
         assert np.array_equal(got[k], want[k]), k
 
 
+@pytest.mark.parametrize("fp16", [False, True])
+def test_transposes_against_numpy(odla, gpu_lib, fp16):
+    """Every kind of move the library has: last two axes swapped (shared-memory tiles, ragged edges), inner axis kept
+    (16-byte units), a general permutation, in fp32 and in two-byte storage."""
+    x = RNG.standard_normal((3, 37, 70)).astype(np.float32)
+    y = RNG.standard_normal((2, 5, 6, 16)).astype(np.float32)
+
+    def build(g):
+        a = g.Argument("x", (3, 37, 70))
+        b = g.Argument("y", (2, 5, 6, 16))
+        g.Output(g.Transpose(a, (0, 2, 1), (3, 70, 37), "t_last2"))
+        g.Output(g.Transpose(a, (2, 1, 0), (70, 37, 3), "t_rev"))
+        g.Output(g.Transpose(b, (0, 2, 1, 3), (2, 6, 5, 16), "t_heads"))
+        g.Output(g.Transpose(b, (0, 3, 1, 2), (2, 16, 5, 6), "t_nchw"))
+    g = odla.Graph(gpu_lib, "tr", fp16=fp16)
+    build(g)
+    got = g.run({"x": x, "y": y})
+    g.close()
+    if fp16:
+        x, y = x.astype(np.float16).astype(np.float32), y.astype(np.float16).astype(np.float32)
+    want = {"t_last2": x.transpose(0, 2, 1), "t_rev": x.transpose(2, 1, 0), "t_heads": y.transpose(0, 2, 1, 3), "t_nchw": y.transpose(0, 3, 1, 2)}
+    for k, v in want.items():
+        assert np.array_equal(got[k], v), k
+
+
 def test_empty_batch_dimension_is_handled(odla, gpu_lib):
     g = odla.Graph(gpu_lib, "empty")
     x = g.Argument("x", (0, 8))
