@@ -4,13 +4,17 @@
     python bench.py --gpus N --steps K --warmup W            (N > 1: launched by torchrun, one rank per GPU)
     python bench.py --impl reference ...                      (the reference's CPU kernels on the host cores)
 
-One step = one odla_ExecuteComputation over a batch of 256 synthetic NHWC fp16 images (BASELINE
-config 2).  `value` is measured with the inputs already resident in HBM (device pointers bound),
-`e2e` with pinned host buffers bound, so the host-to-device copy of the images and the
-device-to-host copy of the probabilities are inside the timed region.  Times come from CUDA events
-recorded by the library on the stream its kernels run on; multi-rank numbers take the maximum over
-ranks.  Each rank owns one GPU and a full copy of the weights; there is no collective on the data
-path (weak scaling).
+    python bench.py --inlib-gpus N                            (one process; one execute sharded over N GPUs by the library)
+
+One step = one odla_ExecuteComputation over a batch of 256 synthetic NHWC fp16 images (ResNet-50
+v1.5 at 224 x 224, random He-normal weights with folded batch norm).  `value` is measured with the
+inputs already resident in HBM (device pointers bound), `e2e` with pinned host buffers bound, so the
+host-to-device copy of the images and the device-to-host copy of the probabilities are inside the
+timed region (wall clock around the synchronous call).  Device times come from CUDA events recorded
+by the library on the stream its kernels run on; multi-rank numbers take the maximum over ranks.
+Each rank owns one GPU and a full copy of the weights; there is no collective on the data path
+(weak scaling).  The same network in int8 quantise/dequantise form is measured the same way and
+reported as the `int8` object of the line.
 """
 import argparse
 import importlib
@@ -114,8 +118,10 @@ def measured_peaks():
 
 
 def run_reference(args, rank, world):
-    """The reference's own CPU kernels (runtime/generic, compiled into oracle/_ref) driven through
-    the oracle ODLA platform on every host thread; a bounded sample of the workload per step."""
+    """The reference's own CPU kernels (runtime/generic, compiled into oracle/_ref) driven through the oracle ODLA
+    platform: every step runs one image per host thread (the reference kernels are single-threaded per image) through
+    the same fp32 ResNet-50 graph.  The run is bounded in time: steps beyond the budget are not executed and the line
+    reports the number that were."""
     if rank != 0:
         return
     pkg = importlib.import_module(PKG)
@@ -128,38 +134,31 @@ def run_reference(args, rank, world):
     cores = ref.cpuref_Threads()
     kind = "reference" if ref.cpuref_UsesReference() else "port"
     w = rn.weights()
-
-    def make(batch):
-        g = odla.Graph(ref, "resnet50")
-        rn.build(g, batch, w)
-        return g, rn.inputs(batch, seed=11)
-
-    # One image per host thread runs each image through the reference's scalar kernels; if that
-    # cannot finish in a few minutes fall back to one image split by output rows over the threads.
-    sample = cores if kind == "reference" else 1
-    g, x = make(sample)
+    sample = cores
+    g = odla.Graph(ref, "resnet50")
+    rn.build(g, sample, w)
+    x = rn.inputs(sample, seed=11)
+    budget = float(os.environ.get("BENCH_REFERENCE_BUDGET_S", "300"))
+    t_begin = time.time()
     t0 = time.time()
-    g.run(x)
+    g.run(x)                                   # warm-up (page-in, thread start); also tells how long a step takes
     first = time.time() - t0
-    budget = 200.0
-    if first * (args.steps + args.warmup) > budget and sample > 1:
-        g.close()
-        sample = 1
-        os.environ["ODLA_CPUREF_NO_REFLIB"] = "1"
-        g, x = make(sample)
-        kind = "port"
-    for _ in range(max(args.warmup - 1, 0)):
+    warm = 1
+    steps, dt = 0, 0.0
+    while steps < args.steps and (steps == 0 or (time.time() - t_begin) + first < budget):
+        t0 = time.time()
         g.run(x)
-    t0 = time.time()
-    for _ in range(args.steps):
-        g.run(x)
-    dt = time.time() - t0
+        dt += time.time() - t0
+        steps += 1
     g.close()
-    value = sample * args.steps / dt
-    desc = "%d image(s) of the 256-image batch per step, fp32, %s kernels on %d host threads" % (sample, "runtime/generic" if kind == "reference" else "restated", cores)
-    print(json.dumps({"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-                      "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-                      "data": "synthetic", "config": {"workload": "resnet50_v1.5_nhwc_b256", "sample_images_per_step": sample},
+    value = sample * steps / dt
+    desc = "%d images (one per host thread) of the 256-image batch per step, fp32, %s kernels on %d host threads; %d of %d steps ran inside the %.0f s budget" % (
+        sample, "runtime/generic" if kind == "reference" else "restated", cores, steps, args.steps, budget)
+    print(json.dumps({"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps, "warmup": warm,
+                      "steps_requested": args.steps, "warmup_requested": args.warmup,
+                      "ms_per_step": dt / steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+                      "data": "synthetic", "config": {"workload": "resnet50_v1.5_nhwc_fp16_b%d" % BATCH, "sample_images_per_step": sample,
+                                                      "note": "same graph and weights as the GPU arm, evaluated in fp32 on a sample of the batch"},
                       "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": desc},
                       "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
@@ -183,83 +182,40 @@ def cpu_baseline_leg(pkg, rn, w, seconds=20.0):
             break
     dt = time.time() - t0
     g.close()
-    return {"value": sample * n / dt, "unit": UNIT, "cores": cores, "kind": kind,
-            "sample": "%d pass(es) over %d images (fp32, one image per host thread)" % (n, sample)}
+    return {"value": sample * n / dt, "unit": UNIT, "cores": min(cores, sample), "kind": kind,
+            "sample": "%d pass(es) over %d images (fp32, one image per host thread, %d threads busy)" % (n, sample, min(cores, sample))}
 
 
-def run_b200(args, rank, world, local_rank):
-    import torch
-    pkg = importlib.import_module(PKG)
-    odla = pkg.odla
-    rn = importlib.import_module(PKG + ".halo_models.resnet50")
-    os.environ["ODLA_B200_DEVICE"] = str(local_rank)
-    os.environ["ODLA_B200_NUM_GPUS"] = "1"
-    torch.cuda.set_device(local_rank)
-    lib = pkg.load()
-    if lib.b200_DeviceCount() < 1:
-        raise RuntimeError("bench.py needs a CUDA device: libodla_b200 has no CPU fallback")
-    w = rn.weights()
-    BATCH = args.batch
-    g = odla.Graph(lib, "resnet50", fp16=True, n_gpus=1)
-    rn.build(g, BATCH, w, input_type=odla.FLOAT16)
-    x_host = torch.from_numpy(rn.inputs(BATCH, seed=rank_seed(10 + BATCH, rank), dtype=np.float16)["input"]).pin_memory()
-    y_host = torch.empty((BATCH, 1000), dtype=torch.float32).pin_memory()
-    x_dev = x_host.cuda()
-    y_dev = torch.empty((BATCH, 1000), dtype=torch.float32, device="cuda")
-    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")   # larger than the 126 MB L2
-    h2d, d2h = x_host.numel() * 2, y_host.numel() * 4
+def bind_to_gpu_numa_node(index):
+    """Pins this process to the CPUs next to GPU `index` (NVML's affinity mask) before any pinned buffer is allocated,
+    so that eight ranks' host-to-device copies do not all cross the same socket.  Best effort; returns what it did."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        cpus = [64 * i + b for i, wd in enumerate(words) for b in range(64) if (wd >> b) & 1]
+        allowed = sorted(set(cpus) & set(os.sched_getaffinity(0)))
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+            return "%d cpus near gpu %d" % (len(allowed), index)
+    except Exception as e:   # no NVML, no permission: leave the affinity alone
+        return "unchanged (%s)" % type(e).__name__
+    return "unchanged"
 
-    # The end-to-end leg binds host buffers; there the library pipelines the batch over sub-batches
-    # (ODLA_BATCHES_PER_STEP) so that one sub-batch's input copy runs under another's kernels.
-    g.context()   # odla_CreateContext attaches to the most recently created computation: make it now
-    g_host = g
-    if args.sub_batches > 1:
-        g_host = odla.Graph(lib, "resnet50_host", fp16=True, n_gpus=1, sub_batches=args.sub_batches)
-        rn.build(g_host, BATCH, w, input_type=odla.FLOAT16)
-        g_host.context()
 
-    def bind(device_resident):
-        gg = g if device_resident else g_host
-        gg.bind_input("input", x_dev.data_ptr() if device_resident else x_host.data_ptr())
-        gg.bind_output("prob", y_dev.data_ptr() if device_resident else y_host.data_ptr())
-        return gg
+# ResNet-50 dram__bytes_read.sum + dram__bytes_write.sum of the tensor-core kernel, summed over its launches of one
+# execute and divided by their number: one ncu capture at a smaller batch (the full batch breaks the capture-size rule),
+# scaled in proportion to the batch (activation traffic grows with it; the 25 / 51 MB of weights do not, which makes the
+# scaled figure a slight over-estimate).  See profiles/.
+NCU_TRAFFIC = {"f16": {"bytes_per_launch": 1.9707e8, "launches": 54, "at_batch": 256, "source": "ncu capture of all 54 launches at B=128, scaled x2"},
+               "s8": None}
 
-    def step(gg):
-        flush.zero_()
-        torch.cuda.synchronize()
-        st = gg.execute()
-        if st != 0:
-            raise RuntimeError("odla_ExecuteComputation failed with status %d" % st)
-        return gg.device_ms()
 
-    def timed(device_resident, sampler=None):
-        gg = bind(device_resident)
-        for _ in range(args.warmup):
-            step(gg)
-        barrier()
-        torch.cuda.synchronize()
-        if sampler:
-            sampler.start()
-        t0 = time.time()
-        ms = sum(step(gg) for _ in range(args.steps))
-        torch.cuda.synchronize()
-        wall = time.time() - t0
-        barrier()
-        return max_over_ranks(ms), max_over_ranks(wall * 1e3)
-
-    sampler = ClockSampler(local_rank)
-    dev_ms, wall_ms = timed(True, sampler)
-    clocks = sampler.summary()
-    launches = g.launches() * args.steps
-    e2e_ms, _ = timed(False)
-    total_images = sum_over_ranks(BATCH * args.steps)
-    value = total_images / (dev_ms / 1e3)
-    e2e_value = total_images / (e2e_ms / 1e3)
-    top1 = int(y_host.argmax(dim=1)[0])
-
-    # per-kernel durations: a pass with every launch bracketed by CUDA events on the library's stream
-    bind(True)
-    prof = g.profile(runs=max(2, min(5, args.steps)))
+def tensor_roofline(prof, ms_per_step, peaks, peak_kind, clocks, int8, batch):
+    """Roofline of the tensor-core kernel from the timed step: its share of the step comes from a pass that brackets
+    every launch with events (serialised, so only the SHARE is used), its time is that share of the measured
+    ms_per_step -- never more than the step it sits in."""
     fam = {}
     for p in prof:
         f = fam.setdefault(p["op"], {"launches": 0, "ms": 0.0, "flops": 0.0, "bytes": 0.0})
@@ -268,69 +224,148 @@ def run_b200(args, rank, world, local_rank):
         f["flops"] += p["flops"]
         f["bytes"] += p["bytes"]
     tc = [f for k, f in fam.items() if k.endswith("_umma")]
-    tc_ms = sum(f["ms"] for f in tc)
+    all_ms = max(sum(f["ms"] for f in fam.values()), 1e-9)
+    share = sum(f["ms"] for f in tc) / all_ms
     tc_flops = sum(f["flops"] for f in tc)
+    tc_bytes = sum(f["bytes"] for f in tc)
     tc_launches = sum(f["launches"] for f in tc)
-    peaks, peak_kind = measured_peaks()
-    peak = float(peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops")))
-    achieved = tc_flops / (tc_ms * 1e-3) / 1e12 if tc_ms > 0 else 0.0
-    roofline = {"bound": "tensor", "kernel": "umma_conv_kernel (tcgen05 implicit-GEMM conv / GEMM, %d launches per step)" % tc_launches,
-                "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak if peak else None, "peak_source": peak_kind + " bf16 sustained",
-                "avg_launch_ms": tc_ms / max(tc_launches, 1), "share_of_step": tc_ms / max(sum(f["ms"] for f in fam.values()), 1e-9),
-                # dram__bytes_read.sum + dram__bytes_write.sum of this kernel, average per launch: one ncu capture of all 54
-                # launches at B=128 (5.321 GB; activations already exceed the 126 MB L2 there), scaled by 2 to B=256.
-                "traffic": 1.9707e8 * (BATCH / 256.0), "traffic_unit": "bytes per launch (54 launches per step)",
-                "algorithmic_bytes_per_launch": sum(f["bytes"] for f in tc) / max(tc_launches, 1),
-                "hbm_view": {"achieved_gbs": sum(f["bytes"] for f in tc) / (tc_ms * 1e-3) / 1e9 if tc_ms > 0 else 0.0, "peak_gbs": float(peaks.get("hbm_gbs", 0))}}
-    families = {k: {"launches": v["launches"], "ms": round(v["ms"], 4)} for k, v in sorted(fam.items(), key=lambda kv: -kv[1]["ms"])}
-    g.close()
+    kernel_ms = ms_per_step * share
+    mult = 2.0 if int8 else 1.0
+    burst, sustained = mult * float(peaks.get("bf16_tflops", 0)), mult * float(peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops", 0)))
+    sm, sm_max = clocks.get("sm_mhz"), clocks.get("sm_max_mhz")
+    regime = "burst" if (sm and sm_max and sm >= 0.93 * sm_max) else "sustained"
+    peak = burst if regime == "burst" else sustained
+    achieved = tc_flops / (kernel_ms * 1e-3) / 1e12 if kernel_ms > 0 else 0.0
+    tr = NCU_TRAFFIC["s8" if int8 else "f16"]
+    roof = {"bound": "tensor", "kernel": "umma_conv_kernel (tcgen05 implicit-GEMM conv / GEMM, %d launches per step)" % tc_launches,
+            "achieved": achieved, "peak": peak, "unit": "TOP/s" if int8 else "TFLOP/s", "frac": achieved / peak if peak else None,
+            "peak_source": ("2 x " if int8 else "") + peak_kind + " bf16 " + regime + (" (no int8 peak is measured; the tensor pipe runs kind::i8 at twice the 16-bit rate)" if int8 else ""),
+            "regime": regime, "frac_vs_burst": achieved / burst if burst else None, "frac_vs_sustained": achieved / sustained if sustained else None,
+            "flops_per_step": tc_flops, "kernel_ms_per_step": kernel_ms, "share_of_step": share, "avg_launch_ms": kernel_ms / max(tc_launches, 1),
+            "whole_step_achieved": tc_flops / (ms_per_step * 1e-3) / 1e12,
+            "ms_per_step_x_sm_mhz": ms_per_step * sm if sm else None,
+            "algorithmic_bytes_per_launch": tc_bytes / max(tc_launches, 1),
+            "traffic": tr["bytes_per_launch"] * batch / tr["at_batch"] if tr else None,
+            "traffic_source": tr["source"] if tr else None,
+            "hbm_view": {"achieved_gbs": tc_bytes / (kernel_ms * 1e-3) / 1e9 if kernel_ms > 0 else 0.0, "peak_gbs": float(peaks.get("hbm_gbs", 0))}}
+    families = {k: {"launches": v["launches"], "share": round(v["ms"] / all_ms, 4)} for k, v in sorted(fam.items(), key=lambda kv: -kv[1]["ms"])}
+    return roof, families
 
-    # Secondary measurement: the same network in int8 quantise/dequantise form (BASELINE config 3),
-    # device-resident fp32 input, same timing method.  int8 tensor peak is taken as 2x the measured bf16 figure.
+
+def run_b200(args, rank, world, local_rank):
+    numa = bind_to_gpu_numa_node(local_rank) if world > 1 else "single rank: not pinned"
+    import torch
+    pkg = importlib.import_module(PKG)
+    odla = pkg.odla
+    rn = importlib.import_module(PKG + ".halo_models.resnet50")
+    inlib = args.inlib_gpus
+    if not inlib:
+        os.environ["ODLA_B200_DEVICE"] = str(local_rank)
+        os.environ["ODLA_B200_NUM_GPUS"] = "1"
+    torch.cuda.set_device(local_rank)
+    lib = pkg.load()
+    if lib.b200_DeviceCount() < 1:
+        raise RuntimeError("bench.py needs a CUDA device: libodla_b200 has no CPU fallback")
+    n_lib_gpus = inlib if inlib else 1
+    w = rn.weights()
+    BATCH = args.batch * n_lib_gpus
+    peaks, peak_kind = measured_peaks()
+    flush = [torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda:%d" % d) for d in (range(n_lib_gpus) if inlib else [local_rank])]   # larger than the 126 MB L2
+    x_np = rn.inputs(BATCH, seed=rank_seed(10 + BATCH, rank), dtype=np.float16)["input"]
+    x_host = torch.from_numpy(x_np).pin_memory()
+    y_host = torch.empty((BATCH, 1000), dtype=torch.float32).pin_memory()
+    x_dev = x_host.cuda()
+    y_dev = torch.empty((BATCH, 1000), dtype=torch.float32, device="cuda")
+    h2d, d2h = x_host.numel() * 2, y_host.numel() * 4
+    total_images = sum_over_ranks(BATCH * args.steps)
+
+    def measure(build, tag, int8):
+        """value (device-resident), e2e (pinned host buffers) and the roofline for one form of the network."""
+        g = odla.Graph(lib, "resnet50_" + tag, fp16=not int8, n_gpus=n_lib_gpus)
+        build(g)
+        g.context()   # odla_CreateContext attaches to the most recently created computation: make it now
+        # The end-to-end leg binds host buffers; there the library pipelines the batch over sub-batches
+        # (ODLA_BATCHES_PER_STEP) so that one sub-batch's input copy runs under another's kernels.
+        g_host = g
+        if args.sub_batches > 1:
+            g_host = odla.Graph(lib, "resnet50_%s_host" % tag, fp16=not int8, n_gpus=n_lib_gpus, sub_batches=args.sub_batches)
+            build(g_host)
+            g_host.context()
+
+        def step(gg):
+            for f in flush:
+                f.zero_()
+            for d in range(len(flush)):
+                torch.cuda.synchronize(flush[d].device)
+            t0 = time.perf_counter()
+            st = gg.execute()
+            wall = time.perf_counter() - t0
+            if st != 0:
+                raise RuntimeError("odla_ExecuteComputation failed with status %d" % st)
+            return gg.device_ms(), wall * 1e3
+
+        def timed(gg, device_resident, sampler=None):
+            gg.bind_input("input", x_dev.data_ptr() if device_resident else x_host.data_ptr())
+            gg.bind_output("prob", y_dev.data_ptr() if device_resident else y_host.data_ptr())
+            for _ in range(args.warmup):
+                step(gg)
+            barrier()
+            torch.cuda.synchronize()
+            if sampler:
+                sampler.start()
+            dev = wall = 0.0
+            for _ in range(args.steps):
+                d, wl = step(gg)
+                dev += d
+                wall += wl
+            torch.cuda.synchronize()
+            barrier()
+            return max_over_ranks(dev), max_over_ranks(wall)
+
+        sampler = ClockSampler(local_rank)
+        dev_ms, _ = timed(g, True, sampler)
+        clocks = sampler.summary()
+        launches = g.launches() * args.steps
+        e2e_dev_ms, e2e_wall_ms = timed(g_host, False)
+        top1 = int(y_host.argmax(dim=1)[0])
+        g.bind_input("input", x_dev.data_ptr())
+        g.bind_output("prob", y_dev.data_ptr())
+        prof = g.profile(runs=max(2, min(5, args.steps)))
+        roof, families = tensor_roofline(prof, dev_ms / args.steps, peaks, peak_kind, clocks, int8, args.batch)
+        g.close()
+        if g_host is not g:
+            g_host.close()
+        return {"value": total_images / (dev_ms / 1e3), "ms_per_step": dev_ms / args.steps,
+                "e2e": {"value": total_images / (e2e_wall_ms / 1e3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                        "ms_per_step": e2e_wall_ms / args.steps, "device_ms_per_step": e2e_dev_ms / args.steps, "sub_batches": args.sub_batches,
+                        "h2d_gbs_per_rank": h2d / (e2e_wall_ms / args.steps * 1e-3) / 1e9, "timing": "wall clock around the synchronous odla_ExecuteComputation, max over ranks"},
+                "gpu_launches": launches, "clocks": clocks, "roofline": roof, "families": families, "top1": top1}
+
+    fp16 = measure(lambda g: rn.build(g, BATCH, w, input_type=odla.FLOAT16), "fp16", False)
     int8 = None
     if not args.no_int8:
         scales = rn.calibrate(w, n_images=8)
         wq = rn.quantize_weights(w)
-        g8 = odla.Graph(lib, "resnet50_int8", n_gpus=1)
-        rn.build_int8(g8, BATCH, w, wq, scales)
-        x8 = x_host.float().cuda()
-        g8.bind_input("input", x8.data_ptr())
-        g8.bind_output("prob", y_dev.data_ptr())
-
-        def step8():
-            flush.zero_()
-            torch.cuda.synchronize()
-            if g8.execute() != 0:
-                raise RuntimeError("int8 execute failed")
-            return g8.device_ms()
-        for _ in range(args.warmup):
-            step8()
-        barrier()
-        ms8 = max_over_ranks(sum(step8() for _ in range(args.steps)))
-        prof8 = g8.profile(runs=2)
-        tc8 = [q for q in prof8 if q["op"].endswith("_umma")]
-        tc8_ms, tc8_ops = sum(q["ms"] for q in tc8), sum(q["flops"] for q in tc8)
-        int8 = {"value": total_images / (ms8 / 1e3), "unit": UNIT, "ms_per_step": ms8 / args.steps, "dtype": "s8 (int32 accumulate)",
-                "roofline": {"bound": "tensor", "achieved": tc8_ops / (tc8_ms * 1e-3) / 1e12 if tc8_ms else 0.0, "peak": 2 * peak, "unit": "TOP/s",
-                             "frac": (tc8_ops / (tc8_ms * 1e-3) / 1e12) / (2 * peak) if tc8_ms else None, "peak_source": "2 x " + peak_kind + " bf16 sustained (no int8 measurement available)"}}
-        g8.close()
+        r8 = measure(lambda g: rn.build_int8(g, BATCH, w, wq, scales, input_type=odla.FLOAT16), "int8", True)
+        int8 = {"value": r8["value"], "unit": UNIT, "ms_per_step": r8["ms_per_step"], "dtype": "s8 (int32 accumulate; per-channel weight scales, per-tensor activation scales)",
+                "e2e": r8["e2e"], "gpu_launches": r8["gpu_launches"], "clocks": r8["clocks"], "roofline": r8["roofline"], "kernel_families_share": r8["families"],
+                "check": {"top1_of_first_image": r8["top1"]}}
 
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and not inlib:
         cpu = cpu_baseline_leg(pkg, rn, w)
     if rank == 0:
         print(json.dumps({
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": dev_ms / args.steps, "wall_ms_per_step": wall_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "metric": METRIC, "value": fp16["value"], "unit": UNIT, "n_gpus": world * n_lib_gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": fp16["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f16", "data": "synthetic",
-            "config": {"workload": "resnet50_v1.5_nhwc_fp16_b%d" % BATCH, "batch_per_gpu": BATCH, "global_batch": BATCH * world, "input": "NHWC fp16 N(0,1)",
-                       "weights": "He-normal, folded BN, random init", "l2": "256 MiB buffer written between steps", "parallelism": "dp%d" % world,
-                       "timing": "CUDA events on the library's stream around each odla_ExecuteComputation, summed over the steps, max over ranks"},
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps,
-                    "sub_batches": args.sub_batches},
-            "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "kernel_families_ms_per_step": families,
-            "int8": int8, "cpu_baseline": cpu, "check": {"top1_of_first_image": top1}}))
-
+            "config": {"workload": "resnet50_v1.5_nhwc_fp16_b%d" % args.batch, "batch_per_gpu": args.batch, "global_batch": BATCH * world, "input": "NHWC fp16 N(0,1)",
+                       "weights": "He-normal, folded BN, random init", "l2": "256 MiB buffer written between steps",
+                       "parallelism": ("one process, odla_ExecuteComputation shards dim 0 over %d GPUs" % inlib) if inlib else "dp%d (one process per GPU)" % world,
+                       "timing": "CUDA events on the library's stream around each odla_ExecuteComputation, summed over the steps, max over ranks",
+                       "host_affinity": numa},
+            "e2e": fp16["e2e"], "gpu_launches": fp16["gpu_launches"], "clocks": fp16["clocks"], "roofline": fp16["roofline"],
+            "kernel_families_share": fp16["families"], "int8": int8, "cpu_baseline": cpu, "check": {"top1_of_first_image": fp16["top1"]}}))
 
 
 def run_secondary(args, rank, world, local_rank):
@@ -442,6 +477,7 @@ def main():
                     help="resnet50 is the benchmark line; yolov3 (B=16) and bert (B=64) are the secondary BASELINE configurations")
     ap.add_argument("--sub-batches", type=int, default=2, help="ODLA_BATCHES_PER_STEP of the end-to-end (host-bound) leg; 1 = off")
     ap.add_argument("--batch", type=int, default=BATCH, help="images per GPU per step (256 = the benchmark configuration; smaller values are for profiling)")
+    ap.add_argument("--inlib-gpus", type=int, default=0, help="single process: one odla_ExecuteComputation shards a batch of N x --batch images over N GPUs inside the library")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else max(args.warmup, 1)
     rank, world, local_rank = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))

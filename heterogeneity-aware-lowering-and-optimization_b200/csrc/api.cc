@@ -304,15 +304,16 @@ odla_status odla_SetComputationItem(odla_computation c, odla_item_type type, odl
         c->planned = false;
       }
       break;
-    case ODLA_DYNAMIC_BATCH: case ODLA_MIN_BATCH_SIZE: case ODLA_MAX_BATCH_SIZE: case ODLA_OPT_BATCH_SIZE:
     case ODLA_BATCHES_PER_STEP:  // sub-batches one execute is pipelined over (copy of one under the kernels of another)
       c->sub_batches = value ? *(int*)value : 0;
-      c->planned = false;
       break;
+    // Generated code for a dynamic-batch model sets all four of these (generic_cxx_codegen.cc, EmitComputationItems);
+    // the run batch size of this library is ODLA_RUN_BATCH_SIZE on the context, so they carry no information here.
+    case ODLA_DYNAMIC_BATCH: case ODLA_MIN_BATCH_SIZE: case ODLA_MAX_BATCH_SIZE: case ODLA_OPT_BATCH_SIZE:
     case ODLA_USE_SIM_MODE: case ODLA_LOAD_ENGINE_MODE: case ODLA_ENABLE_ENGINE_CACHE:
     case ODLA_CACHE_DIR:
       B2_INFO("computation item %d accepted and ignored", (int)type);
-      break;
+      return ODLA_SUCCESS;
     default:
       B2_ERR("unsupported computation item %d", (int)type);
       return ODLA_FAILURE;

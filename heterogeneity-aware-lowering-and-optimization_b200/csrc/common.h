@@ -104,7 +104,7 @@ struct Plan {
   int64_t arena_bytes = 0;
   char* consts = nullptr;          // converted / repacked constants
   int64_t const_bytes = 0;
-  int* status = nullptr;           // device word: non-zero when a bounded wait expired
+  int* status = nullptr;           // device status block (kStatusBytes): word 0 non-zero when a bounded wait expired
   std::vector<void*> extra_allocs; // uploaded constants and scratch
   std::vector<UmmaLaunch*> umma;   // prepared tensor-core launches (own their tensor maps)
   cudaGraphExec_t graph = nullptr; // captured launch list (optional)

@@ -38,8 +38,8 @@ extern "C" int odla_b200_conv_umma(const odla_b200_conv_desc* d, const void* x, 
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   int* status = nullptr;
-  if (cudaMalloc((void**)&status, 1024) != cudaSuccess) return -2;
-  cudaMemsetAsync(status, 0, 1024, (cudaStream_t)stream);
+  if (cudaMalloc((void**)&status, kStatusBytes) != cudaSuccess) return -2;
+  cudaMemsetAsync(status, 0, kStatusBytes, (cudaStream_t)stream);
   UmmaLaunch* L = umma_conv_prepare(c, x, w, y, ep, status, sms);
   if (!L) { cudaFree(status); return -2; }
   int rc = umma_conv_run(L, (cudaStream_t)stream);

@@ -7,6 +7,10 @@
 
 namespace b200 {
 
+// Size of the device status block every tensor-core launch is given: word 0 = code of the wait that expired, word 1 =
+// the CTA; a debug build (UMMA_DEBUG_TS) also keeps time stamps and per-site wait counters up to byte 512.
+constexpr size_t kStatusBytes = 1024;
+
 // Storage element types of tensors held in HBM.
 enum { DT_F32 = 0, DT_F16 = 1, DT_BF16 = 2, DT_S8 = 3, DT_U8 = 4, DT_S32 = 5, DT_S64 = 6 };
 
@@ -45,6 +49,9 @@ struct Epilogue {
   float out_scale = 1.f;
   float out_inv = 1.f;   // fl(1 / out_scale)
   int out_multiply = 0;
+  // int32 accumulators proven (from the filter values) to stay inside (-2^22, 2^22): the tensor-core epilogue may then
+  // convert them to fp32 with an integer add and a floating-point subtract instead of a conversion instruction.
+  int acc_small = 0;
 };
 
 // 2-d convolution geometry.  Data is addressed through element strides so NHWC and NCHW share

@@ -507,6 +507,22 @@ __device__ __forceinline__ void fadd2_rn(float& a0, float& a1, float b0, float b
       : "+f"(a0), "+f"(a1)
       : "f"(b0), "f"(b1));
 }
+__device__ __forceinline__ void fmul2_rn(float& a0, float& a1, float b0, float b1) {
+  asm("{\n\t.reg .b64 x, y;\n\tmov.b64 x, {%0, %1};\n\tmov.b64 y, {%2, %3};\n\tmul.rn.f32x2 x, x, y;\n\tmov.b64 {%0, %1}, x;\n\t}"
+      : "+f"(a0), "+f"(a1)
+      : "f"(b0), "f"(b1));
+}
+// Exact conversions without the conversion pipe (its rate, a quarter of the ALU's, bounded the int8 epilogue):
+//   int32 -> fp32 for |a| < 2^22: 0x4B400000 is 2^23 + 2^22 = 12582912.f, whose ulp is 1, so adding a to the bit pattern
+//     gives 12582912 + a exactly and the subtraction is exact as well;
+//   int8 -> fp32: the byte with its sign bit flipped (b + 128, 0..255) placed in the mantissa of 2^23 is 8388608 + 128 + b;
+//   fp32 -> int8 with round-to-nearest-even and saturation: clamp to [-128, 127] (or [0, 127] under a ReLU), add
+//     12582912.f -- the addition rounds to an integer, ties to even -- and take the low byte (two's complement).
+constexpr uint32_t kMagicBits = 0x4B400000u;
+constexpr float kMagic = 12582912.f;
+__device__ __forceinline__ float s8_byte_to_float(uint32_t word_flipped, int b) {
+  return __fadd_rn(__uint_as_float(__byte_perm(word_flipped, 0x4B000000u, 0x7540u + (uint32_t)b)), -8388736.f);
+}
 // The staged epilogue's chunk: 16 consecutive channels of one output row, residual read from and result
 // written to the row's place in the staging box.  Only what a staged launch can need is here (the launcher
 // sends everything else to the direct epilogue), so the loop around it stays small.
@@ -519,11 +535,11 @@ __device__ __forceinline__ void epilogue_chunk_staged(const UmmaParams& p, float
   if (ep.mul) {
     load_vec<16>(ep.mul, col0, kmax, full, cv);
 #pragma unroll
-    for (int j = 0; j < 16; ++j) v[j] = __fmul_rn(v[j], cv[j]);
+    for (int j = 0; j < 16; j += 2) fmul2_rn(v[j], v[j + 1], cv[j], cv[j + 1]);
   }
   if (ep.alpha != 1.f) {
 #pragma unroll
-    for (int j = 0; j < 16; ++j) v[j] = __fmul_rn(v[j], ep.alpha);
+    for (int j = 0; j < 16; j += 2) fmul2_rn(v[j], v[j + 1], ep.alpha, ep.alpha);
   }
   if (ep.add1) {
     load_vec<16>(ep.add1, col0, kmax, full, cv);
@@ -542,8 +558,13 @@ __device__ __forceinline__ void epilogue_chunk_staged(const UmmaParams& p, float
       const uint32_t* w = (const uint32_t*)&u;
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
+        const uint32_t wf = w[t] ^ 0x80808080u;
 #pragma unroll
-        for (int b = 0; b < 4; ++b) v[t * 4 + b] = __fadd_rn(v[t * 4 + b], __fmul_rn((float)(signed char)(w[t] >> (8 * b)), ep.res_scale));
+        for (int b = 0; b < 4; b += 2) {
+          float r0 = s8_byte_to_float(wf, b), r1 = s8_byte_to_float(wf, b + 1);
+          fmul2_rn(r0, r1, ep.res_scale, ep.res_scale);
+          fadd2_rn(v[t * 4 + b], v[t * 4 + b + 1], r0, r1);
+        }
       }
     } else {
 #pragma unroll
@@ -559,13 +580,29 @@ __device__ __forceinline__ void epilogue_chunk_staged(const UmmaParams& p, float
   }
   if (ANYACT) {
     if (!ep.act_first) apply_act_all<16>(ep.act, v, ep.act_a, ep.act_b);
-  } else if (ep.act == ACT_RELU && OUT == DT_S8) {
-#pragma unroll
-    for (int j = 0; j < 16; ++j) v[j] = fmaxf(v[j], 0.f);
   }
+  // (plain int8 outputs take their ReLU as the lower bound of the saturating clamp below)
   // (two-byte outputs take their ReLU after packing, two values per instruction: rounding is monotonic and keeps the sign)
   const bool relu_packed = !ANYACT && ep.act == ACT_RELU && OUT != DT_S8;
-  if (OUT == DT_S8) {
+  if (OUT == DT_S8 && !ANYACT) {
+    // requantisation by multiplication; the ReLU (if any) is the lower clamp: max(v, 0) * m == max(v * m, 0) for m > 0
+    const float lo = ep.act == ACT_RELU && ep.out_inv > 0.f ? 0.f : -128.f;
+    uint4 u;
+    uint32_t* w = (uint32_t*)&u;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      float q[4];
+#pragma unroll
+      for (int b = 0; b < 4; b += 2) {
+        q[b] = v[t * 4 + b]; q[b + 1] = v[t * 4 + b + 1];
+        fmul2_rn(q[b], q[b + 1], ep.out_inv, ep.out_inv);
+        q[b] = fminf(fmaxf(q[b], lo), 127.f); q[b + 1] = fminf(fmaxf(q[b + 1], lo), 127.f);
+        fadd2_rn(q[b], q[b + 1], kMagic, kMagic);
+      }
+      w[t] = __byte_perm(__byte_perm(__float_as_uint(q[0]), __float_as_uint(q[1]), 0x0040), __byte_perm(__float_as_uint(q[2]), __float_as_uint(q[3]), 0x0040), 0x5410);
+    }
+    sts128(stage_piece(sp, 0), u);
+  } else if (OUT == DT_S8) {
     uint4 u;
     uint32_t* w = (uint32_t*)&u;
 #pragma unroll
@@ -573,7 +610,7 @@ __device__ __forceinline__ void epilogue_chunk_staged(const UmmaParams& p, float
       uint32_t qb[4];
 #pragma unroll
       for (int b = 0; b < 4; ++b) {
-        const float t4 = (!ANYACT || ep.out_multiply) ? __fmul_rn(v[t * 4 + b], ep.out_inv) : __fdiv_rn(v[t * 4 + b], ep.out_scale);
+        const float t4 = ep.out_multiply ? __fmul_rn(v[t * 4 + b], ep.out_inv) : __fdiv_rn(v[t * 4 + b], ep.out_scale);
         qb[b] = (uint32_t)rne_sat_s8(t4);
       }
       w[t] = __byte_perm(__byte_perm(qb[0], qb[1], 0x0040), __byte_perm(qb[2], qb[3], 0x0040), 0x5410);
@@ -898,8 +935,16 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               tmem_ld_wait_regs<CW>(r);
               float v[CW];
               if (p.acc_int) {
+                if (p.ep.acc_small) {
 #pragma unroll
-                for (int j = 0; j < CW; ++j) v[j] = (float)(int32_t)r[j];
+                  for (int j = 0; j < CW; j += 2) {
+                    v[j] = __uint_as_float(r[j] + kMagicBits); v[j + 1] = __uint_as_float(r[j + 1] + kMagicBits);
+                    fadd2_rn(v[j], v[j + 1], -kMagic, -kMagic);
+                  }
+                } else {
+#pragma unroll
+                  for (int j = 0; j < CW; ++j) v[j] = (float)(int32_t)r[j];
+                }
               } else {
 #pragma unroll
                 for (int j = 0; j < CW; ++j) v[j] = __uint_as_float(r[j]);

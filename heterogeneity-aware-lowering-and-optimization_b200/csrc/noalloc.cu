@@ -11,6 +11,7 @@
 // cudaGetSymbolAddress the first time the entry point runs on a device (with that device current)
 // and cached.  That first call therefore does driver work; make it before starting a stream
 // capture.  Every later call only enqueues kernels.
+#include <atomic>
 #include <cstdio>
 
 #include "../../include/odla_b200.h"
@@ -23,7 +24,7 @@ constexpr long long kHalfFloats = 1ll << 20;
 static __device__ __align__(256) float g_reduce_scratch[2 * kHalfFloats];
 
 constexpr int kMaxDevices = 64;
-float* g_scratch_addr[kMaxDevices] = {nullptr};
+std::atomic<float*> g_scratch_addr[kMaxDevices];   // zero-initialised; two threads that race on a first call store the same address
 
 // Device address of the scratch array on the current device, or nullptr (error already printed).
 float* scratch_on_current_device() {
@@ -32,16 +33,18 @@ float* scratch_on_current_device() {
     fprintf(stderr, "[odla_b200] reduce_mean_noalloc: no usable current CUDA device\n");
     return nullptr;
   }
-  if (!g_scratch_addr[dev]) {
+  float* cached = g_scratch_addr[dev].load(std::memory_order_acquire);
+  if (!cached) {
     float* p = nullptr;
     cudaError_t e = cudaGetSymbolAddress((void**)&p, g_reduce_scratch);
     if (e != cudaSuccess || !p) {
       fprintf(stderr, "[odla_b200] reduce_mean_noalloc: cudaGetSymbolAddress failed on device %d: %s\n", dev, cudaGetErrorString(e));
       return nullptr;
     }
-    g_scratch_addr[dev] = p;
+    g_scratch_addr[dev].store(p, std::memory_order_release);
+    cached = p;
   }
-  return g_scratch_addr[dev];
+  return cached;
 }
 
 }  // namespace
@@ -52,6 +55,10 @@ extern "C" int odla_b200_reduce_mean_noalloc(const void* x, void* y, int dtype, 
   if (!x || !y || !dims || !axes || rank < 1 || rank > ODLA_MAX_DIMENSION || n_axes < 1 || n_axes > rank) return -1;
   const int dt = dtype == 0 ? DT_F32 : dtype == 1 ? DT_F16 : dtype == 2 ? DT_BF16 : -1;
   if (dt < 0) return -1;
+  if (x == y) return -1;  // a pass reads rows that another block of the same pass would already have overwritten
+  for (int k = 0; k < n_axes; ++k)
+    for (int j = 0; j < k; ++j)
+      if (axes[j] == axes[k]) return -1;  // an axis can be reduced once
   long long d[ODLA_MAX_DIMENSION];
   for (int i = 0; i < rank; ++i) {
     if (dims[i] < 1) return -1;

@@ -18,6 +18,7 @@
 #include <cstring>
 #include <functional>
 #include <set>
+#include <thread>
 
 #include "common.h"
 
@@ -287,7 +288,15 @@ odla_status Builder::analyse() {
   for (auto& n : c_->nodes) {
     V v = n.get();
     if (v->kind == OP_CONST) continue;
-    if (v->kind == OP_ARG) { dt_[v] = storage_of(v); continue; }
+    if (v->kind == OP_ARG) {
+      dt_[v] = storage_of(v);
+      // A float argument that only feeds Quantize nodes is quantised straight from the caller's element type
+      // (no conversion pass over the input; the values are the same numbers in either type).
+      bool only_q = is_float_type(v->type.element_type) && !consumers_[v].empty() && !v->is_output;
+      for (V cons : consumers_[v]) if (cons->kind != OP_QUANTIZE || cons->in[0] != v) only_q = false;
+      if (only_q && api_dt(v->type.element_type) >= 0) dt_[v] = api_dt(v->type.element_type);
+      continue;
+    }
     if (v->kind == OP_RESHAPE) { alias_[v] = v->in[0]; continue; }
     auto fi = fused_into_.find(v);
     if (fi != fused_into_.end() && fused_[fi->second]->out != v) continue;  // swallowed, not the chain end
@@ -516,8 +525,8 @@ odla_status Builder::place() {
   p_->arena_bytes = arena.top;
   if (inject_fault("alloc") || cudaMalloc((void**)&p_->arena, (size_t)std::max<int64_t>(p_->arena_bytes, 1024)) != cudaSuccess)
     return fail(ODLA_MEM_ERROR, "arena allocation failed");
-  if (cudaMalloc((void**)&p_->status, 256) != cudaSuccess) return fail(ODLA_MEM_ERROR, "status word allocation failed");
-  cudaMemset(p_->status, 0, 256);
+  if (cudaMalloc((void**)&p_->status, kStatusBytes) != cudaSuccess) return fail(ODLA_MEM_ERROR, "status word allocation failed");
+  cudaMemset(p_->status, 0, kStatusBytes);
   return ODLA_SUCCESS;
 }
 
@@ -537,6 +546,23 @@ odla_status Builder::emit_fused(const Item& it) {
     std::vector<float> m((size_t)K);
     for (int64_t k = 0; k < K; ++k) m[k] = sx[0] * sw[sw.size() == 1 ? 0 : k];
     ep.mul = upload_f32(m);
+    // |accumulator| <= 128 * sum |w[k,:]| (activations lie in [-128, 127]); below 2^22 for every output channel the
+    // epilogue can convert the accumulators without the conversion pipe.
+    if (f.w->kind == OP_CONST && api_dt(f.w->type.element_type) == DT_S8 && !getenv("ODLA_B200_NO_ACC_SMALL")) {
+      const int8_t* wq = (const int8_t*)f.w->host;
+      const int64_t n = numel(f.w->type.shape);
+      // filters are [.., K] (HWIO) and Gemm weights [Kd, N] or, transposed, [N, Kd]: the output channel is the last
+      // axis unless the Gemm's B is transposed
+      const bool k_last = !(root->kind == OP_GEMM && root->ia[1] != 0);
+      std::vector<int64_t> sum((size_t)K, 0);
+      if (n % K == 0) {
+        const int64_t inner = n / K;
+        for (int64_t i = 0; i < n; ++i) sum[(size_t)(k_last ? i % K : i / inner)] += std::abs((int)wq[i]);
+        int64_t worst = 0;
+        for (int64_t k = 0; k < K; ++k) worst = std::max(worst, sum[(size_t)k]);
+        ep.acc_small = worst * 128 < (1ll << 22) ? 1 : 0;
+      }
+    }
   }
   if (f.add_const) ep.add2 = (const float*)const_dev(f.add_const, DT_F32);
   if (f.res) {
@@ -1207,6 +1233,15 @@ bool graph_shardable(_odla_computation* c, int64_t* batch_out) {
     if (!b) continue;
     const auto& s = v->type.shape;
     if (s.size == 0 || s.dims[0] % B != 0) return false;
+    // An operand that does not depend on the arguments (a constant, or a function of constants) but spans the whole
+    // batch extent would have to be offset by the shard's first row; such graphs run unsharded instead.
+    auto spans_batch = [&](V o) {
+      if (!o || cb[o]) return false;
+      const auto& os = o->type.shape;
+      return s.dims[0] > 1 && os.size == s.size && os.dims[0] == s.dims[0];
+    };
+    if (v->kind == OP_BINARY || v->kind == OP_CONCAT || v->kind == OP_GEMM)
+      for (auto i : v->in) if (spans_batch(i)) return false;
     switch (v->kind) {
       case OP_TRANSPOSE: if (v->ia[0] != 0) return false; break;
       case OP_SOFTMAX: if (v->ia[0] == 0) return false; break;
@@ -1244,23 +1279,23 @@ void destroy_replicas(std::vector<Replica>& reps) {
   reps.clear();
 }
 
-// Builds the replicas (streams, arenas, constant pools, launch lists) that run `run_batch` rows of a graph
-// recorded with `B` rows in dim 0.
-static odla_status build_replicas(_odla_computation* c, int visible, int64_t B, int64_t run_batch, std::vector<Replica>& reps) {
+// One replica's share of an execute: which GPU, which rows of dim 0.
+struct Shard { int device; int64_t start, rows; };
+
+// How `run_batch` rows of a graph are split: an even split over the GPUs (the first `run_batch % G` GPUs take one row
+// more), and within a GPU over S sub-batches (ODLA_BATCHES_PER_STEP), each with its own stream, so that one
+// sub-batch's host-to-device copy runs under another's kernels.  Needs no device: the arithmetic is tested on the host.
+static std::vector<Shard> shard_layout(_odla_computation* c, int visible, int64_t B, int64_t run_batch) {
   int want = c->n_gpus > 0 ? c->n_gpus : visible;
   int G = c->shardable ? (int)std::min<int64_t>(std::min(want, visible), std::max<int64_t>(run_batch, 1)) : 1;
   if (G < 1) G = 1;
-  // Sub-batches: S replicas per GPU, each with its own stream, so that one sub-batch's host-to-device copy runs
-  // under another's kernels (the call stays synchronous).  Pays when inputs are bound as host pointers.
   int S = c->sub_batches > 0 ? c->sub_batches : (getenv("ODLA_B200_SUBBATCHES") ? atoi(getenv("ODLA_B200_SUBBATCHES")) : 1);
   if (!c->shardable || S < 1) S = 1;
   while (S > 1 && (int64_t)G * S > run_batch) --S;
   const int devices = G;
   G *= S;
-  reps.resize((size_t)G);
-  // Rows per replica: an even split over the GPUs; within a GPU the sub-batches grow geometrically by `growth`
-  // (1 = even), so that each one's input copy still fits under the kernels of the smaller one before it while the
-  // first, exposed, copy is short.
+  // Within a GPU the sub-batches grow geometrically by `growth` (1 = even), so that each one's input copy still fits
+  // under the kernels of the smaller one before it while the first, exposed, copy is short.
   // Measured on ResNet-50 (B = 256, inputs 300 KB and outputs 4 KB per image): two sub-batches of 64 and 192 rows beat
   // 128 + 128 by 4 %; when the outputs are the larger transfer the last sub-batch's copy-out is the exposed one and
   // the split stays even.
@@ -1288,13 +1323,30 @@ static odla_status build_replicas(_odla_computation* c, int visible, int64_t B, 
     }
     if (growth == 1.0) for (int k = 0; k < S; ++k) r[k] = share / S + (k < share % S ? 1 : 0);
   }
+  std::vector<Shard> out((size_t)G);
   int64_t start = 0;
   for (int i = 0; i < G; ++i) {
+    out[(size_t)i].device = (c->first_device + i / S) % std::max(visible, 1);
+    out[(size_t)i].rows = c->shardable ? rows[(size_t)i] : B;
+    out[(size_t)i].start = start;
+    start += out[(size_t)i].rows;
+  }
+  return out;
+}
+
+// Builds the replicas (streams, arenas, constant pools, launch lists) that run `run_batch` rows of a graph
+// recorded with `B` rows in dim 0.
+static odla_status build_replicas(_odla_computation* c, int visible, int64_t B, int64_t run_batch, std::vector<Replica>& reps) {
+  const std::vector<Shard> layout = shard_layout(c, visible, B, run_batch);
+  const int G = (int)layout.size();
+  reps.resize((size_t)G);
+  // any failure below releases what the replicas built so far own (streams, events, pinned status words, plans)
+  struct Guard { std::vector<Replica>& r; bool armed = true; ~Guard() { if (armed) destroy_replicas(r); } } guard{reps};
+  for (int i = 0; i < G; ++i) {
     Replica& r = reps[i];
-    r.device = (c->first_device + i / S) % visible;
-    r.shard_batch = c->shardable ? rows[(size_t)i] : B;
-    r.shard_start = start;
-    start += r.shard_batch;
+    r.device = layout[(size_t)i].device;
+    r.shard_batch = layout[(size_t)i].rows;
+    r.shard_start = layout[(size_t)i].start;
     B2_CUDA("setdevice", cudaSetDevice(r.device), ODLA_FAILURE);
     B2_CUDA("stream", cudaStreamCreateWithFlags(&r.stream, cudaStreamNonBlocking), ODLA_FAILURE);
     B2_CUDA("event", cudaEventCreate(&r.ev_begin), ODLA_FAILURE);
@@ -1306,7 +1358,7 @@ static odla_status build_replicas(_odla_computation* c, int visible, int64_t B, 
     r.plan->batch = r.shard_batch;
     Builder b(c, r.plan.get(), c->shardable ? B : r.shard_batch, r.shard_batch, r.shard_start);
     odla_status s = b.run();
-    if (s != ODLA_SUCCESS) { destroy_replicas(reps); return s; }
+    if (s != ODLA_SUCCESS) return s;
     B2_INFO("GPU %d: rows [%lld,%lld), %zu launches, arena %.1f MiB, constants %.1f MiB", r.device, (long long)r.shard_start,
             (long long)(r.shard_start + r.shard_batch), r.plan->launches.size(), r.plan->arena_bytes / 1048576.0, r.plan->const_bytes / 1048576.0);
   }
@@ -1318,6 +1370,7 @@ static odla_status build_replicas(_odla_computation* c, int visible, int64_t B, 
       cudaDeviceCanAccessPeer(&can, reps[i].device, reps[j].device);
       if (can) { cudaSetDevice(reps[i].device); cudaError_t e = cudaDeviceEnablePeerAccess(reps[j].device, 0); if (e != cudaSuccess) cudaGetLastError(); }
     }
+  guard.armed = false;
   return ODLA_SUCCESS;
 }
 
@@ -1414,57 +1467,90 @@ int run_launches(Replica& r, _odla_context* ctx, bool use_graph, long long* n_la
 }
 }  // namespace
 
+// Enqueues one replica's share of an execute on its own stream: input copies, the launch list, output copies, the
+// status read-back and the two events that time it.  Nothing here waits for the GPU.
+static odla_status enqueue_replica(Replica& r, size_t index, _odla_context* ctx, bool use_graph, long long* launched) {
+  Plan& p = *r.plan;
+  auto fail_here = [&](odla_status s, const char* what) { B2_ERR("GPU %d: %s failed", r.device, what); return s; };
+  if (cudaSetDevice(r.device) != cudaSuccess) return fail_here(ODLA_FAILURE, "cudaSetDevice");
+  cudaEventRecord(r.ev_begin, r.stream);
+  for (auto& io : p.inputs) {
+    const char* src = (const char*)ctx->in.find(io.v)->second + io.user_offset;  // every argument is bound (checked by the caller)
+    int pd = pointer_device(src);
+    cudaError_t e;
+    if (inject_fault("h2d")) e = cudaErrorUnknown;
+    else if (pd >= 0 && pd != r.device) e = cudaMemcpyPeerAsync(p.arena + io.stage, r.device, src, pd, (size_t)io.api_bytes, r.stream);
+    else e = cudaMemcpyAsync(p.arena + io.stage, src, (size_t)io.api_bytes, pd >= 0 ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, r.stream);
+    if (e != cudaSuccess) return fail_here(ODLA_FAILURE, "input copy");
+  }
+  int rc = run_launches(r, ctx, use_graph, launched);
+  if (rc) return fail_here(ODLA_FAILURE, "kernel launch");
+  for (auto& io : p.outputs) {
+    auto bound = ctx->out.find(io.v);
+    if (bound == ctx->out.end()) continue;
+    if (!io.per_shard && index != 0) continue;  // a value that does not depend on the batch: the first replica writes it
+    char* dst = (char*)bound->second + io.user_offset;
+    int pd = pointer_device(dst);
+    cudaError_t e;
+    if (inject_fault("d2h")) e = cudaErrorUnknown;
+    else if (io.const_host) {
+      e = cudaMemcpyAsync(dst, io.const_host, (size_t)io.api_bytes, pd >= 0 ? cudaMemcpyHostToDevice : cudaMemcpyHostToHost, r.stream);
+    } else if (pd >= 0 && pd != r.device) {
+      e = inject_fault("peer") ? cudaErrorUnknown : cudaMemcpyPeerAsync(dst, pd, p.arena + io.stage, r.device, (size_t)io.api_bytes, r.stream);
+    } else e = cudaMemcpyAsync(dst, p.arena + io.stage, (size_t)io.api_bytes, pd >= 0 ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, r.stream);
+    if (e != cudaSuccess) return fail_here(ODLA_FAILURE, "output copy");
+  }
+  cudaMemcpyAsync(r.host_status, p.status, sizeof(int) * 4, cudaMemcpyDeviceToHost, r.stream);
+  cudaEventRecord(r.ev_end, r.stream);
+  return ODLA_SUCCESS;
+}
+
 odla_status execute(_odla_computation* c, _odla_context* ctx) {
   for (V a : c->args)
     if (!ctx->in.count(a)) { B2_ERR("argument '%s' is not bound", a->name.c_str()); return ODLA_INVALID_PARAM; }
   odla_status result = ODLA_SUCCESS;
   long long launched = 0;
-  size_t enq = 0;
   std::vector<Replica>* reps_p = nullptr;
   if (odla_status rs = replicas_for_batch(c, ctx->run_batch, &reps_p)) return rs;
   std::vector<Replica>& reps = *reps_p;
-  // enqueue everything on every GPU, then wait; on a failure stop enqueuing and drain what started
-  for (; enq < reps.size() && result == ODLA_SUCCESS; ++enq) {
-    Replica& r = reps[enq];
-    Plan& p = *r.plan;
-    auto fail_here = [&](odla_status s, const char* what) { B2_ERR("GPU %d: %s failed", r.device, what); result = s; };
-    if (cudaSetDevice(r.device) != cudaSuccess) { fail_here(ODLA_FAILURE, "cudaSetDevice"); break; }
-    cudaEventRecord(r.ev_begin, r.stream);
-    for (auto& io : p.inputs) {
-      const char* src = (const char*)ctx->in[io.v] + io.user_offset;
-      int pd = pointer_device(src);
-      cudaError_t e;
-      if (inject_fault("h2d")) e = cudaErrorUnknown;
-      else if (pd >= 0 && pd != r.device) e = cudaMemcpyPeerAsync(p.arena + io.stage, r.device, src, pd, (size_t)io.api_bytes, r.stream);
-      else e = cudaMemcpyAsync(p.arena + io.stage, src, (size_t)io.api_bytes, pd >= 0 ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, r.stream);
-      if (e != cudaSuccess) { fail_here(ODLA_FAILURE, "input copy"); break; }
+  std::vector<char> started(reps.size(), 0);
+  // Enqueue everything on every GPU, then wait.  With more than one GPU each GPU is fed by a host thread of its own:
+  // a copy from pageable host memory blocks the calling thread until it is staged, and eight GPUs fed from one
+  // thread would start one after the other.  A failure stops that GPU's enqueuing; what started is drained below.
+  bool several_devices = false;
+  for (auto& r : reps) if (r.device != reps[0].device) several_devices = true;
+  if (several_devices && !getenv("ODLA_B200_INJECT") && !ctx->profiling && !getenv("ODLA_B200_SERIAL_ENQUEUE")) {
+    std::map<int, std::vector<size_t>> by_device;
+    for (size_t i = 0; i < reps.size(); ++i) by_device[reps[i].device].push_back(i);
+    std::vector<std::thread> workers;
+    std::vector<odla_status> st(by_device.size(), ODLA_SUCCESS);
+    std::vector<long long> nl(by_device.size(), 0);
+    size_t w = 0;
+    for (auto& kv : by_device) {
+      const std::vector<size_t>* idx = &kv.second;
+      odla_status* s_out = &st[w];
+      long long* n_out = &nl[w];
+      ++w;
+      workers.emplace_back([&, idx, s_out, n_out] {
+        for (size_t i : *idx) {
+          started[i] = 1;
+          *s_out = enqueue_replica(reps[i], i, ctx, c->use_graph, n_out);
+          if (*s_out != ODLA_SUCCESS) break;
+        }
+      });
     }
-    if (result != ODLA_SUCCESS) break;
-    int rc = run_launches(r, ctx, c->use_graph, &launched);
-    if (rc) { fail_here(ODLA_FAILURE, "kernel launch"); break; }
-    for (auto& io : p.outputs) {
-      auto bound = ctx->out.find(io.v);
-      if (bound == ctx->out.end()) continue;
-      if (!io.per_shard && enq != 0) continue;  // a value that does not depend on the batch: GPU 0 writes it
-      char* dst = (char*)bound->second + io.user_offset;
-      int pd = pointer_device(dst);
-      cudaError_t e;
-      if (inject_fault("d2h")) e = cudaErrorUnknown;
-      else if (io.const_host) {
-        e = cudaMemcpyAsync(dst, io.const_host, (size_t)io.api_bytes, pd >= 0 ? cudaMemcpyHostToDevice : cudaMemcpyHostToHost, r.stream);
-      } else if (pd >= 0 && pd != r.device) {
-        e = inject_fault("peer") ? cudaErrorUnknown : cudaMemcpyPeerAsync(dst, pd, p.arena + io.stage, r.device, (size_t)io.api_bytes, r.stream);
-      } else e = cudaMemcpyAsync(dst, p.arena + io.stage, (size_t)io.api_bytes, pd >= 0 ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, r.stream);
-      if (e != cudaSuccess) { fail_here(ODLA_FAILURE, "output copy"); break; }
+    for (auto& t : workers) t.join();
+    for (size_t k = 0; k < st.size(); ++k) { if (st[k] != ODLA_SUCCESS && result == ODLA_SUCCESS) result = st[k]; launched += nl[k]; }
+  } else {
+    for (size_t i = 0; i < reps.size() && result == ODLA_SUCCESS; ++i) {
+      started[i] = 1;
+      result = enqueue_replica(reps[i], i, ctx, c->use_graph, &launched);
     }
-    if (result != ODLA_SUCCESS) break;
-    cudaMemcpyAsync(r.host_status, p.status, sizeof(int) * 4, cudaMemcpyDeviceToHost, r.stream);
-    cudaEventRecord(r.ev_end, r.stream);
   }
   if (result != ODLA_SUCCESS) cudaGetLastError();
   float worst = 0.f;
-  size_t started = std::min(enq + (result == ODLA_SUCCESS ? 0 : 1), reps.size());
-  for (size_t i = 0; i < started; ++i) {
+  for (size_t i = 0; i < reps.size(); ++i) {
+    if (!started[i]) continue;
     Replica& r = reps[i];
     cudaSetDevice(r.device);
     cudaError_t e = cudaStreamSynchronize(r.stream);
@@ -1474,7 +1560,7 @@ odla_status execute(_odla_computation* c, _odla_context* ctx) {
       if (cudaEventElapsedTime(&ms, r.ev_begin, r.ev_end) == cudaSuccess) worst = std::max(worst, ms); else cudaGetLastError();
       if (r.host_status[0] != 0) {
         B2_ERR("GPU %d: a bounded wait inside a kernel expired (code %d, detail %d)", r.device, r.host_status[0], r.host_status[1]);
-        cudaMemsetAsync(r.plan->status, 0, 256, r.stream);
+        cudaMemsetAsync(r.plan->status, 0, kStatusBytes, r.stream);
         cudaStreamSynchronize(r.stream);
         result = ODLA_TIMEOUT;
       }
@@ -1509,6 +1595,22 @@ int odla_b200_GetProfile(odla_context ctx, odla_b200_profile_entry* entries, int
     entries[i].flops = ls[i].flops; entries[i].bytes = ls[i].bytes;
   }
   return (int)ls.size();
+}
+int odla_b200_PlanShards(odla_computation c, long long run_batch, int visible_devices, int* device, long long* start, long long* rows, int capacity) {
+  if (!c || visible_devices < 1) return 0;
+  int64_t B = 1;
+  // the same decisions ensure_planned takes, on a scratch copy of the two fields they write
+  const bool was_shardable = c->shardable;
+  c->shardable = graph_shardable(c, &B);
+  if (run_batch <= 0) run_batch = B;
+  const std::vector<Shard> layout = shard_layout(c, visible_devices, B, run_batch);
+  c->shardable = was_shardable;
+  for (size_t i = 0; i < layout.size() && (int)i < capacity; ++i) {
+    if (device) device[i] = layout[i].device;
+    if (start) start[i] = layout[i].start;
+    if (rows) rows[i] = layout[i].rows;
+  }
+  return (int)layout.size();
 }
 int odla_b200_DescribePlan(odla_computation c, char* buf, int capacity) {
   if (!c) return 0;

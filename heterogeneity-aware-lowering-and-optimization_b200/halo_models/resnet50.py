@@ -171,11 +171,11 @@ def build(g, batch, w, input_type=odla.FLOAT32, softmax=True):
     return g
 
 
-def build_int8(g, batch, w, wq, scales, softmax=True, extra_outputs=()):
+def build_int8(g, batch, w, wq, scales, softmax=True, extra_outputs=(), input_type=odla.FLOAT32):
     """Quantise/dequantise form.  `scales` maps tensor name -> per-tensor activation scale."""
     NHWC, SIO = odla.CHANNELS_LAST, odla.SIO
     F32, I8 = odla.FLOAT32, odla.INT8
-    x = g.Argument("input", (batch, 224, 224, 3), F32)
+    x = g.Argument("input", (batch, 224, 224, 3), input_type)
     sc_const = {}
 
     def scale(name):

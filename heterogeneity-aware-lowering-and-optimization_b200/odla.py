@@ -23,6 +23,8 @@ FLOAT16, BFLOAT16, FLOAT32, FLOAT64, BOOL = 16, 17, 18, 19, 20
 ITEM_BF16_MODE, ITEM_FP16_MODE, ITEM_PROCESSOR_NUM, ITEM_USE_DATA_TYPE, ITEM_AGGREGATE_OPS = 13, 14, 16, 18, 23
 ITEM_QUANT_TABLE, ITEM_QUANT_TABLE_SIZE = 21, 22
 ITEM_BATCHES_PER_STEP = 17
+ITEM_DYNAMIC_BATCH, ITEM_MIN_BATCH_SIZE, ITEM_MAX_BATCH_SIZE, ITEM_OPT_BATCH_SIZE = 0, 1, 2, 3
+ITEM_LOAD_ENGINE_MODE, ITEM_ENABLE_ENGINE_CACHE, ITEM_CACHE_DIR = 19, 24, 25
 ITEM_RUN_BATCH_SIZE, ITEM_ASYNC_CALLBACK_FUNC, ITEM_ASYNC_CALLBACK_ARG = 4, 26, 27
 ASYNC_CALLBACK = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int)   # int (*)(void* arg, odla_status)
 # odla_memory_layout
@@ -169,6 +171,7 @@ _OPTIONAL = {
     "odla_b200_SetProfiling": (C.c_int, [_V, C.c_int]),
     "odla_b200_GetProfile": (C.c_int, [_V, C.POINTER(ProfileEntry), C.c_int]),
     "odla_b200_DescribePlan": (C.c_int, [_V, C.c_char_p, C.c_int]),
+    "odla_b200_PlanShards": (C.c_int, [_V, C.c_longlong, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_longlong), C.POINTER(C.c_longlong), C.c_int]),
     "odla_b200_conv_umma": (C.c_int, [C.POINTER(ConvDesc), _V, _V, _V, _V, _V, _V, _V]),
     "odla_b200_reduce_mean_noalloc": (C.c_int, [_V, _V, C.c_int, C.POINTER(C.c_longlong), C.c_int, C.POINTER(C.c_int), C.c_int, _V]),
     "odla_cpuref_UsesReference": (C.c_int, []),
@@ -509,6 +512,13 @@ class Graph:
 
     def launches(self):
         return int(self.lib.b200_LastExecuteLaunches(self.context()))
+
+    def plan_shards(self, visible_devices, run_batch=0):
+        """[(device, first_row, rows), ...]: how an execute would be split over `visible_devices` GPUs (no GPU needed)."""
+        cap = 256
+        dev, start, rows = (C.c_int * cap)(), (C.c_longlong * cap)(), (C.c_longlong * cap)()
+        n = self.lib.b200_PlanShards(self.comp, run_batch, visible_devices, dev, start, rows, cap)
+        return [(dev[i], start[i], rows[i]) for i in range(min(n, cap))]
 
     def describe(self, first_gpu_only=False):
         """The launch list of every replica ("gpu <d> rows [a,b) ..." header, then one line per launch), or of the

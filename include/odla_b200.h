@@ -378,6 +378,14 @@ long long odla_b200_LastExecuteLaunches(odla_context context);
 /* Text description of the launch list (one line per kernel) into buf; returns bytes needed. */
 int odla_b200_DescribePlan(odla_computation computation, char* buf, int capacity);
 
+/* How one odla_ExecuteComputation of `run_batch` rows (<= 0: the recorded batch) would be split if
+ * `visible_devices` GPUs were visible: one entry per replica (GPU x sub-batch) with its device index,
+ * first row and row count.  Needs no GPU -- it is the planner's shard arithmetic on its own, for
+ * tests and capacity planning.  A graph whose dim 0 is not an independent batch yields one replica
+ * holding every row.  Returns the number of replicas (entries beyond `capacity` are not written). */
+int odla_b200_PlanShards(odla_computation computation, long long run_batch, int visible_devices,
+                         int* device, long long* first_row, long long* rows, int capacity);
+
 /* Raw kernel entry points over DEVICE pointers on the current device and the given stream
  * (a cudaStream_t passed as void*; NULL is the default stream).  They return 0 or a negative
  * error code (-1 bad argument, -2 CUDA error, -3 a bounded wait inside the kernel expired).
@@ -412,7 +420,8 @@ int odla_b200_conv_umma(const odla_b200_conv_desc* desc, const void* x, const vo
  *
  *   x, y    device pointers on the current device; x holds prod(dims) elements, y the reduced tensor
  *   dtype   0 = fp32, 1 = fp16, 2 = bf16 (input and output)
- *   dims    extents, rank <= 10; axes: the axes to reduce, each in [0, rank)
+ *   dims    extents, rank <= 10; axes: the axes to reduce, each in [0, rank) and each named once
+ *           (a repeated axis, or y == x, is refused with -1: the passes do not work in place)
  *   stream  a cudaStream_t passed as void* (NULL = default stream); the kernels are only enqueued
  *
  * Intermediates between passes live in a fixed 8 MiB array inside the library image (two halves of

@@ -72,6 +72,57 @@ def test_items_and_binding_checks(odla, lib):
     g.close()
 
 
+def test_dynamic_batch_items_leave_one_replica_per_gpu(odla, lib):
+    """Generated code for a dynamic-batch model sets ODLA_DYNAMIC_BATCH / MIN / MAX / OPT_BATCH_SIZE
+    (generic_cxx_codegen.cc, EmitComputationItems); none of them may turn into sub-batches."""
+    g = odla.Graph(lib, "dyn")
+    flag, mn, mx, opt = C.c_bool(True), C.c_int(1), C.c_int(64), C.c_int(32)
+    for key, val in ((odla.ITEM_DYNAMIC_BATCH, flag), (odla.ITEM_MIN_BATCH_SIZE, mn), (odla.ITEM_MAX_BATCH_SIZE, mx), (odla.ITEM_OPT_BATCH_SIZE, opt)):
+        assert lib.SetComputationItem(g.comp, key, C.cast(C.byref(val), C.c_void_p)) == 0
+    x = g.Argument("x", (64, 8))
+    g.Output(g.Relu(x, "y"))
+    assert g.plan_shards(1) == [(0, 0, 64)]
+    assert g.plan_shards(4) == [(0, 0, 16), (1, 16, 16), (2, 32, 16), (3, 48, 16)]
+    g.close()
+
+
+@pytest.mark.parametrize("batch,gpus,subs", [(256, 8, 1), (250, 8, 1), (5, 8, 1), (256, 8, 2), (250, 4, 3), (7, 2, 4), (1, 8, 2), (2048, 8, 1)])
+def test_shard_arithmetic(odla, lib, batch, gpus, subs):
+    """Shards are contiguous, non-empty, sum to the batch, never use more GPUs than rows, and differ by at most
+    one row between GPUs; sub-batches split a GPU's share (even, or growing by 3 when inputs dominate)."""
+    for wide_input in (False, True):
+        g = odla.Graph(lib, "shards", sub_batches=subs)
+        x = g.Argument("x", (batch, 4096 if wide_input else 4))
+        g.Output(g.Relu(x, "y") if wide_input else g.Relu(g.Concat([x] * 64, 1, (batch, 256), "wide"), "y"))
+        shards = g.plan_shards(gpus)
+        g.close()
+        assert [s[1] for s in shards] == [sum(r[2] for r in shards[:i]) for i in range(len(shards))]
+        assert all(s[2] >= 1 for s in shards) and sum(s[2] for s in shards) == batch
+        per_gpu = {}
+        for d, _, r in shards:
+            per_gpu[d] = per_gpu.get(d, 0) + r
+        assert len(per_gpu) == min(gpus, batch) and max(per_gpu.values()) - min(per_gpu.values()) <= 1
+        assert [s[0] for s in shards] == sorted(s[0] for s in shards)
+        assert len(shards) <= len(per_gpu) * subs
+
+
+def test_constants_that_span_the_batch_keep_the_graph_whole(odla, lib):
+    """Binary / Concat / Gemm with a constant operand of full rank whose dim 0 equals the batch cannot be split by rows
+    without offsetting the constant: such graphs run as one replica."""
+    k = np.arange(8 * 4, dtype=np.float32).reshape(8, 4)
+    for build in (lambda g, x: g.Add(x, g.Constant("k", k), "y"),
+                  lambda g, x: g.Concat([x, g.Constant("k", k)], 1, (8, 8), "y"),
+                  lambda g, x: g.Gemm(x, False, g.Constant("w", np.ones((4, 4), np.float32)), False, 1.0, 1.0, g.Constant("k", k), (8, 4), "y")):
+        g = odla.Graph(lib, "spans")
+        g.Output(build(g, g.Argument("x", (8, 4))))
+        assert g.plan_shards(4) == [(0, 0, 8)]
+        g.close()
+    g = odla.Graph(lib, "row_const")       # a per-row-broadcast constant ([1, 4]) splits fine
+    g.Output(g.Add(g.Argument("x", (8, 4)), g.Constant("k", k[:1]), "y"))
+    assert len(g.plan_shards(4)) == 4
+    g.close()
+
+
 def test_device_api_every_item_answers(odla, lib):
     # tests/ODLA/device_test.cc:63-89 in the reference: every odla_GetDeviceInfo item returns SUCCESS
     dev = C.c_void_p()

@@ -1,0 +1,178 @@
+"""Whole-graph parity at the real workload sizes against fixtures the CPU oracle produced offline
+(tests/golden/make_model_golden.py): ResNet-50 v1.5 @224 at batch 1, 32 and 256 in fp32, fp16, bf16 and
+int8; YOLOv3 @416; the 12-layer BERT-base encoder in floating point and in its int8-GEMM form.
+
+Tolerances: fp32 graphs 1e-4 (the reference's unit-test threshold); fp16 / bf16 max-abs 1e-2 on the
+soft-max output and top-1 equal on every image; int8 bit-equal on every tapped int8 tensor (a 64-bit
+hash per image; the small taps also element by element)."""
+import hashlib
+import os
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(HERE, "golden"))
+import make_model_golden as mg   # noqa: E402  (the input recipes and tap lists are shared with the generator)
+
+
+def golden(name):
+    return np.load(os.path.join(HERE, "golden", name), allow_pickle=False)
+
+
+@pytest.fixture(scope="module")
+def rn_weights(models):
+    return models.resnet50.weights()
+
+
+@pytest.mark.parametrize("mode,batch", [("fp32", 32), ("fp16", 1), ("fp16", 32), ("fp16", 256), ("bf16", 32)])
+def test_resnet50_matches_the_batch32_fixture(odla, gpu_lib, models, rn_weights, mode, batch):
+    """Rows of the batch are independent, so a batch-1 run is compared with image 0 and a batch-256 run with its
+    first 32 images (the other 224 differ from run to run of the generator and are checked for sanity only)."""
+    rn = models.resnet50
+    gold = golden("resnet50_b32_fp32.npz")
+    g = odla.Graph(gpu_lib, "resnet50", fp16=(mode == "fp16"), bf16=(mode == "bf16"))
+    rn.build(g, batch, rn_weights)
+    got = g.run(mg.resnet_inputs(rn, batch))["prob"]
+    g.close()
+    n = min(batch, 32)
+    want = gold["prob"][:n]
+    err = float(np.abs(got[:n] - want).max())
+    assert err <= (1e-4 if mode == "fp32" else 1e-2), err
+    assert (got[:n].argmax(1) == want.argmax(1)).all()
+    # the five most probable classes agree as sets (random weights put most images on the same top-1 class)
+    if mode != "bf16":
+        assert all(set(np.argsort(-got[i])[:5]) == set(np.argsort(-want[i])[:5]) for i in range(n))
+    if mode == "fp16":
+        assert err <= 2e-3
+    np.testing.assert_allclose(got.sum(1), 1.0, atol=2e-3)
+
+
+@pytest.mark.parametrize("batch", [1, 32, 256])
+def test_resnet50_int8_is_bit_exact_at_full_batch(odla, gpu_lib, models, rn_weights, batch):
+    rn = models.resnet50
+    gold = golden("resnet50_b32_int8.npz")
+    scales = {str(k): np.float32(v) for k, v in zip(gold["scale_names"], gold["scale_values"])}
+    wq = rn.quantize_weights(rn_weights)
+    g = odla.Graph(gpu_lib, "resnet50_int8")
+    rn.build_int8(g, batch, rn_weights, wq, scales, extra_outputs=mg.RESNET_TAPS)
+    out = g.run(mg.resnet_inputs(rn, batch))
+    desc = g.describe(first_gpu_only=True)
+    g.close()
+    assert desc.count("conv_umma") >= 53 and "gemm_umma" in desc
+    n = min(batch, 32)
+    for t in mg.RESNET_TAPS:
+        a = out[t + "_q"]
+        assert a.dtype == np.int8
+        h = mg.image_hashes(a[:n])
+        bad = np.nonzero(h != gold["hash_" + t][:n])[0]
+        assert bad.size == 0, "%s: images %s differ from the oracle" % (t, bad.tolist())
+        if t in mg.RESNET_FULL_TAPS and n >= 2:
+            assert np.array_equal(a[:2], gold["full_" + t])
+    assert np.abs(out["prob"][:n] - gold["prob"][:n]).max() < 1e-6
+
+
+@pytest.mark.parametrize("mode,batch", [("fp32", 1), ("fp16", 1), ("fp16", 16)])
+def test_yolov3_416_heads_match_the_fixture(odla, gpu_lib, models, mode, batch):
+    yo = models.yolov3
+    gold = golden("yolov3_416_b1.npz")
+    w = yo.weights()
+    x = yo.inputs(1)["input"]
+    if batch > 1:
+        x = np.concatenate([x, yo.inputs(batch - 1, seed=555)["input"]], axis=0)
+    g = odla.Graph(gpu_lib, "yolov3", fp16=(mode == "fp16"))
+    yo.build(g, batch, w)
+    got = g.run({"input": x})
+    desc = g.describe(first_gpu_only=True)
+    g.close()
+    if mode == "fp16":
+        assert desc.count("conv_umma") == 75
+    heads = [k for k in gold.files if k != "kernels"]
+    assert sorted(got) == sorted(heads)
+    assert sorted(got[k].shape[1:] for k in heads) == [(13, 13, 255), (26, 26, 255), (52, 52, 255)]
+    for k in heads:
+        want = gold[k].astype(np.float32)
+        scale = max(float(np.abs(want).max()), 1.0)
+        err = float(np.abs(got[k][:1] - want).max())
+        # the fixture is stored in fp16 (relative 2^-11); fp16 evaluation through 75 layers: 2e-2 of the tensor's range
+        assert err <= (2e-3 if mode == "fp32" else 2e-2) * scale, (k, err, scale)
+
+
+@pytest.mark.parametrize("form,mode,batch", [("float", "fp32", 1), ("float", "fp16", 1), ("float", "fp16", 64), ("int8", "fp16", 1), ("int8", "fp16", 64), ("int8", "fp32", 1)])
+def test_bert_base_12_layers_match_the_fixture(odla, gpu_lib, models, form, mode, batch):
+    """Sequence 0 of every batch is the fixture's sequence.  The int8-GEMM form quantises LayerNorm / GELU outputs, so a
+    last-bit difference of the floating-point kernels can move an int8 value by one step: its tolerance is wider."""
+    be = models.bert
+    cfg = be.BASE
+    gold = golden("bert_base_b1.npz")
+    w = be.weights(cfg)
+    quant = None
+    if form == "int8":
+        quant = be.quantize(cfg, w, n_sequences=1)      # int8 weights (deterministic); activation scales from the fixture
+        quant.update({str(k): np.float32(v) for k, v in zip(gold["act_names"], gold["act_scales"])})
+    g = odla.Graph(gpu_lib, "bert", fp16=(mode == "fp16"))
+    be.build(g, batch, cfg, w, quant=quant)
+    got = g.run(mg.bert_inputs(be, cfg, batch))["encoder_out"]
+    desc = g.describe(first_gpu_only=True)
+    g.close()
+    want = gold["encoder_out_" + form].astype(np.float32)
+    err = float(np.abs(got[:1] - want).max())
+    mean_err = float(np.abs(got[:1] - want).mean())
+    tol = {("float", "fp32"): 2e-3, ("float", "fp16"): 3e-2, ("int8", "fp32"): 3e-2, ("int8", "fp16"): 6e-2}[(form, mode)]
+    assert err <= tol and mean_err <= tol / 8, (err, mean_err)
+    if mode == "fp16":
+        assert desc.count("gemm_umma") == 8 * cfg["layers"]     # Q, K, V, out, two FFN layers, scores, context
+        assert "transpose" not in desc
+    if form == "int8":
+        # x (shared by Q, K, V), ctx and x1 are quantised by a kernel of their own; the GELU output is requantised in
+        # the first FFN Gemm's epilogue; every Dequantize is absorbed by an int8 tensor-core Gemm
+        assert desc.count("\n  quantize ") == 3 * cfg["layers"] and "requantize" not in desc and "dequantize" not in desc
+
+
+def test_bert_int8_gemm_layer_is_bit_exact(odla, gpu_lib, ref):
+    """The six int8 Gemm shapes of BERT-base on int8 inputs (no floating-point producer in front): accumulate in
+    int32, scale per output column, add the bias, requantise -- bit-equal with the oracle."""
+    rng = np.random.default_rng(5)
+    for M, K, N in ((256, 768, 768), (256, 768, 3072), (256, 3072, 768)):
+        xq = rng.integers(-128, 128, (M, K), dtype=np.int8)
+        wq = np.clip(np.rint(rng.standard_normal((K, N)) * 40), -127, 127).astype(np.int8)
+        ws = rng.uniform(1e-3, 2e-3, N).astype(np.float32)
+        bias = rng.standard_normal(N).astype(np.float32)
+        outs = []
+        for L in (gpu_lib, ref):
+            g = odla.Graph(L, "gemm_s8", **({"fp16": False}))
+            x = g.Argument("x", (M, K), odla.INT8)
+            sx = g.Constant("sx", np.array([0.03], np.float32))
+            xd = g.Dequantize(x, sx, None, 0, odla.FLOAT32, "xd")
+            wd = g.Dequantize(g.Constant("wq", wq), g.Constant("ws", ws), None, 1, odla.FLOAT32, "wd")
+            y = g.Gemm(xd, False, wd, False, 1.0, 1.0, g.Constant("b", bias), (M, N), "y")
+            g.Output(g.Quantize(y, g.Constant("sy", np.array([0.05], np.float32)), None, 0, odla.INT8, "yq"))
+            outs.append(g.run({"x": xq})["yq"])
+            if L is gpu_lib:
+                assert "gemm_umma" in g.describe(first_gpu_only=True)
+            g.close()
+        assert np.array_equal(outs[0], outs[1]), (M, K, N, int((outs[0] != outs[1]).sum()))
+        assert int(np.abs(outs[1].astype(int)).max()) > 20
+
+
+@pytest.mark.parametrize("mode", ["fp32", "fp16"])
+def test_decomposed_layernorm_graph(odla, gpu_lib, ref, models, mode):
+    """LayerNorm as HALO leaves it with -fuse-layernorm=false: ReduceMean, Sub, Mul, ReduceMean, Add, Rsqrt, Mul, Mul,
+    Add -- every op its own ODLA call -- in a two-layer encoder, against the oracle running the same graph."""
+    be = models.bert
+    cfg = dict(vocab=500, hidden=64, heads=4, ffn=256, layers=2, seq=16)
+    w = be.weights(cfg)
+    x = be.inputs(cfg, 2)
+    outs = []
+    for L in (gpu_lib, ref):
+        g = odla.Graph(L, "bert_dec", **({"fp16": mode == "fp16"} if L is gpu_lib else {}))
+        be.build(g, 2, cfg, w, decomposed_layernorm=True)
+        outs.append(g.run(x)["encoder_out"])
+        if L is gpu_lib:
+            desc = g.describe(first_gpu_only=True)
+        g.close()
+    assert "layernorm" not in desc and desc.count("reduce_mean") == 2 * (1 + 2 * cfg["layers"])
+    err = float(np.abs(outs[0] - outs[1]).max())
+    assert err <= (2e-4 if mode == "fp32" else 3e-2), err
