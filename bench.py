@@ -341,6 +341,13 @@ def run_b200(args, rank, world, local_rank):
                         "h2d_gbs_per_rank": h2d / (e2e_wall_ms / args.steps * 1e-3) / 1e9, "timing": "wall clock around the synchronous odla_ExecuteComputation, max over ranks"},
                 "gpu_launches": launches, "clocks": clocks, "roofline": roof, "families": families, "top1": top1}
 
+    if args.only_int8:   # profiling aid: the int8 form alone, printed as a line of its own
+        scales = rn.calibrate(w, n_images=8)
+        r8 = measure(lambda g: rn.build_int8(g, BATCH, w, rn.quantize_weights(w), scales, input_type=odla.FLOAT16), "int8", True)
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": r8["value"], "unit": UNIT, "dtype": "s8", "config": {"workload": "resnet50_v1.5_nhwc_int8_b%d" % args.batch},
+                              "ms_per_step": r8["ms_per_step"], "e2e": r8["e2e"], "roofline": r8["roofline"], "clocks": r8["clocks"]}))
+        return
     fp16 = measure(lambda g: rn.build(g, BATCH, w, input_type=odla.FLOAT16), "fp16", False)
     int8 = None
     if not args.no_int8:
@@ -473,6 +480,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-int8", action="store_true", help="skip the secondary int8 measurement")
+    ap.add_argument("--only-int8", action="store_true", help="measure only the int8 form (for profiling one of its kernels)")
     ap.add_argument("--workload", default="resnet50", choices=["resnet50", "yolov3", "bert"],
                     help="resnet50 is the benchmark line; yolov3 (B=16) and bert (B=64) are the secondary BASELINE configurations")
     ap.add_argument("--sub-batches", type=int, default=2, help="ODLA_BATCHES_PER_STEP of the end-to-end (host-bound) leg; 1 = off")

@@ -51,7 +51,7 @@ template <bool STAGED> struct EpiCfg {
   static constexpr int kThreads = 32 * (4 + kWarps);
 };
 constexpr int kMaxRing = 8;
-constexpr uint32_t kSpinLimit = 1u << 20;  // attempts of up to 4 us each before a wait gives up
+constexpr uint32_t kSpinLimit = 1u << 18;  // attempts of up to 4 us (plus a short sleep) each before a wait gives up: about a second
 
 struct UmmaParams {
   int M_total, K_out, C, R, S, P, Q;
@@ -78,7 +78,8 @@ struct UmmaParams {
   int pair;            // 1: two CTAs of a cluster share each 256-row tile (tcgen05 cta_group::2), each loading half of B
   int bn_load;         // rows of B this CTA brings into shared memory per k-block (BN, or BN/2 in pair mode)
   int store_mode, store_S, store_NH;  // permuted store through a 4-d map (see UmmaConv)
-  int epi_mode;        // kernel variant: 0 direct, 1 staged, 2 staged with the general activation / division
+  int epi_mode;        // kernel variant: 0 direct, 1 staged straight-line form, 2 staged general form
+  int fast_variant;    // mode 1: accumulator conversion (0 fp32, 1 int32 by conversion, 2 int32 by integer add) * 2 + residual
   int tmem_cols;
   void* y;
   int* status;
@@ -502,6 +503,10 @@ __device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, float (&v)[C
 }
 
 // Two fp32 additions in one instruction (add.rn.f32x2, sm_100): same rounding as two __fadd_rn.
+// CAUTION: an add.rn.f32x2 that consumes the result of a mul.rn.f32x2 is contracted into one fused multiply-add by
+// the assembler in spite of the .rn qualifiers (measured: 27 % of random inputs differ in the last bit from
+// mul-then-add; each instruction on its own, and a packed multiply followed by scalar __fadd_rn, are exact).  A sum
+// whose operand comes from fmul2_rn therefore uses __fadd_rn.
 __device__ __forceinline__ void fadd2_rn(float& a0, float& a1, float b0, float b1) {
   asm("{\n\t.reg .b64 x, y;\n\tmov.b64 x, {%0, %1};\n\tmov.b64 y, {%2, %3};\n\tadd.rn.f32x2 x, x, y;\n\tmov.b64 {%0, %1}, x;\n\t}"
       : "+f"(a0), "+f"(a1)
@@ -541,15 +546,26 @@ __device__ __forceinline__ void epilogue_chunk_staged(const UmmaParams& p, float
 #pragma unroll
     for (int j = 0; j < 16; j += 2) fmul2_rn(v[j], v[j + 1], ep.alpha, ep.alpha);
   }
+  const bool after_mul = ep.mul != nullptr || ep.alpha != 1.f;  // v[] comes out of a packed multiplication
   if (ep.add1) {
     load_vec<16>(ep.add1, col0, kmax, full, cv);
+    if (after_mul) {
 #pragma unroll
-    for (int j = 0; j < 16; j += 2) fadd2_rn(v[j], v[j + 1], cv[j], cv[j + 1]);
+      for (int j = 0; j < 16; ++j) v[j] = __fadd_rn(v[j], cv[j]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; j += 2) fadd2_rn(v[j], v[j + 1], cv[j], cv[j + 1]);
+    }
   }
   if (ep.add2) {
     load_vec<16>(ep.add2, col0, kmax, full, cv);
+    if (after_mul && !ep.add1) {
 #pragma unroll
-    for (int j = 0; j < 16; j += 2) fadd2_rn(v[j], v[j + 1], cv[j], cv[j + 1]);
+      for (int j = 0; j < 16; ++j) v[j] = __fadd_rn(v[j], cv[j]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; j += 2) fadd2_rn(v[j], v[j + 1], cv[j], cv[j + 1]);
+    }
   }
   if (ANYACT && ep.act_first) apply_act_all<16>(ep.act, v, ep.act_a, ep.act_b);
   if (p.res_tma) {
@@ -563,7 +579,8 @@ __device__ __forceinline__ void epilogue_chunk_staged(const UmmaParams& p, float
         for (int b = 0; b < 4; b += 2) {
           float r0 = s8_byte_to_float(wf, b), r1 = s8_byte_to_float(wf, b + 1);
           fmul2_rn(r0, r1, ep.res_scale, ep.res_scale);
-          fadd2_rn(v[t * 4 + b], v[t * 4 + b + 1], r0, r1);
+          v[t * 4 + b] = __fadd_rn(v[t * 4 + b], r0);
+          v[t * 4 + b + 1] = __fadd_rn(v[t * 4 + b + 1], r1);
         }
       }
     } else {
@@ -573,7 +590,8 @@ __device__ __forceinline__ void epilogue_chunk_staged(const UmmaParams& p, float
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
           const float2 f = OUT == DT_F16 ? __half22float2(((const __half2*)&u)[t]) : __bfloat1622float2(((const __nv_bfloat162*)&u)[t]);
-          fadd2_rn(v[q * 8 + 2 * t], v[q * 8 + 2 * t + 1], f.x, f.y);
+          if (after_mul && !ep.add1 && !ep.add2) { v[q * 8 + 2 * t] = __fadd_rn(v[q * 8 + 2 * t], f.x); v[q * 8 + 2 * t + 1] = __fadd_rn(v[q * 8 + 2 * t + 1], f.y); }
+          else fadd2_rn(v[q * 8 + 2 * t], v[q * 8 + 2 * t + 1], f.x, f.y);
         }
       }
     }
@@ -597,7 +615,7 @@ __device__ __forceinline__ void epilogue_chunk_staged(const UmmaParams& p, float
         q[b] = v[t * 4 + b]; q[b + 1] = v[t * 4 + b + 1];
         fmul2_rn(q[b], q[b + 1], ep.out_inv, ep.out_inv);
         q[b] = fminf(fmaxf(q[b], lo), 127.f); q[b + 1] = fminf(fmaxf(q[b + 1], lo), 127.f);
-        fadd2_rn(q[b], q[b + 1], kMagic, kMagic);
+        fadd2_rn(q[b], q[b + 1], kMagic, kMagic);  // (the clamp sits between the multiplication and this addition)
       }
       w[t] = __byte_perm(__byte_perm(__float_as_uint(q[0]), __float_as_uint(q[1]), 0x0040), __byte_perm(__float_as_uint(q[2]), __float_as_uint(q[3]), 0x0040), 0x5410);
     }
@@ -640,10 +658,133 @@ __device__ __forceinline__ void epilogue_chunk_staged(const UmmaParams& p, float
   }
 }
 
+
+// The staged epilogue of the common layer forms as straight-line code (MODE 1): every decision that does not depend on
+// the data is a template parameter or was made on the host, because the general chunk above spends a fifth of its
+// instructions on branches over the launch's configuration.  The launcher guarantees: full 16-column chunks, alpha = 1,
+// exactly one per-channel addend (`addv`), a per-channel multiplier exactly when the accumulators are integers,
+// activation none or ReLU after the residual, int8 outputs requantised by multiplication.
+//   ACC 0: fp32 accumulators; 1: int32 -> fp32 by conversion; 2: int32 -> fp32 by the exact integer-add form (|acc| < 2^22)
+//   RES: a residual tile of the output's type waits in the staging box
+template <int OUT, int ACC, bool RES>
+__device__ __forceinline__ void chunk_fast(const uint32_t (&r)[16], const float* __restrict__ mulv, const float* __restrict__ addv, float res_scale,
+                                           float out_inv, float lo, uint32_t relu_floor, const StagePos& sp) {
+  float v[16];
+  if (ACC == 2) {
+#pragma unroll
+    for (int j = 0; j < 16; j += 2) {
+      v[j] = __uint_as_float(r[j] + kMagicBits); v[j + 1] = __uint_as_float(r[j + 1] + kMagicBits);
+      fadd2_rn(v[j], v[j + 1], -kMagic, -kMagic);
+    }
+  } else if (ACC == 1) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = (float)(int32_t)r[j];
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+  }
+  float cv[16];
+  if (ACC != 0) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) { const float4 f = __ldg((const float4*)mulv + q); cv[4 * q] = f.x; cv[4 * q + 1] = f.y; cv[4 * q + 2] = f.z; cv[4 * q + 3] = f.w; }
+#pragma unroll
+    for (int j = 0; j < 16; j += 2) fmul2_rn(v[j], v[j + 1], cv[j], cv[j + 1]);
+  }
+#pragma unroll
+  for (int q = 0; q < 4; ++q) { const float4 f = __ldg((const float4*)addv + q); cv[4 * q] = f.x; cv[4 * q + 1] = f.y; cv[4 * q + 2] = f.z; cv[4 * q + 3] = f.w; }
+  if (ACC != 0) {  // the sum consumes a packed product: scalar additions (see fadd2_rn)
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = __fadd_rn(v[j], cv[j]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; j += 2) fadd2_rn(v[j], v[j + 1], cv[j], cv[j + 1]);
+  }
+  if (OUT == DT_S8) {
+    if (RES) {
+      const uint4 u = lds128(stage_piece(sp, 0));
+      const uint32_t* w = (const uint32_t*)&u;
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const uint32_t wf = w[t] ^ 0x80808080u;
+#pragma unroll
+        for (int b = 0; b < 4; b += 2) {
+          float r0 = s8_byte_to_float(wf, b), r1 = s8_byte_to_float(wf, b + 1);
+          fmul2_rn(r0, r1, res_scale, res_scale);
+          v[t * 4 + b] = __fadd_rn(v[t * 4 + b], r0);
+          v[t * 4 + b + 1] = __fadd_rn(v[t * 4 + b + 1], r1);
+        }
+      }
+    }
+    uint4 u;
+    uint32_t* w = (uint32_t*)&u;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      float q[4];
+#pragma unroll
+      for (int b = 0; b < 4; b += 2) {
+        q[b] = v[t * 4 + b]; q[b + 1] = v[t * 4 + b + 1];
+        fmul2_rn(q[b], q[b + 1], out_inv, out_inv);
+        q[b] = fminf(fmaxf(q[b], lo), 127.f); q[b + 1] = fminf(fmaxf(q[b + 1], lo), 127.f);
+        fadd2_rn(q[b], q[b + 1], kMagic, kMagic);  // (the clamp sits between the multiplication and this addition)
+      }
+      w[t] = __byte_perm(__byte_perm(__float_as_uint(q[0]), __float_as_uint(q[1]), 0x0040), __byte_perm(__float_as_uint(q[2]), __float_as_uint(q[3]), 0x0040), 0x5410);
+    }
+    sts128(stage_piece(sp, 0), u);
+  } else {
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      uint4 u;
+      if (RES) {
+        u = lds128(stage_piece(sp, q));
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float2 f = OUT == DT_F16 ? __half22float2(((const __half2*)&u)[t]) : __bfloat1622float2(((const __nv_bfloat162*)&u)[t]);
+          fadd2_rn(v[q * 8 + 2 * t], v[q * 8 + 2 * t + 1], f.x, f.y);   // v[] comes out of an addition here
+        }
+      }
+      // ReLU after packing, two values per instruction: rounding is monotonic and keeps the sign; without a ReLU the
+      // floor is -inf and the maximum changes nothing
+      if (OUT == DT_F16) {
+        __half2* h = (__half2*)&u;
+        const __half2 fl = *(const __half2*)&relu_floor;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) h[t] = __hmax2(__floats2half2_rn(v[q * 8 + 2 * t], v[q * 8 + 2 * t + 1]), fl);
+      } else {
+        __nv_bfloat162* h = (__nv_bfloat162*)&u;
+        const __nv_bfloat162 fl = *(const __nv_bfloat162*)&relu_floor;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) h[t] = __hmax2(__floats2bfloat162_rn(v[q * 8 + 2 * t], v[q * 8 + 2 * t + 1]), fl);
+      }
+      sts128(stage_piece(sp, q), u);
+    }
+  }
+}
+// One box's share of chunks for one epilogue warp, straight-line form.
+template <int OUT, int ACC, bool RES>
+__device__ __forceinline__ void box_fast(const UmmaParams& p, uint32_t taddr, int first, int last, int step, int n0, int bx, int chunks_per_box, StagePos sp,
+                                         float lo, uint32_t relu_floor) {
+  const float res_scale = p.ep.res_scale, out_inv = p.ep.out_inv;
+  const float* mulv = p.ep.mul;
+  const float* addv = p.ep.add1 ? p.ep.add1 : p.ep.add2;
+  const int j_shift = OUT == DT_S8 ? 0 : 1;   // 16 columns are one (int8) or two (16-bit types) 16-byte pieces
+#pragma unroll 1
+  for (int ch = first; ch < last; ch += step) {
+    const int col0 = n0 + ch * 16;
+    if (col0 >= p.K_out) break;
+    uint32_t r[16];
+    tmem_ld16(taddr + (uint32_t)(ch * 16), r);
+    tmem_ld_wait_regs<16>(r);
+    sp.j0 = (ch - bx * chunks_per_box) << j_shift;
+    chunk_fast<OUT, ACC, RES>(r, mulv + col0, addv + col0, res_scale, out_inv, lo, relu_floor, sp);
+  }
+}
+
 // --------------------------------------------------------------------- kernel ----
 // MODE 0: direct epilogue (any output type, rows written straight to global memory).
-// MODE 1: staged epilogue, activation none / ReLU after the residual, int8 requantisation by multiplication.
-// MODE 2: staged epilogue with every activation, activation before the residual and division requantisation.
+// MODE 1: staged epilogue, straight-line forms (box_fast): activation none / ReLU after the residual, one per-channel
+//         addend, int8 requantisation by multiplication.
+// MODE 2: staged epilogue, general form: every activation, activation before the residual, division requantisation,
+//         any combination of per-channel vectors, a ragged last chunk.
 // PAIR: CTA-pair variant (its cta_group::2 instructions make the kernel launchable only as clusters of two).
 template <int OUT, int MODE, bool PAIR>
 __global__ void __launch_bounds__(EpiCfg<MODE != 0>::kThreads, 1)
@@ -861,6 +1002,13 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         for (int bx = 0; bx < p.stage_boxes; ++bx) {
           const int x0 = n0 + bx * cols_per_box;
           if (x0 >= p.K_out) break;
+          // Nothing to send yet: use the wait to let the last store finish reading its box and hand that box back,
+          // so that the next tile's epilogue never waits for this tile's boxes to be stored.
+          if (prev >= 0 && !mbar_try_wait(box_done + slot, ph)) {
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            mbar_arrive(box_free + prev);
+            prev = -1;
+          }
           if (!mbar_wait(box_done + slot, ph, abort_flag, p.status, 7)) { ok = false; break; }
           if (p.store_mode == 0) {
             asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"((uint64_t)&tmY),
@@ -909,6 +1057,10 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int ch_lo = cgroup * per_group, ch_hi = ch_lo + per_group;
       int slot = 0;
       uint32_t ph = 0;
+      // ReLU of the straight-line forms: the lower clamp of an int8 output, a packed floor for 16-bit outputs
+      const bool fast_relu = p.ep.act == ACT_RELU;
+      const float fast_lo = fast_relu ? 0.f : -128.f;
+      const uint32_t fast_floor = fast_relu ? 0u : (OUT == DT_F16 ? 0xFC00FC00u : 0xFF80FF80u);
       for (int tile = tile_first; tile < p.total_tiles && ok; tile += tile_step, ++tcount) {
         const uint32_t acc = tcount & 1, acc_ph = (tcount >> 1) & 1;
         const int n0 = (tile / p.m_tiles) * p.BN;
@@ -926,6 +1078,17 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             StagePos sp;
             sp.row_addr = staging_u32 + (uint32_t)slot * 16384u + (uint32_t)r_in_tile * 128u;
             sp.rxor = r_in_tile & 7;
+            if constexpr (MODE == 1) {
+              // straight-line forms, chosen once per launch on the host (p.fast_variant = ACC * 2 + RES)
+              switch (p.fast_variant) {
+                case 0: box_fast<OUT, 0, false>(p, taddr, first, last, step, n0, bx, chunks_per_box, sp, fast_lo, fast_floor); break;
+                case 1: box_fast<OUT, 0, true>(p, taddr, first, last, step, n0, bx, chunks_per_box, sp, fast_lo, fast_floor); break;
+                case 2: box_fast<OUT, 1, false>(p, taddr, first, last, step, n0, bx, chunks_per_box, sp, fast_lo, fast_floor); break;
+                case 3: box_fast<OUT, 1, true>(p, taddr, first, last, step, n0, bx, chunks_per_box, sp, fast_lo, fast_floor); break;
+                case 4: box_fast<OUT, 2, false>(p, taddr, first, last, step, n0, bx, chunks_per_box, sp, fast_lo, fast_floor); break;
+                default: box_fast<OUT, 2, true>(p, taddr, first, last, step, n0, bx, chunks_per_box, sp, fast_lo, fast_floor); break;
+              }
+            } else {
 #pragma unroll 1
             for (int ch = first; ch < last; ch += step) {
               const int col0 = n0 + ch * CW;
@@ -950,7 +1113,8 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 for (int j = 0; j < CW; ++j) v[j] = __uint_as_float(r[j]);
               }
               sp.j0 = ((ch - bx * chunks_per_box) * CW * p.out_esz) >> 4;
-              epilogue_chunk_staged<OUT, MODE == 2>(p, v, col0, sp);
+              epilogue_chunk_staged<OUT, true>(p, v, col0, sp);
+            }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the bulk-copy engine must see these writes
             __syncwarp();
@@ -1146,19 +1310,29 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
              ((uintptr_t)y % 16 == 0) && !getenv("ODLA_B200_DIRECT_EPILOGUE");
   p.stage_boxes = p.staged ? (p.BN * p.out_esz + 127) / 128 : 0;
   p.res_tma = p.staged && ep.res;
-  const bool plain_act = !ep.act_first && (ep.act == ACT_NONE || ep.act == ACT_RELU) && (ep.out_dt != DT_S8 || ep.out_multiply);
-  p.epi_mode = !p.staged ? 0 : (plain_act ? 1 : 2);
+  const bool plain_act = !ep.act_first && (ep.act == ACT_NONE || ep.act == ACT_RELU) && (ep.out_dt != DT_S8 || (ep.out_multiply && ep.out_inv > 0.f));
+  // what the straight-line epilogue assumes (see chunk_fast); everything else takes the general staged form
+  const bool fast_ok = plain_act && c.K % 16 == 0 && ep.alpha == 1.f && ((ep.add1 != nullptr) != (ep.add2 != nullptr)) &&
+                       ((ep.mul != nullptr) == (c.in_dt == DT_S8)) && (ep.out_dt != DT_S8 || c.in_dt == DT_S8) && !getenv("ODLA_B200_GENERAL_EPILOGUE");
+  p.epi_mode = !p.staged ? 0 : (fast_ok ? 1 : 2);
+  p.fast_variant = (c.in_dt == DT_S8 ? (ep.acc_small ? 2 : 1) : 0) * 2 + (ep.res ? 1 : 0);
   // Shared memory: pipeline stages first (up to 4, or what one tile needs), then as many staging
   // boxes as fit (at least one tile's worth, at most 8) so residual loads run ahead of the epilogue
   // and stores drain behind it; what is left goes back to the pipeline.
+  // A memory-bound layer needs enough bytes in flight per SM to cover the latency of HBM (about 64 KB at 6.5 TB/s
+  // over 148 SMs): boxes armed ahead carry the residual loads, stages armed ahead the operand loads, so neither is
+  // limited to what one tile needs.
   const int budget = 224 * 1024;
   int want_stages = p.num_it + 1 < 4 ? p.num_it + 1 : 4;
   if (want_stages < 2) want_stages = 2;
   p.ring_boxes = 0;
   if (p.staged) {
+    int ring_want = ep.res ? 4 * p.stage_boxes : 2 * p.stage_boxes;
+    if (ring_want < 4) ring_want = 4;
+    if (getenv("ODLA_B200_RING")) ring_want = atoi(getenv("ODLA_B200_RING"));
     p.ring_boxes = (budget - want_stages * stage_bytes) / 16384;
     if (p.ring_boxes > kMaxRing) p.ring_boxes = kMaxRing;
-    if (p.ring_boxes > 2 * p.stage_boxes) p.ring_boxes = 2 * p.stage_boxes;
+    if (p.ring_boxes > ring_want) p.ring_boxes = ring_want;
     if (p.ring_boxes < p.stage_boxes) p.ring_boxes = p.stage_boxes;
     if (p.ring_boxes < 2) p.ring_boxes = 2;  // the store of box i frees box i-1
   }
@@ -1175,7 +1349,12 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
   }
   p.stages = (budget - p.ring_boxes * 16384) / stage_bytes;
   if (p.stages > 8) p.stages = 8;
-  if (p.stages > p.num_it + 1) p.stages = p.num_it + 1;
+  {
+    // stages beyond one tile's worth let the producer run into the following tiles (the stage ring spans tiles)
+    int cap = p.num_it + 1 > 6 ? p.num_it + 1 : 6;
+    if (getenv("ODLA_B200_STAGE_CAP")) cap = atoi(getenv("ODLA_B200_STAGE_CAP")) + p.num_it;
+    if (p.stages > cap) p.stages = cap;
+  }
   if (p.stages < 2) p.stages = 2;
   p.acc_int = c.in_dt == DT_S8;
   p.store_mode = c.store_mode; p.store_S = c.store_S; p.store_NH = c.store_NH;
