@@ -375,8 +375,92 @@ def run_b200(args, rank, world, local_rank):
             "kernel_families_share": fp16["families"], "int8": int8, "cpu_baseline": cpu, "check": {"top1_of_first_image": fp16["top1"]}}))
 
 
+def run_ops(args, rank, world, local_rank):
+    """The memory-bound kernels one at a time, each as a single-op ODLA graph at the shape it has in the ResNet-50 /
+    YOLOv3 / BERT-base workloads: device-resident tensors, CUDA events around the kernel's own launch, achieved GB/s =
+    algorithmic bytes (input + output, each once) / time against the measured copy bandwidth."""
+    import torch
+    pkg = importlib.import_module(PKG)
+    odla = pkg.odla
+    os.environ["ODLA_B200_DEVICE"] = str(local_rank)
+    os.environ["ODLA_B200_NUM_GPUS"] = "1"
+    torch.cuda.set_device(local_rank)
+    lib = pkg.load()
+    if lib.b200_DeviceCount() < 1:
+        raise RuntimeError("bench.py needs a CUDA device: libodla_b200 has no CPU fallback")
+    peaks, peak_kind = measured_peaks()
+    hbm = float(peaks["hbm_gbs"])
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    F16, F32, I8, I32 = odla.FLOAT16, odla.FLOAT32, odla.INT8, odla.INT32
+    NHWC = odla.CHANNELS_LAST
+    tdt = {F16: torch.float16, F32: torch.float32, I8: torch.int8, I32: torch.int32}
+    B = args.batch
+    sc = lambda g: g.Constant("scale", np.array([0.05], np.float32))
+    cases = [
+        ("maxpool 3x3/2 [%d,112,112,64] f16" % B, "maxpool", True, [("x", (B, 112, 112, 64), F16)],
+         lambda g, a: g.MaxPool(a[0], NHWC, (3, 3), (2, 2), (1, 1), (1, 1), (B, 56, 56, 64), "y")),
+        ("maxpool 3x3/2 [%d,112,112,64] s8" % B, "maxpool", False, [("x", (B, 112, 112, 64), I8)],
+         lambda g, a: g.MaxPool(a[0], NHWC, (3, 3), (2, 2), (1, 1), (1, 1), (B, 56, 56, 64), "y")),
+        ("reduce_mean (1,2) [%d,7,7,2048] f16" % B, "reduce_mean", True, [("x", (B, 7, 7, 2048), F16)],
+         lambda g, a: g.ReduceMean(a[0], (1, 2), True, (B, 1, 1, 2048), "y")),
+        ("dequantize+reduce_mean (1,2) [%d,7,7,2048] s8" % B, "reduce_mean", False, [("x", (B, 7, 7, 2048), I8)],
+         lambda g, a: g.ReduceMean(g.Dequantize(a[0], sc(g), None, 0, F32, "xd"), (1, 2), True, (B, 1, 1, 2048), "y")),
+        ("softmax rows [%d,128] f16 (BERT scores, B=%d)" % (B // 4 * 12 * 128, B // 4), "softmax", True, [("x", (B // 4 * 12 * 128, 128), F16)],
+         lambda g, a: g.Softmax(a[0], -1, "y")),
+        ("softmax rows [%d,1000] f32 (classifier)" % B, "softmax", False, [("x", (B, 1000), F32)], lambda g, a: g.Softmax(a[0], -1, "y")),
+        ("layernorm rows [%d,768] f16 (BERT, B=%d)" % (B // 4 * 128, B // 4), "layernorm", True, [("x", (B // 4 * 128, 768), F16)],
+         lambda g, a: g.LayerNorm(a[0], (-1,), 1e-12, g.Constant("g", np.ones(768, np.float32)), g.Constant("b", np.zeros(768, np.float32)), "y")),
+        ("quantize f16->s8 [%d,224,224,3]" % B, "quantize", False, [("x", (B, 224, 224, 3), F16)], lambda g, a: g.Quantize(a[0], sc(g), None, 0, I8, "y")),
+        ("dequantize s8->f32 [%d,56,56,256]" % (B // 4), "dequantize", False, [("x", (B // 4, 56, 56, 256), I8)], lambda g, a: g.Dequantize(a[0], sc(g), None, 0, F32, "y")),
+        ("resize nearest x2 [%d,26,26,256] f16 (YOLOv3, B=%d)" % (B // 4, B // 4), "resize", True, [("x", (B // 4, 26, 26, 256), F16)],
+         lambda g, a: g.Resize(a[0], (B // 4, 52, 52, 256), "y")),
+        ("concat channels [%d,52,52,128+256] f16 (YOLOv3)" % (B // 4), "concat", True, [("a", (B // 4, 52, 52, 128), F16), ("b", (B // 4, 52, 52, 256), F16)],
+         lambda g, a: g.Concat([a[0], a[1]], 3, (B // 4, 52, 52, 384), "y")),
+        ("gather rows [30522,768]->[%d,768] f16 (BERT embedding)" % (B // 4 * 128), "gather", True, [("ids", (B // 4, 128), I32)],
+         lambda g, a: g.Gather(g.Constant("emb", (np.arange(30522 * 768, dtype=np.float32) % 97).astype(np.float16).reshape(30522, 768)), a[0], 0, (B // 4, 128, 768), "y")),
+        ("transpose (0,2,1,3) [%d,128,12,64] f16 (BERT heads)" % (B // 4), "transpose", True, [("x", (B // 4, 128, 12, 64), F16)],
+         lambda g, a: g.Transpose(a[0], (0, 2, 1, 3), (B // 4, 12, 128, 64), "y")),
+        ("add same shape [%d,56,56,256] f16" % (B // 4), "binary", True, [("a", (B // 4, 56, 56, 256), F16), ("b", (B // 4, 56, 56, 256), F16)],
+         lambda g, a: g.Add(a[0], a[1], "y")),
+    ]
+    rows = []
+    for title, op, fp16, arg_specs, build in cases:
+        g = odla.Graph(lib, "op", fp16=fp16, n_gpus=1)
+        a = [g.Argument(n, shp, dt) for n, shp, dt in arg_specs]
+        out = build(g, a)
+        # the output keeps the storage type so that no conversion kernel runs: declare it in that type
+        g.Output(out)
+        ins = {n: (torch.randint(0, 30522, shp, dtype=torch.int32, device="cuda") if dt == I32 else
+                   torch.randint(-100, 100, shp, dtype=torch.int8, device="cuda") if dt == I8 else torch.randn(shp, device="cuda").to(tdt[dt])) for n, shp, dt in arg_specs}
+        on = g.out_names[0]
+        y = torch.empty(g.shapes[on], dtype=tdt[g.dtypes[on]], device="cuda")
+        for n, t in ins.items():
+            g.bind_input(n, t.data_ptr())
+        g.bind_output(on, y.data_ptr())
+        ms, prof, other = [], [], []
+        for i in range(args.warmup + args.steps):
+            flush.zero_()
+            torch.cuda.synchronize()
+            entries = g.profile(runs=1)      # plain launches, each bracketed by CUDA events on the library's stream
+            prof = [q for q in entries if q["op"] == op]
+            other = [q["op"] for q in entries if q["op"] != op]
+            if i >= args.warmup:
+                ms.append(sum(q["ms"] for q in prof))
+        g.close()
+        t = sorted(ms)[len(ms) // 2]
+        nbytes = sum(q["bytes"] for q in prof)
+        rows.append({"kernel": title, "launch_op": op, "other_launches": other, "ms": round(t, 5), "algorithmic_mb": round(nbytes / 1e6, 2),
+                     "gbs": round(nbytes / (t * 1e-3) / 1e9, 1), "frac_of_hbm": round(nbytes / (t * 1e-3) / 1e9 / hbm, 3)})
+    if rank == 0:
+        print(json.dumps({"metric": "memory_bound_kernels_achieved_bandwidth", "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+                          "peak": hbm, "peak_source": peak_kind + " copy bandwidth", "data": "synthetic",
+                          "config": {"workload": "single-op graphs at the shapes of the ResNet-50 (B=%d) / YOLOv3 / BERT-base workloads" % B,
+                                     "timing": "CUDA events around the kernel's launch(es) on the library's stream, median; 256 MiB L2 flush before each execute (the execute's own device-to-device copy of the bound input into the arena then leaves up to 126 MB of it in L2)"},
+                          "kernels": rows}))
+
+
 def run_secondary(args, rank, world, local_rank):
-    """The other BASELINE configurations (YOLOv3-416, BERT-base S=128) through the same path and timing
+    """The other two networks (YOLOv3-416, BERT-base S=128) through the same path and timing
     method as the ResNet-50 line: fp16 storage, device-resident `value`, host-bound `e2e`, tensor-core roofline."""
     import torch
     pkg = importlib.import_module(PKG)
@@ -481,8 +565,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-int8", action="store_true", help="skip the secondary int8 measurement")
     ap.add_argument("--only-int8", action="store_true", help="measure only the int8 form (for profiling one of its kernels)")
-    ap.add_argument("--workload", default="resnet50", choices=["resnet50", "yolov3", "bert"],
-                    help="resnet50 is the benchmark line; yolov3 (B=16) and bert (B=64) are the secondary BASELINE configurations")
+    ap.add_argument("--workload", default="resnet50", choices=["resnet50", "yolov3", "bert", "ops"],
+                    help="resnet50 is the benchmark line; yolov3 (B=16) and bert (B=64) are the other two networks; ops times every memory-bound kernel on its own")
     ap.add_argument("--sub-batches", type=int, default=2, help="ODLA_BATCHES_PER_STEP of the end-to-end (host-bound) leg; 1 = off")
     ap.add_argument("--batch", type=int, default=BATCH, help="images per GPU per step (256 = the benchmark configuration; smaller values are for profiling)")
     ap.add_argument("--inlib-gpus", type=int, default=0, help="single process: one odla_ExecuteComputation shards a batch of N x --batch images over N GPUs inside the library")
@@ -500,6 +584,8 @@ def main():
     try:
         if args.workload == "resnet50":
             run_b200(args, rank, world, local_rank)
+        elif args.workload == "ops":
+            run_ops(args, rank, world, local_rank)
         else:
             run_secondary(args, rank, world, local_rank)
     finally:

@@ -139,7 +139,7 @@ int softmax(int dt, const void* x, void* y, int64_t outer, int64_t dim, int64_t 
             cudaStream_t stream);
 // Mean over one axis, sum in ascending order then a single division (bit-reproducible).
 int reduce_mean_axis(int dt_in, int dt_out, const void* x, void* y, int64_t before, int64_t dim, int64_t after,
-                     cudaStream_t stream);
+                     cudaStream_t stream, float in_scale = 1.f);  // in_scale: dequantisation scale of an int8 input
 int layernorm(int dt, const void* x, void* y, const float* gamma, const float* beta, int64_t rows, int64_t dim,
               float eps, cudaStream_t stream);
 

@@ -165,27 +165,36 @@ template <> struct VecMax<float, 4> {
     for (int i = 0; i < 4; ++i) pa[i] = fmaxf(pa[i], pv[i]);
   }
 };
+// One grid row per output row (n, p): a thread owns one 16-byte channel vector of one output pixel, so the index
+// arithmetic is a single small division, consecutive threads read consecutive 16-byte pieces of the input rows, and
+// the rows shared by neighbouring output rows are found in L2.
 template <typename T, int VEC>
 __global__ void maxpool_nhwc_vec_kernel(PoolGeom g, const T* __restrict__ x, T* __restrict__ y) {
-  int cv = g.C / VEC;
-  int64_t total = (int64_t)g.N * g.P * g.Q * cv;
-  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
-    int c = (int)(e % cv) * VEC;
-    int64_t pix = e / cv;
-    int q = (int)(pix % g.Q), p = (int)((pix / g.Q) % g.P), n = (int)(pix / ((int64_t)g.Q * g.P));
-    uint4 acc;
-    VecMax<T, VEC>::init(acc);
-    for (int r = 0; r < g.R; ++r) {
-      int h = p * g.stride_h - g.pad_t + r;
-      if (h < 0 || h >= g.H) continue;
-      for (int s = 0; s < g.S; ++s) {
-        int w = q * g.stride_w - g.pad_l + s;
-        if (w < 0 || w >= g.W) continue;
-        uint4 v = *(const uint4*)(x + ((int64_t)(n * g.H + h) * g.W + w) * g.C + c);
-        VecMax<T, VEC>::upd(acc, v);
+  const int cv = g.C / VEC, row_items = g.Q * cv;
+  const int rows = g.N * g.P;
+  for (int row = blockIdx.y; row < rows; row += gridDim.y) {
+    const int n = row / g.P, p = row - n * g.P;
+    const int h0 = p * g.stride_h - g.pad_t;
+    const T* xin = x + (int64_t)n * g.H * g.W * g.C;
+    T* yout = y + (int64_t)row * g.Q * g.C;
+    for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < row_items; e += gridDim.x * blockDim.x) {
+      const int q = e / cv, c = (e - q * cv) * VEC;
+      const int w0 = q * g.stride_w - g.pad_l;
+      uint4 acc;
+      VecMax<T, VEC>::init(acc);
+      for (int r = 0; r < g.R; ++r) {
+        const int h = h0 + r;
+        if (h < 0 || h >= g.H) continue;
+        const T* xr = xin + ((int64_t)h * g.W) * g.C + c;
+#pragma unroll 3
+        for (int s = 0; s < g.S; ++s) {
+          const int w = w0 + s;
+          if (w < 0 || w >= g.W) continue;
+          VecMax<T, VEC>::upd(acc, *(const uint4*)(xr + (int64_t)w * g.C));
+        }
       }
+      *(uint4*)(yout + (int64_t)q * g.C + c) = acc;
     }
-    *(uint4*)(y + pix * g.C + c) = acc;
   }
 }
 
@@ -674,6 +683,13 @@ int gemm_simt(const GemmGeom& g, int in_dt, const void* A, const void* B, void* 
   }
   return check_launch();
 }
+static dim3 pool_grid(const PoolGeom& g, int vec) {
+  const int row_items = g.Q * (g.C / vec);
+  const int gx = (row_items + 255) / 256;
+  int64_t gy = (int64_t)g.N * g.P;
+  if (gy > 65535) gy = 65535;
+  return dim3((unsigned)(gx > 0 ? gx : 1), (unsigned)gy);
+}
 int pool2d(const PoolGeom& g, int dt, bool is_max, const void* x, void* y, cudaStream_t s) {
   int64_t total = (int64_t)g.N * g.P * g.Q * g.C;
   if (total <= 0) return 0;
@@ -681,10 +697,10 @@ int pool2d(const PoolGeom& g, int dt, bool is_max, const void* x, void* y, cudaS
                     g.ys_h == (int64_t)g.Q * g.C && g.ys_n == (int64_t)g.P * g.Q * g.C && g.xs_n == (int64_t)g.H * g.W * g.C;
   bool aligned = ((uintptr_t)x % 16 == 0) && ((uintptr_t)y % 16 == 0);
   if (is_max && nhwc_dense && aligned) {
-    if (dt == DT_F16 && g.C % 8 == 0) { maxpool_nhwc_vec_kernel<__half, 8><<<grid_for(total / 8, 256), 256, 0, s>>>(g, (const __half*)x, (__half*)y); return check_launch(); }
-    if (dt == DT_BF16 && g.C % 8 == 0) { maxpool_nhwc_vec_kernel<__nv_bfloat16, 8><<<grid_for(total / 8, 256), 256, 0, s>>>(g, (const __nv_bfloat16*)x, (__nv_bfloat16*)y); return check_launch(); }
-    if (dt == DT_S8 && g.C % 16 == 0) { maxpool_nhwc_vec_kernel<int8_t, 16><<<grid_for(total / 16, 256), 256, 0, s>>>(g, (const int8_t*)x, (int8_t*)y); return check_launch(); }
-    if (dt == DT_F32 && g.C % 4 == 0) { maxpool_nhwc_vec_kernel<float, 4><<<grid_for(total / 4, 256), 256, 0, s>>>(g, (const float*)x, (float*)y); return check_launch(); }
+    if (dt == DT_F16 && g.C % 8 == 0) { maxpool_nhwc_vec_kernel<__half, 8><<<pool_grid(g, 8), 256, 0, s>>>(g, (const __half*)x, (__half*)y); return check_launch(); }
+    if (dt == DT_BF16 && g.C % 8 == 0) { maxpool_nhwc_vec_kernel<__nv_bfloat16, 8><<<pool_grid(g, 8), 256, 0, s>>>(g, (const __nv_bfloat16*)x, (__nv_bfloat16*)y); return check_launch(); }
+    if (dt == DT_S8 && g.C % 16 == 0) { maxpool_nhwc_vec_kernel<int8_t, 16><<<pool_grid(g, 16), 256, 0, s>>>(g, (const int8_t*)x, (int8_t*)y); return check_launch(); }
+    if (dt == DT_F32 && g.C % 4 == 0) { maxpool_nhwc_vec_kernel<float, 4><<<pool_grid(g, 4), 256, 0, s>>>(g, (const float*)x, (float*)y); return check_launch(); }
   }
   if (is_max) pool_generic_kernel<true><<<grid_for(total, 256), 256, 0, s>>>(g, dt, x, y);
   else pool_generic_kernel<false><<<grid_for(total, 256), 256, 0, s>>>(g, dt, x, y);
@@ -724,23 +740,136 @@ int channel_affine(int dt, const void* x, void* y, const float* a, const float* 
   channel_affine_kernel<<<grid_for(total, 256), 256, 0, s>>>(dt, x, y, a, b, total, C, inner);
   return check_launch();
 }
+// fp32 rows of up to 32 * NP elements, one warp per row: the row is read once into registers (lane l holds elements
+// l, l + 32, ...), reduced with shuffles and written once.  Same arithmetic as softmax_rows_kernel / layernorm_kernel.
+template <int NP, bool SOFTMAX>
+__global__ void rows_f32_reg_kernel(const float* __restrict__ x, float* __restrict__ y, const float* __restrict__ gamma, const float* __restrict__ beta,
+                                    int64_t rows, int dim, float eps, int log_form) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t row = warp; row < rows; row += nwarps) {
+    const float* xr = x + row * dim;
+    float* yr = y + row * dim;
+    float v[NP];
+#pragma unroll
+    for (int i = 0; i < NP; ++i) { const int d = lane + 32 * i; v[i] = d < dim ? xr[d] : 0.f; }
+    if (SOFTMAX) {
+      float mx = -3.402823466e+38f;
+#pragma unroll
+      for (int i = 0; i < NP; ++i) if (lane + 32 * i < dim) mx = fmaxf(mx, v[i]);
+      mx = warp_max(mx);
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < NP; ++i) if (lane + 32 * i < dim) sum += expf(v[i] - mx);
+      sum = warp_sum(sum);
+      const float lsum = logf(sum);
+#pragma unroll
+      for (int i = 0; i < NP; ++i) {
+        const int d = lane + 32 * i;
+        if (d < dim) { const float t = v[i] - mx; yr[d] = log_form ? t - lsum : __fdiv_rn(expf(t), sum); }
+      }
+    } else {
+      float s = 0.f;
+#pragma unroll
+      for (int i = 0; i < NP; ++i) if (lane + 32 * i < dim) s += v[i];
+      const float mean = warp_sum(s) / (float)dim;
+      float q = 0.f;
+#pragma unroll
+      for (int i = 0; i < NP; ++i) if (lane + 32 * i < dim) { const float t = v[i] - mean; q += t * t; }
+      const float inv = 1.0f / sqrtf(warp_sum(q) / (float)dim + eps);
+#pragma unroll
+      for (int i = 0; i < NP; ++i) {
+        const int d = lane + 32 * i;
+        if (d < dim) { const float t = (v[i] - mean) * inv; yr[d] = t * (gamma ? gamma[d] : 1.f) + (beta ? beta[d] : 0.f); }
+      }
+    }
+  }
+}
+static bool launch_rows_f32(bool is_softmax, const void* x, void* y, const float* gamma, const float* beta, int64_t rows, int64_t dim, float eps,
+                            int log_form, cudaStream_t s) {
+  if (dim > 2048) return false;
+  const int grid = grid_for(rows * 32, 128);
+#define B2_ROWS32(NP)                                                                                                                              \
+  do {                                                                                                                                             \
+    if (is_softmax) rows_f32_reg_kernel<NP, true><<<grid, 128, 0, s>>>((const float*)x, (float*)y, gamma, beta, rows, (int)dim, eps, log_form);     \
+    else rows_f32_reg_kernel<NP, false><<<grid, 128, 0, s>>>((const float*)x, (float*)y, gamma, beta, rows, (int)dim, eps, log_form);               \
+  } while (0)
+  if (dim <= 128) B2_ROWS32(4);
+  else if (dim <= 512) B2_ROWS32(16);
+  else if (dim <= 1024) B2_ROWS32(32);
+  else B2_ROWS32(64);
+#undef B2_ROWS32
+  return true;
+}
 int softmax(int dt, const void* x, void* y, int64_t outer, int64_t dim, int64_t inner, bool log_form, cudaStream_t s) {
   if (outer * dim * inner <= 0) return 0;
+  if (inner == 1 && dt == DT_F32 && launch_rows_f32(true, x, y, nullptr, nullptr, outer, dim, 0.f, log_form, s)) return check_launch();
   if (inner == 1 && dt == DT_F16 && launch_rows_vec<__half>(true, x, y, nullptr, nullptr, outer, dim, 0.f, log_form, s)) return check_launch();
   if (inner == 1 && dt == DT_BF16 && launch_rows_vec<__nv_bfloat16>(true, x, y, nullptr, nullptr, outer, dim, 0.f, log_form, s)) return check_launch();
   if (inner == 1) softmax_rows_kernel<<<grid_for(outer * 32, 256), 256, 0, s>>>(dt, x, y, outer, dim, log_form);
   else softmax_strided_kernel<<<grid_for(outer * inner, 128), 128, 0, s>>>(dt, x, y, outer, dim, inner, log_form);
   return check_launch();
 }
-int reduce_mean_axis(int dt_in, int dt_out, const void* x, void* y, int64_t before, int64_t dim, int64_t after, cudaStream_t s) {
+// Mean along one axis with 16-byte loads across the kept inner axis: a thread owns VEC neighbouring outputs and adds
+// their `dim` terms one after the other (left to right, fp32, one division at the end), so every output is computed
+// exactly as by the scalar kernel; only the memory accesses change.  IN = float, __half, __nv_bfloat16 or int8_t (int8
+// terms are dequantised on the fly: fl(q * in_scale), the value a Dequantize node in front would have produced).
+template <typename IN> struct RedVec { static constexpr int N = 16 / (int)sizeof(IN); };
+template <typename IN> __device__ __forceinline__ void red_load(const IN* p, float in_scale, float (&f)[RedVec<IN>::N]) {
+  const uint4 u = *(const uint4*)p;
+  if constexpr (sizeof(IN) == 4) { const float* v = (const float*)&u; for (int i = 0; i < 4; ++i) f[i] = v[i]; }
+  else if constexpr (sizeof(IN) == 1) { const int8_t* v = (const int8_t*)&u; for (int i = 0; i < 16; ++i) f[i] = __fmul_rn((float)v[i], in_scale); }
+  else { const IN* v = (const IN*)&u; for (int i = 0; i < 8; ++i) f[i] = (float)v[i]; }
+}
+template <typename IN>
+__global__ void reduce_mean_axis_vec_kernel(int dt_out, const IN* __restrict__ x, void* __restrict__ y, int64_t before, int64_t dim, int64_t after, float in_scale) {
+  constexpr int VEC = RedVec<IN>::N;
+  const int64_t av = after / VEC, total = before * av;
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t i = e / av, k = (e - i * av) * VEC;
+    const IN* p = x + (i * dim) * after + k;
+    float s[VEC], t[VEC];
+    red_load<IN>(p, in_scale, s);
+    for (int64_t j = 1; j < dim; ++j) {
+      red_load<IN>(p + j * after, in_scale, t);
+#pragma unroll
+      for (int q = 0; q < VEC; ++q) s[q] = __fadd_rn(s[q], t[q]);
+    }
+    const float d = (float)dim;
+#pragma unroll
+    for (int q = 0; q < VEC; ++q) store_from_float(y, dt_out, i * after + k + q, __fdiv_rn(s[q], d));
+  }
+}
+__global__ void reduce_mean_axis_s8_kernel(int dt_out, const int8_t* x, void* y, int64_t before, int64_t dim, int64_t after, float in_scale) {
+  int64_t total = before * after;
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    int64_t i = e / after, k = e % after;
+    float s = __fmul_rn((float)x[(i * dim) * after + k], in_scale);
+    for (int64_t j = 1; j < dim; ++j) s = __fadd_rn(s, __fmul_rn((float)x[(i * dim + j) * after + k], in_scale));
+    store_from_float(y, dt_out, e, __fdiv_rn(s, (float)dim));
+  }
+}
+int reduce_mean_axis(int dt_in, int dt_out, const void* x, void* y, int64_t before, int64_t dim, int64_t after, cudaStream_t s, float in_scale) {
   if (before * after <= 0) return 0;
-  reduce_mean_axis_kernel<<<grid_for(before * after, 128), 128, 0, s>>>(dt_in, dt_out, x, y, before, dim, after);
+  const int esz = dt_in == DT_F32 ? 4 : (dt_in == DT_S8 ? 1 : 2), vec = 16 / esz;
+  if ((dt_in == DT_F32 || dt_in == DT_F16 || dt_in == DT_BF16 || dt_in == DT_S8) && after % vec == 0 && (uintptr_t)x % 16 == 0) {
+    const int64_t work = before * (after / vec);
+    const int grid = grid_for(work, 128);
+    if (dt_in == DT_F32) reduce_mean_axis_vec_kernel<float><<<grid, 128, 0, s>>>(dt_out, (const float*)x, y, before, dim, after, in_scale);
+    else if (dt_in == DT_F16) reduce_mean_axis_vec_kernel<__half><<<grid, 128, 0, s>>>(dt_out, (const __half*)x, y, before, dim, after, in_scale);
+    else if (dt_in == DT_BF16) reduce_mean_axis_vec_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>(dt_out, (const __nv_bfloat16*)x, y, before, dim, after, in_scale);
+    else reduce_mean_axis_vec_kernel<int8_t><<<grid, 128, 0, s>>>(dt_out, (const int8_t*)x, y, before, dim, after, in_scale);
+    return check_launch();
+  }
+  if (dt_in == DT_S8) reduce_mean_axis_s8_kernel<<<grid_for(before * after, 128), 128, 0, s>>>(dt_out, (const int8_t*)x, y, before, dim, after, in_scale);
+  else reduce_mean_axis_kernel<<<grid_for(before * after, 128), 128, 0, s>>>(dt_in, dt_out, x, y, before, dim, after);
   return check_launch();
 }
 int layernorm(int dt, const void* x, void* y, const float* gamma, const float* beta, int64_t rows, int64_t dim, float eps, cudaStream_t s) {
   if (rows * dim <= 0) return 0;
   if (dt == DT_F16 && launch_rows_vec<__half>(false, x, y, gamma, beta, rows, dim, eps, 0, s)) return check_launch();
   if (dt == DT_BF16 && launch_rows_vec<__nv_bfloat16>(false, x, y, gamma, beta, rows, dim, eps, 0, s)) return check_launch();
+  if (dt == DT_F32 && launch_rows_f32(false, x, y, gamma, beta, rows, dim, eps, 0, s)) return check_launch();
   layernorm_kernel<<<grid_for(rows * 32, 256), 256, 0, s>>>(dt, x, y, gamma, beta, rows, dim, eps);
   return check_launch();
 }
@@ -782,8 +911,64 @@ int quantize(int dt_in, const void* x, void* q, const float* scale, const int* z
   quantize_kernel<<<grid_for(total, 256), 256, 0, s>>>(dt_in, x, q, scale, zp, total, adim, inner, per_axis, is_unsigned);
   return check_launch();
 }
+// Per-tensor int8 -> float storage type, 16 elements per thread: x = fl(float(q) * scale), one rounding to the storage type.
+template <typename OUT>
+__global__ void dequantize_s8_vec_kernel(const uint4* __restrict__ q, OUT* __restrict__ x, const float* __restrict__ scale, int64_t n16) {
+  const float s = scale[0];
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n16; i += (int64_t)gridDim.x * blockDim.x) {
+    const uint4 u = q[i];
+    const int8_t* b = (const int8_t*)&u;
+    if constexpr (sizeof(OUT) == 4) {
+      float4* o = (float4*)(x + i * 16);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) o[k] = make_float4(__fmul_rn((float)b[4 * k], s), __fmul_rn((float)b[4 * k + 1], s), __fmul_rn((float)b[4 * k + 2], s), __fmul_rn((float)b[4 * k + 3], s));
+    } else {
+      __align__(16) OUT h[16];
+#pragma unroll
+      for (int k = 0; k < 16; ++k) h[k] = (OUT)__fmul_rn((float)b[k], s);
+      uint4* o = (uint4*)(x + i * 16);
+      o[0] = ((const uint4*)h)[0];
+      o[1] = ((const uint4*)h)[1];
+    }
+  }
+}
+// Requantisation of a value computed from int32 accumulators: q = sat(rne(x * inv)), 16 elements per thread.
+template <typename IN>
+__global__ void requantize_vec_kernel(const IN* __restrict__ x, uint4* __restrict__ q, float inv, int64_t n16) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n16; i += (int64_t)gridDim.x * blockDim.x) {
+    float f[16];
+    if constexpr (sizeof(IN) == 4) {
+      const float4* p = (const float4*)(x + i * 16);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) { const float4 v = p[k]; f[4 * k] = v.x; f[4 * k + 1] = v.y; f[4 * k + 2] = v.z; f[4 * k + 3] = v.w; }
+    } else {
+      const uint4* p = (const uint4*)(x + i * 16);
+      const uint4 a = p[0], b = p[1];
+      const IN* ha = (const IN*)&a; const IN* hb = (const IN*)&b;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) { f[k] = (float)ha[k]; f[8 + k] = (float)hb[k]; }
+    }
+    uint4 out;
+    uint32_t* o = (uint32_t*)&out;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      uint32_t w = 0;
+#pragma unroll
+      for (int b = 0; b < 4; ++b) w |= ((uint32_t)rne_sat_s8(__fmul_rn(f[4 * k + b], inv)) & 0xffu) << (8 * b);
+      o[k] = w;
+    }
+    q[i] = out;
+  }
+}
 int requantize(int dt_in, const void* x, void* q, float inv_scale, int64_t n, cudaStream_t s) {
   if (n <= 0) return 0;
+  if (n % 16 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)q % 16 == 0 && (dt_in == DT_F32 || dt_in == DT_F16 || dt_in == DT_BF16)) {
+    const int grid = grid_for(n / 16, 256);
+    if (dt_in == DT_F32) requantize_vec_kernel<float><<<grid, 256, 0, s>>>((const float*)x, (uint4*)q, inv_scale, n / 16);
+    else if (dt_in == DT_F16) requantize_vec_kernel<__half><<<grid, 256, 0, s>>>((const __half*)x, (uint4*)q, inv_scale, n / 16);
+    else requantize_vec_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, (uint4*)q, inv_scale, n / 16);
+    return check_launch();
+  }
   requantize_kernel<<<grid_for(n, 256), 256, 0, s>>>(dt_in, x, (int8_t*)q, inv_scale, n);
   return check_launch();
 }
@@ -791,6 +976,14 @@ int dequantize(int dt_out, const void* q, void* x, const float* scale, const int
                bool per_axis, bool is_unsigned, cudaStream_t s) {
   int64_t total = outer * adim * inner;
   if (total <= 0) return 0;
+  if (!per_axis && !zp && !is_unsigned && total % 16 == 0 && (uintptr_t)q % 16 == 0 && (uintptr_t)x % 16 == 0 &&
+      (dt_out == DT_F32 || dt_out == DT_F16 || dt_out == DT_BF16)) {
+    const int grid = grid_for(total / 16, 256);
+    if (dt_out == DT_F32) dequantize_s8_vec_kernel<float><<<grid, 256, 0, s>>>((const uint4*)q, (float*)x, scale, total / 16);
+    else if (dt_out == DT_F16) dequantize_s8_vec_kernel<__half><<<grid, 256, 0, s>>>((const uint4*)q, (__half*)x, scale, total / 16);
+    else dequantize_s8_vec_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const uint4*)q, (__nv_bfloat16*)x, scale, total / 16);
+    return check_launch();
+  }
   dequantize_kernel<<<grid_for(total, 256), 256, 0, s>>>(dt_out, q, x, scale, zp, total, adim, inner, per_axis, is_unsigned);
   return check_launch();
 }
@@ -810,8 +1003,29 @@ __global__ void convert_rows_kernel(int dt_in, int dt_out, const void* x, void* 
     store_from_float(y, dt_out, e, load_as_float(x, dt_in, r * Kp + k));
   }
 }
+// Two-byte rows of pitch Kp (a multiple of 8) -> dense fp32 rows of K: a thread reads one 16-byte piece and writes its
+// (up to) eight values; neighbouring threads write neighbouring floats.
+template <typename IN>
+__global__ void convert_rows_h_f32_kernel(const uint4* __restrict__ x, float* __restrict__ y, int64_t rows, int K, int Kp8) {
+  const int64_t total = rows * Kp8;
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = e / Kp8;
+    const int k0 = (int)(e - r * Kp8) * 8;
+    const uint4 u = x[e];
+    const IN* h = (const IN*)&u;
+    float* o = y + r * K + k0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) if (k0 + j < K) o[j] = (float)h[j];
+  }
+}
 int convert_rows(int dt_in, int dt_out, const void* x, void* y, int64_t rows, int64_t K, int64_t Kp, cudaStream_t s) {
   if (rows * K <= 0) return 0;
+  if ((dt_in == DT_F16 || dt_in == DT_BF16) && dt_out == DT_F32 && Kp % 8 == 0 && (uintptr_t)x % 16 == 0 && K < (1 << 30)) {
+    const int grid = grid_for(rows * (Kp / 8), 256);
+    if (dt_in == DT_F16) convert_rows_h_f32_kernel<__half><<<grid, 256, 0, s>>>((const uint4*)x, (float*)y, rows, (int)K, (int)(Kp / 8));
+    else convert_rows_h_f32_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const uint4*)x, (float*)y, rows, (int)K, (int)(Kp / 8));
+    return check_launch();
+  }
   convert_rows_kernel<<<grid_for(rows * K, 256), 256, 0, s>>>(dt_in, dt_out, x, y, rows, K, Kp);
   return check_launch();
 }
@@ -939,6 +1153,11 @@ int stem_pad(int esz, const void* x, void* y, int N, int H, int W, int C, int pi
 int resize_nearest(int esz, const void* x, void* y, int N, int H, int W, int C, int P, int Q, bool nhwc, cudaStream_t s) {
   int64_t total = (int64_t)N * P * Q * C;
   if (total <= 0) return 0;
+  if (nhwc && ((int64_t)C * esz) % 16 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0) {  // whole 16-byte pieces of a pixel per thread
+    const int C16 = (int)((int64_t)C * esz / 16);
+    resize_nearest_kernel<uint4><<<grid_for((int64_t)N * P * Q * C16, 256), 256, 0, s>>>((const uint4*)x, (uint4*)y, N, H, W, C16, P, Q, 1);
+    return check_launch();
+  }
   int grid = grid_for(total, 256);
   switch (esz) {
     case 1: resize_nearest_kernel<uint8_t><<<grid, 256, 0, s>>>((const uint8_t*)x, (uint8_t*)y, N, H, W, C, P, Q, nhwc); break;
@@ -952,6 +1171,11 @@ int gather(int esz, const void* x, const void* idx, int idx_dt, void* y, int64_t
            cudaStream_t s) {
   int64_t total = outer * n_idx * inner;
   if (total <= 0) return 0;
+  if ((inner * esz) % 16 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0) {  // rows are copied in 16-byte pieces
+    const int64_t inner16 = inner * esz / 16;
+    gather_kernel<uint4><<<grid_for(outer * n_idx * inner16, 256), 256, 0, s>>>((const uint4*)x, idx, idx_dt, (uint4*)y, outer, axis_dim, n_idx, inner16);
+    return check_launch();
+  }
   int grid = grid_for(total, 256);
   switch (esz) {
     case 1: gather_kernel<uint8_t><<<grid, 256, 0, s>>>((const uint8_t*)x, idx, idx_dt, (uint8_t*)y, outer, axis_dim, n_idx, inner); break;

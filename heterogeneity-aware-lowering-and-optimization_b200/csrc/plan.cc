@@ -280,6 +280,8 @@ odla_status Builder::analyse() {
         if (f.int8 && (root->in[0] == v || root->in[1] == v) && cons == root) absorbed = true;
         if (f.res_scale && cons != root && (cons->in[0] == v || cons->in[1] == v) && f.res == v->in[0]) absorbed = true;
       }
+      // ReduceMean dequantises int8 terms as it reads them
+      if (cons->kind == OP_REDUCE_MEAN && cons->in[0] == v && is_per_tensor_dq(v) && !getenv("ODLA_B200_NO_DQ_REDUCE")) absorbed = true;
       if (!absorbed) ++need;
     }
     dq_unabsorbed_[v] = need;
@@ -313,7 +315,11 @@ odla_status Builder::analyse() {
       if (root->kind == OP_GEMM && root->in[2] && root->in[2]->kind != OP_CONST) it.reads.push_back(root->in[2]);
       dt_[v] = f->quant_scale ? DT_S8 : FS();
     } else {
-      for (auto i : v->in) if (i && i->kind != OP_CONST) it.reads.push_back(i);
+      for (auto i : v->in) {
+        if (!i || i->kind == OP_CONST) continue;
+        const bool through_dq = v->kind == OP_REDUCE_MEAN && i == v->in[0] && i->kind == OP_DEQUANTIZE && dq_unabsorbed_[i] == 0;
+        it.reads.push_back(through_dq ? i->in[0] : i);
+      }
       dt_[v] = storage_of(v);
     }
     items_.push_back(std::move(it));
@@ -1007,7 +1013,13 @@ odla_status Builder::emit_plain(const Item& it) {
       return ODLA_SUCCESS;
     }
     case OP_REDUCE_MEAN: {
-      int xdt; const void* x = operand(v->in[0], &xdt);
+      V xin = v->in[0];
+      float in_scale = 1.f;
+      if (xin->kind == OP_DEQUANTIZE && dq_unabsorbed_.count(xin) && dq_unabsorbed_[xin] == 0 && is_per_tensor_dq(xin)) {
+        in_scale = const_as_f32(xin->in[1])[0];   // the first pass reads the int8 tensor and scales each term as Dequantize would
+        xin = xin->in[0];
+      }
+      int xdt; const void* x = operand(xin, &xdt);
       odla_value_shape xs = shape(v->in[0]);
       std::vector<int64_t> d(xs.dims, xs.dims + xs.size);
       struct Pass { const void* src; void* dst; int sdt, ddt; int64_t before, dim, after; };
@@ -1029,8 +1041,9 @@ odla_status Builder::emit_plain(const Item& it) {
         passes.push_back({cur, dst, cdt, ddt, before, d[a], after});
         d[a] = 1; cur = dst; cdt = ddt;
       }
-      add_launch("reduce_mean", v, 0, tensor_bytes(v->in[0]) + out_bytes, [=](cudaStream_t s) {
-        for (auto& p : passes) { int r = reduce_mean_axis(p.sdt, p.ddt, p.src, p.dst, p.before, p.dim, p.after, s); if (r) return r; }
+      add_launch("reduce_mean", v, 0, tensor_bytes(xin) + out_bytes, [=](cudaStream_t s) {
+        bool first = true;
+        for (auto& p : passes) { int r = reduce_mean_axis(p.sdt, p.ddt, p.src, p.dst, p.before, p.dim, p.after, s, first ? in_scale : 1.f); if (r) return r; first = false; }
         return 0;
       });
       p_->launches.back().n_kernels = (int)passes.size();

@@ -262,6 +262,31 @@ def test_batch_is_sharded_over_every_visible_gpu(odla, gpu_lib, ref, models):
         assert desc.count("gpu ") == min(want_gpus, n, 11)
 
 
+@pytest.mark.parametrize("mode,batch", [("int8", 250), ("int8", 5), ("fp16", 64)])
+def test_resnet50_sharded_over_the_gpus_equals_one_gpu(odla, gpu_lib, models, rn_weights, mode, batch):
+    """One odla_ExecuteComputation shards dim 0 over every visible GPU (uneven shards at 250 images, fewer GPUs than
+    visible at 5); each image's result is bit-identical to the single-GPU run: rows are independent and every GPU runs
+    the same kernels.  On a one-GPU machine both runs take the same path and the test only checks the plumbing."""
+    rn = models.resnet50
+    n = gpu_lib.b200_DeviceCount()
+    x = rn.inputs(batch, seed=99)
+    outs = []
+    for gpus in (1, n):
+        g = odla.Graph(gpu_lib, "resnet50_" + mode, fp16=(mode == "fp16"), n_gpus=gpus)
+        if mode == "int8":
+            sc = {k: np.float32(0.05) for k in ["input", "pool"] + [c[0] for c in rn.conv_list()]}
+            rn.build_int8(g, batch, rn_weights, rn.quantize_weights(rn_weights), sc, extra_outputs=("s1b0_c3", "s4b2_c3"))
+        else:
+            rn.build(g, batch, rn_weights)
+        outs.append(g.run(x))
+        assert g.describe().count("gpu ") == min(gpus, batch)
+        shards = g.plan_shards(gpus)
+        assert sum(s[2] for s in shards) == batch and len(shards) == min(gpus, batch)
+        g.close()
+    for k in outs[0]:
+        assert np.array_equal(outs[0][k], outs[1][k]), k
+
+
 def test_sub_batches_pipeline_one_gpu(odla, gpu_lib, models, rn_weights):
     """ODLA_BATCHES_PER_STEP = S gives every GPU S replicas (own stream and arena) so that copies of one
     sub-batch overlap kernels of another; an image's result does not depend on how the batch was cut."""
