@@ -151,6 +151,12 @@ struct _odla_computation {
   std::deque<std::string> quant_names;   // owns the value ids the table's records point to
   bool quant_applied = false;      // the table has been folded into the graph (quant_table.cc)
   std::vector<std::unique_ptr<std::vector<uint8_t>>> owned_consts;  // data of constants the library synthesised
+  // Constants in the form the kernels read them (converted to the storage type, filters repacked K-major, ...), keyed
+  // by "<node index>|<form>".  Filled by the first plan, shared by every replica's plan after it, written into and
+  // read back from a stored executable so that a loaded one skips the conversions.
+  std::map<std::string, std::shared_ptr<std::vector<uint8_t>>> prepared;
+  std::mutex prepared_mutex;
+  long long prepared_hits = 0, prepared_misses = 0;
   // built lazily at first context / execute
   bool planned = false;
   bool shardable = true;           // dim 0 of every argument/output is an independent batch

@@ -209,11 +209,26 @@ class Builder {
     if (it != const_cache_.end()) return it->second;
     void* d;
     if (api_dt(v->type.element_type) == dt) d = upload(v->host, (size_t)(numel(v->type.shape) * storage_size(dt)));
-    else { auto bytes = f32_to_storage(const_as_f32(v), dt); d = upload(bytes.data(), bytes.size()); }
+    else { auto bytes = prepared(v, "dt" + std::to_string(dt), [&] { return f32_to_storage(const_as_f32(v), dt); }); d = upload(bytes->data(), bytes->size()); }
     const_cache_[key] = d;
     return d;
   }
   float* upload_f32(const std::vector<float>& f) { return (float*)upload(f.data(), f.size() * sizeof(float)); }
+  // The bytes of constant `v` in form `form`: taken from the computation's prepared set, or produced by `make` and
+  // added to it (other replicas' plans and a stored executable reuse them).
+  std::shared_ptr<std::vector<uint8_t>> prepared(V v, const std::string& form, const std::function<std::vector<uint8_t>()>& make) {
+    const std::string key = std::to_string(v->index) + "|" + form;
+    {
+      std::lock_guard<std::mutex> lock(c_->prepared_mutex);
+      auto it = c_->prepared.find(key);
+      if (it != c_->prepared.end()) { ++c_->prepared_hits; return it->second; }
+    }
+    auto blob = std::make_shared<std::vector<uint8_t>>(make());
+    std::lock_guard<std::mutex> lock(c_->prepared_mutex);
+    ++c_->prepared_misses;
+    c_->prepared[key] = blob;
+    return blob;
+  }
 
   odla_status analyse();
   void try_fuse(V root);
@@ -713,29 +728,33 @@ odla_status Builder::emit_fused(const Item& it) {
     }
     if (allow_umma && nhwc && groups == 1 && umma_conv_supported(uc)) {
       // filters HWIO -> [K][R*S*C] so that each output channel's taps are contiguous (K-major B operand)
-      auto wf = const_as_f32(f.w);
-      int64_t rs = (int64_t)g.R * g.S;
-      std::vector<float> w2;
-      if (widened) {
-        // [gq*K][R][wide_c]: element el of a window is pixel el / cp, channel el % cp; the window starts wide_lp pixels
-        // left of column (q - q % gq) * stride_w, the taps of the group's column j start pad_l - j*stride_w pixels left
-        // of it: filter column = el / cp - wide_lp + pad_l - j * stride_w
-        w2.assign((size_t)(K * wide_gq * g.R * wide_c), 0.f);
-        for (int j = 0; j < wide_gq; ++j)
-          for (int64_t r = 0; r < g.R; ++r)
-            for (int el = 0; el < wide_c; ++el) {
-              int sc = el / wide_cp - wide_lp + g.pad_l - j * g.stride_w, c = el % wide_cp;
-              if (sc < 0 || sc >= g.S || c >= g.C) continue;
-              for (int64_t k = 0; k < K; ++k) w2[(size_t)(((j * K + k) * g.R + r) * wide_c + el)] = wf[(size_t)(((r * g.S + sc) * g.C + c) * K + k)];
-            }
-      } else {
-        w2.assign((size_t)(K * rs * Cp), 0.f);
-        for (int64_t t = 0; t < rs; ++t)
-          for (int64_t c = 0; c < g.C; ++c)
-            for (int64_t k = 0; k < K; ++k) w2[(size_t)((k * rs + t) * Cp + c)] = wf[(size_t)((t * g.C + c) * K + k)];
-      }
-      auto wb = f32_to_storage(w2, in_dt);
-      void* wd = upload(wb.data(), wb.size());
+      char form[160];
+      snprintf(form, sizeof(form), "conv_kmajor dt%d w%d gq%d wc%d cp%d lp%d pl%d sw%d Cp%d", in_dt, widened ? 1 : 0, wide_gq, wide_c, wide_cp, wide_lp, g.pad_l, g.stride_w, Cp);
+      auto wb = prepared(f.w, form, [&] {
+        auto wf = const_as_f32(f.w);
+        int64_t rs = (int64_t)g.R * g.S;
+        std::vector<float> w2;
+        if (widened) {
+          // [gq*K][R][wide_c]: element el of a window is pixel el / cp, channel el % cp; the window starts wide_lp pixels
+          // left of column (q - q % gq) * stride_w, the taps of the group's column j start pad_l - j*stride_w pixels left
+          // of it: filter column = el / cp - wide_lp + pad_l - j * stride_w
+          w2.assign((size_t)(K * wide_gq * g.R * wide_c), 0.f);
+          for (int j = 0; j < wide_gq; ++j)
+            for (int64_t r = 0; r < g.R; ++r)
+              for (int el = 0; el < wide_c; ++el) {
+                int sc = el / wide_cp - wide_lp + g.pad_l - j * g.stride_w, c = el % wide_cp;
+                if (sc < 0 || sc >= g.S || c >= g.C) continue;
+                for (int64_t k = 0; k < K; ++k) w2[(size_t)(((j * K + k) * g.R + r) * wide_c + el)] = wf[(size_t)(((r * g.S + sc) * g.C + c) * K + k)];
+              }
+        } else {
+          w2.assign((size_t)(K * rs * Cp), 0.f);
+          for (int64_t t = 0; t < rs; ++t)
+            for (int64_t c = 0; c < g.C; ++c)
+              for (int64_t k = 0; k < K; ++k) w2[(size_t)((k * rs + t) * Cp + c)] = wf[(size_t)((t * g.C + c) * K + k)];
+        }
+        return f32_to_storage(w2, in_dt);
+      });
+      void* wd = upload(wb->data(), wb->size());
       if (!wd) return err_status_;
       if (pitch_.count(f.out)) uc.y_pitch = (int)pitch_[f.out];
       UmmaLaunch* ul = umma_conv_prepare(uc, x_umma, wd, y, ep, p_->status, sms);
@@ -850,12 +869,14 @@ odla_status Builder::emit_fused(const Item& it) {
     UmmaConv uc{1, 1, (int)Mt, (int)Kd, (int)N, 1, 1, 1, (int)Mt, 1, 1, 0, 0, in_dt};
     if (store_direct) set_store(uc);
     if (Mt < (1ll << 31) && umma_conv_supported(uc)) {
-      auto wf = const_as_f32(f.w);
-      std::vector<float> w2;
-      if (tb) w2 = wf;  // already [N][K]
-      else { w2.resize(wf.size()); for (int64_t k = 0; k < Kd; ++k) for (int64_t n = 0; n < N; ++n) w2[(size_t)(n * Kd + k)] = wf[(size_t)(k * N + n)]; }
-      auto wb = f32_to_storage(w2, in_dt);
-      void* wd = upload(wb.data(), wb.size());
+      auto wb = prepared(f.w, std::string("gemm_kmajor dt") + std::to_string(in_dt) + (tb ? " t" : " n"), [&] {
+        auto wf = const_as_f32(f.w);
+        std::vector<float> w2;
+        if (tb) w2 = wf;  // already [N][K]
+        else { w2.resize(wf.size()); for (int64_t k = 0; k < Kd; ++k) for (int64_t n = 0; n < N; ++n) w2[(size_t)(n * Kd + k)] = wf[(size_t)(k * N + n)]; }
+        return f32_to_storage(w2, in_dt);
+      });
+      void* wd = upload(wb->data(), wb->size());
       if (!wd) return err_status_;
       UmmaLaunch* ul = umma_conv_prepare(uc, x, wd, y, ep, p_->status, sms);
       if (!ul) return fail(ODLA_FAILURE, "'" + root->name + "': tensor-map encoding failed");

@@ -66,6 +66,10 @@ class QuantInfo(C.Structure):
     _fields_ = [("value_id", C.c_char_p), ("ch_idx", C.c_int), ("scale", C.c_float), ("offset", C.c_float), ("min", C.c_float), ("max", C.c_float)]
 
 
+class ResourceLocation(C.Structure):
+    _fields_ = [("location_type", C.c_int), ("location", C.c_void_p), ("size", C.c_uint64)]
+
+
 class ProfileEntry(C.Structure):
     _fields_ = [("op", C.c_char * 32), ("name", C.c_char * 64), ("total_ms", C.c_double),
                 ("launches", C.c_longlong), ("flops", C.c_double), ("bytes", C.c_double)]
@@ -171,6 +175,10 @@ _OPTIONAL = {
     "odla_b200_SetProfiling": (C.c_int, [_V, C.c_int]),
     "odla_b200_GetProfile": (C.c_int, [_V, C.POINTER(ProfileEntry), C.c_int]),
     "odla_b200_DescribePlan": (C.c_int, [_V, C.c_char_p, C.c_int]),
+    "odla_b200_PreparedConstantStats": (None, [_V, C.POINTER(C.c_longlong), C.POINTER(C.c_longlong), C.POINTER(C.c_longlong)]),
+    "odla_StoreExecutable": (C.c_int, [ResourceLocation, _V]),
+    "odla_LoadExecutable": (C.c_int, [ResourceLocation, _V, C.POINTER(_V)]),
+    "odla_CompileComputation": (C.c_int, [_V, _V, C.POINTER(_V)]),
     "odla_b200_PlanShards": (C.c_int, [_V, C.c_longlong, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_longlong), C.POINTER(C.c_longlong), C.c_int]),
     "odla_b200_conv_umma": (C.c_int, [C.POINTER(ConvDesc), _V, _V, _V, _V, _V, _V, _V]),
     "odla_b200_reduce_mean_noalloc": (C.c_int, [_V, _V, C.c_int, C.POINTER(C.c_longlong), C.c_int, C.POINTER(C.c_int), C.c_int, _V]),
@@ -546,6 +554,49 @@ class Graph:
             self.lib.b200_SetProfiling(ctx, 0)
         return [dict(op=e.op.decode(), name=e.name.decode(), ms=e.total_ms / max(e.launches, 1), launches=e.launches,
                      flops=e.flops, bytes=e.bytes) for e in arr]
+
+    def store(self, path):
+        """odla_StoreExecutable: the computation (graph, constants, items, prepared constants) as one file."""
+        p = C.create_string_buffer(path.encode())
+        self._keep.append(p)
+        loc = ResourceLocation(0, C.cast(p, C.c_void_p), 0)
+        self._check(self.lib.StoreExecutable(loc, self.comp), "odla_StoreExecutable")
+
+    @classmethod
+    def load(cls, lib, path):
+        """odla_LoadExecutable: a Graph bound to the computation the file describes; arguments and outputs are
+        discovered through the getters, as a program that only has the file would do."""
+        g = cls.__new__(cls)
+        g.lib, g.name = lib, os.path.basename(path)
+        g._keep, g.shapes, g.dtypes, g._handles = [], {}, {}, {}
+        g.cc_consts, g.cc_body, g.cc_items, g.const_arrays = [], [], [], {}
+        g.arg_names, g.out_names, g.ctx = [], [], None
+        p = C.create_string_buffer(path.encode())
+        g._keep.append(p)
+        exe = _V()
+        cls._check(lib.LoadExecutable(ResourceLocation(0, C.cast(p, C.c_void_p), 0), None, C.byref(exe)), "odla_LoadExecutable")
+        g.comp = exe
+        for count, by_idx, names in ((lib.GetNumOfArgsFromComputation, lib.GetArgFromComputationByIdx, g.arg_names),
+                                     (lib.GetNumOfOutputsFromComputation, lib.GetOutputFromComputationByIdx, g.out_names)):
+            n = C.c_uint32()
+            count(g.comp, C.byref(n))
+            for i in range(n.value):
+                h, vt, vid = _V(), ValueType(), C.c_char_p()
+                by_idx(g.comp, i, C.byref(h))
+                lib.GetValueType(h, C.byref(vt))
+                lib.GetValueId(h, C.byref(vid))
+                name = vid.value.decode()
+                names.append(name)
+                g._handles[name] = h
+                g.shapes[name] = tuple(vt.shape.dims[k] for k in range(vt.shape.size))
+                g.dtypes[name] = vt.element_type
+        g.context()   # odla_CreateContext attaches to the current computation, which the load just made this one
+        return g
+
+    def prepared_stats(self):
+        h, m, e = C.c_longlong(), C.c_longlong(), C.c_longlong()
+        self.lib.b200_PreparedConstantStats(self.comp, C.byref(h), C.byref(m), C.byref(e))
+        return {"hits": h.value, "misses": m.value, "entries": e.value}
 
     def close(self):
         if self.ctx is not None:

@@ -208,6 +208,16 @@ odla_status odla_CompileComputation(const odla_computation computation, const od
                                     odla_executable* executable);
 odla_status odla_LaunchExecutable(odla_executable executable, odla_context context);
 odla_status odla_DestroyExecutable(odla_executable executable);
+/* ODLA/include/ODLA/odla_compute.h:347-369; shape of ODLA/platforms/tensorrt/odla_tensorrt.cc:537-559,703-811.
+ * odla_StoreExecutable writes the computation behind `executable` as one self-contained file (ODLA_LOCATION_PATH):
+ * the recorded graph, the constants, the computation's items and -- once it has been compiled or executed -- the
+ * constants in the form the kernels read them (converted, filters repacked), so that a loaded executable plans
+ * without repeating those conversions.  odla_LoadExecutable (path or memory) creates a new computation from such a
+ * file, makes it the current one (odla_CreateContext attaches to it; arguments and outputs are found by id) and
+ * returns it as the executable; destroy it with odla_DestroyComputation.  Nothing device-specific is stored: arenas,
+ * tensor maps and CUDA graphs are rebuilt by the first execute on the GPUs the loading process sees. */
+odla_status odla_LoadExecutable(odla_resource_location location, odla_device device, odla_executable* executable);
+odla_status odla_StoreExecutable(odla_resource_location location, odla_executable executable);
 odla_status odla_ExecuteComputation(const odla_computation computation, const odla_context context,
                                     const odla_compute_mode mode, odla_device device);
 odla_status odla_GetNumOfArgsFromComputation(const odla_computation computation,
@@ -385,6 +395,10 @@ int odla_b200_DescribePlan(odla_computation computation, char* buf, int capacity
  * holding every row.  Returns the number of replicas (entries beyond `capacity` are not written). */
 int odla_b200_PlanShards(odla_computation computation, long long run_batch, int visible_devices,
                          int* device, long long* first_row, long long* rows, int capacity);
+
+/* How many constants planning found already prepared (hits), had to convert itself (misses), and how many prepared
+ * constants the computation holds now -- what a stored executable would carry. */
+void odla_b200_PreparedConstantStats(odla_computation computation, long long* hits, long long* misses, long long* entries);
 
 /* Raw kernel entry points over DEVICE pointers on the current device and the given stream
  * (a cudaStream_t passed as void*; NULL is the default stream).  They return 0 or a negative

@@ -123,6 +123,37 @@ def test_constants_that_span_the_batch_keep_the_graph_whole(odla, lib):
     g.close()
 
 
+def test_executable_file_round_trip(tmp_path, odla, lib, models):
+    """odla_StoreExecutable / odla_LoadExecutable need no GPU: the file holds the graph, the constants and the items.
+    A loaded computation exposes the same arguments and outputs, stores to the same bytes, and a damaged or foreign
+    file is refused."""
+    g = odla.Graph(lib, "mnist_simple", fp16=True, n_gpus=2, sub_batches=2)
+    models.mnist.build(g)
+    a = str(tmp_path / "a.odlab200")
+    g.store(a)
+    h = odla.Graph.load(lib, a)
+    assert h.arg_names == g.arg_names and h.out_names == g.out_names
+    assert all(h.shapes[n] == tuple(g.shapes[n]) and h.dtypes[n] == g.dtypes[n] for n in g.arg_names + g.out_names)
+    assert h.plan_shards(4) == g.plan_shards(4)          # items travelled: two GPUs, two sub-batches each
+    b = str(tmp_path / "b.odlab200")
+    h.store(b)
+    blob = open(a, "rb").read()
+    assert open(b, "rb").read() == blob
+    h.close()
+    g.close()
+    lib.SetLogLevel(0)
+    try:
+        bad = bytearray(blob)
+        bad[len(bad) // 2] ^= 0x40
+        (tmp_path / "bad.odlab200").write_bytes(bytes(bad))
+        (tmp_path / "foreign.bin").write_bytes(b"ptrt" + bytes(64))
+        for name in ("bad.odlab200", "foreign.bin", "missing.odlab200"):
+            with pytest.raises(RuntimeError):
+                odla.Graph.load(lib, str(tmp_path / name))
+    finally:
+        lib.SetLogLevel(3)
+
+
 def test_device_api_every_item_answers(odla, lib):
     # tests/ODLA/device_test.cc:63-89 in the reference: every odla_GetDeviceInfo item returns SUCCESS
     dev = C.c_void_p()

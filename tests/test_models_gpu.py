@@ -287,6 +287,32 @@ def test_resnet50_sharded_over_the_gpus_equals_one_gpu(odla, gpu_lib, models, rn
         assert np.array_equal(outs[0][k], outs[1][k]), k
 
 
+@pytest.mark.parametrize("mode", ["fp16", "int8"])
+def test_stored_executable_runs_like_the_original(tmp_path, odla, gpu_lib, models, rn_weights, mode):
+    """A ResNet-50 stored after its first execute carries the prepared constants (filters converted and repacked
+    K-major); the loaded computation plans from them without converting anything again and returns identical bits."""
+    rn = models.resnet50
+    x = rn.inputs(4, seed=21)
+    g = odla.Graph(gpu_lib, "resnet50", fp16=(mode == "fp16"))
+    if mode == "int8":
+        sc = {k: np.float32(0.05) for k in ["input", "pool"] + [c[0] for c in rn.conv_list()]}
+        rn.build_int8(g, 4, rn_weights, rn.quantize_weights(rn_weights), sc)
+    else:
+        rn.build(g, 4, rn_weights)
+    want = g.run(x)["prob"]
+    st = g.prepared_stats()
+    assert st["misses"] >= 54 and st["entries"] == st["misses"]     # every convolution filter and the classifier's matrix
+    path = str(tmp_path / "resnet50.odlab200")
+    g.store(path)
+    g.close()
+    h = odla.Graph.load(gpu_lib, path)
+    got = h.run(x)["prob"]
+    st = h.prepared_stats()
+    h.close()
+    assert st["misses"] == 0 and st["hits"] >= 54
+    assert np.array_equal(got, want)
+
+
 def test_sub_batches_pipeline_one_gpu(odla, gpu_lib, models, rn_weights):
     """ODLA_BATCHES_PER_STEP = S gives every GPU S replicas (own stream and arena) so that copies of one
     sub-batch overlap kernels of another; an image's result does not depend on how the batch was cut."""
