@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libodla_b200.so")
-SOURCES = ["api.cc", "plan.cc", "quant_table.cc", "executable.cc", "kabi.cu", "noalloc.cu", "kernels_simt.cu", "kernels_umma.cu"]
+SOURCES = ["api.cc", "plan.cc", "quant_table.cc", "executable.cc", "kabi.cu", "noalloc.cu", "kernels_simt.cu", "kernels_detect.cu", "kernels_umma.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC,-fvisibility=default,-Wall,-Wno-unused-function", "-x", "cu",

@@ -59,7 +59,7 @@ bool inject_fault(const char* site) {
 const char* op_name(OpKind k) {
   static const char* n[] = {"arg", "const", "conv", "gemm", "maxpool", "avgpool", "batchnorm", "unary", "binary",
                             "softmax", "reduce_mean", "layernorm", "quantize", "dequantize", "reshape", "transpose",
-                            "concat", "resize", "gather", "slice", "cast"};
+                            "concat", "resize", "gather", "slice", "cast", "nms", "postprocess", "postprocess_num"};
   return n[k];
 }
 int elem_size(odla_element_type t) {
@@ -698,6 +698,50 @@ odla_value odla_Slice(odla_value x, const odla_int32* start, const odla_int32* e
   for (int i = 0; i < rank; ++i) ia.push_back(start[i]);
   for (int i = 0; i < rank; ++i) ia.push_back(stride ? stride[i] : 1);
   return add_node(OP_SLICE, x->type.element_type, od, id, {x}, ia);
+}
+// ODLA/include/ODLA/ops/odla_ops_nn.h:504-507.  The emitter maps ONNX NonMaxSuppression to it
+// (lib/target/generic_cpp/nms.cc:22-69) with the result typed [max_num_outputs, 3]: rows (batch, class, box), -1 in rows
+// that no selection fills.  boxes [B, N, 4], scores [B, C, N]; at most max_num_outputs boxes per (batch, class).
+odla_value odla_NMS(odla_value boxes, odla_value scores, odla_uint32 max_num_outputs, odla_float32 iou_threshold, odla_float32 score_threshold,
+                    odla_value_type output_value_type, const odla_value_id id) {
+  if (any_null({boxes, scores})) return fail_node(ODLA_INVALID_PARAM, id, "odla_NMS: null operand");
+  const auto& bs = boxes->type.shape; const auto& ss = scores->type.shape;
+  if (bs.size != 3 || ss.size != 3 || bs.dims[2] != 4 || bs.dims[0] != ss.dims[0] || bs.dims[1] != ss.dims[2])
+    return fail_node(ODLA_INVALID_PARAM, id, "odla_NMS: boxes must be [B, N, 4] and scores [B, C, N]");
+  if (output_value_type.element_type != ODLA_INT32 && output_value_type.element_type != ODLA_INT64)
+    return fail_node(ODLA_UNSUPPORTED_DATATYPE, id, "odla_NMS: the result is int32 or int64");
+  if (output_value_type.shape.size != 2 || output_value_type.shape.dims[1] != 3)
+    return fail_node(ODLA_INVALID_PARAM, id, "odla_NMS: the result is [rows, 3]");
+  return add_node(OP_NMS, output_value_type.element_type, output_value_type.shape, id, {boxes, scores}, {(int64_t)max_num_outputs}, {iou_threshold, score_threshold});
+}
+// ODLA/include/ODLA/ops/odla_ops_nn.h:757-759; semantics of the only implementation the reference has
+// (ODLA/platforms/odla_popart/custom_ops/postprocess.cc, codelets_nms.cpp): YOLOv3 heads at 13, 26 and 52 cells, batch 1,
+// decoded against the 9 anchors, per class a greedy suppression at IoU 0.45 / score 0.3 -> selected_info
+// [classes, N/169, 5] (y_min, x_min, y_max, x_max, score) and selected_num [classes].
+odla_values odla_PostProcess(odla_value orig_img_w, odla_value orig_img_h, odla_value bb13, odla_value bb26, odla_value bb52, const odla_value_id id) {
+  odla_values out{};
+  const std::string base = id ? std::string((const char*)id) : std::string("postprocess");
+  const std::string n0 = base + "0", n1 = base + "1";
+  auto failed = [&](odla_status st, const char* msg) { out.size = 2; out.values[0] = fail_node(st, (const odla_value_id)n0.c_str(), "%s", msg); out.values[1] = out.values[0]; return out; };
+  if (any_null({orig_img_w, orig_img_h, bb13, bb26, bb52})) return failed(ODLA_INVALID_PARAM, "odla_PostProcess: null operand");
+  int64_t ch = -1;
+  const int want[3] = {13, 26, 52};
+  odla_value heads[3] = {bb13, bb26, bb52};
+  for (int i = 0; i < 3; ++i) {
+    const auto& s = heads[i]->type.shape;
+    if (s.size != 4 || s.dims[0] != 1) return failed(ODLA_INVALID_PARAM, "odla_PostProcess: heads are rank 4 with batch 1");
+    const bool nchw = s.dims[2] == want[i] && s.dims[3] == want[i], nhwc = s.dims[1] == want[i] && s.dims[2] == want[i];
+    if (!nchw && !nhwc) return failed(ODLA_INVALID_PARAM, "odla_PostProcess: heads must have 13, 26 and 52 cells");
+    const int64_t c = nchw ? s.dims[1] : s.dims[3];
+    if ((ch >= 0 && c != ch) || c % 3 != 0 || c / 3 <= 5) return failed(ODLA_INVALID_PARAM, "odla_PostProcess: heads must have 3 * (classes + 5) channels");
+    ch = c;
+  }
+  const int64_t cls = ch / 3 - 5, N = 3 * (13 * 13 + 26 * 26 + 52 * 52);
+  odla_value_shape s0{3, {cls, N / 169, 5}}, s1{1, {cls}};
+  odla_value info = add_node(OP_POSTPROCESS, ODLA_FLOAT32, s0, (const odla_value_id)n0.c_str(), {orig_img_w, orig_img_h, bb13, bb26, bb52}, {cls});
+  odla_value num = add_node(OP_POSTPROCESS_NUM, ODLA_UINT32, s1, (const odla_value_id)n1.c_str(), {info}, {cls});
+  out.size = 2; out.values[0] = info; out.values[1] = num;
+  return out;
 }
 odla_value odla_Cast(odla_value x, odla_element_type target, const odla_value_id id) {
   if (!x) return fail_node(ODLA_INVALID_PARAM, id, "odla_Cast: null operand");

@@ -48,7 +48,7 @@ bool inject_fault(const char* site);
 enum OpKind {
   OP_ARG, OP_CONST, OP_CONV, OP_GEMM, OP_MAXPOOL, OP_AVGPOOL, OP_BATCHNORM, OP_UNARY, OP_BINARY,
   OP_SOFTMAX, OP_REDUCE_MEAN, OP_LAYERNORM, OP_QUANTIZE, OP_DEQUANTIZE, OP_RESHAPE, OP_TRANSPOSE,
-  OP_CONCAT, OP_RESIZE, OP_GATHER, OP_SLICE, OP_CAST
+  OP_CONCAT, OP_RESIZE, OP_GATHER, OP_SLICE, OP_CAST, OP_NMS, OP_POSTPROCESS, OP_POSTPROCESS_NUM
 };
 const char* op_name(OpKind k);
 
@@ -107,6 +107,7 @@ struct Plan {
   int* status = nullptr;           // device status block (kStatusBytes): word 0 non-zero when a bounded wait expired
   std::vector<void*> extra_allocs; // uploaded constants and scratch
   std::vector<UmmaLaunch*> umma;   // prepared tensor-core launches (own their tensor maps)
+  std::map<const _odla_value*, unsigned*> pp_counts;  // odla_PostProcess: where a node's per-class counts are on the device
   cudaGraphExec_t graph = nullptr; // captured launch list (optional)
   bool graph_failed = false;       // capture was tried and refused: stay on plain launches
   // How arguments enter and outputs leave the arena.  `stage` is where the caller's bytes land

@@ -182,4 +182,14 @@ int resize_nearest(int esz, const void* x, void* y, int N, int H, int W, int C, 
 int gather(int esz, const void* x, const void* idx, int idx_dt, void* y, int64_t outer, int64_t axis_dim,
            int64_t n_idx, int64_t inner, cudaStream_t stream);
 
+// Greedy non-maximum suppression (odla_NMS): boxes [B, N, 4] (y1, x1, y2, x2), scores [B, C, N]; `out` gets out_rows rows
+// (batch, class, box) as int32 or int64, -1 beyond the selected ones.  sel [B*C*max_sel] and cnt [B*C] are scratch.
+int nms(int B, int C, int N, int max_sel, float iou_thr, float score_thr, int box_dt, const void* boxes, int score_dt, const void* scores, int out_rows,
+        int out64, void* out, int* sel, int* cnt, cudaStream_t stream);
+// YOLOv3 post-processing (odla_PostProcess): three heads [1, 3*(cls+5), S, S] (nchw) or [1, S, S, 3*(cls+5)] with
+// S = 13, 26, 52 -> info [cls, N/169, 5] (y_min, x_min, y_max, x_max, score) and num [cls]; boxes [N, 4], scores [cls, N],
+// sel [cls * N/169] and cnt [cls] are scratch, anchors18 the 3 x 6 anchor table in device memory.
+int yolo_postprocess(int cls, const int* S3, const void* const* heads, int dt, const int* nchw3, const unsigned* anchors18, const unsigned* img_w,
+                     const unsigned* img_h, float* boxes, float* scores, int* sel, int* cnt, float* info, unsigned* num, cudaStream_t stream);
+
 }  // namespace b200

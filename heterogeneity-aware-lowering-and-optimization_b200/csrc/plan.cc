@@ -1196,6 +1196,68 @@ odla_status Builder::emit_plain(const Item& it) {
       add_launch("slice", v, 0, 2 * out_bytes, [=](cudaStream_t s) { return move(g, esz, x, y, s); });
       return ODLA_SUCCESS;
     }
+    case OP_NMS: {
+      int bdt, sdt; const void* boxes = operand(v->in[0], &bdt); const void* scores = operand(v->in[1], &sdt);
+      const auto& ss = v->in[1]->type.shape;
+      const int B = (int)ss.dims[0], C = (int)ss.dims[1], N = (int)ss.dims[2], rows = (int)os.dims[0];
+      const int max_sel = (int)std::min<int64_t>(v->ia[0] > 0 ? v->ia[0] : rows, std::max(N, 1));
+      if ((int64_t)B * C > 1024) return fail(ODLA_UNSUPPORTED_OP, "'" + v->name + "': more than 1024 (batch, class) pairs");
+      int* scratch = nullptr;
+      if (cudaMalloc((void**)&scratch, sizeof(int) * ((size_t)B * C * std::max(max_sel, 1) + (size_t)B * C)) != cudaSuccess) return fail(ODLA_MEM_ERROR, "scratch allocation failed");
+      p_->extra_allocs.push_back(scratch);
+      int* cnt = scratch + (size_t)B * C * std::max(max_sel, 1);
+      const float iou = v->fa[0], thr = v->fa[1];
+      const int out64 = odt == DT_S64;
+      add_launch("nms", v, 0, tensor_bytes(v->in[0]) + tensor_bytes(v->in[1]) + out_bytes,
+                 [=](cudaStream_t s) { return nms(B, C, N, max_sel, iou, thr, bdt, boxes, sdt, scores, rows, out64, y, scratch, cnt, s); });
+      p_->launches.back().n_kernels = 2;
+      return ODLA_SUCCESS;
+    }
+    case OP_POSTPROCESS: {
+      const int cls = (int)v->ia[0];
+      int wdt, hdt; const void* iw = operand(v->in[0], &wdt); const void* ih = operand(v->in[1], &hdt);
+      if (wdt != DT_S32 || hdt != DT_S32) return fail(ODLA_UNSUPPORTED_DATATYPE, "'" + v->name + "': the image extents are 32-bit integers");
+      struct Heads { const void* p[3]; int S[3], nchw[3]; } hd{};
+      int hdt0 = -1;
+      for (int i = 0; i < 3; ++i) {
+        int dt; hd.p[i] = operand(v->in[2 + i], &dt);
+        if (hdt0 >= 0 && dt != hdt0) return fail(ODLA_UNSUPPORTED_DATATYPE, "'" + v->name + "': heads of different storage types");
+        hdt0 = dt;
+        const auto& s = v->in[2 + i]->type.shape;
+        hd.nchw[i] = s.dims[2] == s.dims[3] && s.dims[1] == 3 * (cls + 5) ? 1 : 0;
+        hd.S[i] = (int)s.dims[2];
+      }
+      const int N = 3 * (hd.S[0] * hd.S[0] + hd.S[1] * hd.S[1] + hd.S[2] * hd.S[2]), per_class = N / 169;
+      static const unsigned anchors[18] = {10, 13, 16, 30, 33, 23, 30, 61, 62, 45, 59, 119, 116, 90, 156, 198, 373, 326};  // yolo_anchors.txt
+      const unsigned* anc = (const unsigned*)upload(anchors, sizeof(anchors));
+      // scratch: boxes [N,4], scores [cls,N], selections, counts, fp32 result (when the storage type is narrower)
+      const size_t f_boxes = (size_t)N * 4, f_scores = (size_t)cls * N, f_info = (size_t)cls * per_class * 5;
+      char* scratch = nullptr;
+      const size_t bytes = 4 * (f_boxes + f_scores + f_info + (size_t)cls * per_class + 2 * (size_t)cls);
+      if (!anc || cudaMalloc((void**)&scratch, bytes) != cudaSuccess) return fail(ODLA_MEM_ERROR, "scratch allocation failed");
+      p_->extra_allocs.push_back(scratch);
+      float* boxes = (float*)scratch; float* scores = boxes + f_boxes; float* info32 = scores + f_scores;
+      int* sel = (int*)(info32 + f_info); int* cnt = sel + (size_t)cls * per_class; unsigned* num = (unsigned*)(cnt + cls);
+      p_->pp_counts[v] = num;
+      const int dt = hdt0; const int64_t n_info = (int64_t)f_info;
+      add_launch("postprocess", v, 0, tensor_bytes(v->in[2]) + tensor_bytes(v->in[3]) + tensor_bytes(v->in[4]) + out_bytes, [=](cudaStream_t s) {
+        float* info = odt == DT_F32 ? (float*)y : info32;
+        int rc = yolo_postprocess(cls, hd.S, hd.p, dt, hd.nchw, anc, (const unsigned*)iw, (const unsigned*)ih, boxes, scores, sel, cnt, info, num, s);
+        if (rc || odt == DT_F32) return rc;
+        return convert(DT_F32, odt, info32, y, n_info, s);
+      });
+      p_->launches.back().n_kernels = 5 + (odt == DT_F32 ? 0 : 1);
+      return ODLA_SUCCESS;
+    }
+    case OP_POSTPROCESS_NUM: {
+      auto it2 = p_->pp_counts.find(v->in[0]);
+      if (it2 == p_->pp_counts.end()) return fail(ODLA_INTERNAL_LOGIC_ERR, "'" + v->name + "': its PostProcess has not been planned");
+      const void* src = it2->second;
+      const size_t nb = (size_t)count(v) * 4;
+      add_launch("postprocess_num", v, 0, 2.0 * nb, [=](cudaStream_t s) { return cudaMemcpyAsync(y, src, nb, cudaMemcpyDeviceToDevice, s) == cudaSuccess ? 0 : -2; });
+      p_->launches.back().n_kernels = 0;
+      return ODLA_SUCCESS;
+    }
     case OP_CAST: {
       int xdt; const void* x = operand(v->in[0], &xdt);
       int64_t n = count(v);
@@ -1277,6 +1339,7 @@ bool graph_shardable(_odla_computation* c, int64_t* batch_out) {
     if (v->kind == OP_BINARY || v->kind == OP_CONCAT || v->kind == OP_GEMM)
       for (auto i : v->in) if (spans_batch(i)) return false;
     switch (v->kind) {
+      case OP_NMS: case OP_POSTPROCESS: case OP_POSTPROCESS_NUM: return false;   // rows of the result are not rows of the batch
       case OP_TRANSPOSE: if (v->ia[0] != 0) return false; break;
       case OP_SOFTMAX: if (v->ia[0] == 0) return false; break;
       case OP_REDUCE_MEAN: for (size_t k = 1; k < v->ia.size(); ++k) if (v->ia[k] == 0) return false; break;

@@ -33,12 +33,12 @@ CHANNELS_FIRST, CHANNELS_LAST, SIO, SOI, OIS, IOS = range(6)
 SUCCESS, INVALID_PARAM, UNSUPPORTED_OP, TIMEOUT, FAILURE = 0, 3, 7, 8, 14
 
 _NP2ODLA = {np.dtype(np.float32): FLOAT32, np.dtype(np.float16): FLOAT16, np.dtype(np.int8): INT8,
-            np.dtype(np.uint8): UINT8, np.dtype(np.int32): INT32, np.dtype(np.int64): INT64}
+            np.dtype(np.uint8): UINT8, np.dtype(np.int32): INT32, np.dtype(np.int64): INT64, np.dtype(np.uint32): UINT32}
 _ODLA2NP = {v: k for k, v in _NP2ODLA.items()}
 _CTYPE = {FLOAT32: "float", FLOAT16: "odla_float16", INT8: "signed char", UINT8: "unsigned char",
-          INT32: "int", INT64: "long long"}
+          INT32: "int", INT64: "long long", UINT32: "unsigned int"}
 _ENUM = {FLOAT32: "ODLA_FLOAT32", FLOAT16: "ODLA_FLOAT16", INT8: "ODLA_INT8", UINT8: "ODLA_UINT8",
-         INT32: "ODLA_INT32", INT64: "ODLA_INT64", BFLOAT16: "ODLA_BFLOAT16"}
+         INT32: "ODLA_INT32", INT64: "ODLA_INT64", BFLOAT16: "ODLA_BFLOAT16", UINT32: "ODLA_UINT32"}
 
 
 class Shape(C.Structure):
@@ -137,6 +137,8 @@ _SIGNATURES = {
     "odla_BatchNormalization": (_V, [_V, C.c_int, _V, _V, C.c_float, _V, _V, C.c_float, C.c_float, _ID]),
     "odla_Clamp": (_V, [_V, C.c_float, C.c_float, _ID]),
     "odla_LeakyRelu": (_V, [_V, C.c_float, _ID]),
+    "odla_NMS": (_V, [_V, _V, C.c_uint32, C.c_float, C.c_float, ValueType, _ID]),
+    "odla_PostProcess": (Values, [_V, _V, _V, _V, _V, _ID]),
     "odla_Gelu": (_V, [_V, C.c_uint32, _ID]),
     "odla_Softmax": (_V, [_V, C.c_int32, _ID]),
     "odla_LogSoftmax": (_V, [_V, C.c_int32, _ID]),
@@ -461,6 +463,24 @@ class Graph:
         h = self.lib.Slice(x[1], _i32(start), _i32(end), _i32(stride), shape(out_dims), self._id(name))
         self._line(name, "odla_Slice(%s, %s, %s, %s, %s" % (self._n(x), self._ca(start, "odla_int32"), self._ca(end, "odla_int32"), self._ca(stride, "odla_int32"), self._cs(out_dims)))
         return self._reg(name, h, out_dims, self.dtypes[x[0]])
+
+    def NMS(self, boxes, scores, max_num_outputs, iou_threshold, score_threshold, out_rows, name, index_type=INT32):
+        h = self.lib.NMS(boxes[1], scores[1], int(max_num_outputs), float(iou_threshold), float(score_threshold), vtype(index_type, (out_rows, 3)), self._id(name))
+        self._line(name, "odla_NMS(%s, %s, %d, %r, %r, {%s, %s}" % (self._n(boxes), self._n(scores), max_num_outputs, float(iou_threshold), float(score_threshold),
+                                                                  _ENUM[index_type], self._cs((out_rows, 3))))
+        return self._reg(name, h, (out_rows, 3), index_type)
+
+    def PostProcess(self, img_w, img_h, bb13, bb26, bb52, name):
+        """odla_PostProcess returns two values: <name>0 = selected_info [classes, N/169, 5], <name>1 = selected_num [classes]."""
+        vs = self.lib.PostProcess(img_w[1], img_h[1], bb13[1], bb26[1], bb52[1], self._id(name))
+        dims = self.shapes[bb13[0]]
+        ch = dims[1] if dims[2] == dims[3] else dims[3]
+        cls = ch // 3 - 5
+        self.cc_body.append("  auto %s = odla_PostProcess(%s, %s, %s, %s, %s, (const odla_value_id)\"%s\");" % (
+            _cname(name), self._n(img_w), self._n(img_h), self._n(bb13), self._n(bb26), self._n(bb52), name))
+        info = self._reg(name + "0", vs.values[0], (cls, 10647 // 169, 5), FLOAT32)
+        num = self._reg(name + "1", vs.values[1], (cls,), UINT32)
+        return info, num
 
     def Cast(self, x, target, name):
         h = self.lib.Cast(x[1], target, self._id(name))

@@ -318,6 +318,16 @@ odla_value odla_ReduceMean(odla_value input, odla_size_t num_of_axes, const odla
  *      114-115 (Concat), 168-169 (Gather), 249-250 (Reshape), 282-284 (Resize),
  *      336-338 (Slice), 434-435 (Transpose) ---- */
 odla_value odla_Cast(odla_value input, odla_element_type target_type, const odla_value_id value_id);
+/* ODLA/include/ODLA/ops/odla_ops_nn.h:504-507: greedy non-maximum suppression (the ONNX NonMaxSuppression rule, as
+ * lib/target/generic_cpp/nms.cc emits it).  boxes [B, N, 4] (y1, x1, y2, x2), scores [B, C, N]; the result is
+ * [rows, 3] int32 / int64 rows (batch, class, box) in batch, class, descending-score order, -1 where nothing is selected. */
+odla_value odla_NMS(odla_value boxes, odla_value scores, odla_uint32 max_num_outputs, odla_float32 iou_threshold,
+                    odla_float32 score_threshold, odla_value_type output_value_type, const odla_value_id value_id);
+/* ODLA/include/ODLA/ops/odla_ops_nn.h:757-759: YOLOv3 decoding + per-class suppression of the three heads (13, 26, 52
+ * cells; batch 1; NCHW or NHWC), as ODLA/platforms/odla_popart/custom_ops/postprocess.cc defines it.  Returns
+ * selected_info [classes, N/169, 5] = (y_min, x_min, y_max, x_max, score) named <id>0 and selected_num [classes] named <id>1. */
+odla_values odla_PostProcess(odla_value orig_img_w, odla_value orig_img_h, odla_value bb13, odla_value bb26, odla_value bb52,
+                             const odla_value_id value_id);
 odla_value odla_Concat(odla_values inputs, odla_int32 axis, odla_value_shape output_shape,
                        const odla_value_id value_id);
 odla_value odla_Gather(odla_value input, odla_value indices, odla_int32 axis,

@@ -458,3 +458,116 @@ void ora_slice(void* out, const void* in, int rank, const int64_t* ishape, const
     }
   }
 }
+
+/* ---- detection post-processing ------------------------------------------------------------------------------ */
+/* ONNX NonMaxSuppression, the rule odla_NMS stands for (lib/target/generic_cpp/nms.cc:22-69 emits the ONNX operator's
+ * operands unchanged): per (batch, class) the candidates with score > score_threshold in descending score order (ties:
+ * lower index first), each kept unless its IoU with an already kept box exceeds iou_threshold; boxes are (y1, x1, y2,
+ * x2) with the corners in any order.  out: rows (batch, class, box), -1 in unused rows. */
+static int ora_iou_over(const float* a, const float* b, float thr) {
+  float ay1 = fminf(a[0], a[2]), ay2 = fmaxf(a[0], a[2]), ax1 = fminf(a[1], a[3]), ax2 = fmaxf(a[1], a[3]);
+  float by1 = fminf(b[0], b[2]), by2 = fmaxf(b[0], b[2]), bx1 = fminf(b[1], b[3]), bx2 = fmaxf(b[1], b[3]);
+  float ih = fminf(ay2, by2) - fmaxf(ay1, by1), iw = fminf(ax2, bx2) - fmaxf(ax1, bx1);
+  if (ih <= 0.f || iw <= 0.f) return 0;
+  float inter = ih * iw;
+  float area_a = (ay2 - ay1) * (ax2 - ax1), area_b = (by2 - by1) * (bx2 - bx1);
+  float uni = (area_a + area_b) - inter;
+  if (uni <= 0.f) return 0;
+  return inter / uni > thr;
+}
+/* order[]: indices sorted by (score descending, index ascending); insertion sort keeps this file free of callbacks */
+static void ora_sort_desc(const float* score, int32_t* order, int64_t n) {
+  for (int64_t i = 1; i < n; ++i) {
+    int32_t v = order[i];
+    int64_t j = i - 1;
+    while (j >= 0 && (score[order[j]] < score[v] || (score[order[j]] == score[v] && order[j] > v))) { order[j + 1] = order[j]; --j; }
+    order[j + 1] = v;
+  }
+}
+void ora_nms(int64_t* out, int64_t out_rows, const float* boxes, const float* scores, int64_t B, int64_t C, int64_t N, int64_t max_per_class,
+             float iou_thr, float score_thr, int32_t* order_scratch, int32_t* kept_scratch) {
+  int64_t row = 0;
+  for (int64_t i = 0; i < out_rows * 3; ++i) out[i] = -1;
+  for (int64_t b = 0; b < B; ++b)
+    for (int64_t c = 0; c < C; ++c) {
+      const float* sc = scores + (b * C + c) * N;
+      const float* bx = boxes + b * N * 4;
+      int64_t n = 0, kept = 0;
+      for (int64_t i = 0; i < N; ++i) if (sc[i] > score_thr) order_scratch[n++] = (int32_t)i;
+      ora_sort_desc(sc, order_scratch, n);
+      for (int64_t k = 0; k < n && kept < max_per_class; ++k) {
+        int32_t i = order_scratch[k];
+        int drop = 0;
+        for (int64_t j = 0; j < kept && !drop; ++j) drop = ora_iou_over(bx + 4 * kept_scratch[j], bx + 4 * i, iou_thr);
+        if (drop) continue;
+        kept_scratch[kept++] = i;
+        if (row < out_rows) { out[row * 3] = b; out[row * 3 + 1] = c; out[row * 3 + 2] = i; ++row; }
+      }
+    }
+}
+/* YOLOv3 post-processing as ODLA/platforms/odla_popart/custom_ops/postprocess.cc + codelets_nms.cpp define it: the heads
+ * (NHWC after the transposition at postprocess.cc:150-152) are exponentiated (:154-156), decoded cell by cell against
+ * the anchors of yolo_anchors.txt -- rows 2, 1, 0 for 13, 26, 52 cells (:170-228) -- by DecodeVertex
+ * (codelets_nms.cpp:73-120), concatenated 13, 26, 52 (:232-234), and each class is walked in descending score order:
+ * scores below 0.3 are skipped and a box is kept unless it overlaps the LAST kept one by more than 0.45
+ * (codelets_nms.cpp:48-69).  info: [cls][N/169][5] = (y_min, x_min, y_max, x_max, score), zero beyond num[cls]. */
+void ora_yolo_postprocess(float* info, uint32_t* num, const float* const* heads, const int* nchw3, const int* S3, int64_t cls, uint32_t img_w, uint32_t img_h,
+                          float* boxes_scratch, float* scores_scratch, int32_t* order_scratch) {
+  static const unsigned anchors[3][6] = {{10, 13, 16, 30, 33, 23}, {30, 61, 62, 45, 59, 119}, {116, 90, 156, 198, 373, 326}};
+  int64_t N = 0, first[3];
+  for (int i = 0; i < 3; ++i) { first[i] = N; N += (int64_t)S3[i] * S3[i] * 3; }
+  const int64_t per_class = N / 169, ch = cls + 5;
+  float scale = (float)fmin(416.0 / img_h, 416.0 / img_w);
+  float new_h = roundf(img_h * scale), new_w = roundf(img_w * scale);
+  float off_h = (float)((416 - new_h) / 2.0 / 416), off_w = (float)((416 - new_w) / 2.0 / 416);
+  float sc_h = 416 / new_h, sc_w = 416 / new_w;
+  for (int h = 0; h < 3; ++h) {
+    const int S = S3[h];
+    const unsigned* an = anchors[2 - h];
+    for (int y = 0; y < S; ++y)
+      for (int x = 0; x < S; ++x)
+        for (int a = 0; a < 3; ++a) {
+          float e[5];
+          int64_t n = first[h] + ((int64_t)y * S + x) * 3 + a;
+#define ORA_AT(k) expf(heads[h][nchw3[h] ? (((int64_t)(a * ch + (k))) * S + y) * S + x : ((int64_t)y * S + x) * (3 * ch) + a * ch + (k)])
+          for (int k = 0; k < 5; ++k) e[k] = ORA_AT(k);
+          float dx = ((e[0] / (e[0] + 1)) + x) / S;
+          dx = (dx - off_w) * sc_w;
+          float dy = ((e[1] / (e[1] + 1)) + y) / S;
+          dy = (dy - off_h) * sc_h;
+          float dw = (e[2] * an[a << 1]) / 416 * sc_w, dh = (e[3] * an[a << 1 | 1]) / 416 * sc_h;
+          boxes_scratch[n * 4 + 0] = (float)((dy - dh / 2.0) * img_h);
+          boxes_scratch[n * 4 + 1] = (float)((dx - dw / 2.0) * img_w);
+          boxes_scratch[n * 4 + 2] = (float)((dy + dh / 2.0) * img_h);
+          boxes_scratch[n * 4 + 3] = (float)((dx + dw / 2.0) * img_w);
+          float conf = e[4] / (e[4] + 1);
+          for (int64_t c = 0; c < cls; ++c) { float ec = ORA_AT(5 + c); scores_scratch[c * N + n] = ec / (ec + 1) * conf; }
+#undef ORA_AT
+        }
+  }
+  for (int64_t c = 0; c < cls; ++c) {
+    const float* sc = scores_scratch + c * N;
+    int64_t n = 0, kept = 0, last = -1;
+    for (int64_t i = 0; i < N; ++i) if (!(sc[i] < 0.3f)) order_scratch[n++] = (int32_t)i;
+    ora_sort_desc(sc, order_scratch, n);
+    for (int64_t k = 0; k < per_class * 5; ++k) info[c * per_class * 5 + k] = 0.f;
+    for (int64_t k = 0; k < n && kept < per_class; ++k) {
+      int32_t i = order_scratch[k];
+      if (last >= 0) {
+        const float* s = boxes_scratch + 4 * last; const float* b = boxes_scratch + 4 * i;
+        float y_top = fmaxf(s[0], b[0]), x_left = fmaxf(s[1], b[1]), y_bot = fminf(s[2], b[2]), x_right = fminf(s[3], b[3]);
+        if (!(x_right < x_left || y_bot < y_top)) {
+          float comm = (x_right - x_left) * (y_bot - y_top);
+          float sa = (s[2] - s[0]) * (s[3] - s[1]), ca = (b[2] - b[0]) * (b[3] - b[1]);
+          if (comm / ((sa + ca) - comm) > 0.45f) continue;
+        }
+      }
+      last = i;
+      float* o = info + (c * per_class + kept) * 5;
+      for (int j = 0; j < 4; ++j) o[j] = boxes_scratch[4 * i + j];
+      o[4] = sc[i];
+      ++kept;
+    }
+    num[c] = (uint32_t)kept;
+  }
+}

@@ -73,6 +73,8 @@ void ora_concat_part(void*, const void*, int64_t, int64_t, int64_t, int64_t, int
 void ora_resize_nearest(void*, const void*, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t,
                         int, int);
 void ora_gather(void*, const void*, const int64_t*, int64_t, int64_t, int64_t, int64_t, int);
+void ora_nms(int64_t*, int64_t, const float*, const float*, int64_t, int64_t, int64_t, int64_t, float, float, int32_t*, int32_t*);
+void ora_yolo_postprocess(float*, uint32_t*, const float* const*, const int*, const int*, int64_t, uint32_t, uint32_t, float*, float*, int32_t*);
 void ora_slice(void*, const void*, int, const int64_t*, const int64_t*, const int64_t*,
                const int64_t*, int);
 }
@@ -641,6 +643,45 @@ odla_value odla_Slice(odla_value in, const odla_int32* start, const odla_int32* 
   odla_value out = new_value(in->api_type.element_type, od, id);
   g_comp->ops.push_back([=] { ora_slice(out->buf.data(), in->buf.data(), rank, in->shape().dims, out->shape().dims, st.data(), sp.data(), elem_size(in->store)); });
   return out;
+}
+odla_value odla_NMS(odla_value boxes, odla_value scores, odla_uint32 max_num_outputs, odla_float32 iou, odla_float32 thr, odla_value_type ot, const odla_value_id id) {
+  const auto& ss = scores->shape();
+  if (boxes->shape().size != 3 || ss.size != 3) return fail("NMS: boxes [B,N,4], scores [B,C,N]");
+  int64_t B = ss.dims[0], C = ss.dims[1], N = ss.dims[2], rows = ot.shape.dims[0];
+  odla_value out = new_value(ot.element_type, ot.shape, id);
+  g_comp->ops.push_back([=] {
+    std::vector<int64_t> r((size_t)rows * 3);
+    std::vector<int32_t> order((size_t)N + 1), kept((size_t)N + 1);
+    ora_nms(r.data(), rows, boxes->f(), scores->f(), B, C, N, max_num_outputs ? (int64_t)max_num_outputs : rows, iou, thr, order.data(), kept.data());
+    for (size_t i = 0; i < r.size(); ++i) { if (out->store == ODLA_INT64) ((int64_t*)out->buf.data())[i] = r[i]; else ((int32_t*)out->buf.data())[i] = (int32_t)r[i]; }
+  });
+  return out;
+}
+odla_values odla_PostProcess(odla_value iw, odla_value ih, odla_value b13, odla_value b26, odla_value b52, const odla_value_id id) {
+  odla_values res{};
+  std::string base = id ? (const char*)id : "postprocess", n0 = base + "0", n1 = base + "1";
+  odla_value heads[3] = {b13, b26, b52};
+  int S3[3], nchw3[3];
+  int64_t chn = 0;
+  for (int i = 0; i < 3; ++i) {
+    const auto& s = heads[i]->shape();
+    nchw3[i] = s.dims[2] == s.dims[3] && s.dims[1] % 3 == 0 && s.dims[1] / 3 > 5 && s.dims[1] != s.dims[2];
+    S3[i] = (int)s.dims[2];
+    chn = nchw3[i] ? s.dims[1] : s.dims[3];
+  }
+  const int64_t cls = chn / 3 - 5, N = 3 * ((int64_t)S3[0] * S3[0] + (int64_t)S3[1] * S3[1] + (int64_t)S3[2] * S3[2]);
+  odla_value_shape s0{3, {cls, N / 169, 5}}, s1{1, {cls}};
+  odla_value info = new_value(ODLA_FLOAT32, s0, (const odla_value_id)n0.c_str());
+  odla_value num = new_value(ODLA_UINT32, s1, (const odla_value_id)n1.c_str());
+  std::vector<int> S(S3, S3 + 3), L(nchw3, nchw3 + 3);
+  g_comp->ops.push_back([=] {
+    const float* hp[3] = {b13->f(), b26->f(), b52->f()};
+    std::vector<float> bx((size_t)N * 4), sc((size_t)cls * N);
+    std::vector<int32_t> order((size_t)N + 1);
+    ora_yolo_postprocess(info->f(), (uint32_t*)num->buf.data(), hp, L.data(), S.data(), cls, *(uint32_t*)iw->buf.data(), *(uint32_t*)ih->buf.data(), bx.data(), sc.data(), order.data());
+  });
+  res.size = 2; res.values[0] = info; res.values[1] = num;
+  return res;
 }
 odla_value odla_Cast(odla_value in, odla_element_type tt, const odla_value_id id) {
   odla_value out = new_value(tt, in->shape(), id);
