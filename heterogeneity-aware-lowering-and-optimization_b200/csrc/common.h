@@ -85,6 +85,12 @@ struct Launch {
   // profiling accumulators
   double prof_ms = 0;
   long long prof_n = 0;
+  // what the entry leaves in memory, for range profiling (out_ptr == nullptr: not a dense tensor of out_count elements)
+  const _odla_value* out_v = nullptr;
+  const void* out_ptr = nullptr;
+  int out_dt = 0;
+  int64_t out_count = 0, out_channels = 1;
+  unsigned* range_stats = nullptr;   // device: [2 + 2 * out_channels] order-preserving keys of min / max, whole tensor then per channel
 };
 
 // Where a value lives inside a replica's arena.
@@ -121,6 +127,7 @@ struct Plan {
     const void* const_host = nullptr;  // output that is a constant: copied straight from here
   };
   std::vector<Io> inputs, outputs;
+  std::vector<unsigned*> input_range_stats;  // per input, like Launch::range_stats
   ~Plan();
 };
 
@@ -177,6 +184,7 @@ struct _odla_context {
   float last_ms = -1.f;
   long long last_launches = 0;
   bool profiling = false;
+  bool range_profiling = false;    // accumulate min / max of every materialised value (odla_b200_SetRangeProfiling)
   int64_t run_batch = 0;           // ODLA_RUN_BATCH_SIZE; 0 = the recorded batch
   // odla_AsyncExecuteComputation: one worker at a time per context
   std::thread worker;

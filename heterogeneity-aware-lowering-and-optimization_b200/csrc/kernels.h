@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <cstring>
 
 namespace b200 {
 
@@ -181,6 +182,13 @@ int resize_nearest(int esz, const void* x, void* y, int N, int H, int W, int C, 
 // out[o, k, :] = in[o, idx[k], :]; idx int32 or int64.
 int gather(int esz, const void* x, const void* idx, int idx_dt, void* y, int64_t outer, int64_t axis_dim,
            int64_t n_idx, int64_t inner, cudaStream_t stream);
+
+// Running minimum / maximum of a dense float tensor (fp32 / fp16 / bf16) whose last axis has `channels` entries:
+// stats[0], stats[1] = whole tensor, stats[2 + c], stats[2 + channels + c] = channel c, all as order-preserving
+// unsigned keys (range_key_init / range_key_decode) updated with atomicMin / atomicMax, so calls accumulate.
+int range_minmax(int dt, const void* x, int64_t count, int64_t channels, unsigned* stats, cudaStream_t stream);
+int range_stats_reset(unsigned* stats, int64_t channels, cudaStream_t stream);
+inline float range_key_decode(unsigned k) { unsigned b = (k & 0x80000000u) ? (k & 0x7fffffffu) : ~k; float f; memcpy(&f, &b, 4); return f; }
 
 // Greedy non-maximum suppression (odla_NMS): boxes [B, N, 4] (y1, x1, y2, x2), scores [B, C, N]; `out` gets out_rows rows
 // (batch, class, box) as int32 or int64, -1 beyond the selected ones.  sel [B*C*max_sel] and cnt [B*C] are scratch.

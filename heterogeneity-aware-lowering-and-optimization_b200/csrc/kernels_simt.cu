@@ -6,6 +6,8 @@
 // the SM count.
 #include <cstdio>
 
+#include <algorithm>
+
 #include "epilogue.cuh"
 
 namespace b200 {
@@ -1027,6 +1029,52 @@ int convert_rows(int dt_in, int dt_out, const void* x, void* y, int64_t rows, in
     return check_launch();
   }
   convert_rows_kernel<<<grid_for(rows * K, 256), 256, 0, s>>>(dt_in, dt_out, x, y, rows, K, Kp);
+  return check_launch();
+}
+// ---- range profiling: min / max per tensor and per channel (last axis) ----
+// A float maps to an unsigned key that orders the same way (sign bit flipped for positives, all bits for negatives).
+__device__ __forceinline__ unsigned range_key(float f) { const unsigned b = __float_as_uint(f); return (b & 0x80000000u) ? ~b : (b | 0x80000000u); }
+__global__ void range_reset_kernel(unsigned* stats, int64_t channels) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < 2 + 2 * channels; i += (int64_t)gridDim.x * blockDim.x)
+    stats[i] = (i == 0 || (i >= 2 && i < 2 + channels)) ? 0xffffffffu : 0u;   // minima start at the largest key, maxima at the smallest
+}
+// A block takes a contiguous run of rows; thread t keeps channels t, t + 256, ... (up to 16 of them) in registers and
+// publishes them with one atomic pair per channel at the end.
+__global__ void range_minmax_kernel(int dt, const void* __restrict__ x, int64_t rows, int channels, unsigned* __restrict__ stats) {
+  const int64_t per_block = (rows + gridDim.x - 1) / gridDim.x, r0 = blockIdx.x * per_block, r1 = min(rows, r0 + per_block);
+  for (int c0 = 0; c0 < channels; c0 += 16 * blockDim.x) {
+    float mn[16], mx[16];
+#pragma unroll
+    for (int k = 0; k < 16; ++k) { mn[k] = 3.402823466e+38f; mx[k] = -3.402823466e+38f; }
+    for (int64_t r = r0; r < r1; ++r) {
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        const int c = c0 + threadIdx.x + k * blockDim.x;
+        if (c < channels) { const float v = load_as_float(x, dt, r * channels + c); mn[k] = fminf(mn[k], v); mx[k] = fmaxf(mx[k], v); }
+      }
+    }
+    if (r1 > r0) {
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        const int c = c0 + threadIdx.x + k * blockDim.x;
+        if (c < channels) {
+          atomicMin(stats + 2 + c, range_key(mn[k])); atomicMax(stats + 2 + channels + c, range_key(mx[k]));
+          atomicMin(stats, range_key(mn[k])); atomicMax(stats + 1, range_key(mx[k]));
+        }
+      }
+    }
+  }
+}
+int range_stats_reset(unsigned* stats, int64_t channels, cudaStream_t s) {
+  range_reset_kernel<<<grid_for(2 + 2 * channels, 256), 256, 0, s>>>(stats, channels);
+  return check_launch();
+}
+int range_minmax(int dt, const void* x, int64_t count, int64_t channels, unsigned* stats, cudaStream_t s) {
+  if (count <= 0 || channels <= 0 || count % channels != 0 || channels > (1 << 30)) return 0;
+  if (dt != DT_F32 && dt != DT_F16 && dt != DT_BF16) return 0;
+  const int64_t rows = count / channels;
+  int grid = (int)std::min<int64_t>(rows, (int64_t)sm_count() * 8);
+  range_minmax_kernel<<<grid > 0 ? grid : 1, 256, 0, s>>>(dt, x, rows, (int)channels, stats);
   return check_launch();
 }
 // out[b][n][k] = in[b][k][n]: the last two axes swapped, through 32 x 32 shared-memory tiles so that both the reads

@@ -238,6 +238,11 @@ class Builder {
   odla_status emit_plain(const Item& it);
   void add_launch(const char* op, V out, double flops, double bytes, std::function<int(cudaStream_t)> fn) {
     Launch l; l.op = op; l.name = out->name; l.flops = flops; l.bytes = bytes; l.fn = std::move(fn);
+    l.out_v = out;
+    if (dt_.count(out) && !pitch_.count(out) && p_->slots.count(out)) {
+      const odla_value_shape sh = shape(out);
+      l.out_ptr = dev_ptr(out); l.out_dt = dt_[out]; l.out_count = count(out); l.out_channels = sh.size ? sh.dims[sh.size - 1] : 1;
+    }
     p_->launches.push_back(std::move(l));
   }
   double tensor_bytes(V v) const { return (double)count(v) * storage_size(dt_.count(resolve(v)) ? dt_.at(resolve(v)) : storage_of(v)); }
@@ -1536,6 +1541,39 @@ int run_launches(Replica& r, _odla_context* ctx, bool use_graph, long long* n_la
     cudaEventDestroy(a); cudaEventDestroy(b);
     return 0;
   }
+  if (ctx->range_profiling) {
+    // plain launches, each followed by a min / max pass over what it left in memory (allocated on first use)
+    auto stats_for = [&](unsigned*& st, int64_t channels) {
+      if (st) return true;
+      if (cudaMalloc((void**)&st, sizeof(unsigned) * (size_t)(2 + 2 * channels)) != cudaSuccess) { st = nullptr; cudaGetLastError(); return false; }
+      p.extra_allocs.push_back(st);
+      return range_stats_reset(st, channels, r.stream) == 0;
+    };
+    p.input_range_stats.resize(p.inputs.size(), nullptr);
+    for (size_t i = 0; i < p.inputs.size(); ++i) {
+      const auto& io = p.inputs[i];
+      const auto& sl = p.slots[io.v];
+      if (sl.dt != DT_F32 && sl.dt != DT_F16 && sl.dt != DT_BF16) continue;
+      const auto& sh = io.v->type.shape;
+      const int64_t ch = sh.size ? sh.dims[sh.size - 1] : 1, n = sl.bytes / storage_size(sl.dt);
+      // an argument that is converted on the device is measured in its API type at the staging slot
+      const bool staged = io.stage != io.slot;
+      const int dt = staged ? DT_F32 : sl.dt;
+      const int64_t cnt = staged ? io.api_bytes / 4 : n;
+      if (staged && io.v->type.element_type != ODLA_FLOAT32) continue;
+      if (!stats_for(p.input_range_stats[i], ch)) return -2;
+      if (range_minmax(dt, p.arena + io.stage, cnt, ch, p.input_range_stats[i], r.stream)) return -2;
+    }
+    for (auto& l : p.launches) {
+      int rc = l.fn(r.stream);
+      if (rc) return rc;
+      *n_launched += l.n_kernels;
+      if (!l.out_ptr || (l.out_dt != DT_F32 && l.out_dt != DT_F16 && l.out_dt != DT_BF16)) continue;
+      if (!stats_for(l.range_stats, l.out_channels)) return -2;
+      if (range_minmax(l.out_dt, l.out_ptr, l.out_count, l.out_channels, l.range_stats, r.stream)) return -2;
+    }
+    return 0;
+  }
   if (use_graph && !p.graph && !p.graph_failed && !p.launches.empty()) {
     cudaGraph_t g = nullptr;
     bool ok = cudaStreamBeginCapture(r.stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
@@ -1692,6 +1730,77 @@ int odla_b200_GetProfile(odla_context ctx, odla_b200_profile_entry* entries, int
     entries[i].flops = ls[i].flops; entries[i].bytes = ls[i].bytes;
   }
   return (int)ls.size();
+}
+odla_status odla_b200_SetRangeProfiling(odla_context ctx, int enabled) {
+  if (!ctx) return ODLA_INVALID_PARAM;
+  ctx->range_profiling = enabled != 0;
+  return ODLA_SUCCESS;
+}
+int odla_b200_GetQuantTable(odla_context ctx, odla_value_quant_info* records, int capacity) {
+  if (!ctx || !ctx->comp) return 0;
+  _odla_computation* c = ctx->comp;
+  // name -> (min, max, per-channel min / max), merged over every replica (each saw its own rows of the batch)
+  struct R { float mn = 3.402823466e+38f, mx = -3.402823466e+38f; std::vector<float> cmn, cmx; const _odla_value* v = nullptr; };
+  std::map<const _odla_value*, R> seen;
+  std::vector<const _odla_value*> order;
+  auto take = [&](const _odla_value* v, unsigned* dev, int64_t channels, int device) {
+    if (!dev || !v) return;
+    std::vector<unsigned> h((size_t)(2 + 2 * channels));
+    cudaSetDevice(device);
+    if (cudaMemcpy(h.data(), dev, h.size() * sizeof(unsigned), cudaMemcpyDeviceToHost) != cudaSuccess) { cudaGetLastError(); return; }
+    if (h[0] == 0xffffffffu && h[1] == 0u) return;   // never updated
+    if (!seen.count(v)) order.push_back(v);
+    R& r = seen[v];
+    r.v = v;
+    r.mn = std::min(r.mn, range_key_decode(h[0])); r.mx = std::max(r.mx, range_key_decode(h[1]));
+    if (r.cmn.empty()) { r.cmn.assign((size_t)channels, 3.402823466e+38f); r.cmx.assign((size_t)channels, -3.402823466e+38f); }
+    for (int64_t k = 0; k < channels && k < (int64_t)r.cmn.size(); ++k) {
+      r.cmn[(size_t)k] = std::min(r.cmn[(size_t)k], range_key_decode(h[(size_t)(2 + k)]));
+      r.cmx[(size_t)k] = std::max(r.cmx[(size_t)k], range_key_decode(h[(size_t)(2 + channels + k)]));
+    }
+  };
+  auto scan = [&](std::vector<Replica>& reps) {
+    for (auto& rep : reps) {
+      if (!rep.plan) continue;
+      cudaSetDevice(rep.device);
+      cudaStreamSynchronize(rep.stream);
+      Plan& p = *rep.plan;
+      for (size_t i = 0; i < p.inputs.size() && i < p.input_range_stats.size(); ++i) {
+        const auto& sh = p.inputs[i].v->type.shape;
+        take(p.inputs[i].v, p.input_range_stats[i], sh.size ? sh.dims[sh.size - 1] : 1, rep.device);
+      }
+      for (auto& l : p.launches) take(l.out_v, l.range_stats, l.out_channels, rep.device);
+    }
+  };
+  scan(c->replicas);
+  for (auto& kv : c->batch_replicas) scan(kv.second);
+  // Reshape results share their source's memory: give them a per-value record under their own name
+  std::vector<std::pair<const _odla_value*, const _odla_value*>> aliases;
+  for (auto& n : c->nodes) {
+    if (n->kind != OP_RESHAPE) continue;
+    const _odla_value* src = n->in[0];
+    while (src && src->kind == OP_RESHAPE) src = src->in[0];
+    if (src && seen.count(src)) aliases.push_back({n.get(), src});
+  }
+  int n_rec = 0;
+  auto emit = [&](const _odla_value* v, int ch_idx, float scale, float mn, float mx) {
+    if (records && n_rec < capacity) {
+      odla_value_quant_info q{};
+      q.value_id = (odla_value_id)v->name.c_str(); q.ch_idx = ch_idx; q.scale = scale; q.offset = 0.f; q.min = mn; q.max = mx;
+      records[n_rec] = q;
+    }
+    ++n_rec;
+  };
+  auto sym = [](float mn, float mx) { const float a = std::max(std::fabs(mn), std::fabs(mx)); return a > 0.f ? a / 127.f : 1.f; };
+  // layout of utils/halo_pgq.py:309-327: one record per value with ch_idx = -channels, then one per channel
+  for (const _odla_value* v : order) {
+    const R& r = seen[v];
+    const int chs = v->type.shape.size >= 3 ? (int)r.cmn.size() : 1;   // channel-wise ranges for image-like tensors only
+    emit(v, -chs, sym(r.mn, r.mx), r.mn, r.mx);
+    if (chs > 1) for (int k = 0; k < chs; ++k) emit(v, k, 0.f, r.cmn[(size_t)k], r.cmx[(size_t)k]);
+  }
+  for (auto& a : aliases) { const R& r = seen[a.second]; emit(a.first, -1, sym(r.mn, r.mx), r.mn, r.mx); }
+  return n_rec;
 }
 int odla_b200_PlanShards(odla_computation c, long long run_batch, int visible_devices, int* device, long long* start, long long* rows, int capacity) {
   if (!c || visible_devices < 1) return 0;

@@ -181,6 +181,8 @@ _OPTIONAL = {
     "odla_StoreExecutable": (C.c_int, [ResourceLocation, _V]),
     "odla_LoadExecutable": (C.c_int, [ResourceLocation, _V, C.POINTER(_V)]),
     "odla_CompileComputation": (C.c_int, [_V, _V, C.POINTER(_V)]),
+    "odla_b200_SetRangeProfiling": (C.c_int, [_V, C.c_int]),
+    "odla_b200_GetQuantTable": (C.c_int, [_V, C.POINTER(QuantInfo), C.c_int]),
     "odla_b200_PlanShards": (C.c_int, [_V, C.c_longlong, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_longlong), C.POINTER(C.c_longlong), C.c_int]),
     "odla_b200_conv_umma": (C.c_int, [C.POINTER(ConvDesc), _V, _V, _V, _V, _V, _V, _V]),
     "odla_b200_reduce_mean_noalloc": (C.c_int, [_V, _V, C.c_int, C.POINTER(C.c_longlong), C.c_int, C.POINTER(C.c_int), C.c_int, _V]),
@@ -540,6 +542,17 @@ class Graph:
 
     def launches(self):
         return int(self.lib.b200_LastExecuteLaunches(self.context()))
+
+    def range_profiling(self, enabled=True):
+        """Accumulate min / max of every materialised value during the following executes (calibration)."""
+        self._check(self.lib.b200_SetRangeProfiling(self.context(), 1 if enabled else 0), "odla_b200_SetRangeProfiling")
+
+    def quant_table(self):
+        """The ranges collected so far as set_quant_table() records: [(value_id, ch_idx, scale, offset, min, max), ...]."""
+        n = self.lib.b200_GetQuantTable(self.context(), None, 0)
+        arr = (QuantInfo * max(n, 1))()
+        n = self.lib.b200_GetQuantTable(self.context(), arr, n)
+        return [(arr[i].value_id.decode(), arr[i].ch_idx, arr[i].scale, arr[i].offset, arr[i].min, arr[i].max) for i in range(n)]
 
     def plan_shards(self, visible_devices, run_batch=0):
         """[(device, first_row, rows), ...]: how an execute would be split over `visible_devices` GPUs (no GPU needed)."""

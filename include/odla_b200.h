@@ -398,6 +398,19 @@ long long odla_b200_LastExecuteLaunches(odla_context context);
 /* Text description of the launch list (one line per kernel) into buf; returns bytes needed. */
 int odla_b200_DescribePlan(odla_computation computation, char* buf, int capacity);
 
+/* Range profiling on the GPU -- what the reference does with a wrapper platform that evaluates every op on the host and
+ * records its range (ODLA/platforms/odla_profiler.cc:155-200) plus a script that turns the records into a table
+ * (utils/halo_pgq.py:309-327).  While it is enabled on a context, every execute runs its launch list un-captured and
+ * follows each launch by a min / max pass over the tensor it wrote (whole tensor and per channel of the last axis);
+ * arguments are measured too; ranges accumulate over executes (calibration batches).  odla_b200_GetQuantTable then
+ * writes the table in halo_pgq's layout -- per value one record with ch_idx = -channels, scale = max(|min|, |max|) / 127
+ * and offset 0 (the symmetric int8 scheme of this library), followed by one record per channel -- ready for
+ * ODLA_QUANT_TABLE.  Values that a fused kernel never writes to memory (a convolution's result before its bias and
+ * ReLU) have no record; every tensor a convolution or Gemm READS has one.  Returns the number of records; call with
+ * records == NULL to size the array.  The value ids point into the computation and live as long as it does. */
+odla_status odla_b200_SetRangeProfiling(odla_context context, int enabled);
+int odla_b200_GetQuantTable(odla_context context, odla_value_quant_info* records, int capacity);
+
 /* How one odla_ExecuteComputation of `run_batch` rows (<= 0: the recorded batch) would be split if
  * `visible_devices` GPUs were visible: one entry per replica (GPU x sub-batch) with its device index,
  * first row and row count.  Needs no GPU -- it is the planner's shard arithmetic on its own, for

@@ -149,3 +149,76 @@ def test_resnet50_float_graph_with_table_runs_int8(odla, gpu_lib, models):
     cc = g.emit_cc()
     assert "extern const odla_value_quant_info quant_infos[];" in cc and "ODLA_QUANT_TABLE_SIZE" in cc
     assert "quant_infos_size = %d" % len(records) in g.emit_quant_table_c()
+
+
+def test_range_profiler_matches_host_ranges(odla, gpu_lib, ref):
+    """odla_b200_SetRangeProfiling + odla_b200_GetQuantTable: per-value and per-channel min / max of every materialised
+    value, accumulated over two calibration executes, against numpy on the oracle's values; halo_pgq's record layout."""
+    rng = np.random.default_rng(3)
+    w1 = (rng.standard_normal((3, 3, 8, 16)) * 0.2).astype(np.float32)
+    b1 = rng.standard_normal((1, 1, 1, 16)).astype(np.float32)
+    xs = [rng.standard_normal((2, 10, 10, 8)).astype(np.float32) * s for s in (1.0, 3.0)]
+
+    def net(g):
+        x = g.Argument("x", (2, 10, 10, 8))
+        y = g.Conv(x, odla.CHANNELS_LAST, 1, g.Constant("w1", w1), odla.SIO, (1, 1), (1, 1), (1, 1), (1, 1), None, (2, 10, 10, 16), "c1")
+        r = g.Relu(g.Add(y, g.Constant("b1", b1), "c1_b"), "r1")
+        p = g.MaxPool(r, odla.CHANNELS_LAST, (2, 2), (2, 2), (0, 0), (0, 0), (2, 5, 5, 16), "p1")
+        g.Output(g.Reshape(p, (2, 400), "flat"))
+        g.Output(r)
+        return g
+
+    g = net(odla.Graph(gpu_lib, "prof"))
+    g.range_profiling(True)
+    for x in xs:
+        g.run({"x": x})
+    table = g.quant_table()
+    g.range_profiling(False)
+    g.close()
+    h = net(odla.Graph(ref, "prof_ref"))
+    want = [h.run({"x": x}) for x in xs]
+    h.close()
+    rec = {}
+    for vid, ch, scale, off, mn, mx in table:
+        rec.setdefault(vid, []).append((ch, scale, off, mn, mx))
+    assert set(rec) == {"x", "r1", "p1", "flat"}                       # c1 and c1_b only exist inside the fused kernel
+    r1 = np.concatenate([o["r1"] for o in want])
+    for vid, arr in (("x", np.concatenate(xs)), ("r1", r1)):
+        head = rec[vid][0]
+        assert head[0] == -arr.shape[-1] and head[2] == 0.0
+        np.testing.assert_allclose([head[3], head[4]], [arr.min(), arr.max()], rtol=1e-5, atol=1e-6)
+        np.testing.assert_allclose(head[1], max(abs(arr.min()), abs(arr.max())) / 127.0, rtol=1e-5)
+        chans = rec[vid][1:]
+        assert [c[0] for c in chans] == list(range(arr.shape[-1]))
+        np.testing.assert_allclose([c[3] for c in chans], arr.reshape(-1, arr.shape[-1]).min(0), rtol=1e-5, atol=1e-6)
+        np.testing.assert_allclose([c[4] for c in chans], arr.reshape(-1, arr.shape[-1]).max(0), rtol=1e-5, atol=1e-6)
+    flat = np.concatenate([o["flat"] for o in want])
+    assert len(rec["flat"]) == 1 and rec["flat"][0][0] == -1
+    np.testing.assert_allclose(rec["flat"][0][4], flat.max(), rtol=1e-5)
+
+
+def test_resnet50_calibrated_on_the_gpu_runs_int8(odla, gpu_lib, models):
+    """Calibration without the host: the float graph profiles its own ranges on a calibration batch, the table goes
+    back in through ODLA_QUANT_TABLE, and the int8 plan agrees with the float run."""
+    rn = models.resnet50
+    w = rn.weights()
+    x = rn.inputs(8)
+    g = odla.Graph(gpu_lib, "resnet50", fp16=True)
+    rn.build(g, 8, w)
+    ref_prob = g.run(x)["prob"]
+    g.range_profiling(True)
+    g.run(rn.inputs(8, seed=77))
+    table = g.quant_table()
+    g.range_profiling(False)
+    g.close()
+    ids = {t[0] for t in table}
+    assert {"input", "pool1", "s1b0_c1_relu", "s4b2_c3_relu", "flatten"} <= ids
+    q = odla.Graph(gpu_lib, "resnet50_qt", fp16=True)
+    rn.build(q, 8, w)
+    q.set_quant_table(table)
+    prob = q.run(x)["prob"]
+    desc = q.describe(first_gpu_only=True)
+    q.close()
+    assert desc.count("_qt_q") + desc.count("quantize") >= 16
+    assert np.abs(prob - ref_prob).max() < 0.1
+    assert (prob.argmax(1) == ref_prob.argmax(1)).mean() >= 0.75
