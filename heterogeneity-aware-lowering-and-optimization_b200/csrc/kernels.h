@@ -99,6 +99,10 @@ struct UmmaConv {
   // Row pitch of y in elements when it is wider than K (0 = K): lets an output with rows that are not 16-byte
   // multiples use the TMA-store epilogue; columns K .. y_pitch-1 receive unspecified values.
   int y_pitch = 0;
+  // Filter terms: w holds [K][w_terms * R*S][C] and the accumulator is the sum over the terms, each walking the same
+  // R x S window of x.  A filter whose values do not fit the operand type is split into terms that do (uint8 weights
+  // minus their zero point span [-255, 255]: two or three int8 terms).  0 and 1 both mean a single term.
+  int w_terms = 0;
 };
 // True when the tensor-core kernel can run this problem.
 bool umma_conv_supported(const UmmaConv& p);

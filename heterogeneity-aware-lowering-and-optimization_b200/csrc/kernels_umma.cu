@@ -890,7 +890,7 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               if (c0 >= p.C) {
                 c0 = 0;
                 ++tap;
-                if (++fs == p.S) { fs = 0; ++fr; }
+                if (++fs == p.S) { fs = 0; if (++fr == p.R) fr = 0; }   // the next filter term walks the window again
               }
             }
             if (++s == p.stages) { s = 0; ph ^= 1; }
@@ -908,7 +908,7 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (c0 >= p.C) {
               c0 = 0;
               ++tap;
-              if (++fs == p.S) { fs = 0; ++fr; }
+              if (++fs == p.S) { fs = 0; if (++fr == p.R) fr = 0; }   // the next filter term walks the window again
             }
           }
           if (++s == p.stages) { s = 0; ph ^= 1; }
@@ -1235,7 +1235,8 @@ bool umma_conv_supported(const UmmaConv& c) {
   int es = elem_bytes(c.in_dt);
   if (((int64_t)c.C * es) % 16 != 0) return false;   // TMA strides and channel coordinates must be 16-byte multiples
   if (c.C * es < 32) return false;
-  if (c.K < 1 || c.R < 1 || c.S < 1 || c.R * c.S > 4096) return false;
+  if (c.K < 1 || c.R < 1 || c.S < 1 || c.R * c.S * (c.w_terms > 1 ? c.w_terms : 1) > 4096) return false;
+  if (c.w_terms > 1 && c.w_batches > 0) return false;
   if (c.stride_h < 1 || c.stride_w < 1 || c.stride_h > 8 || c.stride_w > 8) return false;
   if (c.pad_t > 127 || c.pad_l > 127 || c.R > 128 || c.S > 128) return false;  // im2col corners are 8-bit
   if ((int64_t)c.N * c.P * c.Q >= (1ll << 31)) return false;
@@ -1266,7 +1267,8 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
   p.kb_bytes = pick_kb_bytes(c.C * es);
   p.kbe = p.kb_bytes / es;
   p.chunks_per_tap = (c.C + p.kbe - 1) / p.kbe;
-  p.num_kb = c.R * c.S * p.chunks_per_tap;
+  const int terms = c.w_terms > 1 ? c.w_terms : 1;
+  p.num_kb = c.R * c.S * terms * p.chunks_per_tap;
   p.BN = pick_bn(c.K);
   p.m_tiles = (p.M_total + BM - 1) / BM;
   p.n_tiles = (c.K + p.BN - 1) / p.BN;
@@ -1411,8 +1413,8 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
     return nullptr;
   }
   {
-    cuuint64_t dims[3] = {(cuuint64_t)c.C, (cuuint64_t)(c.R * c.S), (cuuint64_t)c.K};
-    cuuint64_t strides[2] = {(cuuint64_t)c.C * es, (cuuint64_t)c.R * c.S * c.C * es};
+    cuuint64_t dims[3] = {(cuuint64_t)c.C, (cuuint64_t)(c.R * c.S * terms), (cuuint64_t)c.K};
+    cuuint64_t strides[2] = {(cuuint64_t)c.C * es, (cuuint64_t)c.R * c.S * terms * c.C * es};
     cuuint32_t box[3] = {(cuuint32_t)p.kbe, 1, (cuuint32_t)p.bn_load};
     if (c.w_batches > 0) {  // [batches][K][C]: the box spans BN rows of one matrix
       dims[1] = (cuuint64_t)c.K; dims[2] = (cuuint64_t)c.w_batches;

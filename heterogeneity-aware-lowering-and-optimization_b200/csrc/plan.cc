@@ -130,6 +130,7 @@ struct Fused {
   V x_scale = nullptr;      // per-tensor activation scale (int8)
   V w = nullptr;            // constant weights actually read (int8 source when int8)
   V w_scale = nullptr;      // per-tensor or per-output-channel weight scale (int8)
+  V w_zp = nullptr;         // per-tensor zero point of asymmetric uint8 weights (the filter is W_u - zp)
   V add_const = nullptr;    // per-channel Add operand
   V res = nullptr;          // residual tensor actually read
   V res_scale = nullptr;    // Dequantize scale when the residual is int8
@@ -359,15 +360,20 @@ void Builder::try_fuse(V root) {
   bool channel_last = root->kind == OP_GEMM || root->ia[0];
   // int8 operands
   V xin = root->in[0], win = root->in[1];
-  if (is_per_tensor_dq(xin) && win && win->kind == OP_DEQUANTIZE && !win->in[2] && win->in[0]->kind == OP_CONST &&
-      win->in[0]->type.element_type == ODLA_INT8 && channel_last &&
-      (numel(win->in[1]->type.shape) == 1 || numel(win->in[1]->type.shape) == K) &&
-      (root->kind == OP_CONV ? root->ia[1] == 1 : root->type.shape.size == 2)) {
+  const bool w_s8 = win && win->kind == OP_DEQUANTIZE && !win->in[2] && win->in[0]->kind == OP_CONST && win->in[0]->type.element_type == ODLA_INT8 &&
+                    (numel(win->in[1]->type.shape) == 1 || numel(win->in[1]->type.shape) == K);
+  // asymmetric uint8 weights as -quantize-weights=quint8 leaves them (lib/quantizer/weights_quantizer.cc:84-182): one
+  // scale and one zero point per tensor
+  const bool w_u8 = win && win->kind == OP_DEQUANTIZE && win->in[2] && win->in[2]->kind == OP_CONST && numel(win->in[2]->type.shape) == 1 &&
+                    win->in[0]->kind == OP_CONST && (win->in[0]->type.element_type == ODLA_UINT8 || win->in[0]->type.element_type == ODLA_QUINT8) &&
+                    win->in[1]->kind == OP_CONST && numel(win->in[1]->type.shape) == 1;
+  if (is_per_tensor_dq(xin) && (w_s8 || w_u8) && channel_last && (root->kind == OP_CONV ? root->ia[1] == 1 : root->type.shape.size == 2)) {
     f->int8 = true;
     f->x = xin->in[0];
     f->x_scale = xin->in[1];
     f->w = win->in[0];
     f->w_scale = win->in[1];
+    if (w_u8) f->w_zp = win->in[2];
   }
   V cur = root;
   fused_into_[root] = root;
@@ -567,16 +573,30 @@ odla_status Builder::emit_fused(const Item& it) {
   int64_t K = root->kind == OP_CONV ? (root->ia[0] ? root->type.shape.dims[3] : root->type.shape.dims[1])
                                     : root->type.shape.dims[root->type.shape.size - 1];
   Epilogue ep;
+  std::vector<int> wint;   // int8 path: the filter as integers
+  int w_terms = 1;         // ... and how many int8 terms they need
   if (f.int8) {
     auto sx = const_as_f32(f.x_scale), sw = const_as_f32(f.w_scale);
     std::vector<float> m((size_t)K);
     for (int64_t k = 0; k < K; ++k) m[k] = sx[0] * sw[sw.size() == 1 ? 0 : k];
     ep.mul = upload_f32(m);
+    // Integer filter values: int8 as they are, uint8 minus the zero point (a 9-bit range that is split into int8 terms).
+    const int64_t wn = numel(f.w->type.shape);
+    wint.resize((size_t)wn);
+    if (f.w_zp) {
+      const int zp = (int)const_as_f32(f.w_zp)[0];
+      for (int64_t i = 0; i < wn; ++i) wint[(size_t)i] = (int)((const uint8_t*)f.w->host)[i] - zp;
+      int lo = 0, hi = 0;
+      for (int v : wint) { lo = std::min(lo, v); hi = std::max(hi, v); }
+      while (lo < -128 * w_terms || hi > 127 * w_terms) ++w_terms;
+    } else {
+      for (int64_t i = 0; i < wn; ++i) wint[(size_t)i] = ((const int8_t*)f.w->host)[i];
+    }
     // |accumulator| <= 128 * sum |w[k,:]| (activations lie in [-128, 127]); below 2^22 for every output channel the
     // epilogue can convert the accumulators without the conversion pipe.
-    if (f.w->kind == OP_CONST && api_dt(f.w->type.element_type) == DT_S8 && !getenv("ODLA_B200_NO_ACC_SMALL")) {
-      const int8_t* wq = (const int8_t*)f.w->host;
-      const int64_t n = numel(f.w->type.shape);
+    if (f.w->kind == OP_CONST && !getenv("ODLA_B200_NO_ACC_SMALL")) {
+      const int* wq = wint.data();
+      const int64_t n = wn;
       // filters are [.., K] (HWIO) and Gemm weights [Kd, N] or, transposed, [N, Kd]: the output channel is the last
       // axis unless the Gemm's B is transposed
       const bool k_last = !(root->kind == OP_GEMM && root->ia[1] != 0);
@@ -733,10 +753,32 @@ odla_status Builder::emit_fused(const Item& it) {
     }
     if (allow_umma && nhwc && groups == 1 && umma_conv_supported(uc)) {
       // filters HWIO -> [K][R*S*C] so that each output channel's taps are contiguous (K-major B operand)
-      char form[160];
+      char form[256];
       snprintf(form, sizeof(form), "conv_kmajor dt%d w%d gq%d wc%d cp%d lp%d pl%d sw%d Cp%d", in_dt, widened ? 1 : 0, wide_gq, wide_c, wide_cp, wide_lp, g.pad_l, g.stride_w, Cp);
+      if (w_terms > 1) {
+        if (widened || Cp != g.C) return fail(ODLA_UNSUPPORTED_OP, "'" + root->name + "': asymmetric uint8 filters over fewer than 32 bytes of channels");
+        uc.w_terms = w_terms;
+        snprintf(form + strlen(form), sizeof(form) - strlen(form), " terms%d", w_terms);
+      }
+      if (f.w_zp) snprintf(form + strlen(form), sizeof(form) - strlen(form), " zp%d", (int)const_as_f32(f.w_zp)[0]);
       auto wb = prepared(f.w, form, [&] {
-        auto wf = const_as_f32(f.w);
+        if (w_terms > 1) {
+          // [K][terms * R*S][C] int8: term t holds clamp(remainder, -128, 127) of every filter value
+          const int64_t rs = (int64_t)g.R * g.S;
+          std::vector<uint8_t> out((size_t)(K * w_terms * rs * g.C));
+          for (int64_t t2 = 0; t2 < rs; ++t2)
+            for (int64_t c = 0; c < g.C; ++c)
+              for (int64_t k = 0; k < K; ++k) {
+                int rem = wint[(size_t)((t2 * g.C + c) * K + k)];
+                for (int t = 0; t < w_terms; ++t) {
+                  const int part = std::max(-128, std::min(127, rem));
+                  rem -= part;
+                  out[(size_t)(((k * w_terms + t) * rs + t2) * g.C + c)] = (uint8_t)(int8_t)part;
+                }
+              }
+          return out;
+        }
+        auto wf = f.int8 ? std::vector<float>(wint.begin(), wint.end()) : const_as_f32(f.w);
         int64_t rs = (int64_t)g.R * g.S;
         std::vector<float> w2;
         if (widened) {
@@ -783,6 +825,7 @@ odla_status Builder::emit_fused(const Item& it) {
       }
       return ODLA_SUCCESS;
     }
+    if (f.w_zp) return fail(ODLA_UNSUPPORTED_OP, "'" + root->name + "': asymmetric uint8 filters need the tensor-core path (NHWC, one group, 16-byte channel rows)");
     const void* wd = const_dev(f.w, in_dt);
     if (!wd) return err_status_;
     if (nhwc) {
@@ -874,8 +917,24 @@ odla_status Builder::emit_fused(const Item& it) {
     UmmaConv uc{1, 1, (int)Mt, (int)Kd, (int)N, 1, 1, 1, (int)Mt, 1, 1, 0, 0, in_dt};
     if (store_direct) set_store(uc);
     if (Mt < (1ll << 31) && umma_conv_supported(uc)) {
-      auto wb = prepared(f.w, std::string("gemm_kmajor dt") + std::to_string(in_dt) + (tb ? " t" : " n"), [&] {
-        auto wf = const_as_f32(f.w);
+      if (w_terms > 1) uc.w_terms = w_terms;
+      auto wb = prepared(f.w, std::string("gemm_kmajor dt") + std::to_string(in_dt) + (tb ? " t" : " n") + " terms" + std::to_string(w_terms) +
+                                  (f.w_zp ? " zp" + std::to_string((int)const_as_f32(f.w_zp)[0]) : std::string()), [&] {
+        if (w_terms > 1) {
+          // [N][terms][Kd] int8
+          std::vector<uint8_t> out((size_t)(N * w_terms * Kd));
+          for (int64_t n = 0; n < N; ++n)
+            for (int64_t k = 0; k < Kd; ++k) {
+              int rem = wint[(size_t)(tb ? n * Kd + k : k * N + n)];
+              for (int t = 0; t < w_terms; ++t) {
+                const int part = std::max(-128, std::min(127, rem));
+                rem -= part;
+                out[(size_t)((n * w_terms + t) * Kd + k)] = (uint8_t)(int8_t)part;
+              }
+            }
+          return out;
+        }
+        auto wf = f.int8 ? std::vector<float>(wint.begin(), wint.end()) : const_as_f32(f.w);
         std::vector<float> w2;
         if (tb) w2 = wf;  // already [N][K]
         else { w2.resize(wf.size()); for (int64_t k = 0; k < Kd; ++k) for (int64_t n = 0; n < N; ++n) w2[(size_t)(n * Kd + k)] = wf[(size_t)(k * N + n)]; }
@@ -923,6 +982,7 @@ odla_status Builder::emit_fused(const Item& it) {
       return ODLA_SUCCESS;
     }
   }
+  if (f.w_zp) return fail(ODLA_UNSUPPORTED_OP, "'" + root->name + "': asymmetric uint8 weights need the tensor-core path (rows of 16-byte multiples)");
   GemmGeom g{};
   g.batch = batch; g.M = M; g.N = N; g.K = Kd;
   g.a_row = ta ? 1 : ac; g.a_col = ta ? ac : 1; g.a_batch = ar * ac;

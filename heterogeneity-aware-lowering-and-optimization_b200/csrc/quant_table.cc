@@ -11,6 +11,7 @@
 // constant itself.  For every convolution (channels-last, one group) and rank-2 Gemm whose data
 // operand has a record and whose weights are a float constant, the rewrite inserts
 //     x -> Quantize(s_x) -> Dequantize(s_x) -> op      and      W -> Dequantize(int8 W_q, s_w[k]) -> op
+// (and, for weights the compiler already quantised to asymmetric uint8, W_u -> Dequantize(W_u, s_w, zp_w) -> op),
 // which is exactly what a hand-written QDQ model holds; everything downstream (operand absorption,
 // requantising epilogues, bit-exact int32 accumulation) is the planner's existing int8 path.
 #include <cmath>
@@ -23,7 +24,7 @@ namespace b200 {
 namespace {
 
 struct Range {
-  float mn = 0.f, mx = 0.f, scale = 0.f;
+  float mn = 0.f, mx = 0.f, scale = 0.f, offset = 0.f;
   bool have = false;
   std::vector<std::pair<float, float>> ch;  // per-channel (min, max)
   std::vector<bool> ch_have;
@@ -48,7 +49,7 @@ odla_status apply_quant_table(_odla_computation* c) {
     Range& r = table[id];
     if (rec.ch_idx < 0) {
       r.have = true;
-      r.mn = rec.min; r.mx = rec.max; r.scale = rec.scale;
+      r.mn = rec.min; r.mx = rec.max; r.scale = rec.scale; r.offset = rec.offset;
     } else {
       if ((size_t)rec.ch_idx >= r.ch.size()) { r.ch.resize((size_t)rec.ch_idx + 1); r.ch_have.resize((size_t)rec.ch_idx + 1, false); }
       r.ch[(size_t)rec.ch_idx] = {rec.min, rec.max};
@@ -89,6 +90,49 @@ odla_status apply_quant_table(_odla_computation* c) {
     bool gemm = v->kind == OP_GEMM && v->type.shape.size == 2 && v->ia.size() >= 2 && v->ia[0] == 0;
     odla_value x = (conv || gemm) ? v->in[0] : nullptr, w = (conv || gemm) ? v->in[1] : nullptr;
     auto xr = x ? table.find(x->name) : table.end();
+    // ---- weights already quantised by the compiler: -quantize-weights=quint8 turns every float constant into uint8
+    // with one scale and one zero point (lib/quantizer/weights_quantizer.cc:84-182: q = clamp(round(w / scale + zp), 0,
+    // 255)) and the bias of a convolution / Gemm into int32 with scale s_in * s_w (:139-172); the table carries those
+    // scales.  The filter becomes Dequantize(uint8, scale, zp), the bias a float constant b_q * (s_in * s_w).
+    auto wr8 = w ? table.find(w->name) : table.end();
+    if ((conv || gemm) && x && w && !v->poison && x->kind != OP_CONST && is_float_type(x->type.element_type) && w->kind == OP_CONST &&
+        (w->type.element_type == ODLA_UINT8 || w->type.element_type == ODLA_QUINT8) && w->host && xr != table.end() && xr->second.have &&
+        wr8 != table.end() && wr8->second.have && wr8->second.scale > 0.f) {
+      odla_value xdq;
+      auto hit = dq_of.find(x);
+      if (hit != dq_of.end()) xdq = hit->second;
+      else {
+        float sx = symmetric_scale(xr->second.mn, xr->second.mx, xr->second.scale);
+        odla_value sc = scalar_const(x->name + "_qt_scale", sx);
+        int64_t last = x->type.shape.size - 1;
+        odla_value q = make(x->name + "_qt_q", OP_QUANTIZE, ODLA_INT8, x->type.shape, {x, sc, nullptr}, {last});
+        xdq = make(x->name + "_qt_dq", OP_DEQUANTIZE, x->type.element_type, x->type.shape, {q, sc, nullptr}, {last});
+        dq_of[x] = xdq;
+      }
+      odla_value wsc = scalar_const(w->name + "_qt_scale", wr8->second.scale);
+      odla_value_shape one{};
+      one.size = 1; one.dims[0] = 1;
+      odla_value wzp = make(w->name + "_qt_zp", OP_CONST, ODLA_INT32, one, {}, {});
+      const int32_t zp = (int32_t)std::nearbyintf(wr8->second.offset);
+      wzp->host = own(&zp, sizeof(zp));
+      odla_value wdq = make(w->name + "_qt_dq", OP_DEQUANTIZE, ODLA_FLOAT32, w->type.shape, {w, wsc, wzp}, {0});
+      v->in[0] = xdq;
+      v->in[1] = wdq;
+      odla_value b = v->in.size() > 2 ? v->in[2] : nullptr;
+      if (b && b->kind == OP_CONST && (b->type.element_type == ODLA_INT32 || b->type.element_type == ODLA_QINT32) && b->host) {
+        // the scales the compiler divided the bias by are the table's own records of the two operands
+        const float sb = xr->second.scale * wr8->second.scale;
+        const int64_t nb = numel(b->type.shape);
+        std::vector<float> bf((size_t)nb);
+        for (int64_t i = 0; i < nb; ++i) bf[(size_t)i] = (float)((const int32_t*)b->host)[i] * sb;
+        odla_value bc = make(b->name + "_qt_f", OP_CONST, ODLA_FLOAT32, b->type.shape, {}, {});
+        bc->host = own(bf.data(), bf.size() * sizeof(float));
+        v->in[2] = bc;
+      }
+      ++rewritten;
+      out.push_back(std::move(up));
+      continue;
+    }
     if ((conv || gemm) && x && w && !v->poison && x->kind != OP_CONST && is_float_type(x->type.element_type) && w->kind == OP_CONST &&
         w->type.element_type == ODLA_FLOAT32 && w->host && xr != table.end() && xr->second.have) {
       // ---- activation ----

@@ -86,6 +86,50 @@ void ora_conv2d_s8(int32_t* out, const int8_t* in, const int8_t* ker, int64_t N,
   free(acc);
 }
 
+/* The same sum with 16-bit filter values: a uint8 filter minus its zero point lies in [-255, 255].  The asymmetric
+ * uint8 weights are what lib/quantizer/weights_quantizer.cc:84-182 produces for -quantize-weights=quint8
+ * (q = clamp(round(w / scale + zp), 0, 255)); a product with such a filter is sum x_q * (W_u - zp), exactly, in int32. */
+void ora_conv2d_s8_w16(int32_t* out, const int8_t* in, const int16_t* ker, int64_t N, int64_t H,
+                       int64_t W, int64_t C, int64_t P, int64_t Q, int64_t K, int64_t R, int64_t S,
+                       int64_t sh, int64_t sw, int64_t pt, int64_t pl, int64_t row_begin,
+                       int64_t row_end) {
+  (void)N;
+  int32_t* acc = (int32_t*)malloc(sizeof(int32_t) * (size_t)K);
+  for (int64_t row = row_begin; row < row_end; ++row) {
+    int64_t b = row / P, i = row % P;
+    for (int64_t j = 0; j < Q; ++j) {
+      memset(acc, 0, sizeof(int32_t) * (size_t)K);
+      for (int64_t m = 0; m < R; ++m)
+        for (int64_t n = 0; n < S; ++n) {
+          int64_t h = i * sh - pt + m, w = j * sw - pl + n;
+          if (h < 0 || h >= H || w < 0 || w >= W) continue;
+          const int8_t* px = in + ((b * H + h) * W + w) * C;
+          for (int64_t k = 0; k < C; ++k) {
+            int32_t v = px[k];
+            if (!v) continue;
+            const int16_t* kr = ker + ((m * S + n) * C + k) * K;
+            for (int64_t c = 0; c < K; ++c) acc[c] += v * (int32_t)kr[c];
+          }
+        }
+      memcpy(out + ((b * P + i) * Q + j) * K, acc, sizeof(int32_t) * (size_t)K);
+    }
+  }
+  free(acc);
+}
+void ora_matmul_s8_w16(int32_t* out, const int8_t* A, const int16_t* B, int64_t M, int64_t N,
+                       int64_t Kd, int ta, int tb) {
+  for (int64_t i = 0; i < M; ++i)
+    for (int64_t j = 0; j < N; ++j) {
+      int32_t s = 0;
+      for (int64_t k = 0; k < Kd; ++k) {
+        int32_t a = ta ? A[k * M + i] : A[i * Kd + k];
+        int32_t b = tb ? B[j * Kd + k] : B[k * N + j];
+        s += a * b;
+      }
+      out[i * N + j] = s;
+    }
+}
+
 /* -------------------------------------------------------------------- GEMM ---- */
 /* out[M,N] = op(A) op(B), k ascending, as runtime/generic/math/matmul.cc:22-59. */
 void ora_matmul_f32(float* out, const float* A, const float* B, int64_t M, int64_t N, int64_t Kd,

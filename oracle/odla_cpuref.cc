@@ -16,8 +16,9 @@
 //
 // int8 rule (this build's definition; the reference has no int8 execution): a Conv or Gemm
 // whose data operand is odla_Dequantize(int8, per-tensor scale) and whose weight operand is
-// odla_Dequantize(int8, per-tensor or per-output-channel scale), both without zero point, is
-// computed exactly in integers and scaled once: out = float(acc_int32) * (s_in * s_w[k]), the
+// odla_Dequantize(int8, per-tensor or per-output-channel scale), both without zero point -- or
+// odla_Dequantize(uint8, per-tensor scale, per-tensor zero point), the asymmetric weights of
+// -quantize-weights=quint8, taken as W_u - zp -- is computed exactly in integers and scaled once: out = float(acc_int32) * (s_in * s_w[k]), the
 // product s_in*s_w[k] rounded to fp32 first.  Everything after that (bias add, residual add,
 // relu) is ordinary node-by-node fp32 arithmetic.  A value "comes from accumulators" if it is such a
 // Conv/Gemm result or an element-wise (unary / binary / reshape) function of one; odla_Quantize of
@@ -49,6 +50,9 @@ void ora_conv2d_s8(int32_t*, const int8_t*, const int8_t*, int64_t, int64_t, int
 void ora_matmul_f32(float*, const float*, const float*, int64_t, int64_t, int64_t, int, int);
 void ora_gemm_finish_f32(float*, const float*, int64_t, int64_t, int64_t, float, float);
 void ora_matmul_s8(int32_t*, const int8_t*, const int8_t*, int64_t, int64_t, int64_t, int, int);
+void ora_conv2d_s8_w16(int32_t*, const int8_t*, const int16_t*, int64_t, int64_t, int64_t, int64_t,
+                       int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t);
+void ora_matmul_s8_w16(int32_t*, const int8_t*, const int16_t*, int64_t, int64_t, int64_t, int, int);
 void ora_maxpool_f32(float*, const float*, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t,
                      int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int);
 void ora_maxpool_s8(int8_t*, const int8_t*, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t,
@@ -194,6 +198,7 @@ struct _odla_value {
   bool is_arg = false, is_const = false;
   // producer info used by the int8 rule
   odla_value dq_src = nullptr, dq_scale = nullptr; bool dq_zp = false; int dq_axis = -1;
+  odla_value dq_zp_value = nullptr;   // the zero-point operand itself (asymmetric uint8 weights)
   std::vector<int32_t> acc;        // int32 accumulators of the last int8 Conv/Gemm (for tests)
   bool from_acc = false;           // computed from int32 accumulators through element-wise ops only
   float* f() { return (float*)buf.data(); }
@@ -321,6 +326,17 @@ odla_value odla_CreateArgument(const odla_value_type t, const odla_value_id id) 
 odla_value odla_CreateConstant(const odla_value_type t, const odla_void* p, const odla_value_id id) {
   odla_value v = new_value(t.element_type, t.shape, id); v->is_const = true; load_external(v, p); return v; }
 
+// Asymmetric uint8 weights (per-tensor scale and zero point): the integer rule applies to W_u - zp.
+static bool is_u8_weight(odla_value w) {
+  return w->dq_src && w->dq_zp && w->dq_zp_value && w->dq_src->store == ODLA_UINT8 && w->dq_scale->n() == 1 && w->dq_zp_value->n() == 1;
+}
+static std::vector<int16_t> u8_weight_minus_zp(odla_value w) {
+  odla_value zp = w->dq_zp_value;
+  int32_t z = zp->store == ODLA_INT8 ? ((int8_t*)zp->buf.data())[0] : zp->store == ODLA_UINT8 ? ((uint8_t*)zp->buf.data())[0] : ((int32_t*)zp->buf.data())[0];
+  std::vector<int16_t> r((size_t)w->dq_src->n());
+  for (size_t i = 0; i < r.size(); ++i) r[i] = (int16_t)((int32_t)((uint8_t*)w->dq_src->buf.data())[i] - z);
+  return r;
+}
 // ---- convolution: argument meaning as ODLA/include/ODLA/ops/odla_ops_nn.h:213-219 ----
 odla_value odla_Conv(odla_value in, odla_memory_layout il, odla_uint32 group, odla_value ker, odla_memory_layout kl,
                      const odla_uint32* st, const odla_uint32* dil, const odla_uint32* pf, const odla_uint32* pb,
@@ -336,15 +352,19 @@ odla_value odla_Conv(odla_value in, odla_memory_layout il, odla_uint32 group, od
   int64_t P = nhwc ? od.dims[1] : od.dims[2], Q = nhwc ? od.dims[2] : od.dims[3];
   int64_t sh = st[0], sw = st[1], pt = pf[0], pl = pf[1], g = group ? group : 1;
   odla_value out = new_value(ODLA_FLOAT32, od, id);
-  bool int_path = in->dq_src && ker->dq_src && !in->dq_zp && !ker->dq_zp && in->dq_src->store == ODLA_INT8 &&
-                  ker->dq_src->store == ODLA_INT8 && in->dq_scale->n() == 1 && nhwc && g == 1;
+  const bool u8w = is_u8_weight(ker);
+  bool int_path = in->dq_src && ker->dq_src && !in->dq_zp && (u8w || (!ker->dq_zp && ker->dq_src->store == ODLA_INT8)) && in->dq_src->store == ODLA_INT8 &&
+                  in->dq_scale->n() == 1 && nhwc && g == 1;
   if (int_path) {
     odla_value xq = in->dq_src, wq = ker->dq_src, sx = in->dq_scale, sw_ = ker->dq_scale;
     out->from_acc = true;
     g_comp->ops.push_back([=] {
       out->acc.resize((size_t)out->n());
+      std::vector<int16_t> w16;
+      if (u8w) w16 = u8_weight_minus_zp(ker);
       parallel_for(N * P, [&](int64_t b, int64_t e) {
-        ora_conv2d_s8(out->acc.data(), (int8_t*)xq->buf.data(), (int8_t*)wq->buf.data(), N, H, W, C, P, Q, K, R, S, sh, sw, pt, pl, b, e); });
+        if (u8w) ora_conv2d_s8_w16(out->acc.data(), (int8_t*)xq->buf.data(), w16.data(), N, H, W, C, P, Q, K, R, S, sh, sw, pt, pl, b, e);
+        else ora_conv2d_s8(out->acc.data(), (int8_t*)xq->buf.data(), (int8_t*)wq->buf.data(), N, H, W, C, P, Q, K, R, S, sh, sw, pt, pl, b, e); });
       for (int64_t i = 0; i < out->n(); ++i) {
         float m = sx->f()[0] * sw_->f()[sw_->n() == 1 ? 0 : i % K];
         float v = (float)out->acc[i] * m;
@@ -383,14 +403,16 @@ odla_value odla_Gemm(odla_value A, odla_bool ta, odla_value B, odla_bool tb, odl
   if (bbatch != batch && bbatch != 1) return fail("Gemm: batch dimensions differ");
   odla_value out = new_value(ODLA_FLOAT32, od, id);
   if (out->n() != batch * M * N) return fail("Gemm: output_dims do not match operands");
-  bool int_path = A->dq_src && B->dq_src && !A->dq_zp && !B->dq_zp && A->dq_src->store == ODLA_INT8 &&
-                  B->dq_src->store == ODLA_INT8 && A->dq_scale->n() == 1 && batch == 1;
+  const bool u8w = is_u8_weight(B);
+  bool int_path = A->dq_src && B->dq_src && !A->dq_zp && (u8w || (!B->dq_zp && B->dq_src->store == ODLA_INT8)) && A->dq_src->store == ODLA_INT8 &&
+                  A->dq_scale->n() == 1 && batch == 1;
   if (int_path) {
     odla_value aq = A->dq_src, bq = B->dq_src, sa = A->dq_scale, sb = B->dq_scale;
     out->from_acc = true;
     g_comp->ops.push_back([=] {
       out->acc.resize((size_t)out->n());
-      ora_matmul_s8(out->acc.data(), (int8_t*)aq->buf.data(), (int8_t*)bq->buf.data(), M, N, Kd, ta, tb);
+      if (u8w) { auto w16 = u8_weight_minus_zp(B); ora_matmul_s8_w16(out->acc.data(), (int8_t*)aq->buf.data(), w16.data(), M, N, Kd, ta, tb); }
+      else ora_matmul_s8(out->acc.data(), (int8_t*)aq->buf.data(), (int8_t*)bq->buf.data(), M, N, Kd, ta, tb);
       for (int64_t i = 0; i < out->n(); ++i) {
         float m = sa->f()[0] * sb->f()[sb->n() == 1 ? 0 : i % N];
         out->f()[i] = (float)out->acc[i] * m;
@@ -577,7 +599,7 @@ odla_value odla_Dequantize(odla_value in, odla_value scale, odla_value zp, odla_
   int64_t outer, adim, inner; int per_axis;
   axis_split(in->shape(), axis, scale->n(), &outer, &adim, &inner, &per_axis);
   odla_value out = new_value(ODLA_FLOAT32, in->shape(), id);
-  out->dq_src = in; out->dq_scale = scale; out->dq_zp = zp != nullptr; out->dq_axis = axis;
+  out->dq_src = in; out->dq_scale = scale; out->dq_zp = zp != nullptr; out->dq_axis = axis; out->dq_zp_value = zp;
   g_comp->ops.push_back([=] {
     std::vector<int32_t> z;
     if (zp) { z.resize((size_t)zp->n()); for (int64_t i = 0; i < zp->n(); ++i) z[i] = zp->store == ODLA_INT8 ? ((int8_t*)zp->buf.data())[i] : zp->store == ODLA_UINT8 ? ((uint8_t*)zp->buf.data())[i] : ((int32_t*)zp->buf.data())[i]; }

@@ -222,3 +222,65 @@ def test_resnet50_calibrated_on_the_gpu_runs_int8(odla, gpu_lib, models):
     assert desc.count("_qt_q") + desc.count("quantize") >= 16
     assert np.abs(prob - ref_prob).max() < 0.1
     assert (prob.argmax(1) == ref_prob.argmax(1)).mean() >= 0.75
+
+
+def _quint8(w):
+    """A float constant as -quantize-weights=quint8 leaves it (lib/quantizer/weights_quantizer.cc:84-182 of the reference):
+    one scale and one zero point per tensor, q = clamp(round(w / scale + zp), 0, 255)."""
+    mn, mx = min(float(w.min()), 0.0), float(w.max())
+    scale = np.float32((mx - mn) / 255.0)
+    zp = float(np.clip(np.round(0 - mn / scale), 0, 255))
+    q = np.clip(np.round(w * np.float32(1.0 / scale) + zp), 0, 255).astype(np.uint8)
+    return q, scale, int(zp)
+
+
+@pytest.mark.parametrize("skew", [0.0, 0.6, -0.9])
+def test_asymmetric_uint8_weights_conv_and_gemm_are_bit_exact(odla, gpu_lib, ref, skew):
+    """uint8 weights with a zero point (and an int32 bias quantised with s_in * s_w), handed over as the compiler emits
+    them -- QUINT8 / INT32 constants plus table records -- against the oracle's hand-written form
+    Dequantize(uint8, scale, zp): int32 accumulators of sum x_q * (W_u - zp) and the requantised int8 results bit-equal.
+    skew moves the zero point away from 128, which is what needs more than one int8 filter term."""
+    rng = np.random.default_rng(int(abs(skew) * 10) + 1)
+    F32, I8, U8, I32, NHWC, SIO = odla.FLOAT32, odla.INT8, odla.UINT8, odla.INT32, odla.CHANNELS_LAST, odla.SIO
+    x = rng.standard_normal((2, 12, 12, 32)).astype(np.float32)
+    w1 = (rng.standard_normal((3, 3, 32, 64)) * 0.1 + skew * 0.1).astype(np.float32)
+    w2 = (rng.standard_normal((64, 48)) * 0.1 - skew * 0.1).astype(np.float32)
+    (q1, s1, z1), (q2, s2, z2) = _quint8(w1), _quint8(w2)
+    sx, sy = np.float32(np.abs(x).max() / 127), np.float32(0.08)
+    b1 = np.round(rng.standard_normal(64) * 0.2 / (sx * s1)).astype(np.int32)           # int32 bias, scale s_in * s_w
+
+    def net(g, table):
+        xa = g.Argument("x", x.shape, F32)
+        if table:
+            xin, win, bias = xa, g.Constant("w1", q1), g.Constant("b1", b1)
+        else:
+            s = g.Constant("x_s", np.array([sx], np.float32))
+            xin = g.Dequantize(g.Quantize(xa, s, None, 0, I8, "x_q"), s, None, 0, F32, "x_dq")
+            win = g.Dequantize(g.Constant("w1_q", q1), g.Constant("w1_s", np.array([s1], np.float32)), g.Constant("w1_z", np.array([z1], np.int32)), 0, F32, "w1_dq")
+            bias = g.Constant("b1_f", (b1.astype(np.float32) * np.float32(sx * s1)).astype(np.float32))
+        y = g.Conv(xin, NHWC, 1, win, SIO, (1, 1), (1, 1), (1, 1), (1, 1), bias, (2, 12, 12, 64), "c1")
+        r = g.Relu(y, "r1")
+        if table:
+            flat, w2in = g.Reshape(r, (288, 64), "flat"), g.Constant("w2", q2)
+        else:
+            s = g.Constant("y_s", np.array([sy], np.float32))
+            rq = g.Quantize(g.Reshape(r, (288, 64), "flat"), s, None, 0, I8, "r1_q")     # the Gemm reads Dequantize directly: the integer rule applies
+            g.Output(rq)
+            flat = g.Dequantize(rq, s, None, 0, F32, "r1_dq")
+            w2in = g.Dequantize(g.Constant("w2_q", q2), g.Constant("w2_s", np.array([s2], np.float32)), g.Constant("w2_z", np.array([z2], np.int32)), 0, F32, "w2_dq")
+        g.Output(g.Gemm(flat, False, w2in, False, 1.0, 0.0, None, (288, 48), "fc"))
+        return g
+
+    g = net(odla.Graph(gpu_lib, "u8"), True)
+    # activation records that give the scale itself (min = max = 0), weight records with the compiler's scale and zero point
+    g.set_quant_table([("x", -1, float(sx), 0.0, 0.0, 0.0), ("w1_", -1, float(s1), float(z1), 0.0, 0.0), ("w2_", -1, float(s2), float(z2), 0.0, 0.0),
+                       ("flat", -1, float(sy), 0.0, 0.0, 0.0)])
+    got = g.run({"x": x})["fc"]
+    desc = g.describe(first_gpu_only=True)
+    g.close()
+    h = net(odla.Graph(ref, "u8_ref"), False)
+    want = h.run({"x": x})
+    h.close()
+    assert "conv_umma" in desc and "gemm_umma" in desc
+    assert np.array_equal(got, want["fc"]), float(np.abs(got - want["fc"]).max())
+    assert int(np.abs(want["r1_q"].astype(int)).max()) > 20
