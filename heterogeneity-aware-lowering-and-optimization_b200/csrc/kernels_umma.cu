@@ -51,7 +51,7 @@ template <bool STAGED> struct EpiCfg {
   static constexpr int kThreads = 32 * (4 + kWarps);
 };
 constexpr int kMaxRing = 8;
-constexpr uint32_t kSpinLimit = 1u << 18;  // attempts of up to 4 us (plus a short sleep) each before a wait gives up: about a second
+constexpr uint32_t kSpinLimit = 1u << 18;  // default number of attempts (up to 4 us each) before a wait gives up: about a second
 
 struct UmmaParams {
   int M_total, K_out, C, R, S, P, Q;
@@ -81,6 +81,8 @@ struct UmmaParams {
   int epi_mode;        // kernel variant: 0 direct, 1 staged straight-line form, 2 staged general form
   int fast_variant;    // mode 1: accumulator conversion (0 fp32, 1 int32 by conversion, 2 int32 by integer add) * 2 + residual
   int tmem_cols;
+  uint32_t spin_limit;  // attempts before a bounded wait gives up
+  int test_skip_stage;  // test hook: the producer of CTA 0 leaves the last stage of its first tile unarmed, so the MMA lane's wait runs out
   void* y;
   int* status;
   Epilogue ep;
@@ -123,24 +125,24 @@ __device__ __forceinline__ bool mbar_try_wait_suspend(uint64_t* bar, uint32_t pa
   return ok != 0;
 }
 // Bounded wait.  Returns false when the limit expired or another role already aborted.
-__device__ __forceinline__ bool mbar_wait_impl(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code);
+__device__ __forceinline__ bool mbar_wait_impl(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code, uint32_t limit);
 // Debug builds add up, per wait site (and per epilogue group), the cycles block 0 spent waiting.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code, uint32_t limit) {
 #ifdef UMMA_DEBUG_TS
   const long long t0 = clock64();
-  const bool ok = mbar_wait_impl(bar, parity, abort_flag, status, code);
+  const bool ok = mbar_wait_impl(bar, parity, abort_flag, status, code, limit);
   const int warp = threadIdx.x >> 5;
   const bool epi = code == 4 || code == 6;
   if (blockIdx.x == 0 && status && (!epi || ((threadIdx.x & 31) == 0 && ((warp - 2) & 3) == 0)))
     atomicAdd((unsigned long long*)status + 32 + code * 4 + (epi ? (warp - 2) >> 2 : 0), (unsigned long long)(clock64() - t0));
   return ok;
 #else
-  return mbar_wait_impl(bar, parity, abort_flag, status, code);
+  return mbar_wait_impl(bar, parity, abort_flag, status, code, limit);
 #endif
 }
-__device__ __forceinline__ bool mbar_wait_impl(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+__device__ __forceinline__ bool mbar_wait_impl(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code, uint32_t limit) {
   if (mbar_try_wait(bar, parity)) return true;
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+  for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait_suspend(bar, parity, 4000u)) return true;
     if ((i & 63) == 63 && *abort_flag) return false;
   }
@@ -868,7 +870,7 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         int tap = 0, fr = 0, fs = 0, c0 = 0, left = p.num_kb;
         const int bidx = p.rows_per_batch ? m0 / p.rows_per_batch : 0;
         for (int it = 0; it < p.num_it; ++it) {
-          if (!mbar_wait(empty_bar + s, ph ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
+          if (!mbar_wait(empty_bar + s, ph ^ 1, abort_flag, p.status, 1, p.spin_limit)) { ok = false; break; }
           const int nb = left < p.bps ? left : p.bps;
           left -= nb;
           uint8_t* sa = smem + (size_t)s * stage_bytes;
@@ -896,11 +898,16 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (++s == p.stages) { s = 0; ph ^= 1; }
             continue;
           }
-          mbar_expect_tx(fb, (uint32_t)nb * (a_box + b_box));
+          // Test hook (never set by the planner): this stage is neither armed nor loaded, so its barrier can never
+          // complete and the MMA lane's bounded wait reports a timeout; nothing faults and nothing spins for ever.
+          const bool skip = p.test_skip_stage && blockIdx.x == 0 && tile == tile_first && it == p.num_it - 1;
+          if (!skip) mbar_expect_tx(fb, (uint32_t)nb * (a_box + b_box));
           for (int j = 0; j < nb; ++j) {
-            if (p.im2col) tma_load_im2col_4d(sa, &tmA, fb, c0, w0, h0, img, (uint16_t)fs, (uint16_t)fr);
+            if (skip) {}
+            else if (p.im2col) tma_load_im2col_4d(sa, &tmA, fb, c0, w0, h0, img, (uint16_t)fs, (uint16_t)fr);
             else tma_load_2d(sa, &tmA, fb, c0, m0);
-            if (p.rows_per_batch) tma_load_3d(sb, &tmB, fb, c0, n0, bidx);
+            if (skip) {}
+            else if (p.rows_per_batch) tma_load_3d(sb, &tmB, fb, c0, n0, bidx);
             else tma_load_3d(sb, &tmB, fb, c0, tap, n0);
             sa += a_box;
             sb += b_box;
@@ -932,13 +939,13 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int ksteps = p.kb_bytes >> 5;  // 32 bytes of K per instruction
       for (int tile = tile_first; tile < p.total_tiles && ok; tile += tile_step, ++tcount) {
         const uint32_t acc = tcount & 1, acc_ph = (tcount >> 1) & 1;
-        if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1, abort_flag, p.status, 2)) { ok = false; break; }
+        if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1, abort_flag, p.status, 2, p.spin_limit)) { ok = false; break; }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * (uint32_t)p.BN;
         int left = p.num_kb;
         uint32_t accum = 0;
         for (int it = 0; it < p.num_it; ++it) {
-          if (!mbar_wait(full_bar + s, ph, abort_flag, p.status, 3)) { ok = false; break; }
+          if (!mbar_wait(full_bar + s, ph, abort_flag, p.status, 3, p.spin_limit)) { ok = false; break; }
           tc_fence_after();
           const int nb = left < p.bps ? left : p.bps;
           left -= nb;
@@ -978,7 +985,7 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         for (int bx = 0; bx < p.stage_boxes; ++bx) {
           const int x0 = n0 + bx * cols_per_box;
           if (x0 >= p.K_out) break;
-          if (!mbar_wait(box_free + slot, ph ^ 1, abort_flag, p.status, 5)) { ok = false; break; }
+          if (!mbar_wait(box_free + slot, ph ^ 1, abort_flag, p.status, 5, p.spin_limit)) { ok = false; break; }
           if (p.res_tma) {
             mbar_expect_tx(box_full + slot, 16384u);
             tma_load_2d(staging + slot * 16384, &tmR, box_full + slot, x0, m0);
@@ -987,6 +994,12 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           if (++slot == p.ring_boxes) { slot = 0; ph ^= 1; }
         }
+      }
+      if (!ok && p.res_tma) {
+        // residual loads already in flight get a bounded chance to land before shared memory goes away
+        for (int i = 0; i < p.ring_boxes; ++i)
+          for (uint32_t k = 0; k < 4096; ++k)
+            if (mbar_try_wait(&box_full[i], 0) || mbar_try_wait(&box_full[i], 1)) break;
       }
     }
   } else if (warp == kStorerWarp) {
@@ -1009,7 +1022,7 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             mbar_arrive(box_free + prev);
             prev = -1;
           }
-          if (!mbar_wait(box_done + slot, ph, abort_flag, p.status, 7)) { ok = false; break; }
+          if (!mbar_wait(box_done + slot, ph, abort_flag, p.status, 7, p.spin_limit)) { ok = false; break; }
           if (p.store_mode == 0) {
             asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"((uint64_t)&tmY),
                          "r"(staging_u32 + (uint32_t)slot * 16384u), "r"(x0), "r"(m0)
@@ -1064,7 +1077,7 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int tile = tile_first; tile < p.total_tiles && ok; tile += tile_step, ++tcount) {
         const uint32_t acc = tcount & 1, acc_ph = (tcount >> 1) & 1;
         const int n0 = (tile / p.m_tiles) * p.BN;
-        if (!mbar_wait(&tfull_bar[acc], acc_ph, abort_flag, p.status, 4)) { ok = false; break; }
+        if (!mbar_wait(&tfull_bar[acc], acc_ph, abort_flag, p.status, 4, p.spin_limit)) { ok = false; break; }
         tc_fence_after();
         if (tcount == 0 && threadIdx.x == 64) TS(4);
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * (uint32_t)p.BN;
@@ -1074,7 +1087,7 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (p.epi_interleave) { first = bx * chunks_per_box + cgroup; last = min((bx + 1) * chunks_per_box, n_chunks); step = kGroups; }
           else { first = max(ch_lo, bx * chunks_per_box); last = min(ch_hi, (bx + 1) * chunks_per_box); step = 1; }
           if (first < last) {
-            if (!mbar_wait(box_full + slot, ph, abort_flag, p.status, 6)) { ok = false; break; }
+            if (!mbar_wait(box_full + slot, ph, abort_flag, p.status, 6, p.spin_limit)) { ok = false; break; }
             StagePos sp;
             sp.row_addr = staging_u32 + (uint32_t)slot * 16384u + (uint32_t)r_in_tile * 128u;
             sp.rxor = r_in_tile & 7;
@@ -1149,7 +1162,7 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             for (int q = 0; q < 4; ++q) if (q < res_q) pre[i][q] = __ldg(rp + q);
           }
         }
-        if (!mbar_wait(&tfull_bar[acc], acc_ph, abort_flag, p.status, 4)) { ok = false; break; }
+        if (!mbar_wait(&tfull_bar[acc], acc_ph, abort_flag, p.status, 4, p.spin_limit)) { ok = false; break; }
         tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * (uint32_t)p.BN;
 #pragma unroll
@@ -1371,6 +1384,11 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
   const uint32_t sbo = (uint32_t)(8 * p.kb_bytes) >> 4;                             // 8-row group pitch, 16-byte units
   p.desc_hi = sbo | (1u << 14) | (layout << 29);                                    // bits 32-45 SBO, 46-47 version 1, 61-63 layout
   p.y = y; p.status = status; p.ep = ep;
+  p.spin_limit = kSpinLimit;
+  p.test_skip_stage = 0;
+  // Test hooks for the time-out path (tests/test_conv_umma_gpu.py): a short limit and one deliberately unarmed stage.
+  if (const char* e = getenv("ODLA_B200_TEST_SPIN_LIMIT")) { const long v = atol(e); if (v >= 64 && v <= (1l << 18)) p.spin_limit = (uint32_t)v; }
+  if (getenv("ODLA_B200_TEST_SKIP_STAGE") && !p.pair) p.test_skip_stage = 1;
   L->grid = p.pair ? (2 * p.total_tiles < (sms & ~1) ? 2 * p.total_tiles : (sms & ~1)) : (p.total_tiles < sms ? p.total_tiles : sms);
   L->smem = (size_t)p.stages * stage_bytes + (size_t)p.ring_boxes * 16384 + 1024 /*alignment slack*/ + 1024 /*barriers*/;
   if (L->smem > 227 * 1024) { delete L; return nullptr; }

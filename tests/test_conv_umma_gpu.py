@@ -113,3 +113,53 @@ def test_conv_umma_rejects_what_tma_cannot_address(odla, gpu_lib):
                       alpha=0, res_scale=1, out_scale=1)
     x = torch.zeros(8 * 8 * 3, dtype=torch.float16, device="cuda")
     assert gpu_lib.b200_conv_umma(C.byref(d), x.data_ptr(), x.data_ptr(), None, None, None, x.data_ptr(), None) == -1   # 3 channels: rows are not 16-byte multiples
+
+
+def test_a_bounded_wait_that_runs_out_reports_a_timeout_and_the_next_launch_is_correct(odla, gpu_lib, monkeypatch):
+    """The failure path of the tensor-core kernel, without faulting anything: a test hook makes the producer of one
+    CTA leave a pipeline stage unarmed, the MMA lane's wait on that stage gives up after a short limit (a few hundred
+    attempts instead of ~2^18), the CTA raises its abort flag, every role falls through to the common exit (tensor
+    memory released, copies drained) and the entry point returns -3 -- the code odla_ExecuteComputation turns into
+    ODLA_TIMEOUT.  The context stays usable: the same launch without the hook then gives the exact result."""
+    N, H, W, Cc, K, R = 2, 14, 14, 64, 64, 3
+    rng = np.random.default_rng(4)
+    x = rng.integers(-128, 128, (N, H, W, Cc), dtype=np.int8)
+    w = rng.integers(-127, 128, (K, R * R * Cc), dtype=np.int8)
+    xt, wt = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda()
+    y = torch.zeros((N, H, W, K), dtype=torch.int32, device="cuda")
+    d = odla.ConvDesc(n=N, h=H, w=W, c=Cc, k=K, r=R, s=R, stride_h=1, stride_w=1, pad_top=1, pad_left=1, p=H, q=W, dtype=2, out_kind=3,
+                      res_kind=0, act=0, alpha=0, res_scale=1, out_scale=1)
+    monkeypatch.setenv("ODLA_B200_TEST_SPIN_LIMIT", "256")
+    monkeypatch.setenv("ODLA_B200_TEST_SKIP_STAGE", "1")
+    assert gpu_lib.b200_conv_umma(C.byref(d), xt.data_ptr(), wt.data_ptr(), None, None, None, y.data_ptr(), None) == -3
+    monkeypatch.delenv("ODLA_B200_TEST_SKIP_STAGE")
+    monkeypatch.delenv("ODLA_B200_TEST_SPIN_LIMIT")
+    torch.cuda.synchronize()
+    y.zero_()
+    assert gpu_lib.b200_conv_umma(C.byref(d), xt.data_ptr(), wt.data_ptr(), None, None, None, y.data_ptr(), None) == 0
+    assert np.array_equal(y.cpu().numpy(), conv_ref(x, w, R, R, 1, 1, H, W, np.int64).astype(np.int32))
+
+
+def test_timeout_through_the_graph_path(odla, gpu_lib, ref, monkeypatch):
+    """The same hook under odla_ExecuteComputation: the execute returns ODLA_TIMEOUT (the status word travels back with
+    the outputs), and a computation planned afterwards without the hook runs and matches the oracle."""
+    import blocks
+    monkeypatch.setenv("ODLA_B200_TEST_SPIN_LIMIT", "256")
+    monkeypatch.setenv("ODLA_B200_TEST_SKIP_STAGE", "1")
+    gpu_lib.SetLogLevel(0)
+    try:
+        g = odla.Graph(gpu_lib, "timeout", fp16=True)
+        x = g.Argument("x", (2, 14, 14, 64))
+        wgt = (np.random.default_rng(1).standard_normal((3, 3, 64, 64)) * 0.05).astype(np.float32)
+        g.Output(g.Conv(x, odla.CHANNELS_LAST, 1, g.Constant("w", wgt), odla.SIO, (1, 1), (1, 1), (1, 1), (1, 1), None, (2, 14, 14, 64), "y"))
+        xin = np.zeros((2, 14, 14, 64), np.float32)
+        yout = np.zeros((2, 14, 14, 64), np.float32)
+        g.bind_input("x", xin.ctypes.data)
+        g.bind_output("y", yout.ctypes.data)
+        assert g.execute() == odla.TIMEOUT
+        g.close()
+    finally:
+        gpu_lib.SetLogLevel(3)
+    monkeypatch.delenv("ODLA_B200_TEST_SKIP_STAGE")
+    monkeypatch.delenv("ODLA_B200_TEST_SPIN_LIMIT")
+    blocks.check_block(odla, gpu_lib, ref, mode="fp16", batch=2, hw=14, cin=64, cout=64)
