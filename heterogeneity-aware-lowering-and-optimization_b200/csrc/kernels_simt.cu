@@ -611,7 +611,7 @@ __global__ void stem_widen_kernel(const T* __restrict__ x, uint4* __restrict__ y
 // to Wp pixels on the right.
 template <typename T, int CP>
 __global__ void stem_pad_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int W, int C, int lp, int Wp) {
-  static_assert(sizeof(T) * CP == 8 || sizeof(T) * CP == 16, "a padded pixel is 8 or 16 bytes");
+  static_assert(sizeof(T) * CP == 4 || sizeof(T) * CP == 8 || sizeof(T) * CP == 16, "a padded pixel is 4, 8 or 16 bytes");
   const int64_t total = rows * Wp;
   for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
     const int wp = (int)(e % Wp);
@@ -624,7 +624,8 @@ __global__ void stem_pad_kernel(const T* __restrict__ x, T* __restrict__ y, int6
 #pragma unroll
       for (int c = 0; c < CP; ++c) if (c < C) px[c] = x[(row * W + w) * C + c];
     }
-    if (sizeof(T) * CP == 8) *(uint2*)(y + e * CP) = *(const uint2*)px;
+    if (sizeof(T) * CP == 4) *(uint32_t*)(y + e * CP) = *(const uint32_t*)px;
+    else if (sizeof(T) * CP == 8) *(uint2*)(y + e * CP) = *(const uint2*)px;
     else *(uint4*)(y + e * CP) = *(const uint4*)px;
   }
 }
@@ -1191,7 +1192,8 @@ int stem_pad(int esz, const void* x, void* y, int N, int H, int W, int C, int pi
   const int cp = pixel_bytes / esz;
   if (C > cp || (uintptr_t)y % 16 != 0) return -1;
   int grid = grid_for(total, 256);
-  if (esz == 1 && cp == 8) stem_pad_kernel<uint8_t, 8><<<grid, 256, 0, s>>>((const uint8_t*)x, (uint8_t*)y, rows, W, C, lp, Wp);
+  if (esz == 1 && cp == 4) stem_pad_kernel<uint8_t, 4><<<grid, 256, 0, s>>>((const uint8_t*)x, (uint8_t*)y, rows, W, C, lp, Wp);
+  else if (esz == 1 && cp == 8) stem_pad_kernel<uint8_t, 8><<<grid, 256, 0, s>>>((const uint8_t*)x, (uint8_t*)y, rows, W, C, lp, Wp);
   else if (esz == 1 && cp == 16) stem_pad_kernel<uint8_t, 16><<<grid, 256, 0, s>>>((const uint8_t*)x, (uint8_t*)y, rows, W, C, lp, Wp);
   else if (esz == 2 && cp == 4) stem_pad_kernel<uint16_t, 4><<<grid, 256, 0, s>>>((const uint16_t*)x, (uint16_t*)y, rows, W, C, lp, Wp);
   else if (esz == 2 && cp == 8) stem_pad_kernel<uint16_t, 8><<<grid, 256, 0, s>>>((const uint16_t*)x, (uint16_t*)y, rows, W, C, lp, Wp);

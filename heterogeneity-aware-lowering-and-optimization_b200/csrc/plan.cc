@@ -677,18 +677,29 @@ odla_status Builder::emit_fused(const Item& it) {
       // than the pixel size describes directly.  If the driver refuses such a map, a stride-2 stem falls back to a
       // materialised widened copy, others to plain channel padding.
       if (umma_conv_supported(uw) && !getenv("ODLA_B200_NO_OVERLAP")) {
-        const int pb = 16 / g.stride_w;
-        // Column groups: gq neighbouring output columns share one 128-byte window (their taps span
-        // (gq-1)*stride_w + S pixels) and become gq*K "channels" of one output pixel -- the same bytes in memory.
-        // That divides the number of rows the TMA unit has to deliver, which is what bounds a stem, by gq and gives
-        // the tensor pipe gq times wider instructions.
+        int pb = 16 / g.stride_w;
+        // Column groups: gq neighbouring output columns share one window (their taps span (gq-1)*stride_w + S
+        // pixels) and become gq*K "channels" of one output pixel -- the same bytes in memory.  That divides the number
+        // of rows the TMA unit has to deliver, which is what bounds a stem, by gq and gives the tensor pipe gq times
+        // wider instructions.  A group's window starts every gq*stride_w pixels, so pixels may be narrower than
+        // 16/stride_w bytes as long as that distance stays a multiple of 16 bytes: int8 RGB pixels take 4 bytes, which
+        // halves the window (and the number of tensor-core instructions per tile) against 8-byte pixels.
         int gq = 1;
         if (!f.res && !getenv("ODLA_B200_NO_COLUMN_GROUPS"))
-          for (int cand = 4; cand >= 2; cand /= 2)
-            if (g.Q % cand == 0 && (int64_t)cand * K <= 256 && (cand - 1) * g.stride_w + g.S <= 128 / pb) { gq = cand; break; }
-        const int win_bytes = gq > 1 ? 128 : 64, wp = win_bytes / pb;
+          for (int cand = 4; cand >= 2 && gq == 1; cand /= 2) {
+            if (g.Q % cand != 0 || (int64_t)cand * K > 256) continue;
+            int px = 4;
+            while (px < g.C * esz0) px *= 2;
+            for (; px <= 16 / g.stride_w; px *= 2)
+              if ((cand * g.stride_w * px) % 16 == 0 && ((cand - 1) * g.stride_w + g.S) * px <= 128 && !getenv("ODLA_B200_WIDE_PIXELS")) break;
+            if (px > 16 / g.stride_w) { px = 16 / g.stride_w; if ((cand - 1) * g.stride_w + g.S > 128 / px) continue; }
+            gq = cand; pb = px;
+          }
+        int win_bytes = 64;
+        if (gq > 1) { const int need = ((gq - 1) * g.stride_w + g.S) * pb; win_bytes = need > 64 ? 128 : (need > 32 ? 64 : 32); }
+        const int wp = win_bytes / pb;
         int Wp = std::max(g.pad_l + g.W, (g.Q / gq - 1) * gq * g.stride_w + wp);
-        Wp = (Wp + 1) & ~1;  // rows are 16-byte multiples also with 8-byte pixels
+        { const int unit = 16 / pb > 1 ? 16 / pb : 1; Wp = (Wp + unit - 1) / unit * unit; }  // rows are 16-byte multiples for every pixel size
         UmmaConv uo = uw;
         uo.C = win_bytes / esz0;
         uo.W = g.Q / gq; uo.Q = g.Q / gq; uo.K = (int)(K * gq);

@@ -412,7 +412,7 @@ void ora_quantize_f32(void* out, const float* in, const float* scale, const int3
 }
 /* Requantisation: q = saturate(round_to_nearest_even(x * inv_scale)) with inv_scale = fl(1/scale) computed by
  * the caller.  This build's definition for an odla_Quantize whose input was computed from int32
- * accumulators (BASELINE's "requantisation uses an fp32 multiplier with round-half-even"); every other
+ * accumulators (the int8 workload is specified as "requantisation uses an fp32 multiplier with round-half-even"); every other
  * odla_Quantize divides, like the reference.  int8, per tensor, no zero point. */
 void ora_requantize_f32(int8_t* out, const float* in, float inv_scale, int64_t n) {
   for (int64_t i = 0; i < n; ++i) out[i] = (int8_t)ora_sat(nearbyintf(in[i] * inv_scale), -128.f, 127.f);

@@ -10,7 +10,8 @@ import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 HEADER = os.path.join(ROOT, "include", "odla_b200.h")
-REF_INC = "/root/reference/ODLA/include"
+# the reference checkout, when there is one: ODLA_REFERENCE_DIR, else a "reference" directory beside this repository
+REF_INC = os.path.join(os.environ.get("ODLA_REFERENCE_DIR") or os.path.join(os.path.dirname(ROOT), "reference"), "ODLA", "include")
 
 
 def declared_functions():

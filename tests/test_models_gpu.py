@@ -1,4 +1,4 @@
-"""Whole-graph parity on the GPU: the BASELINE configurations at sizes the CPU oracle finishes in
+"""Whole-graph parity on the GPU: the benchmark networks (MNIST regression, ResNet-50, YOLOv3, BERT) at sizes the CPU oracle finishes in
 seconds, the HALO-style model.cc linked against both libraries, multi-GPU sharding, host-side fault
 injection, and size-independent properties at the full batch size."""
 import ctypes as C
