@@ -74,22 +74,51 @@ def barrier():
 
 # ------------------------------------------------------------------------- clocks ----
 class ClockSampler(threading.Thread):
-    """Samples nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+    """Samples the SM clock, the power draw and the throttle reasons while the timed region runs: through NVML in this
+    process every 2 ms when the binding is there (a 4 ms step is invisible to a tool that is spawned every 200 ms),
+    else through nvidia-smi every 200 ms.  Reading only; nothing about the GPU is changed."""
     Q = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
 
     def __init__(self, index):
         super().__init__(daemon=True)
         self.index, self.samples, self.stop_flag = index, [], threading.Event()
+        self.nvml = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.sm_max = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nvml = None
 
     def run(self):
+        if self.nvml is not None:
+            nv, h = self.nvml, self.handle
+            bits = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20}
+            while not self.stop_flag.is_set():
+                try:
+                    sm = float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                    pw = nv.nvmlDeviceGetPowerUsage(h) / 1000.0
+                    try:
+                        r = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                    except Exception:
+                        r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                    self.samples.append((sm, self.sm_max, pw, [k for k, b in bits.items() if r & b]))
+                except Exception:
+                    pass
+                self.stop_flag.wait(0.002)
+            return
         while not self.stop_flag.is_set():
             try:
                 out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits"],
                                      capture_output=True, text=True, timeout=5).stdout.strip()
                 f = [x.strip() for x in out.split(",")]
-                if len(f) >= 7:
-                    self.samples.append(f)
+                if len(f) >= 7 and f[0].replace(".", "").isdigit():
+                    names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+                    self.samples.append((float(f[0]), float(f[1]), float(f[2]) if f[2].replace(".", "").isdigit() else 0.0,
+                                         [n for i, n in enumerate(names) if f[3 + i].lower().startswith("active")]))
             except Exception:
                 pass
             self.stop_flag.wait(0.2)
@@ -99,13 +128,14 @@ class ClockSampler(threading.Thread):
         self.join(timeout=6)
         if not self.samples:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        sm = sorted(float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit())
-        reasons = []
-        for i, name in enumerate(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]):
-            if any(s[3 + i].lower().startswith("active") for s in self.samples):
-                reasons.append(name)
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": float(self.samples[0][1]) if self.samples[0][1].replace(".", "").isdigit() else None,
-                "reasons": reasons, "samples": len(self.samples)}
+        # "under load": samples whose power draw is in the upper half of what was seen (the L2 flush and the host-side
+        # gaps between steps draw little)
+        pmax = max(s[2] for s in self.samples)
+        busy = [s for s in self.samples if s[2] >= 0.5 * pmax] or self.samples
+        sm = sorted(s[0] for s in busy)
+        reasons = sorted({r for s in self.samples for r in s[3]})
+        return {"sm_mhz": sm[len(sm) // 2], "sm_min_mhz": sm[0], "sm_max_mhz": self.samples[0][1], "power_w_max": round(pmax, 1), "reasons": reasons,
+                "samples": len(self.samples), "samples_under_load": len(busy), "source": "nvml, 2 ms" if self.nvml is not None else "nvidia-smi, 200 ms"}
 
 
 # ------------------------------------------------------------------- the two arms ----

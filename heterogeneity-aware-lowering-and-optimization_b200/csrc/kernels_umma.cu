@@ -341,8 +341,9 @@ __device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, float (&v)[C
   const bool res_smem = STAGED && res_smem_in;
   const int out_dt = OUT >= 0 ? OUT : ep.out_dt;
   const bool colsall = ncols == CW;
-  const bool full = colsall && (staged || (p.K_out & 15) == 0);      // per-channel vectors can be read 16 bytes at a time
-  const bool gvec = colsall && (p.K_out & 15) == 0;                  // the row segment in global memory is 16-byte aligned
+  const bool full = colsall;                                         // per-channel vectors can be read 16 bytes at a time: col0 is a multiple of CW
+  const bool gvec = colsall && (p.K_out & 15) == 0;                  // the row segment in global memory is 16-byte aligned for every element size
+  const bool gvec32 = (p.K_out & 3) == 0;                            // ... for 4-byte outputs rows of a multiple of 4 elements are enough
   const int kmax = p.K_out - 1;
   const int64_t base = row * p.K_out + col0;
   float rv[CW];
@@ -494,9 +495,9 @@ __device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, float (&v)[C
     }
   } else if (row < p.M_total) {  // DT_F32
     float* out = (float*)p.y + base;
-    if (gvec) {
+    if (gvec32) {   // whole 16-byte pieces, then at most three single elements (ncols is a multiple of 4 here)
 #pragma unroll
-      for (int q = 0; q < CW / 4; ++q) ((float4*)out)[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+      for (int q = 0; q < CW / 4; ++q) if (4 * q + 3 < ncols) ((float4*)out)[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
     } else {
 #pragma unroll
       for (int j = 0; j < CW; ++j) if (j < ncols) out[j] = v[j];
