@@ -238,8 +238,8 @@ def bind_to_gpu_numa_node(index):
 # execute and divided by their number: one ncu capture at a smaller batch (the full batch breaks the capture-size rule),
 # scaled in proportion to the batch (activation traffic grows with it; the 25 / 51 MB of weights do not, which makes the
 # scaled figure a slight over-estimate).  See profiles/.
-NCU_TRAFFIC = {"f16": {"bytes_per_launch": 1.9707e8, "launches": 54, "at_batch": 256, "source": "ncu capture of all 54 launches at B=128, scaled x2"},
-               "s8": None}
+NCU_TRAFFIC = {"f16": {"bytes_per_launch": 9.8226e7, "launches": 54, "at_batch": 128, "source": "ncu capture of all 54 launches at B=128 (4.066 GB read + 1.238 GB written), scaled by batch / 128"},
+               "s8": {"bytes_per_launch": 4.1931e7, "launches": 54, "at_batch": 128, "source": "ncu capture of all 54 launches at B=128 (1.975 GB read + 0.290 GB written), scaled by batch / 128"}}
 
 
 def tensor_roofline(prof, ms_per_step, peaks, peak_kind, clocks, int8, batch):
@@ -569,8 +569,27 @@ def run_secondary(args, rank, world, local_rank):
         f = fam.setdefault(q["op"], {"launches": 0, "ms": 0.0})
         f["launches"] += 1
         f["ms"] = round(f["ms"] + q["ms"], 4)
+    int8 = None
+    if args.workload == "bert" and not args.no_int8:
+        # the same encoder in its int8-GEMM form (Quantize / Dequantize around the six dense layers of every block,
+        # soft-max / LayerNorm / attention products in fp16), device-resident
+        q = m.quantize(m.BASE, w, n_sequences=2)
+        g8 = odla.Graph(lib, "bert_int8", fp16=True, n_gpus=1)
+        m.build(g8, batch, m.BASE, w, quant=q)
+        g8.context()
+        ms8 = timed(g8, x_dev, y_dev)
+        prof8 = g8.profile(runs=2)
+        fam8 = {}
+        for q8 in prof8:
+            f = fam8.setdefault(q8["op"], {"launches": 0, "ms": 0.0})
+            f["launches"] += 1
+            f["ms"] = round(f["ms"] + q8["ms"], 4)
+        int8 = {"value": total / (ms8 / 1e3), "unit": unit, "ms_per_step": ms8 / args.steps, "dtype": "s8 GEMMs (int32 accumulate), f16 elsewhere",
+                "kernel_families_ms_per_step": dict(sorted(fam8.items(), key=lambda kv: -kv[1]["ms"]))}
+        g8.close()
     if rank == 0:
         print(json.dumps({
+            "int8": int8,
             "metric": metric, "value": total / (dev_ms / 1e3), "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": name, "batch_per_gpu": batch, "l2": "256 MiB buffer written between steps", "parallelism": "dp%d" % world,
