@@ -303,10 +303,9 @@ def run_b200(args, rank, world, local_rank):
     flush = [torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda:%d" % d) for d in (range(n_lib_gpus) if inlib else [local_rank])]   # larger than the 126 MB L2
     x_np = rn.inputs(BATCH, seed=rank_seed(10 + BATCH, rank), dtype=np.float16)["input"]
     x_host = torch.from_numpy(x_np).pin_memory()
-    y_host = torch.empty((BATCH, 1000), dtype=torch.float32).pin_memory()
+    x_host2 = x_host.clone().pin_memory()     # the second context's own buffers (same images: results must agree)
     x_dev = x_host.cuda()
-    y_dev = torch.empty((BATCH, 1000), dtype=torch.float32, device="cuda")
-    h2d, d2h = x_host.numel() * 2, y_host.numel() * 4
+    h2d = x_host.numel() * 2
     total_images = sum_over_ranks(BATCH * args.steps)
 
     def measure(build, tag, int8):
@@ -314,6 +313,9 @@ def run_b200(args, rank, world, local_rank):
         g = odla.Graph(lib, "resnet50_" + tag, fp16=not int8, n_gpus=n_lib_gpus)
         build(g)
         g.context()   # odla_CreateContext attaches to the most recently created computation: make it now
+        # a second context of the same computation (a lane of its own in the library) for the pipelined end-to-end leg;
+        # with two executes in flight a whole step's input copy hides under the other step, so no sub-batches there
+        ctx2 = g.extra_context() if args.contexts > 1 else None
         # The end-to-end leg binds host buffers; there the library pipelines the batch over sub-batches
         # (ODLA_BATCHES_PER_STEP) so that one sub-batch's input copy runs under another's kernels.
         g_host = g
@@ -321,6 +323,13 @@ def run_b200(args, rank, world, local_rank):
             g_host = odla.Graph(lib, "resnet50_%s_host" % tag, fp16=not int8, n_gpus=n_lib_gpus, sub_batches=args.sub_batches)
             build(g_host)
             g_host.context()
+        # the probabilities come back in the graph's own output type: fp16 for the fp16 graph fed fp16 images, fp32 for
+        # the quantise/dequantise form
+        y_dt = {odla.FLOAT16: torch.float16, odla.FLOAT32: torch.float32}[g.dtypes["prob"]]
+        y_host = torch.zeros((BATCH, 1000), dtype=y_dt).pin_memory()
+        y_host2 = torch.zeros((BATCH, 1000), dtype=y_dt).pin_memory()
+        y_dev = torch.zeros((BATCH, 1000), dtype=y_dt, device="cuda")
+        d2h = y_host.numel() * y_host.element_size()
 
         def step(gg):
             for f in flush:
@@ -352,12 +361,55 @@ def run_b200(args, rank, world, local_rank):
             barrier()
             return max_over_ranks(dev), max_over_ranks(wall)
 
+        def timed_pipelined(ctxs, bufs):
+            """K steps with `len(ctxs)` executes in flight: step i is started with odla_AsyncExecuteComputation on context
+            i mod n as soon as that context's previous step has delivered its outputs.  Every step still copies its own
+            input from pinned host memory and its result back; the copies of one step run under the kernels of another.
+            No L2 flush is possible between overlapping steps: each step streams 77 MB of fresh input and ~1.5 GB of
+            activations through the 126 MB L2."""
+            for c, (xh, yh) in zip(ctxs, bufs):
+                c.bind_input("input", xh.data_ptr())
+                c.bind_output("prob", yh.data_ptr())
+            def run(n):
+                for i in range(n):
+                    c = ctxs[i % len(ctxs)]
+                    if c.wait() != 0 or c.execute_async() != 0:
+                        raise RuntimeError("asynchronous execute failed")
+                for c in ctxs:
+                    if c.wait() != 0:
+                        raise RuntimeError("asynchronous execute failed")
+            run(max(args.warmup, len(ctxs)))
+            barrier()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            run(args.steps)
+            wall = (time.perf_counter() - t0) * 1e3
+            torch.cuda.synchronize()
+            barrier()
+            return max_over_ranks(wall)
+
         sampler = ClockSampler(local_rank)
         dev_ms, _ = timed(g, True, sampler)
         clocks = sampler.summary()
         launches = g.launches() * args.steps
         e2e_dev_ms, e2e_wall_ms = timed(g_host, False)
-        top1 = int(y_host.argmax(dim=1)[0])
+        top1 = int(y_host.float().argmax(dim=1)[0])
+        if abs(float(y_host.float().sum(dim=1).mean()) - 1.0) > 1e-2:
+            raise RuntimeError("probabilities do not sum to one")
+        e2e = {"value": total_images / (e2e_wall_ms / 1e3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+               "ms_per_step": e2e_wall_ms / args.steps, "device_ms_per_step": e2e_dev_ms / args.steps, "sub_batches": args.sub_batches,
+               "h2d_gbs_per_rank": h2d / (e2e_wall_ms / args.steps * 1e-3) / 1e9, "executes_in_flight": 1,
+               "timing": "wall clock around the synchronous odla_ExecuteComputation, max over ranks"}
+        if ctx2 is not None:
+            pipe_ms = timed_pipelined([g, ctx2], [(x_host, y_host), (x_host2, y_host2)])
+            if not torch.equal(y_host, y_host2):
+                raise RuntimeError("the two contexts disagree on the same input")
+            e2e = {"value": total_images / (pipe_ms / 1e3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                   "ms_per_step": pipe_ms / args.steps, "sub_batches": 1, "h2d_gbs_per_rank": h2d / (pipe_ms / args.steps * 1e-3) / 1e9,
+                   "executes_in_flight": 2,
+                   "timing": "wall clock over K steps issued with odla_AsyncExecuteComputation on two contexts of one computation (each step copies its "
+                             "own input from pinned host memory and its result back; step i+1's input copy runs under step i's kernels), max over ranks",
+                   "one_at_a_time": e2e}
         g.bind_input("input", x_dev.data_ptr())
         g.bind_output("prob", y_dev.data_ptr())
         prof = g.profile(runs=max(2, min(5, args.steps)))
@@ -366,9 +418,7 @@ def run_b200(args, rank, world, local_rank):
         if g_host is not g:
             g_host.close()
         return {"value": total_images / (dev_ms / 1e3), "ms_per_step": dev_ms / args.steps,
-                "e2e": {"value": total_images / (e2e_wall_ms / 1e3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                        "ms_per_step": e2e_wall_ms / args.steps, "device_ms_per_step": e2e_dev_ms / args.steps, "sub_batches": args.sub_batches,
-                        "h2d_gbs_per_rank": h2d / (e2e_wall_ms / args.steps * 1e-3) / 1e9, "timing": "wall clock around the synchronous odla_ExecuteComputation, max over ranks"},
+                "e2e": e2e,
                 "gpu_launches": launches, "clocks": clocks, "roofline": roof, "families": families, "top1": top1}
 
     if args.only_int8:   # profiling aid: the int8 form alone, printed as a line of its own
@@ -617,6 +667,8 @@ def main():
     ap.add_argument("--workload", default="resnet50", choices=["resnet50", "yolov3", "bert", "ops"],
                     help="resnet50 is the benchmark line; yolov3 (B=16) and bert (B=64) are the other two networks; ops times every memory-bound kernel on its own")
     ap.add_argument("--sub-batches", type=int, default=2, help="ODLA_BATCHES_PER_STEP of the end-to-end (host-bound) leg; 1 = off")
+    ap.add_argument("--contexts", type=int, default=2, choices=[1, 2],
+                    help="executes in flight in the end-to-end leg: 2 = two contexts driven with odla_AsyncExecuteComputation (the one-at-a-time figure is reported beside it)")
     ap.add_argument("--batch", type=int, default=BATCH, help="images per GPU per step (256 = the benchmark configuration; smaller values are for profiling)")
     ap.add_argument("--inlib-gpus", type=int, default=0, help="single process: one odla_ExecuteComputation shards a batch of N x --batch images over N GPUs inside the library")
     args = ap.parse_args()

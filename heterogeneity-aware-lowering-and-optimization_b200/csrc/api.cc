@@ -151,6 +151,13 @@ using namespace b200;
 _odla_computation::~_odla_computation() {
   b200::destroy_replicas(replicas);
   for (auto& kv : batch_replicas) b200::destroy_replicas(kv.second);
+  for (auto& lane : lanes)
+    for (auto& kv : lane->batch_replicas) b200::destroy_replicas(kv.second);
+  for (auto& kv : chain) {
+    if (!kv.second || !kv.second->last) continue;
+    if (cudaSetDevice(kv.first) == cudaSuccess) cudaEventDestroy(kv.second->last);
+    else cudaGetLastError();
+  }
 }
 
 extern "C" {
@@ -331,7 +338,21 @@ odla_status odla_CreateContext(odla_context* context) {
   *context = new _odla_context();
   (*context)->comp = g_comp;
   {
+    // The first context takes lane 0; each further one takes the free lane with the lowest number (a lane of its
+    // own: it may then execute while the others do), or shares the least used one when all are taken.
     std::lock_guard<std::mutex> lock(g_comp->ctx_mutex);
+    int max_lanes = 2;
+    if (const char* e = getenv("ODLA_B200_CONTEXT_LANES")) max_lanes = std::max(1, std::min(8, atoi(e)));
+    std::vector<int> users((size_t)max_lanes, 0);
+    for (auto* other : g_comp->contexts) users[(size_t)std::min(other->lane, max_lanes - 1)]++;
+    int lane = 0;
+    for (int k = 1; k < max_lanes; ++k) if (users[(size_t)k] < users[(size_t)lane]) lane = k;
+    if (lane > 0) {
+      std::lock_guard<std::recursive_mutex> plan_lock(g_comp->plan_mutex);
+      while ((int)g_comp->lanes.size() < lane) g_comp->lanes.emplace_back(new b200::Lane());
+      g_comp->multi_lane.store(true);
+    }
+    (*context)->lane = lane;
     g_comp->contexts.insert(*context);
   }
   return ODLA_SUCCESS;
@@ -446,9 +467,14 @@ odla_status odla_BindToOutputById(const odla_value_id id, odla_void* data, odla_
   return odla_BindToOutput(it->second, data, ctx);
 }
 static odla_status execute_locked(odla_computation c, odla_context ctx) {
-  // Contexts of one computation may be driven from different threads; they share the computation's
-  // per-GPU arenas and streams, so executions are serialised here.
-  std::lock_guard<std::mutex> lock(c->exec_mutex);
+  // Contexts of one computation may be driven from different threads.  Those on one lane share that lane's per-GPU
+  // arenas and streams and are serialised here; contexts on different lanes run side by side.
+  std::mutex* lane_mutex = &c->exec_mutex;
+  {
+    std::lock_guard<std::recursive_mutex> plan_lock(c->plan_mutex);
+    if (ctx->lane > 0 && ctx->lane <= (int)c->lanes.size()) lane_mutex = &c->lanes[(size_t)ctx->lane - 1]->exec_mutex;
+  }
+  std::lock_guard<std::mutex> lock(*lane_mutex);
   odla_status s = ensure_planned(c);
   if (s != ODLA_SUCCESS) return s;
   return execute(c, ctx);
@@ -477,6 +503,7 @@ odla_status odla_AsyncExecuteComputation(const odla_computation c, const odla_co
   }
   return ODLA_SUCCESS;
 }
+int odla_b200_ContextLane(odla_context ctx) { return ctx ? ctx->lane : -1; }
 odla_status odla_b200_WaitContext(odla_context ctx) {
   if (!ctx) return ODLA_INVALID_PARAM;
   if (ctx->worker.joinable()) ctx->worker.join();

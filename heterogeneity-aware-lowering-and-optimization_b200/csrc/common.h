@@ -8,6 +8,7 @@
 #include <cstdint>
 #include <deque>
 #include <functional>
+#include <atomic>
 #include <map>
 #include <memory>
 #include <mutex>
@@ -143,6 +144,14 @@ struct Replica {
 }  // namespace b200
 
 struct _odla_context;
+namespace b200 {
+// A further set of arenas, streams and plans for one computation, so that a second context can be in flight while the
+// first one runs (its input copy under the other's kernels).  Lane 0 is the computation's own `replicas`.
+struct Lane {
+  std::map<int64_t, std::vector<Replica>> batch_replicas;  // keyed by the rows an execute runs (the recorded batch included)
+  std::mutex exec_mutex;
+};
+}  // namespace b200
 struct _odla_computation {
   std::vector<std::unique_ptr<_odla_value>> nodes;
   std::vector<odla_value> args, outs;
@@ -171,7 +180,17 @@ struct _odla_computation {
   std::vector<b200::Replica> replicas;
   int64_t graph_batch = 1;         // dim 0 of the recorded graph
   std::map<int64_t, std::vector<b200::Replica>> batch_replicas;  // plans for other run batch sizes (ODLA_RUN_BATCH_SIZE)
-  std::mutex exec_mutex;           // executions of one computation share its arenas: one at a time
+  std::mutex exec_mutex;           // executions that share lane 0's arenas: one at a time
+  // Contexts are spread over `lanes` + 1 sets of arenas (ODLA_B200_CONTEXT_LANES, default 2): contexts on different
+  // lanes execute concurrently, contexts that share a lane take turns.  lanes[k - 1] belongs to lane k.
+  std::vector<std::unique_ptr<b200::Lane>> lanes;
+  std::atomic<bool> multi_lane{false};
+  std::recursive_mutex plan_mutex; // guards planning: `planned`, `replicas`, `batch_replicas`, every lane's plans
+  // Kernels of concurrent executes run one execute after the other on each GPU (only copies overlap kernels): each
+  // execute's launches wait for the event the previous execute recorded behind its own.
+  struct ChainLink { std::mutex enqueue; cudaEvent_t last = nullptr; };
+  std::mutex chain_mutex;          // guards the map, not the links
+  std::map<int, std::unique_ptr<ChainLink>> chain;   // per device
   std::mutex ctx_mutex;            // guards `contexts`
   std::set<_odla_context*> contexts;  // live contexts created for this computation
   ~_odla_computation();
@@ -186,6 +205,7 @@ struct _odla_context {
   bool profiling = false;
   bool range_profiling = false;    // accumulate min / max of every materialised value (odla_b200_SetRangeProfiling)
   int64_t run_batch = 0;           // ODLA_RUN_BATCH_SIZE; 0 = the recorded batch
+  int lane = 0;                    // which set of arenas this context executes on
   // odla_AsyncExecuteComputation: one worker at a time per context
   std::thread worker;
   int (*async_fn)(void*, odla_status) = nullptr;

@@ -1548,6 +1548,7 @@ static odla_status build_replicas(_odla_computation* c, int visible, int64_t B, 
 }
 
 odla_status ensure_planned(_odla_computation* c) {
+  std::lock_guard<std::recursive_mutex> plan_lock(c->plan_mutex);
   if (c->planned) return ODLA_SUCCESS;
   int visible = visible_devices();
   if (visible <= 0) {
@@ -1558,6 +1559,10 @@ odla_status ensure_planned(_odla_computation* c) {
   destroy_replicas(c->replicas);
   for (auto& kv : c->batch_replicas) destroy_replicas(kv.second);
   c->batch_replicas.clear();
+  for (auto& lane : c->lanes) {
+    for (auto& kv : lane->batch_replicas) destroy_replicas(kv.second);
+    lane->batch_replicas.clear();
+  }
   int64_t B = 1;
   c->shardable = graph_shardable(c, &B);
   c->graph_batch = B;
@@ -1567,20 +1572,27 @@ odla_status ensure_planned(_odla_computation* c) {
   return ODLA_SUCCESS;
 }
 
-// The replicas that run `run_batch` rows (ODLA_RUN_BATCH_SIZE); plans for other batch sizes than the recorded one
-// are built on first use and kept.
-odla_status replicas_for_batch(_odla_computation* c, int64_t run_batch, std::vector<Replica>** out) {
+// The replicas that run `run_batch` rows (ODLA_RUN_BATCH_SIZE) on lane `lane`; plans for other batch sizes than the
+// recorded one, and every plan of a lane other than 0, are built on first use and kept.
+odla_status replicas_for_batch(_odla_computation* c, int64_t run_batch, int lane, std::vector<Replica>** out) {
+  std::lock_guard<std::recursive_mutex> plan_lock(c->plan_mutex);
   odla_status s = ensure_planned(c);
   if (s != ODLA_SUCCESS) return s;
-  if (run_batch <= 0 || run_batch == c->graph_batch) { *out = &c->replicas; return ODLA_SUCCESS; }
-  if (!c->shardable) { B2_ERR("ODLA_RUN_BATCH_SIZE needs a graph whose dim 0 is an independent batch"); return ODLA_UNSUPPORTED_OP; }
-  if (run_batch > c->graph_batch) { B2_ERR("ODLA_RUN_BATCH_SIZE %lld exceeds the recorded batch %lld", (long long)run_batch, (long long)c->graph_batch); return ODLA_INVALID_PARAM; }
-  auto it = c->batch_replicas.find(run_batch);
-  if (it == c->batch_replicas.end()) {
+  const bool whole = run_batch <= 0 || run_batch == c->graph_batch;
+  if (whole && lane == 0) { *out = &c->replicas; return ODLA_SUCCESS; }
+  if (!whole) {
+    if (!c->shardable) { B2_ERR("ODLA_RUN_BATCH_SIZE needs a graph whose dim 0 is an independent batch"); return ODLA_UNSUPPORTED_OP; }
+    if (run_batch > c->graph_batch) { B2_ERR("ODLA_RUN_BATCH_SIZE %lld exceeds the recorded batch %lld", (long long)run_batch, (long long)c->graph_batch); return ODLA_INVALID_PARAM; }
+  }
+  if (lane < 0 || lane > (int)c->lanes.size()) { B2_ERR("context lane %d does not exist", lane); return ODLA_INTERNAL_LOGIC_ERR; }
+  std::map<int64_t, std::vector<Replica>>& plans = lane == 0 ? c->batch_replicas : c->lanes[(size_t)lane - 1]->batch_replicas;
+  const int64_t rows = whole ? c->graph_batch : run_batch;
+  auto it = plans.find(rows);
+  if (it == plans.end()) {
     std::vector<Replica> reps;
-    s = build_replicas(c, visible_devices(), c->graph_batch, run_batch, reps);
+    s = build_replicas(c, visible_devices(), c->graph_batch, rows, reps);
     if (s != ODLA_SUCCESS) return s;
-    it = c->batch_replicas.emplace(run_batch, std::move(reps)).first;
+    it = plans.emplace(rows, std::move(reps)).first;
   }
   *out = &it->second;
   return ODLA_SUCCESS;
@@ -1689,7 +1701,27 @@ static odla_status enqueue_replica(Replica& r, size_t index, _odla_context* ctx,
     else e = cudaMemcpyAsync(p.arena + io.stage, src, (size_t)io.api_bytes, pd >= 0 ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, r.stream);
     if (e != cudaSuccess) return fail_here(ODLA_FAILURE, "input copy");
   }
-  int rc = run_launches(r, ctx, use_graph, launched);
+  // With contexts on several lanes in flight, this execute's kernels start behind the kernels of the execute that was
+  // enqueued before it on this GPU (its input copies above do not wait): interleaving two executes layer by layer
+  // would only evict each other's activations from L2.
+  _odla_computation* c = ctx->comp;
+  const bool chained = c && c->multi_lane.load() && !ctx->profiling && !ctx->range_profiling;
+  int rc;
+  if (chained) {
+    _odla_computation::ChainLink* link;
+    {
+      std::lock_guard<std::mutex> map_lock(c->chain_mutex);
+      auto& slot = c->chain[r.device];
+      if (!slot) slot.reset(new _odla_computation::ChainLink());
+      link = slot.get();
+    }
+    std::lock_guard<std::mutex> order(link->enqueue);   // wait + launches + record of one execute stay together
+    if (!link->last) {
+      if (cudaEventCreateWithFlags(&link->last, cudaEventDisableTiming) != cudaSuccess) return fail_here(ODLA_FAILURE, "event creation");
+    } else if (cudaStreamWaitEvent(r.stream, link->last, 0) != cudaSuccess) return fail_here(ODLA_FAILURE, "cudaStreamWaitEvent");
+    rc = run_launches(r, ctx, use_graph, launched);
+    cudaEventRecord(link->last, r.stream);
+  } else rc = run_launches(r, ctx, use_graph, launched);
   if (rc) return fail_here(ODLA_FAILURE, "kernel launch");
   for (auto& io : p.outputs) {
     auto bound = ctx->out.find(io.v);
@@ -1717,7 +1749,7 @@ odla_status execute(_odla_computation* c, _odla_context* ctx) {
   odla_status result = ODLA_SUCCESS;
   long long launched = 0;
   std::vector<Replica>* reps_p = nullptr;
-  if (odla_status rs = replicas_for_batch(c, ctx->run_batch, &reps_p)) return rs;
+  if (odla_status rs = replicas_for_batch(c, ctx->run_batch, ctx->lane, &reps_p)) return rs;
   std::vector<Replica>& reps = *reps_p;
   std::vector<char> started(reps.size(), 0);
   // Enqueue everything on every GPU, then wait.  With more than one GPU each GPU is fed by a host thread of its own:
@@ -1779,6 +1811,17 @@ odla_status execute(_odla_computation* c, _odla_context* ctx) {
 }  // namespace b200
 
 using namespace b200;
+// The whole-batch replicas of the lane `ctx` executes on (lane 0's while that lane has built none yet).
+static std::vector<Replica>& context_replicas(odla_context ctx) {
+  _odla_computation* c = ctx->comp;
+  std::lock_guard<std::recursive_mutex> plan_lock(c->plan_mutex);
+  if (ctx->lane > 0 && ctx->lane <= (int)c->lanes.size()) {
+    auto& plans = c->lanes[(size_t)ctx->lane - 1]->batch_replicas;
+    auto it = plans.find(c->graph_batch);
+    if (it != plans.end()) return it->second;
+  }
+  return c->replicas;
+}
 extern "C" {
 float odla_b200_LastExecuteDeviceMs(odla_context ctx) { return ctx ? ctx->last_ms : -1.f; }
 long long odla_b200_LastExecuteLaunches(odla_context ctx) { return ctx ? ctx->last_launches : 0; }
@@ -1786,13 +1829,15 @@ odla_status odla_b200_SetProfiling(odla_context ctx, int enabled) {
   if (!ctx) return ODLA_INVALID_PARAM;
   ctx->profiling = enabled != 0;
   if (enabled && ctx->comp)
-    for (auto& r : ctx->comp->replicas)
+    for (auto& r : context_replicas(ctx))
       if (r.plan) for (auto& l : r.plan->launches) { l.prof_ms = 0; l.prof_n = 0; }
   return ODLA_SUCCESS;
 }
 int odla_b200_GetProfile(odla_context ctx, odla_b200_profile_entry* entries, int capacity) {
-  if (!ctx || !ctx->comp || ctx->comp->replicas.empty() || !ctx->comp->replicas[0].plan) return 0;
-  auto& ls = ctx->comp->replicas[0].plan->launches;
+  if (!ctx || !ctx->comp) return 0;
+  std::vector<Replica>& reps = context_replicas(ctx);
+  if (reps.empty() || !reps[0].plan) return 0;
+  auto& ls = reps[0].plan->launches;
   for (int i = 0; i < (int)ls.size() && i < capacity && entries; ++i) {
     memset(&entries[i], 0, sizeof(entries[i]));
     snprintf(entries[i].op, sizeof(entries[i].op), "%s", ls[i].op.c_str());
@@ -1845,6 +1890,8 @@ int odla_b200_GetQuantTable(odla_context ctx, odla_value_quant_info* records, in
   };
   scan(c->replicas);
   for (auto& kv : c->batch_replicas) scan(kv.second);
+  for (auto& lane : c->lanes)
+    for (auto& kv : lane->batch_replicas) scan(kv.second);
   // Reshape results share their source's memory: give them a per-value record under their own name
   std::vector<std::pair<const _odla_value*, const _odla_value*>> aliases;
   for (auto& n : c->nodes) {

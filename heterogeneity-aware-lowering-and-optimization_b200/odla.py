@@ -171,6 +171,7 @@ _OPTIONAL = {
     "odla_FreeHostMemory": (C.c_int, [_V]),
     "odla_AsyncExecuteComputation": (C.c_int, [_V, _V, C.c_int, _V]),
     "odla_b200_WaitContext": (C.c_int, [_V]),
+    "odla_b200_ContextLane": (C.c_int, [_V]),
     "odla_b200_DeviceCount": (C.c_int, []),
     "odla_b200_LastExecuteDeviceMs": (C.c_float, [_V]),
     "odla_b200_LastExecuteLaunches": (C.c_longlong, [_V]),
@@ -224,6 +225,40 @@ class OdlaLib:
 
 def _cname(name):
     return "".join(ch if ch.isalnum() or ch == "_" else "_" for ch in name)
+
+
+class Context:
+    """A further odla_context of a Graph's computation, with bindings of its own.  libodla_b200 gives the second context
+    of a computation its own arenas and streams, so two contexts can be in flight: start one with execute_async()
+    while the other still runs and its input copy proceeds under the other's kernels."""
+
+    def __init__(self, graph):
+        self.lib, self.comp, self.graph = graph.lib, graph.comp, graph
+        self.ctx = _V()
+        Graph._check(self.lib.CreateContext(C.byref(self.ctx)), "odla_CreateContext")
+
+    def bind_input(self, name, ptr):
+        Graph._check(self.lib.BindToArgumentById(name.encode(), C.c_void_p(ptr), self.ctx), "odla_BindToArgumentById")
+
+    def bind_output(self, name, ptr):
+        Graph._check(self.lib.BindToOutputById(name.encode(), C.c_void_p(ptr), self.ctx), "odla_BindToOutputById")
+
+    def execute(self):
+        return self.lib.ExecuteComputation(self.comp, self.ctx, 1, None)
+
+    def execute_async(self):
+        return self.lib.AsyncExecuteComputation(self.comp, self.ctx, 1, None)
+
+    def wait(self):
+        return self.lib.b200_WaitContext(self.ctx)
+
+    def lane(self):
+        return self.lib.b200_ContextLane(self.ctx)
+
+    def close(self):
+        if self.ctx is not None:
+            self.lib.DestroyContext(self.ctx)
+            self.ctx = None
 
 
 class Graph:
@@ -496,6 +531,14 @@ class Graph:
             self._check(self.lib.CreateContext(C.byref(self.ctx)), "odla_CreateContext")
         return self.ctx
 
+    def extra_context(self):
+        """Another context of this computation (see Context).  odla_CreateContext attaches to the calling thread's
+        current computation, i.e. the one created last: call this before building another Graph."""
+        self.context()
+        c = Context(self)
+        self._extra = getattr(self, "_extra", []) + [c]
+        return c
+
     def bind_input(self, name, ptr):
         self._check(self.lib.BindToArgumentById(name.encode(), C.c_void_p(ptr), self.context()), "odla_BindToArgumentById")
 
@@ -632,6 +675,9 @@ class Graph:
         return {"hits": h.value, "misses": m.value, "entries": e.value}
 
     def close(self):
+        for c in getattr(self, "_extra", []):
+            c.close()
+        self._extra = []
         if self.ctx is not None:
             self.lib.DestroyContext(self.ctx)
             self.ctx = None

@@ -204,6 +204,12 @@ odla_status odla_AsyncExecuteComputation(const odla_computation computation, con
                                          const odla_compute_mode mode, odla_device device);
 /* Extension (no counterpart in the reference): waits for the context's asynchronous execute and returns its status. */
 odla_status odla_b200_WaitContext(odla_context context);
+/* Extension.  Contexts of one computation are spread over sets of arenas and streams ("lanes": 2 unless the environment
+ * variable ODLA_B200_CONTEXT_LANES says otherwise; the second lane is built when its first context first executes).
+ * Contexts on different lanes execute at the same time -- the way the reference's TensorRT platform gives each
+ * odla_context an execution context and a stream of its own (ODLA/platforms/tensorrt/odla_tensorrt.h:380-394) --, contexts on the same
+ * lane take turns.  Returns the lane of `context` (0, 1, ...), or -1 for a null context. */
+int odla_b200_ContextLane(odla_context context);
 odla_status odla_CompileComputation(const odla_computation computation, const odla_device device,
                                     odla_executable* executable);
 odla_status odla_LaunchExecutable(odla_executable executable, odla_context context);

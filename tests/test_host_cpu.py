@@ -317,3 +317,23 @@ def test_async_execute_reports_failure_through_the_callback_without_a_gpu(odla, 
     finally:
         lib.SetLogLevel(3)
     g.close()
+
+
+def test_contexts_are_spread_over_lanes(odla, lib):
+    """The first context of a computation takes lane 0, the second a lane of its own, the third shares the less used
+    one; destroying a context frees its place.  Nothing here needs a GPU: lanes are built at the first execute."""
+    g = odla.Graph(lib, "lanes")
+    x = g.Argument("x", (4, 8))
+    g.Output(g.Relu(x, "y"))
+    g.context()
+    assert lib.b200_ContextLane(g.ctx) == 0
+    a, b = g.extra_context(), g.extra_context()
+    assert (a.lane(), b.lane()) == (1, 0)
+    c = g.extra_context()
+    assert c.lane() == 1
+    a.close()
+    c.close()
+    d = g.extra_context()
+    assert d.lane() == 1
+    assert lib.b200_ContextLane(None) == -1
+    g.close()

@@ -376,3 +376,48 @@ def test_run_batch_size_and_async_execute(odla, gpu_lib, ref, models):
     assert np.abs(out - want).max() < 1e-5
     assert gpu_lib.DestroyContext(g.ctx) == 0
     g.comp, g.ctx = odla._V(), None
+
+
+def test_two_contexts_in_flight(odla, gpu_lib, models, rn_weights):
+    """Two contexts of one computation execute at the same time, each on arenas and streams of its own: results are
+    those of the contexts run one after the other, bit for bit, over many overlapping steps with different inputs;
+    a third context shares a lane with the first and takes turns with it."""
+    rn = models.resnet50
+    B = 32
+    xs = [rn.inputs(B, seed=s)["input"] for s in (1, 2, 3)]
+    g = odla.Graph(gpu_lib, "resnet50", fp16=True, sub_batches=2)
+    rn.build(g, B, rn_weights)
+    want = [g.run({"input": x})["prob"].copy() for x in xs]
+    assert not np.array_equal(want[0], want[1])
+    ctxs = [g, g.extra_context(), g.extra_context()]
+    outs = [np.full((B, 1000), -1.0, np.float32) for _ in ctxs]
+    for c, x, o in zip(ctxs, xs, outs):
+        c.bind_input("input", x.ctypes.data)
+        c.bind_output("prob", o.ctypes.data)
+    for step in range(12):
+        for c in ctxs:
+            assert c.wait() == 0
+            assert c.execute_async() == 0
+        if step % 4 == 3:
+            for c, o, w in zip(ctxs, outs, want):
+                assert c.wait() == 0
+                assert np.array_equal(o, w)
+                o[:] = -1.0
+    for c in ctxs:
+        assert c.wait() == 0
+    # synchronous executes from two host threads at once
+    import threading
+    errs = []
+
+    def worker(c, o, w):
+        for _ in range(5):
+            o[:] = -1.0
+            if c.execute() != 0 or not np.array_equal(o, w):
+                errs.append(1)
+    ts = [threading.Thread(target=worker, args=(c, o, w)) for c, o, w in zip(ctxs, outs, want)]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join()
+    assert not errs
+    g.close()
