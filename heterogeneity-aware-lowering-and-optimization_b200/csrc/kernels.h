@@ -92,6 +92,10 @@ struct UmmaConv {
   // Batched GEMM (attention): w holds `w_batches` matrices [K][C] back to back and output rows
   // [b*rows_per_batch, (b+1)*rows_per_batch) use matrix b.  rows_per_batch must be a multiple of 128.
   int w_batches = 0, rows_per_batch = 0;
+  // Batched GEMM whose matrices are stored [C][K] (the reduction outermost, e.g. attention probabilities x V): the
+  // tensor cores read B "MN-major" straight from that layout, no transposed copy.  Needs K == 64 two-byte columns
+  // (one 128-byte swizzle span) and C a multiple of 64.
+  int w_n_major = 0;
   // Permuted store (attention head split / merge folded into the GEMM): the output rows are (b, s) [mode 1] or
   // (b, h, s) [mode 2] with s < store_S, the columns are head h x store_D [mode 1] or store_D [mode 2], and element
   // (b, h, s, d) goes to y[b][h][s][d] (mode 1: [B,S,NH*D] -> [B,NH,S,D]) or y[b][s][h][d] (mode 2: [B,NH,S,D] -> [B,S,NH,D]).

@@ -68,6 +68,8 @@ struct UmmaParams {
   uint32_t desc_hi;    // upper 32 bits of the shared-memory matrix descriptors
   int acc_int;         // accumulators are int32
   int rows_per_batch;  // batched GEMM: output rows per B matrix (0 = one shared B)
+  int b_n_major;       // batched GEMM: B boxes hold [k rows][64 columns] (MN-major operand) instead of [n rows][64 k]
+  int b_kstep;         // descriptor advance of B per 32 bytes of K, in 16-byte units: 2 (K-major) or 128 (16 rows of 128 bytes)
   int staged;          // epilogue goes through a shared-memory tile and TMA stores
   int res_tma;         // the residual tile is brought into that tile by TMA
   int out_esz;         // bytes per output element
@@ -908,7 +910,7 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             else if (p.im2col) tma_load_im2col_4d(sa, &tmA, fb, c0, w0, h0, img, (uint16_t)fs, (uint16_t)fr);
             else tma_load_2d(sa, &tmA, fb, c0, m0);
             if (skip) {}
-            else if (p.rows_per_batch) tma_load_3d(sb, &tmB, fb, c0, n0, bidx);
+            else if (p.rows_per_batch) tma_load_3d(sb, &tmB, fb, p.b_n_major ? n0 : c0, p.b_n_major ? c0 : n0, bidx);
             else tma_load_3d(sb, &tmB, fb, c0, tap, n0);
             sa += a_box;
             sb += b_box;
@@ -960,7 +962,7 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 else umma_f16_pair(tmem_d, da + 2 * k, db + 2 * k, p.idesc, accum);
               } else {
                 if (p.acc_int) umma_i8(tmem_d, da + 2 * k, db + 2 * k, p.idesc, accum);
-                else umma_f16(tmem_d, da + 2 * k, db + 2 * k, p.idesc, accum);
+                else umma_f16(tmem_d, da + 2 * k, db + (uint64_t)(p.b_kstep * k), p.idesc, accum);
               }
               accum = 1;
             }
@@ -1256,6 +1258,7 @@ bool umma_conv_supported(const UmmaConv& c) {
   if ((int64_t)c.N * c.P * c.Q >= (1ll << 31)) return false;
   if (c.H < 1 || c.W < 1 || c.P < 1 || c.Q < 1) return false;
   if (c.w_batches > 0 && (c.R != 1 || c.S != 1 || c.rows_per_batch <= 0 || c.rows_per_batch % 128 != 0)) return false;
+  if (c.w_n_major && (c.w_batches <= 0 || es != 2 || c.K != 64 || c.C % 64 != 0)) return false;
   return true;
 }
 
@@ -1381,6 +1384,14 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
   const uint32_t fmt = c.in_dt == DT_BF16 ? 1u : (c.in_dt == DT_S8 ? 1u : 0u);      // bf16 / signed 8-bit / f16
   const uint32_t cfmt = p.acc_int ? 2u : 1u;                                        // s32 / f32 accumulators
   p.idesc = (cfmt << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(p.BN >> 3) << 17) | ((uint32_t)((BM << p.pair) >> 4) << 24);
+  // B stored [k][n]: the instruction reads it MN-major (descriptor bit 16).  A box is then 64 k-rows of 128 bytes: the
+  // 8-row group pitch (SBO) is the same 1024 bytes, and 32 bytes of K are 16 rows = 2048 bytes further on.
+  p.b_n_major = c.w_n_major ? 1 : 0;
+  p.b_kstep = p.b_n_major ? (16 * 128) >> 4 : 2;
+  if (p.b_n_major) {
+    if (p.BN != 64 || p.kb_bytes != 128 || p.pair) { delete L; return nullptr; }
+    p.idesc |= 1u << 16;
+  }
   const uint32_t layout = p.kb_bytes == 128 ? 2u : (p.kb_bytes == 64 ? 4u : 6u);    // swizzle mode of the operand tiles
   const uint32_t sbo = (uint32_t)(8 * p.kb_bytes) >> 4;                             // 8-row group pitch, 16-byte units
   p.desc_hi = sbo | (1u << 14) | (layout << 29);                                    // bits 32-45 SBO, 46-47 version 1, 61-63 layout
@@ -1439,6 +1450,11 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
       dims[1] = (cuuint64_t)c.K; dims[2] = (cuuint64_t)c.w_batches;
       strides[1] = (cuuint64_t)c.K * c.C * es;
       box[1] = (cuuint32_t)p.BN; box[2] = 1;
+    }
+    if (c.w_n_major) {      // [batches][C][K]: the box spans kbe rows (of the reduction) by all 64 columns
+      dims[0] = (cuuint64_t)c.K; dims[1] = (cuuint64_t)c.C;
+      strides[0] = (cuuint64_t)c.K * es;
+      box[0] = (cuuint32_t)c.K; box[1] = (cuuint32_t)p.kbe;
     }
     cuuint32_t estr[3] = {1, 1, 1};
     r = g_encode_tiled(&L->tmB, dt, 3, (void*)w, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,

@@ -962,18 +962,21 @@ odla_status Builder::emit_fused(const Item& it) {
     }
   }
   // Batched product of two run-time tensors (attention scores and context): one tensor-core launch whose B
-  // operand changes with the batch.  B must be K-major; a [batch, K, N] operand is transposed into scratch first.
+  // operand changes with the batch.  A [batch, K, 64] operand is read in place (MN-major); any other [batch, K, N]
+  // operand is transposed into scratch first, because B is otherwise read K-major.
   if (allow_umma && !ta && f.w->kind != OP_CONST && bbatch == batch && batch > 1 && M % 128 == 0 && (in_dt == DT_F16 || in_dt == DT_BF16) &&
       dt_[resolve(f.w)] == in_dt && batch * M < (1ll << 31)) {
     UmmaConv uc{1, 1, (int)(batch * M), (int)Kd, (int)N, 1, 1, 1, (int)(batch * M), 1, 1, 0, 0, in_dt};
     uc.w_batches = (int)batch;
     uc.rows_per_batch = (int)M;
     if (store_direct) set_store(uc);
+    // a [batch, K, 64] operand (attention probabilities x V) is read as it lies; other widths are transposed first
+    if (!tb && N == 64 && Kd % 64 == 0 && !getenv("ODLA_B200_NO_N_MAJOR")) uc.w_n_major = 1;
     if (umma_conv_supported(uc)) {
       const void* bsrc = dev_ptr(f.w);
       void* bt = nullptr;
       MoveGeom mg{};
-      if (!tb) {
+      if (!tb && !uc.w_n_major) {
         if (cudaMalloc(&bt, (size_t)(batch * N * Kd * storage_size(in_dt))) != cudaSuccess) return fail(ODLA_MEM_ERROR, "scratch allocation failed");
         p_->extra_allocs.push_back(bt);
         mg.rank = 3;

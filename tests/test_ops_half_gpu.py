@@ -211,3 +211,31 @@ def test_reduce_mean_two_byte(odla, gpu_lib, mode):
         u = u + t[:, w]
     u = (u / np.float32(7)).reshape(5, 1, 1, 136)
     assert_within_ulps(got, u.astype(np.float64), mode, 0.51)   # the correctly rounded value of the fp32 result
+
+
+@pytest.mark.parametrize("mode", ["fp16", "bf16"])
+@pytest.mark.parametrize("S,D", [(128, 64), (256, 64), (128, 32)])
+def test_batched_gemm_with_untransposed_right_operand(odla, gpu_lib, mode, S, D, monkeypatch):
+    """probabilities [B, H, S, S] x values [B, H, S, D] (attention context): for D = 64 the tensor cores read the values
+    as they lie ([k][n], MN-major operand); other widths, or ODLA_B200_NO_N_MAJOR, go through a transposed copy.  Both
+    routes issue the same multiply-accumulates in the same order, so they must agree bit for bit, and with float64 to
+    the rounding of the two-byte result."""
+    Bt, H = 2, 3
+    pr = to_type(RNG.uniform(0, 1, (Bt, H, S, S)) / S * 4, mode)
+    v = to_type(RNG.standard_normal((Bt, H, S, D)), mode)
+
+    def run():
+        g = graph(odla, gpu_lib, mode)
+        a, b = g.Argument("p", (Bt, H, S, S)), g.Argument("v", (Bt, H, S, D))
+        g.Output(g.Gemm(a, False, b, False, 1.0, 0.0, None, (Bt, H, S, D), "ctx"))
+        out = g.run({"p": pr, "v": v})["ctx"]
+        desc = g.describe(first_gpu_only=True)
+        g.close()
+        return out, desc
+    got, desc = run()
+    assert "gemm_umma" in desc
+    monkeypatch.setenv("ODLA_B200_NO_N_MAJOR", "1")
+    via_copy, _ = run()
+    assert np.array_equal(got, via_copy)
+    want = np.einsum("bhik,bhkd->bhid", pr.astype(np.float64), v.astype(np.float64))
+    assert_within_ulps(got, want, mode, 1.0, floor=0.05)
