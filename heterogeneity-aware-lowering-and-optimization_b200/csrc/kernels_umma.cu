@@ -1288,6 +1288,13 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
   p.num_kb = c.R * c.S * terms * p.chunks_per_tap;
   p.BN = pick_bn(c.K);
   p.m_tiles = (p.M_total + BM - 1) / BM;
+  // Few rows (small batches, the classifier): narrower tiles put more SMs to work on the same reduction; a tile's time
+  // is dominated by its k-blocks, not by its width.
+  // (a staged tile leaves in whole 128-byte boxes, so one-byte outputs keep at least 128 columns)
+  if (!getenv("ODLA_B200_NO_BN_SHRINK")) {
+    const int min_bn = storage_size_of(ep.out_dt) == 1 ? 128 : 64;
+    while (p.BN > min_bn && 2 * p.m_tiles * ((c.K + p.BN - 1) / p.BN) <= sms) p.BN /= 2;
+  }
   p.n_tiles = (c.K + p.BN - 1) / p.BN;
   p.total_tiles = p.m_tiles * p.n_tiles;
   // CTA pairs (tcgen05 cta_group::2): a pair computes 256 rows x BN columns and each CTA loads only half of the

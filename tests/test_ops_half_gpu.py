@@ -233,7 +233,8 @@ def test_batched_gemm_with_untransposed_right_operand(odla, gpu_lib, mode, S, D,
         g.close()
         return out, desc
     got, desc = run()
-    assert "gemm_umma" in desc
+    if D == 64:
+        assert "gemm_umma" in desc
     monkeypatch.setenv("ODLA_B200_NO_N_MAJOR", "1")
     via_copy, _ = run()
     assert np.array_equal(got, via_copy)
