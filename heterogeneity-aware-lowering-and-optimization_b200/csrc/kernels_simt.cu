@@ -200,6 +200,46 @@ __global__ void maxpool_nhwc_vec_kernel(PoolGeom g, const T* __restrict__ x, T* 
   }
 }
 
+// The same for a window known at compile time: all R*S loads of a thread are issued before the first maximum, from
+// addresses clamped into the image, and a tap outside the image is replaced by the identity afterwards.  With the
+// run-time window above every load waits for the one before it (the bounds tests sit between them), which makes a
+// thread's life R*S trips to memory long.
+template <typename T, int VEC, int R, int S>
+__global__ void maxpool_nhwc_win_kernel(PoolGeom g, const T* __restrict__ x, T* __restrict__ y) {
+  const int cv = g.C / VEC, row_items = g.Q * cv;
+  const int rows = g.N * g.P;
+  for (int row = blockIdx.y; row < rows; row += gridDim.y) {
+    const int n = row / g.P, p = row - n * g.P;
+    const int h0 = p * g.stride_h - g.pad_t;
+    const T* xin = x + (int64_t)n * g.H * g.W * g.C;
+    T* yout = y + (int64_t)row * g.Q * g.C;
+    for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < row_items; e += gridDim.x * blockDim.x) {
+      const int q = e / cv, c = (e - q * cv) * VEC;
+      const int w0 = q * g.stride_w - g.pad_l;
+      uint4 v[R * S];
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const int h = min(max(h0 + r, 0), g.H - 1);
+#pragma unroll
+        for (int s2 = 0; s2 < S; ++s2) {
+          const int w = min(max(w0 + s2, 0), g.W - 1);
+          v[r * S + s2] = *(const uint4*)(xin + ((int64_t)h * g.W + w) * g.C + c);
+        }
+      }
+      uint4 acc;
+      VecMax<T, VEC>::init(acc);
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const bool h_in = h0 + r >= 0 && h0 + r < g.H;
+#pragma unroll
+        for (int s2 = 0; s2 < S; ++s2)
+          if (h_in && w0 + s2 >= 0 && w0 + s2 < g.W) VecMax<T, VEC>::upd(acc, v[r * S + s2]);
+      }
+      *(uint4*)(yout + (int64_t)q * g.C + c) = acc;
+    }
+  }
+}
+
 // -------------------------------------------------------------- element-wise ----
 __device__ __forceinline__ float unary_one(int op, float x, float a, float b) {
   switch (op) {
@@ -699,6 +739,19 @@ int pool2d(const PoolGeom& g, int dt, bool is_max, const void* x, void* y, cudaS
   bool nhwc_dense = g.xs_c == 1 && g.xs_w == g.C && g.xs_h == (int64_t)g.W * g.C && g.ys_c == 1 && g.ys_w == g.C &&
                     g.ys_h == (int64_t)g.Q * g.C && g.ys_n == (int64_t)g.P * g.Q * g.C && g.xs_n == (int64_t)g.H * g.W * g.C;
   bool aligned = ((uintptr_t)x % 16 == 0) && ((uintptr_t)y % 16 == 0);
+  if (is_max && nhwc_dense && aligned && g.H >= 1 && g.W >= 1 && ((g.R == 3 && g.S == 3) || (g.R == 2 && g.S == 2)) && !getenv("ODLA_B200_POOL_RUNTIME_WINDOW")) {
+#define B2_POOL_WIN(T, V)                                                                                                          \
+    do {                                                                                                                           \
+      if (g.R == 3) maxpool_nhwc_win_kernel<T, V, 3, 3><<<pool_grid(g, V), 256, 0, s>>>(g, (const T*)x, (T*)y);                    \
+      else maxpool_nhwc_win_kernel<T, V, 2, 2><<<pool_grid(g, V), 256, 0, s>>>(g, (const T*)x, (T*)y);                             \
+      return check_launch();                                                                                                       \
+    } while (0)
+    if (dt == DT_F16 && g.C % 8 == 0) B2_POOL_WIN(__half, 8);
+    if (dt == DT_BF16 && g.C % 8 == 0) B2_POOL_WIN(__nv_bfloat16, 8);
+    if (dt == DT_S8 && g.C % 16 == 0) B2_POOL_WIN(int8_t, 16);
+    if (dt == DT_F32 && g.C % 4 == 0) B2_POOL_WIN(float, 4);
+#undef B2_POOL_WIN
+  }
   if (is_max && nhwc_dense && aligned) {
     if (dt == DT_F16 && g.C % 8 == 0) { maxpool_nhwc_vec_kernel<__half, 8><<<pool_grid(g, 8), 256, 0, s>>>(g, (const __half*)x, (__half*)y); return check_launch(); }
     if (dt == DT_BF16 && g.C % 8 == 0) { maxpool_nhwc_vec_kernel<__nv_bfloat16, 8><<<pool_grid(g, 8), 256, 0, s>>>(g, (const __nv_bfloat16*)x, (__nv_bfloat16*)y); return check_launch(); }

@@ -80,7 +80,7 @@ struct UmmaParams {
   int pair;            // 1: two CTAs of a cluster share each 256-row tile (tcgen05 cta_group::2), each loading half of B
   int bn_load;         // rows of B this CTA brings into shared memory per k-block (BN, or BN/2 in pair mode)
   int store_mode, store_S, store_NH;  // permuted store through a 4-d map (see UmmaConv)
-  int epi_mode;        // kernel variant: 0 direct, 1 staged straight-line form, 2 staged general form
+  int epi_mode;        // kernel variant: 0 direct, 1 staged straight-line forms, 2 staged general form, 3 staged straight-line LeakyReLU form
   int fast_variant;    // mode 1: accumulator conversion (0 fp32, 1 int32 by conversion, 2 int32 by integer add) * 2 + residual
   int tmem_cols;
   uint32_t spin_limit;  // attempts before a bounded wait gives up
@@ -784,7 +784,64 @@ __device__ __forceinline__ void box_fast(const UmmaParams& p, uint32_t taddr, in
   }
 }
 
+// The Darknet layer form as straight-line code (MODE 3): fp32 accumulators, one per-channel addend, LeakyReLU with a
+// slope in [0, 1], then (optionally) the residual tile, two-byte outputs.  For such a slope x < 0 ? fl(a*x) : x equals
+// max(x, fl(a*x)): the product rounds monotonically and keeps the sign.
+template <int OUT, bool RES>
+__device__ __forceinline__ void chunk_leaky(const uint32_t (&r)[16], const float* __restrict__ addv, float slope, const StagePos& sp) {
+  float v[16], cv[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) { const float4 f = __ldg((const float4*)addv + q); cv[4 * q] = f.x; cv[4 * q + 1] = f.y; cv[4 * q + 2] = f.z; cv[4 * q + 3] = f.w; }
+#pragma unroll
+  for (int j = 0; j < 16; j += 2) {
+    fadd2_rn(v[j], v[j + 1], cv[j], cv[j + 1]);
+    float t0 = v[j], t1 = v[j + 1];
+    fmul2_rn(t0, t1, slope, slope);
+    v[j] = fmaxf(v[j], t0); v[j + 1] = fmaxf(v[j + 1], t1);   // (a maximum between the product and any later sum: nothing to contract)
+  }
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    uint4 u;
+    if (RES) {
+      u = lds128(stage_piece(sp, q));
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float2 f = OUT == DT_F16 ? __half22float2(((const __half2*)&u)[t]) : __bfloat1622float2(((const __nv_bfloat162*)&u)[t]);
+        fadd2_rn(v[q * 8 + 2 * t], v[q * 8 + 2 * t + 1], f.x, f.y);
+      }
+    }
+    if (OUT == DT_F16) {
+      __half2* h = (__half2*)&u;
+#pragma unroll
+      for (int t = 0; t < 4; ++t) h[t] = __floats2half2_rn(v[q * 8 + 2 * t], v[q * 8 + 2 * t + 1]);
+    } else {
+      __nv_bfloat162* h = (__nv_bfloat162*)&u;
+#pragma unroll
+      for (int t = 0; t < 4; ++t) h[t] = __floats2bfloat162_rn(v[q * 8 + 2 * t], v[q * 8 + 2 * t + 1]);
+    }
+    sts128(stage_piece(sp, q), u);
+  }
+}
+template <int OUT, bool RES>
+__device__ __forceinline__ void box_leaky(const UmmaParams& p, uint32_t taddr, int first, int last, int step, int n0, int bx, int chunks_per_box, StagePos sp) {
+  const float slope = p.ep.act_a;
+  const float* addv = p.ep.add1 ? p.ep.add1 : p.ep.add2;
+#pragma unroll 1
+  for (int ch = first; ch < last; ch += step) {
+    const int col0 = n0 + ch * 16;
+    if (col0 >= p.K_out) break;
+    uint32_t r[16];
+    tmem_ld16(taddr + (uint32_t)(ch * 16), r);
+    tmem_ld_wait_regs<16>(r);
+    sp.j0 = (ch - bx * chunks_per_box) << 1;
+    chunk_leaky<OUT, RES>(r, addv + col0, slope, sp);
+  }
+}
+
 // --------------------------------------------------------------------- kernel ----
+// MODE 3: staged epilogue, straight-line Darknet form (box_leaky): LeakyReLU before the optional residual, two-byte outputs.
 // MODE 0: direct epilogue (any output type, rows written straight to global memory).
 // MODE 1: staged epilogue, straight-line forms (box_fast): activation none / ReLU after the residual, one per-channel
 //         addend, int8 requantisation by multiplication.
@@ -1104,6 +1161,11 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 case 4: box_fast<OUT, 2, false>(p, taddr, first, last, step, n0, bx, chunks_per_box, sp, fast_lo, fast_floor); break;
                 default: box_fast<OUT, 2, true>(p, taddr, first, last, step, n0, bx, chunks_per_box, sp, fast_lo, fast_floor); break;
               }
+            } else if constexpr (MODE == 3) {
+              if constexpr (OUT == DT_F16 || OUT == DT_BF16) {
+                if (p.ep.res) box_leaky<OUT, true>(p, taddr, first, last, step, n0, bx, chunks_per_box, sp);
+                else box_leaky<OUT, false>(p, taddr, first, last, step, n0, bx, chunks_per_box, sp);
+              }
             } else {
 #pragma unroll 1
             for (int ch = first; ch < last; ch += step) {
@@ -1340,7 +1402,12 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
   // what the straight-line epilogue assumes (see chunk_fast); everything else takes the general staged form
   const bool fast_ok = plain_act && c.K % 16 == 0 && ep.alpha == 1.f && ((ep.add1 != nullptr) != (ep.add2 != nullptr)) &&
                        ((ep.mul != nullptr) == (c.in_dt == DT_S8)) && (ep.out_dt != DT_S8 || c.in_dt == DT_S8) && !getenv("ODLA_B200_GENERAL_EPILOGUE");
-  p.epi_mode = !p.staged ? 0 : (fast_ok ? 1 : 2);
+  // the Darknet form (see chunk_leaky): LeakyReLU with a slope in [0, 1] straight after the per-channel addend, a
+  // residual (if any) after the activation, fp32 accumulators, two-byte outputs
+  const bool leaky_ok = ep.act == ACT_LEAKY && ep.act_a >= 0.f && ep.act_a <= 1.f && (!ep.res || ep.act_first) && c.K % 16 == 0 && ep.alpha == 1.f &&
+                        ((ep.add1 != nullptr) != (ep.add2 != nullptr)) && !ep.mul && c.in_dt != DT_S8 && (ep.out_dt == DT_F16 || ep.out_dt == DT_BF16) &&
+                        !getenv("ODLA_B200_GENERAL_EPILOGUE");
+  p.epi_mode = !p.staged ? 0 : (fast_ok ? 1 : (leaky_ok ? 3 : 2));
   p.fast_variant = (c.in_dt == DT_S8 ? (ep.acc_small ? 2 : 1) : 0) * 2 + (ep.res ? 1 : 0);
   // Shared memory: pipeline stages first (up to 4, or what one tile needs), then as many staging
   // boxes as fit (at least one tile's worth, at most 8) so residual loads run ahead of the epilogue
@@ -1500,7 +1567,7 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
 #define B2_SMEM(O, M)                                                                                                              \
   (cudaFuncSetAttribute(umma_conv_kernel<O, M, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess && \
    cudaFuncSetAttribute(umma_conv_kernel<O, M, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess)
-    bool ok = B2_SMEM(DT_F16, 1) && B2_SMEM(DT_BF16, 1) && B2_SMEM(DT_S8, 1) && B2_SMEM(DT_F16, 2) && B2_SMEM(DT_BF16, 2) && B2_SMEM(DT_S8, 2) && B2_SMEM(-1, 0);
+    bool ok = B2_SMEM(DT_F16, 1) && B2_SMEM(DT_BF16, 1) && B2_SMEM(DT_S8, 1) && B2_SMEM(DT_F16, 2) && B2_SMEM(DT_BF16, 2) && B2_SMEM(DT_S8, 2) && B2_SMEM(DT_F16, 3) && B2_SMEM(DT_BF16, 3) && B2_SMEM(-1, 0);
 #undef B2_SMEM
     if (!ok) { cudaGetLastError(); delete L; return nullptr; }
     attr_set[dev] = true;
@@ -1540,6 +1607,7 @@ int umma_conv_run(UmmaLaunch* L, cudaStream_t stream) {
               : cudaLaunchKernelEx(&cfg, umma_conv_kernel<O, M, false>, L->tmA, L->tmB, L->tmY, L->tmR, p)
   if (p.epi_mode == 0) B2_LAUNCH(-1, 0);
   else if (p.epi_mode == 1) { if (p.ep.out_dt == DT_F16) B2_LAUNCH(DT_F16, 1); else if (p.ep.out_dt == DT_BF16) B2_LAUNCH(DT_BF16, 1); else B2_LAUNCH(DT_S8, 1); }
+  else if (p.epi_mode == 3) { if (p.ep.out_dt == DT_F16) B2_LAUNCH(DT_F16, 3); else B2_LAUNCH(DT_BF16, 3); }
   else { if (p.ep.out_dt == DT_F16) B2_LAUNCH(DT_F16, 2); else if (p.ep.out_dt == DT_BF16) B2_LAUNCH(DT_BF16, 2); else B2_LAUNCH(DT_S8, 2); }
 #undef B2_LAUNCH
   if (le != cudaSuccess) { fprintf(stderr, "[odla_b200] umma_conv launch failed: %s\n", cudaGetErrorString(le)); cudaGetLastError(); return -2; }
