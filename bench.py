@@ -568,6 +568,7 @@ def run_secondary(args, rank, world, local_rank):
     g = odla.Graph(lib, args.workload, fp16=True, n_gpus=1)
     build(g)
     g.context()
+    ctx2 = g.extra_context() if args.contexts > 1 else None   # a second context (own lane) for the pipelined end-to-end leg
     g_host = odla.Graph(lib, args.workload + "_host", fp16=True, n_gpus=1, sub_batches=args.sub_batches)
     build(g_host)
     g_host.context()
@@ -601,12 +602,49 @@ def run_secondary(args, rank, world, local_rank):
         barrier()
         return max_over_ranks(ms)
 
+    def timed_pipelined(ctxs, bufs):
+        """K steps with two executes in flight (odla_AsyncExecuteComputation on two contexts of one computation), every
+        step copying its own inputs from pinned host memory and its outputs back; wall clock, max over ranks."""
+        for c, (xs, ys) in zip(ctxs, bufs):
+            for k, v in xs.items():
+                c.bind_input(k, v.data_ptr())
+            for k, v in ys.items():
+                c.bind_output(k, v.data_ptr())
+
+        def run(n):
+            for i in range(n):
+                c = ctxs[i % len(ctxs)]
+                if c.wait() != 0 or c.execute_async() != 0:
+                    raise RuntimeError("asynchronous execute failed")
+            for c in ctxs:
+                if c.wait() != 0:
+                    raise RuntimeError("asynchronous execute failed")
+        run(max(args.warmup, len(ctxs)))
+        barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        run(args.steps)
+        wall = (time.perf_counter() - t0) * 1e3
+        barrier()
+        return max_over_ranks(wall)
+
     sampler = ClockSampler(local_rank)
     dev_ms = timed(g, x_dev, y_dev, sampler)
     clocks = sampler.summary()
     launches = g.launches() * args.steps
     e2e_ms = timed(g_host, x_host, y_host)
     total = sum_over_ranks(batch * args.steps)
+    e2e = {"value": total / (e2e_ms / 1e3), "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps,
+           "sub_batches": args.sub_batches, "executes_in_flight": 1}
+    if ctx2 is not None:
+        x_host2 = {k: v.clone().pin_memory() for k, v in x_host.items()}
+        y_host2 = {k: torch.empty_like(v).pin_memory() for k, v in y_host.items()}
+        pipe_ms = timed_pipelined([g, ctx2], [(x_host, y_host), (x_host2, y_host2)])
+        for k in y_host:
+            if not torch.equal(y_host[k], y_host2[k]):
+                raise RuntimeError("the two contexts disagree on the same input")
+        e2e = {"value": total / (pipe_ms / 1e3), "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": pipe_ms / args.steps,
+               "sub_batches": 1, "executes_in_flight": 2, "one_at_a_time": e2e}
     prof = g.profile(runs=2)
     tc = [q for q in prof if q["op"].endswith("_umma")]
     tc_ms, tc_flops = sum(q["ms"] for q in tc), sum(q["flops"] for q in tc)
@@ -644,8 +682,7 @@ def run_secondary(args, rank, world, local_rank):
             "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": name, "batch_per_gpu": batch, "l2": "256 MiB buffer written between steps", "parallelism": "dp%d" % world,
                        "work_per_unit_gflop": 2 * mac / 1e9},
-            "e2e": {"value": total / (e2e_ms / 1e3), "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps,
-                    "sub_batches": args.sub_batches},
+            "e2e": e2e,
             "gpu_launches": launches, "clocks": clocks,
             "roofline": {"bound": "tensor", "kernel": "umma_conv_kernel (%d launches per step)" % len(tc), "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak if peak else None, "peak_source": peak_kind + " bf16 sustained", "share_of_step": tc_ms / max(all_ms, 1e-9),
