@@ -314,6 +314,31 @@ __global__ void binary_same_h8_kernel(int op, const uint4* __restrict__ l, const
     y[i] = a;
   }
 }
+// Two-byte left operand and result, right operand repeating with a period (a trailing-dims broadcast such as a bias
+// vector or a position table), stored in the same type or in fp32: eight elements per thread.  Same arithmetic as
+// binary_kernel: one fp32 operation, one rounding to the type.
+template <typename T, typename RT>
+__global__ void binary_period_vec_kernel(int op, const uint4* __restrict__ l, const RT* __restrict__ r, uint4* __restrict__ y, int64_t n8, int64_t period8,
+                                         int act, float act_a) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
+    uint4 a = l[i];
+    const int64_t j = (i % period8) * 8;
+    float b[8];
+    if (sizeof(RT) == 4) {
+      const float4 b0 = *(const float4*)((const float*)r + j), b1 = *(const float4*)((const float*)r + j + 4);
+      b[0] = b0.x; b[1] = b0.y; b[2] = b0.z; b[3] = b0.w; b[4] = b1.x; b[5] = b1.y; b[6] = b1.z; b[7] = b1.w;
+    } else {
+      const uint4 bv = *(const uint4*)((const T*)r + j);
+      const T* hb = (const T*)&bv;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) b[k] = (float)hb[k];
+    }
+    T* ha = (T*)&a;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) ha[k] = (T)apply_act(act, binary_one(op, (float)ha[k], b[k]), act_a, 0.f);
+    y[i] = a;
+  }
+}
 __global__ void channel_affine_kernel(int dt, const void* x, void* y, const float* a, const float* b, int64_t total, int64_t C,
                                       int64_t inner) {
   for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
@@ -410,10 +435,12 @@ __global__ void softmax_rows_vec_kernel(const uint4* __restrict__ x, uint4* __re
     for (int i = 0; i < NP; ++i)
       if (have[i]) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) { v[i][j] -= mx; e[i][j] = expf(v[i][j]); sum += e[i][j]; }
+        for (int j = 0; j < 8; ++j) { v[i][j] -= mx; e[i][j] = __expf(v[i][j]); sum += e[i][j]; }
       }
     sum = group_sum<LPR>(sum);
-    const float lsum = logf(sum);
+    // The results are rounded to a two-byte type: the fast exponential (2 ulp of fp32) and one reciprocal per row instead
+    // of a division per element stay far inside that rounding step.
+    const float lsum = log_form ? logf(sum) : 0.f, inv = __fdiv_rn(1.0f, sum);
 #pragma unroll
     for (int i = 0; i < NP; ++i)
       if (have[i]) {
@@ -421,8 +448,8 @@ __global__ void softmax_rows_vec_kernel(const uint4* __restrict__ x, uint4* __re
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
           // e[][] holds exp(x - max) from the summation pass
-          const float a = log_form ? v[i][2 * t] - lsum : __fdiv_rn(e[i][2 * t], sum);
-          const float b = log_form ? v[i][2 * t + 1] - lsum : __fdiv_rn(e[i][2 * t + 1], sum);
+          const float a = log_form ? v[i][2 * t] - lsum : e[i][2 * t] * inv;
+          const float b = log_form ? v[i][2 * t + 1] - lsum : e[i][2 * t + 1] * inv;
           w[t] = float2_to_pair<T>(a, b);
         }
         y[row * pieces + l + LPR * i] = make_uint4(w[0], w[1], w[2], w[3]);
@@ -786,6 +813,27 @@ int binary(int op, const BinaryGeom& g, int dt_l, int dt_r, int dt_out, const vo
       (uintptr_t)r % 16 == 0 && (uintptr_t)y % 16 == 0) {
     binary_same_h8_kernel<<<grid_for(total / 8, 256), 256, 0, s>>>(op, (const uint4*)l, (const uint4*)r, (uint4*)y, total / 8, act, act_a);
     return check_launch();
+  }
+  // left operand dense, right operand a broadcast over the leading dims (zero strides there, dense strides after)
+  if ((dt_out == DT_F16 || dt_out == DT_BF16) && dt_l == dt_out && (dt_r == dt_out || dt_r == DT_F32) && total % 8 == 0 && (uintptr_t)l % 16 == 0 &&
+      (uintptr_t)r % 16 == 0 && (uintptr_t)y % 16 == 0) {
+    bool l_dense = true, r_suffix = true, in_suffix = true;
+    int64_t dense = 1, period = 1;
+    for (int d = g.rank - 1; d >= 0; --d) {
+      if (g.oshape[d] == 1) continue;
+      if (g.lstride[d] != dense) l_dense = false;
+      if (in_suffix && g.rstride[d] == dense) period = dense * g.oshape[d];
+      else { in_suffix = false; if (g.rstride[d] != 0) r_suffix = false; }
+      dense *= g.oshape[d];
+    }
+    if (l_dense && r_suffix && period % 8 == 0 && period >= 8) {
+      const int grid = grid_for(total / 8, 256);
+      if (dt_out == DT_F16 && dt_r == DT_F16) binary_period_vec_kernel<__half, __half><<<grid, 256, 0, s>>>(op, (const uint4*)l, (const __half*)r, (uint4*)y, total / 8, period / 8, act, act_a);
+      else if (dt_out == DT_F16) binary_period_vec_kernel<__half, float><<<grid, 256, 0, s>>>(op, (const uint4*)l, (const float*)r, (uint4*)y, total / 8, period / 8, act, act_a);
+      else if (dt_r == DT_BF16) binary_period_vec_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, s>>>(op, (const uint4*)l, (const __nv_bfloat16*)r, (uint4*)y, total / 8, period / 8, act, act_a);
+      else binary_period_vec_kernel<__nv_bfloat16, float><<<grid, 256, 0, s>>>(op, (const uint4*)l, (const float*)r, (uint4*)y, total / 8, period / 8, act, act_a);
+      return check_launch();
+    }
   }
   binary_kernel<<<grid_for(total, 256), 256, 0, s>>>(op, g, dt_l, dt_r, dt_out, l, r, y, total, act, act_a);
   return check_launch();

@@ -787,7 +787,22 @@ __device__ __forceinline__ void box_fast(const UmmaParams& p, uint32_t taddr, in
 // The Darknet layer form as straight-line code (MODE 3): fp32 accumulators, one per-channel addend, LeakyReLU with a
 // slope in [0, 1], then (optionally) the residual tile, two-byte outputs.  For such a slope x < 0 ? fl(a*x) : x equals
 // max(x, fl(a*x)): the product rounds monotonically and keeps the sign.
-template <int OUT, bool RES>
+// GELU (erf form) without branches: erf by Abramowitz & Stegun 7.1.26 (absolute error 1.5e-7; the whole expression stays
+// within 5e-7 of 0.5 x (1 + erf(x / sqrt 2)), a fraction of an fp16 or bf16 rounding step) -- the library erff takes two
+// different paths by magnitude, which a warp's 32 rows then both execute.  Used only where the result is rounded to a
+// two-byte type right after.
+__device__ __forceinline__ float gelu_erf_two_byte(float t) {
+  const float z = t * 0.70710678118654752440f, az = fabsf(z);
+  const float k = __fdividef(1.0f, fmaf(0.3275911f, az, 1.0f));
+  float poly = fmaf(1.061405429f, k, -1.453152027f);
+  poly = fmaf(poly, k, 1.421413741f);
+  poly = fmaf(poly, k, -0.284496736f);
+  poly = fmaf(poly, k, 0.254829592f);
+  const float y = copysignf(fmaf(-poly * k, __expf(-az * az), 1.0f), z);
+  return (0.5f * t) * (1.0f + y);
+}
+// ACTF 0: LeakyReLU, 1: GELU (erf form)
+template <int OUT, int ACTF, bool RES>
 __device__ __forceinline__ void chunk_leaky(const uint32_t (&r)[16], const float* __restrict__ addv, float slope, const StagePos& sp) {
   float v[16], cv[16];
 #pragma unroll
@@ -797,9 +812,13 @@ __device__ __forceinline__ void chunk_leaky(const uint32_t (&r)[16], const float
 #pragma unroll
   for (int j = 0; j < 16; j += 2) {
     fadd2_rn(v[j], v[j + 1], cv[j], cv[j + 1]);
-    float t0 = v[j], t1 = v[j + 1];
-    fmul2_rn(t0, t1, slope, slope);
-    v[j] = fmaxf(v[j], t0); v[j + 1] = fmaxf(v[j + 1], t1);   // (a maximum between the product and any later sum: nothing to contract)
+    if (ACTF == 0) {
+      float t0 = v[j], t1 = v[j + 1];
+      fmul2_rn(t0, t1, slope, slope);
+      v[j] = fmaxf(v[j], t0); v[j + 1] = fmaxf(v[j + 1], t1);   // (a maximum between the product and any later sum: nothing to contract)
+    } else {
+      v[j] = gelu_erf_two_byte(v[j]); v[j + 1] = gelu_erf_two_byte(v[j + 1]);
+    }
   }
 #pragma unroll
   for (int q = 0; q < 2; ++q) {
@@ -824,7 +843,7 @@ __device__ __forceinline__ void chunk_leaky(const uint32_t (&r)[16], const float
     sts128(stage_piece(sp, q), u);
   }
 }
-template <int OUT, bool RES>
+template <int OUT, int ACTF, bool RES>
 __device__ __forceinline__ void box_leaky(const UmmaParams& p, uint32_t taddr, int first, int last, int step, int n0, int bx, int chunks_per_box, StagePos sp) {
   const float slope = p.ep.act_a;
   const float* addv = p.ep.add1 ? p.ep.add1 : p.ep.add2;
@@ -836,12 +855,64 @@ __device__ __forceinline__ void box_leaky(const UmmaParams& p, uint32_t taddr, i
     tmem_ld16(taddr + (uint32_t)(ch * 16), r);
     tmem_ld_wait_regs<16>(r);
     sp.j0 = (ch - bx * chunks_per_box) << 1;
-    chunk_leaky<OUT, RES>(r, addv + col0, slope, sp);
+    chunk_leaky<OUT, ACTF, RES>(r, addv + col0, slope, sp);
+  }
+}
+
+// The int8 form of a transformer's first feed-forward layer: int32 accumulators, per-channel multiplier and addend,
+// GELU, requantisation by multiplication to int8.  ACC as in chunk_fast (1: conversion, 2: exact integer-add form).
+template <int ACC>
+__device__ __forceinline__ void chunk_gelu_s8(const uint32_t (&r)[16], const float* __restrict__ mulv, const float* __restrict__ addv, float out_inv, const StagePos& sp) {
+  float v[16], cv[16];
+  if (ACC == 2) {
+#pragma unroll
+    for (int j = 0; j < 16; j += 2) {
+      v[j] = __uint_as_float(r[j] + kMagicBits); v[j + 1] = __uint_as_float(r[j + 1] + kMagicBits);
+      fadd2_rn(v[j], v[j + 1], -kMagic, -kMagic);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = (float)(int32_t)r[j];
+  }
+#pragma unroll
+  for (int q = 0; q < 4; ++q) { const float4 f = __ldg((const float4*)mulv + q); cv[4 * q] = f.x; cv[4 * q + 1] = f.y; cv[4 * q + 2] = f.z; cv[4 * q + 3] = f.w; }
+#pragma unroll
+  for (int j = 0; j < 16; j += 2) fmul2_rn(v[j], v[j + 1], cv[j], cv[j + 1]);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) { const float4 f = __ldg((const float4*)addv + q); cv[4 * q] = f.x; cv[4 * q + 1] = f.y; cv[4 * q + 2] = f.z; cv[4 * q + 3] = f.w; }
+#pragma unroll
+  for (int j = 0; j < 16; ++j) v[j] = gelu_erf_two_byte(__fadd_rn(v[j], cv[j]));   // scalar sum after a packed product (see fadd2_rn)
+  uint4 u;
+  uint32_t* w = (uint32_t*)&u;
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    float q[4];
+#pragma unroll
+    for (int b = 0; b < 4; ++b) q[b] = __fadd_rn(fminf(fmaxf(__fmul_rn(v[t * 4 + b], out_inv), -128.f), 127.f), kMagic);
+    w[t] = __byte_perm(__byte_perm(__float_as_uint(q[0]), __float_as_uint(q[1]), 0x0040), __byte_perm(__float_as_uint(q[2]), __float_as_uint(q[3]), 0x0040), 0x5410);
+  }
+  sts128(stage_piece(sp, 0), u);
+}
+template <int ACC>
+__device__ __forceinline__ void box_gelu_s8(const UmmaParams& p, uint32_t taddr, int first, int last, int step, int n0, int bx, int chunks_per_box, StagePos sp) {
+  const float out_inv = p.ep.out_inv;
+  const float* mulv = p.ep.mul;
+  const float* addv = p.ep.add1 ? p.ep.add1 : p.ep.add2;
+#pragma unroll 1
+  for (int ch = first; ch < last; ch += step) {
+    const int col0 = n0 + ch * 16;
+    if (col0 >= p.K_out) break;
+    uint32_t r[16];
+    tmem_ld16(taddr + (uint32_t)(ch * 16), r);
+    tmem_ld_wait_regs<16>(r);
+    sp.j0 = ch - bx * chunks_per_box;
+    chunk_gelu_s8<ACC>(r, mulv + col0, addv + col0, out_inv, sp);
   }
 }
 
 // --------------------------------------------------------------------- kernel ----
-// MODE 3: staged epilogue, straight-line Darknet form (box_leaky): LeakyReLU before the optional residual, two-byte outputs.
+// MODE 3: staged epilogue, further straight-line forms: LeakyReLU before the optional residual (Darknet) or GELU, two-byte
+//         outputs (box_leaky); int8 operands, GELU, requantised int8 output (box_gelu_s8).
 // MODE 0: direct epilogue (any output type, rows written straight to global memory).
 // MODE 1: staged epilogue, straight-line forms (box_fast): activation none / ReLU after the residual, one per-channel
 //         addend, int8 requantisation by multiplication.
@@ -1162,9 +1233,14 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 default: box_fast<OUT, 2, true>(p, taddr, first, last, step, n0, bx, chunks_per_box, sp, fast_lo, fast_floor); break;
               }
             } else if constexpr (MODE == 3) {
+              if constexpr (OUT == DT_S8) {
+                if (p.ep.acc_small) box_gelu_s8<2>(p, taddr, first, last, step, n0, bx, chunks_per_box, sp);
+                else box_gelu_s8<1>(p, taddr, first, last, step, n0, bx, chunks_per_box, sp);
+              }
               if constexpr (OUT == DT_F16 || OUT == DT_BF16) {
-                if (p.ep.res) box_leaky<OUT, true>(p, taddr, first, last, step, n0, bx, chunks_per_box, sp);
-                else box_leaky<OUT, false>(p, taddr, first, last, step, n0, bx, chunks_per_box, sp);
+                if (p.ep.act == ACT_GELU_ERF) box_leaky<OUT, 1, false>(p, taddr, first, last, step, n0, bx, chunks_per_box, sp);
+                else if (p.ep.res) box_leaky<OUT, 0, true>(p, taddr, first, last, step, n0, bx, chunks_per_box, sp);
+                else box_leaky<OUT, 0, false>(p, taddr, first, last, step, n0, bx, chunks_per_box, sp);
               }
             } else {
 #pragma unroll 1
@@ -1404,10 +1480,17 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
                        ((ep.mul != nullptr) == (c.in_dt == DT_S8)) && (ep.out_dt != DT_S8 || c.in_dt == DT_S8) && !getenv("ODLA_B200_GENERAL_EPILOGUE");
   // the Darknet form (see chunk_leaky): LeakyReLU with a slope in [0, 1] straight after the per-channel addend, a
   // residual (if any) after the activation, fp32 accumulators, two-byte outputs
-  const bool leaky_ok = ep.act == ACT_LEAKY && ep.act_a >= 0.f && ep.act_a <= 1.f && (!ep.res || ep.act_first) && c.K % 16 == 0 && ep.alpha == 1.f &&
+  // (the same kernel carries the GELU form of a transformer's first feed-forward layer: no residual there)
+  const bool act_form = (ep.act == ACT_LEAKY && ep.act_a >= 0.f && ep.act_a <= 1.f && (!ep.res || ep.act_first)) ||
+                        (ep.act == ACT_GELU_ERF && !ep.res && !getenv("ODLA_B200_EXACT_ERF"));
+  const bool leaky_ok = act_form && c.K % 16 == 0 && ep.alpha == 1.f &&
                         ((ep.add1 != nullptr) != (ep.add2 != nullptr)) && !ep.mul && c.in_dt != DT_S8 && (ep.out_dt == DT_F16 || ep.out_dt == DT_BF16) &&
                         !getenv("ODLA_B200_GENERAL_EPILOGUE");
-  p.epi_mode = !p.staged ? 0 : (fast_ok ? 1 : (leaky_ok ? 3 : 2));
+  // ... and its int8 form: int8 operands, multiplier + addend, GELU, requantised int8 output
+  const bool gelu_s8_ok = ep.act == ACT_GELU_ERF && !ep.res && c.in_dt == DT_S8 && ep.out_dt == DT_S8 && ep.mul && ep.out_multiply && ep.out_inv > 0.f &&
+                          c.K % 16 == 0 && ep.alpha == 1.f && ((ep.add1 != nullptr) != (ep.add2 != nullptr)) &&
+                          !getenv("ODLA_B200_EXACT_ERF") && !getenv("ODLA_B200_GENERAL_EPILOGUE");
+  p.epi_mode = !p.staged ? 0 : (fast_ok ? 1 : ((leaky_ok || gelu_s8_ok) ? 3 : 2));
   p.fast_variant = (c.in_dt == DT_S8 ? (ep.acc_small ? 2 : 1) : 0) * 2 + (ep.res ? 1 : 0);
   // Shared memory: pipeline stages first (up to 4, or what one tile needs), then as many staging
   // boxes as fit (at least one tile's worth, at most 8) so residual loads run ahead of the epilogue
@@ -1567,7 +1650,7 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& c, const void* x, const void* w, v
 #define B2_SMEM(O, M)                                                                                                              \
   (cudaFuncSetAttribute(umma_conv_kernel<O, M, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess && \
    cudaFuncSetAttribute(umma_conv_kernel<O, M, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess)
-    bool ok = B2_SMEM(DT_F16, 1) && B2_SMEM(DT_BF16, 1) && B2_SMEM(DT_S8, 1) && B2_SMEM(DT_F16, 2) && B2_SMEM(DT_BF16, 2) && B2_SMEM(DT_S8, 2) && B2_SMEM(DT_F16, 3) && B2_SMEM(DT_BF16, 3) && B2_SMEM(-1, 0);
+    bool ok = B2_SMEM(DT_F16, 1) && B2_SMEM(DT_BF16, 1) && B2_SMEM(DT_S8, 1) && B2_SMEM(DT_F16, 2) && B2_SMEM(DT_BF16, 2) && B2_SMEM(DT_S8, 2) && B2_SMEM(DT_F16, 3) && B2_SMEM(DT_BF16, 3) && B2_SMEM(DT_S8, 3) && B2_SMEM(-1, 0);
 #undef B2_SMEM
     if (!ok) { cudaGetLastError(); delete L; return nullptr; }
     attr_set[dev] = true;
@@ -1607,7 +1690,7 @@ int umma_conv_run(UmmaLaunch* L, cudaStream_t stream) {
               : cudaLaunchKernelEx(&cfg, umma_conv_kernel<O, M, false>, L->tmA, L->tmB, L->tmY, L->tmR, p)
   if (p.epi_mode == 0) B2_LAUNCH(-1, 0);
   else if (p.epi_mode == 1) { if (p.ep.out_dt == DT_F16) B2_LAUNCH(DT_F16, 1); else if (p.ep.out_dt == DT_BF16) B2_LAUNCH(DT_BF16, 1); else B2_LAUNCH(DT_S8, 1); }
-  else if (p.epi_mode == 3) { if (p.ep.out_dt == DT_F16) B2_LAUNCH(DT_F16, 3); else B2_LAUNCH(DT_BF16, 3); }
+  else if (p.epi_mode == 3) { if (p.ep.out_dt == DT_F16) B2_LAUNCH(DT_F16, 3); else if (p.ep.out_dt == DT_BF16) B2_LAUNCH(DT_BF16, 3); else B2_LAUNCH(DT_S8, 3); }
   else { if (p.ep.out_dt == DT_F16) B2_LAUNCH(DT_F16, 2); else if (p.ep.out_dt == DT_BF16) B2_LAUNCH(DT_BF16, 2); else B2_LAUNCH(DT_S8, 2); }
 #undef B2_LAUNCH
   if (le != cudaSuccess) { fprintf(stderr, "[odla_b200] umma_conv launch failed: %s\n", cudaGetErrorString(le)); cudaGetLastError(); return -2; }
