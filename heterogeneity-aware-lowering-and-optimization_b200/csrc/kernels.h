@@ -151,6 +151,10 @@ int reduce_mean_axis(int dt_in, int dt_out, const void* x, void* y, int64_t befo
                      cudaStream_t stream, float in_scale = 1.f);  // in_scale: dequantisation scale of an int8 input
 int layernorm(int dt, const void* x, void* y, const float* gamma, const float* beta, int64_t rows, int64_t dim,
               float eps, cudaStream_t stream);
+// The same, also writing q = sat(rne(y / scale[0])) as int8 for the rounded two-byte result y (what a per-tensor
+// odla_Quantize of y gives); dt must be DT_F16 or DT_BF16.
+int layernorm_quantize(int dt, const void* x, void* y, const float* gamma, const float* beta, int64_t rows, int64_t dim, float eps, void* q,
+                       const float* scale, cudaStream_t stream);
 
 // q = sat(rne(x / scale[a]) + zp[a]); x = (q - zp[a]) * scale[a]; (outer, adim, inner) split.
 int quantize(int dt_in, const void* x, void* q, const float* scale, const int* zp, int64_t outer, int64_t adim,

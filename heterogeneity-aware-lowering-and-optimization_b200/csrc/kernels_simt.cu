@@ -347,6 +347,26 @@ __global__ void channel_affine_kernel(int dt, const void* x, void* y, const floa
   }
 }
 
+// rintf(x / s) for a divisor that stays the same over a whole tensor, without a division per element: x * fl(1 / s) is
+// within two units in the last place of the quotient, so its nearest integer is the quotient's unless the quotient lies
+// that close to a half-integer -- only then is the division done.  Beyond +-256 both round far outside the int8 range and
+// saturate alike.  `QuantDiv` holds s, fl(1 / s) and whether the shortcut is safe for this s (a normal reciprocal).
+struct QuantDiv {
+  float s, inv;
+  bool fast;
+  __device__ __forceinline__ explicit QuantDiv(float scale) {
+    s = scale;
+    inv = __fdiv_rn(1.0f, scale);
+    fast = scale > 1e-30f && scale < 1e30f;
+  }
+  __device__ __forceinline__ float rint_div(float x) const {
+    if (!fast) return rintf(__fdiv_rn(x, s));
+    const float q = x * inv, t = rintf(q);
+    if (fabsf(q) < 256.f && fabsf(fabsf(q - t) - 0.5f) < 1e-4f) return rintf(__fdiv_rn(x, s));
+    return t;
+  }
+};
+
 // ------------------------------------------------------ soft-max / reductions ----
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
@@ -458,7 +478,8 @@ __global__ void softmax_rows_vec_kernel(const uint4* __restrict__ x, uint4* __re
 }
 template <typename T, int NP, int LPR>
 __global__ void layernorm_rows_vec_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, const float* __restrict__ gamma, const float* __restrict__ beta,
-                                          int64_t rows, int pieces, float eps) {
+                                          int64_t rows, int pieces, float eps, uint2* __restrict__ qout, const float* __restrict__ qscale) {
+  const QuantDiv qd(qout ? qscale[0] : 1.f);
   constexpr int RPW = 32 / LPR;
   const int lane = threadIdx.x & 31, l = lane % LPR;
   const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
@@ -501,12 +522,23 @@ __global__ void layernorm_rows_vec_kernel(const uint4* __restrict__ x, uint4* __
           w[t] = float2_to_pair<T>(a, b);
         }
         y[row * pieces + l + LPR * i] = make_uint4(w[0], w[1], w[2], w[3]);
+        if (qout) {   // the int8 copy quantises the values as stored (after their rounding to the two-byte type)
+          uint32_t b[8];
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const float2 f = pair_to_float2<T>(w[t]);
+            b[2 * t] = (uint32_t)(sat_s8(qd.rint_div(f.x)) & 0xff);
+            b[2 * t + 1] = (uint32_t)(sat_s8(qd.rint_div(f.y)) & 0xff);
+          }
+          qout[row * pieces + l + LPR * i] = make_uint2(b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24), b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24));
+        }
       }
   }
 }
 template <typename T>
 bool launch_rows_vec(bool is_softmax, const void* x, void* y, const float* gamma, const float* beta, int64_t rows, int64_t dim, float eps, int log_form,
-                     cudaStream_t s) {
+                     cudaStream_t s, void* q = nullptr, const float* qscale = nullptr) {
+  if ((uintptr_t)q % 8 != 0) return false;
   if (dim % 8 != 0 || dim > 8 * 32 * 8 || (uintptr_t)x % 16 != 0 || (uintptr_t)y % 16 != 0 || (uintptr_t)gamma % 16 != 0 || (uintptr_t)beta % 16 != 0) return false;
   const int pieces = (int)(dim / 8);
   const int lpr = pieces <= 8 ? 8 : (pieces <= 16 ? 16 : 32), np = (pieces + lpr - 1) / lpr;
@@ -514,7 +546,7 @@ bool launch_rows_vec(bool is_softmax, const void* x, void* y, const float* gamma
 #define B2_ROWS(NP, LPR)                                                                                                                      \
   do {                                                                                                                                        \
     if (is_softmax) softmax_rows_vec_kernel<T, NP, LPR><<<grid, 256, 0, s>>>((const uint4*)x, (uint4*)y, rows, pieces, log_form);             \
-    else layernorm_rows_vec_kernel<T, NP, LPR><<<grid, 256, 0, s>>>((const uint4*)x, (uint4*)y, gamma, beta, rows, pieces, eps);              \
+    else layernorm_rows_vec_kernel<T, NP, LPR><<<grid, 256, 0, s>>>((const uint4*)x, (uint4*)y, gamma, beta, rows, pieces, eps, (uint2*)q, qscale); \
   } while (0)
   if (lpr == 8) B2_ROWS(1, 8);
   else if (lpr == 16) B2_ROWS(1, 16);
@@ -580,15 +612,15 @@ __global__ void quantize_kernel(int dt_in, const void* x, void* q, const float* 
 }
 // Per-tensor fp32 -> int8, 16 elements per thread (four 16-byte loads, one 16-byte store).
 __global__ void quantize_f32_s8_vec_kernel(const float4* __restrict__ x, uint4* __restrict__ q, const float* scale, int64_t n16) {
-  float s = scale[0];
+  const QuantDiv qd(scale[0]);
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n16; i += (int64_t)gridDim.x * blockDim.x) {
     uint4 out;
     uint32_t* o = (uint32_t*)&out;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       float4 v = x[i * 4 + j];
-      int a = sat_s8(rintf(__fdiv_rn(v.x, s))), b = sat_s8(rintf(__fdiv_rn(v.y, s)));
-      int c = sat_s8(rintf(__fdiv_rn(v.z, s))), d = sat_s8(rintf(__fdiv_rn(v.w, s)));
+      int a = sat_s8(qd.rint_div(v.x)), b = sat_s8(qd.rint_div(v.y));
+      int c = sat_s8(qd.rint_div(v.z)), d = sat_s8(qd.rint_div(v.w));
       o[j] = (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) | ((uint32_t)(d & 0xff) << 24);
     }
     q[i] = out;
@@ -977,10 +1009,21 @@ int layernorm(int dt, const void* x, void* y, const float* gamma, const float* b
   layernorm_kernel<<<grid_for(rows * 32, 256), 256, 0, s>>>(dt, x, y, gamma, beta, rows, dim, eps);
   return check_launch();
 }
+int quantize(int dt_in, const void* x, void* q, const float* scale, const int* zp, int64_t outer, int64_t adim, int64_t inner,
+             bool per_axis, bool is_unsigned, cudaStream_t s);
+int layernorm_quantize(int dt, const void* x, void* y, const float* gamma, const float* beta, int64_t rows, int64_t dim, float eps, void* q,
+                       const float* scale, cudaStream_t s) {
+  if (rows * dim <= 0) return 0;
+  if (dt == DT_F16 && launch_rows_vec<__half>(false, x, y, gamma, beta, rows, dim, eps, 0, s, q, scale)) return check_launch();
+  if (dt == DT_BF16 && launch_rows_vec<__nv_bfloat16>(false, x, y, gamma, beta, rows, dim, eps, 0, s, q, scale)) return check_launch();
+  // rows the vector kernel does not take: the two passes one after the other
+  if (int rc = layernorm(dt, x, y, gamma, beta, rows, dim, eps, s)) return rc;
+  return quantize(dt, y, q, scale, nullptr, 1, 1, rows * dim, false, false, s);
+}
 // Per-tensor two-byte float -> int8, 16 elements per thread (two 16-byte loads, one 16-byte store).
 template <typename T>
 __global__ void quantize_h_s8_vec_kernel(const uint4* __restrict__ x, uint4* __restrict__ q, const float* scale, int64_t n16) {
-  const float s = scale[0];
+  const QuantDiv qd(scale[0]);
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n16; i += (int64_t)gridDim.x * blockDim.x) {
     uint4 out;
     uint32_t* o = (uint32_t*)&out;
@@ -991,8 +1034,8 @@ __global__ void quantize_h_s8_vec_kernel(const uint4* __restrict__ x, uint4* __r
 #pragma unroll
       for (int t = 0; t < 2; ++t) {
         const float2 f0 = pair_to_float2<T>(w[2 * t]), f1 = pair_to_float2<T>(w[2 * t + 1]);
-        const int a = sat_s8(rintf(__fdiv_rn(f0.x, s))), b = sat_s8(rintf(__fdiv_rn(f0.y, s)));
-        const int c = sat_s8(rintf(__fdiv_rn(f1.x, s))), d = sat_s8(rintf(__fdiv_rn(f1.y, s)));
+        const int a = sat_s8(qd.rint_div(f0.x)), b = sat_s8(qd.rint_div(f0.y));
+        const int c = sat_s8(qd.rint_div(f1.x)), d = sat_s8(qd.rint_div(f1.y));
         o[2 * h + t] = (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) | ((uint32_t)(d & 0xff) << 24);
       }
     }

@@ -148,6 +148,7 @@ struct Item {               // one launch-list entry before emission
   V out = nullptr;          // value it materialises
   std::vector<V> reads;     // materialised values it reads (after alias resolution)
   const Fused* fused = nullptr;
+  V extra_out = nullptr;    // a second value the same launch writes (the int8 copy a LayerNorm makes for a following Quantize)
 };
 
 class Builder {
@@ -165,6 +166,7 @@ class Builder {
   std::map<V, bool> carries_batch_;
   std::map<V, bool> from_acc_;         // computed from int32 accumulators through element-wise ops only
   std::map<V, V> fused_into_;          // node -> root of the chain that swallowed it
+  std::set<V> merged_;                 // Quantize nodes written by their producer's launch (see Item::extra_out)
   std::map<V, std::unique_ptr<Fused>> fused_;  // by root
   std::map<V, int> dq_unabsorbed_;     // Dequantize node -> number of consumers that need it in memory
   std::map<V, V> alias_;               // reshape output -> source
@@ -321,6 +323,7 @@ odla_status Builder::analyse() {
       continue;
     }
     if (v->kind == OP_RESHAPE) { alias_[v] = v->in[0]; continue; }
+    if (merged_.count(v)) continue;
     auto fi = fused_into_.find(v);
     if (fi != fused_into_.end() && fused_[fi->second]->out != v) continue;  // swallowed, not the chain end
     if (v->kind == OP_DEQUANTIZE && dq_unabsorbed_[v] == 0) continue;
@@ -342,6 +345,22 @@ odla_status Builder::analyse() {
         it.reads.push_back(through_dq ? i->in[0] : i);
       }
       dt_[v] = storage_of(v);
+      // LayerNorm over a two-byte tensor whose result is also wanted as int8 (the input of an int8 Gemm; the float
+      // copy feeds the residual): the row kernel writes both, the Quantize launch and its pass over the tensor go.
+      if (v->kind == OP_LAYERNORM && (dt_[v] == DT_F16 || dt_[v] == DT_BF16) && !getenv("ODLA_B200_NO_LN_QUANT")) {
+        const auto& sh = v->type.shape;
+        int64_t dim = 1;
+        for (int i = sh.size - (int)v->ia[0]; i < sh.size; ++i) if (i >= 0) dim *= sh.dims[i];
+        for (V cons : consumers_[v]) {
+          if (cons->kind != OP_QUANTIZE || cons->in[0] != v || cons->in[2] || !cons->in[1] || cons->in[1]->kind != OP_CONST) continue;
+          if (numel(cons->in[1]->type.shape) != 1 || cons->type.element_type != ODLA_INT8 || fused_into_.count(cons)) continue;
+          if (dim % 8 != 0 || dim > 2048 || dim < 8) continue;
+          it.extra_out = cons;
+          merged_.insert(cons);
+          dt_[cons] = DT_S8;
+          break;
+        }
+      }
     }
     items_.push_back(std::move(it));
   }
@@ -520,6 +539,11 @@ odla_status Builder::place() {
     V v = items_[i].out;
     Slot s; s.dt = dt_[v]; s.bytes = bytes_of(v); s.offset = arena.alloc(s.bytes);
     p_->slots[v] = s;
+    if (V e = items_[i].extra_out) {   // allocated while this item's inputs are still held: the launch writes it too
+      Slot se; se.dt = dt_[e]; se.bytes = bytes_of(e); se.offset = arena.alloc(se.bytes);
+      p_->slots[e] = se;
+      if (!last.count(e) && !outputs.count(e)) arena.release(se.offset, se.bytes);
+    }
     for (V r : items_[i].reads) {
       V rr = resolve(r);
       if (rr->kind == OP_ARG || rr->kind == OP_CONST || outputs.count(rr)) continue;
@@ -1157,6 +1181,13 @@ odla_status Builder::emit_plain(const Item& it) {
       const float* b = v->in[2] ? (const float*)const_dev(v->in[2], DT_F32) : nullptr;
       float eps = v->fa[0];
       if (xdt != odt) return fail(ODLA_INTERNAL_LOGIC_ERR, "'" + v->name + "': layernorm changes the storage type");
+      if (V qv = it.extra_out) {
+        void* q = dev_ptr(qv);
+        const float* qs = (const float*)const_dev(qv->in[1], DT_F32);
+        if (!q || !qs) return err_status_;
+        add_launch("layernorm", v, 0, 2 * out_bytes + tensor_bytes(qv), [=](cudaStream_t s) { return layernorm_quantize(odt, x, y, g, b, rows, dim, eps, q, qs, s); });
+        return ODLA_SUCCESS;
+      }
       add_launch("layernorm", v, 0, 2 * out_bytes, [=](cudaStream_t s) { return layernorm(odt, x, y, g, b, rows, dim, eps, s); });
       return ODLA_SUCCESS;
     }

@@ -240,3 +240,34 @@ def test_batched_gemm_with_untransposed_right_operand(odla, gpu_lib, mode, S, D,
     assert np.array_equal(got, via_copy)
     want = np.einsum("bhik,bhkd->bhid", pr.astype(np.float64), v.astype(np.float64))
     assert_within_ulps(got, want, mode, 1.0, floor=0.05)
+
+
+@pytest.mark.parametrize("mode", ["fp16", "bf16"])
+@pytest.mark.parametrize("dim", [64, 768, 2048, 40])
+def test_layernorm_writes_the_int8_copy_a_following_quantize_asks_for(odla, gpu_lib, mode, dim, monkeypatch):
+    """LayerNorm -> {float consumer, per-tensor Quantize}: the row kernel writes the int8 tensor as well, quantising the
+    values as they are stored, so both outputs are identical to the two-launch form (ODLA_B200_NO_LN_QUANT)."""
+    rows = 53
+    x = to_type(RNG.standard_normal((rows, dim)) * 2 + 0.25, mode)
+    gam = RNG.uniform(0.5, 1.5, dim).astype(np.float32)
+    bet = RNG.standard_normal(dim).astype(np.float32)
+
+    def run():
+        g = graph(odla, gpu_lib, mode)
+        a = g.Argument("x", (rows, dim))
+        ln = g.LayerNorm(a, (-1,), 1e-5, g.Constant("g", gam), g.Constant("b", bet), "ln")
+        g.Output(ln)
+        g.Output(g.Quantize(ln, g.Constant("s", np.array([0.03], np.float32)), None, 0, odla.INT8, "q"))
+        out = g.run({"x": x})
+        desc = g.describe(first_gpu_only=True)
+        g.close()
+        return out, desc
+    fused, desc = run()
+    assert "layernorm" in desc and "quantize" not in desc
+    monkeypatch.setenv("ODLA_B200_NO_LN_QUANT", "1")
+    plain, desc2 = run()
+    assert "quantize" in desc2
+    assert np.array_equal(fused["ln"], plain["ln"]) and np.array_equal(fused["q"], plain["q"])
+    want = np.clip(np.rint(fused["ln"].astype(np.float32) / np.float32(0.03)), -128, 127).astype(np.int8)
+    assert np.array_equal(fused["q"], want)
+    assert np.abs(fused["q"].astype(int)).max() > 20   # the comparison is not about zeros
