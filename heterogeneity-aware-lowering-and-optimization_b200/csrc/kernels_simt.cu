@@ -476,10 +476,10 @@ __global__ void softmax_rows_vec_kernel(const uint4* __restrict__ x, uint4* __re
       }
   }
 }
-template <typename T, int NP, int LPR>
+template <typename T, int NP, int LPR, bool QUANT>
 __global__ void layernorm_rows_vec_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, const float* __restrict__ gamma, const float* __restrict__ beta,
                                           int64_t rows, int pieces, float eps, uint2* __restrict__ qout, const float* __restrict__ qscale) {
-  const QuantDiv qd(qout ? qscale[0] : 1.f);
+  const QuantDiv qd(QUANT ? qscale[0] : 1.f);
   constexpr int RPW = 32 / LPR;
   const int lane = threadIdx.x & 31, l = lane % LPR;
   const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
@@ -503,7 +503,7 @@ __global__ void layernorm_rows_vec_kernel(const uint4* __restrict__ x, uint4* __
     for (int i = 0; i < NP; ++i)
       if (have[i]) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) { v[i][j] -= mean; q += v[i][j] * v[i][j]; }
+        for (int j = 0; j < 8; ++j) { v[i][j] -= mean; q = fmaf(v[i][j], v[i][j], q); }   // (spelled out: every instantiation rounds alike)
       }
     const float inv = 1.0f / sqrtf(group_sum<LPR>(q) / dim + eps);
 #pragma unroll
@@ -516,13 +516,13 @@ __global__ void layernorm_rows_vec_kernel(const uint4* __restrict__ x, uint4* __
         uint32_t w[4];
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
-          float a = v[i][2 * t] * inv, b = v[i][2 * t + 1] * inv;
-          if (gamma) { a *= gm[2 * t]; b *= gm[2 * t + 1]; }
-          if (beta) { a += bt[2 * t]; b += bt[2 * t + 1]; }
+          float a = __fmul_rn(v[i][2 * t], inv), b = __fmul_rn(v[i][2 * t + 1], inv);
+          if (gamma) { a = __fmul_rn(a, gm[2 * t]); b = __fmul_rn(b, gm[2 * t + 1]); }
+          if (beta) { a = __fadd_rn(a, bt[2 * t]); b = __fadd_rn(b, bt[2 * t + 1]); }
           w[t] = float2_to_pair<T>(a, b);
         }
         y[row * pieces + l + LPR * i] = make_uint4(w[0], w[1], w[2], w[3]);
-        if (qout) {   // the int8 copy quantises the values as stored (after their rounding to the two-byte type)
+        if (QUANT) {   // the int8 copy quantises the values as stored (after their rounding to the two-byte type)
           uint32_t b[8];
 #pragma unroll
           for (int t = 0; t < 4; ++t) {
@@ -546,12 +546,14 @@ bool launch_rows_vec(bool is_softmax, const void* x, void* y, const float* gamma
 #define B2_ROWS(NP, LPR)                                                                                                                      \
   do {                                                                                                                                        \
     if (is_softmax) softmax_rows_vec_kernel<T, NP, LPR><<<grid, 256, 0, s>>>((const uint4*)x, (uint4*)y, rows, pieces, log_form);             \
-    else layernorm_rows_vec_kernel<T, NP, LPR><<<grid, 256, 0, s>>>((const uint4*)x, (uint4*)y, gamma, beta, rows, pieces, eps, (uint2*)q, qscale); \
+    else if (q) layernorm_rows_vec_kernel<T, NP, LPR, true><<<grid, 256, 0, s>>>((const uint4*)x, (uint4*)y, gamma, beta, rows, pieces, eps, (uint2*)q, qscale); \
+    else layernorm_rows_vec_kernel<T, NP, LPR, false><<<grid, 256, 0, s>>>((const uint4*)x, (uint4*)y, gamma, beta, rows, pieces, eps, nullptr, nullptr); \
   } while (0)
   if (lpr == 8) B2_ROWS(1, 8);
   else if (lpr == 16) B2_ROWS(1, 16);
   else if (np <= 1) B2_ROWS(1, 32);
   else if (np <= 2) B2_ROWS(2, 32);
+  else if (np <= 3) B2_ROWS(3, 32);
   else if (np <= 4) B2_ROWS(4, 32);
   else B2_ROWS(8, 32);
 #undef B2_ROWS
