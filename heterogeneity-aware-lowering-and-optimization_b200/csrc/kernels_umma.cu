@@ -791,15 +791,36 @@ __device__ __forceinline__ void box_fast(const UmmaParams& p, uint32_t taddr, in
 // within 5e-7 of 0.5 x (1 + erf(x / sqrt 2)), a fraction of an fp16 or bf16 rounding step) -- the library erff takes two
 // different paths by magnitude, which a warp's 32 rows then both execute.  Used only where the result is rounded to a
 // two-byte type right after.
-__device__ __forceinline__ float gelu_erf_two_byte(float t) {
-  const float z = t * 0.70710678118654752440f, az = fabsf(z);
-  const float k = __fdividef(1.0f, fmaf(0.3275911f, az, 1.0f));
-  float poly = fmaf(1.061405429f, k, -1.453152027f);
-  poly = fmaf(poly, k, 1.421413741f);
-  poly = fmaf(poly, k, -0.284496736f);
-  poly = fmaf(poly, k, 0.254829592f);
-  const float y = copysignf(fmaf(-poly * k, __expf(-az * az), 1.0f), z);
-  return (0.5f * t) * (1.0f + y);
+// Two values at a time with the packed fp32 instructions (fma / mul / add .f32x2): the polynomial and the
+// scalings take half the issue slots; reciprocal, exponential, absolute value and sign transfer stay scalar.
+__device__ __forceinline__ void ffma2(float& a0, float& a1, float b0, float b1, float c0, float c1) {   // a = a * b + c
+  asm("{\n\t.reg .b64 x, y, z;\n\tmov.b64 x, {%0, %1};\n\tmov.b64 y, {%2, %3};\n\tmov.b64 z, {%4, %5};\n\tfma.rn.f32x2 x, x, y, z;\n\tmov.b64 {%0, %1}, x;\n\t}"
+      : "+f"(a0), "+f"(a1)
+      : "f"(b0), "f"(b1), "f"(c0), "f"(c1));
+}
+__device__ __forceinline__ void gelu_erf_two_byte_pair(float& t0, float& t1) {
+  float z0 = t0, z1 = t1;
+  fmul2_rn(z0, z1, 0.70710678118654752440f, 0.70710678118654752440f);
+  const float a0 = fabsf(z0), a1 = fabsf(z1);
+  float d0 = a0, d1 = a1;
+  ffma2(d0, d1, 0.3275911f, 0.3275911f, 1.0f, 1.0f);
+  const float k0 = __fdividef(1.0f, d0), k1 = __fdividef(1.0f, d1);
+  float p0 = k0, p1 = k1;
+  ffma2(p0, p1, 1.061405429f, 1.061405429f, -1.453152027f, -1.453152027f);
+  ffma2(p0, p1, k0, k1, 1.421413741f, 1.421413741f);
+  ffma2(p0, p1, k0, k1, -0.284496736f, -0.284496736f);
+  ffma2(p0, p1, k0, k1, 0.254829592f, 0.254829592f);
+  fmul2_rn(p0, p1, -k0, -k1);                       // -(polynomial * k)
+  float e0 = a0, e1 = a1;
+  fmul2_rn(e0, e1, a0, a1);
+  fmul2_rn(e0, e1, -1.4426950408889634f, -1.4426950408889634f);
+  asm("ex2.approx.ftz.f32 %0, %0;" : "+f"(e0));
+  asm("ex2.approx.ftz.f32 %0, %0;" : "+f"(e1));
+  ffma2(p0, p1, e0, e1, 1.0f, 1.0f);                // 1 - polynomial * k * exp(-z^2)
+  p0 = copysignf(p0, z0); p1 = copysignf(p1, z1);
+  fadd2_rn(p0, p1, 1.0f, 1.0f);
+  fmul2_rn(t0, t1, 0.5f, 0.5f);
+  fmul2_rn(t0, t1, p0, p1);
 }
 // ACTF 0: LeakyReLU, 1: GELU (erf form)
 template <int OUT, int ACTF, bool RES>
@@ -817,7 +838,7 @@ __device__ __forceinline__ void chunk_leaky(const uint32_t (&r)[16], const float
       fmul2_rn(t0, t1, slope, slope);
       v[j] = fmaxf(v[j], t0); v[j + 1] = fmaxf(v[j + 1], t1);   // (a maximum between the product and any later sum: nothing to contract)
     } else {
-      v[j] = gelu_erf_two_byte(v[j]); v[j + 1] = gelu_erf_two_byte(v[j + 1]);
+      gelu_erf_two_byte_pair(v[j], v[j + 1]);
     }
   }
 #pragma unroll
@@ -881,7 +902,10 @@ __device__ __forceinline__ void chunk_gelu_s8(const uint32_t (&r)[16], const flo
 #pragma unroll
   for (int q = 0; q < 4; ++q) { const float4 f = __ldg((const float4*)addv + q); cv[4 * q] = f.x; cv[4 * q + 1] = f.y; cv[4 * q + 2] = f.z; cv[4 * q + 3] = f.w; }
 #pragma unroll
-  for (int j = 0; j < 16; ++j) v[j] = gelu_erf_two_byte(__fadd_rn(v[j], cv[j]));   // scalar sum after a packed product (see fadd2_rn)
+  for (int j = 0; j < 16; j += 2) {   // scalar sums after a packed product (see fadd2_rn)
+    v[j] = __fadd_rn(v[j], cv[j]); v[j + 1] = __fadd_rn(v[j + 1], cv[j + 1]);
+    gelu_erf_two_byte_pair(v[j], v[j + 1]);
+  }
   uint4 u;
   uint32_t* w = (uint32_t*)&u;
 #pragma unroll
