@@ -1446,8 +1446,11 @@ bool graph_shardable(_odla_computation* c, int64_t* batch_out) {
       const auto& os = o->type.shape;
       return s.dims[0] > 1 && os.size == s.size && os.dims[0] == s.dims[0];
     };
-    if (v->kind == OP_BINARY || v->kind == OP_CONCAT || v->kind == OP_GEMM)
+    if (v->kind == OP_BINARY || v->kind == OP_CONCAT)
       for (auto i : v->in) if (spans_batch(i)) return false;
+    // (a Gemm's right operand has the reduction, not the batch, as its first dimension -- a [2048, 1000] classifier
+    // under a batch of 2048 is not a constant that spans the batch; its left operand and its addend are aligned with the rows)
+    if (v->kind == OP_GEMM && (spans_batch(v->in[0]) || (v->in.size() > 2 && spans_batch(v->in[2])))) return false;
     switch (v->kind) {
       case OP_NMS: case OP_POSTPROCESS: case OP_POSTPROCESS_NUM: return false;   // rows of the result are not rows of the batch
       case OP_TRANSPOSE: if (v->ia[0] != 0) return false; break;

@@ -117,6 +117,12 @@ def test_constants_that_span_the_batch_keep_the_graph_whole(odla, lib):
         g.Output(build(g, g.Argument("x", (8, 4))))
         assert g.plan_shards(4) == [(0, 0, 8)]
         g.close()
+    # a Gemm's weights are not aligned with the rows even when their first dimension happens to equal the batch
+    # (a [2048, 1000] classifier under 2048 images): the graph still splits
+    g = odla.Graph(lib, "square_weights")
+    g.Output(g.Gemm(g.Argument("x", (8, 8)), False, g.Constant("w", np.ones((8, 4), np.float32)), False, 1.0, 0.0, None, (8, 4), "y"))
+    assert len(g.plan_shards(4)) == 4
+    g.close()
     g = odla.Graph(lib, "row_const")       # a per-row-broadcast constant ([1, 4]) splits fine
     g.Output(g.Add(g.Argument("x", (8, 4)), g.Constant("k", k[:1]), "y"))
     assert len(g.plan_shards(4)) == 4
