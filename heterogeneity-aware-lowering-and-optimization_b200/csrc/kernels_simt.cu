@@ -1142,6 +1142,9 @@ int convert(int dt_in, int dt_out, const void* x, void* y, int64_t n, cudaStream
     convert_f32_f16_vec_kernel<<<grid_for(n / 8, 256), 256, 0, s>>>((const float4*)x, (uint4*)y, n / 8);
     return check_launch();
   }
+  // two-byte -> fp32 (an fp16 / bf16 graph whose API outputs are fp32): four values per thread, as one long row
+  if ((dt_in == DT_F16 || dt_in == DT_BF16) && dt_out == DT_F32 && n % 4 == 0 && n < (1 << 30) && (uintptr_t)x % 8 == 0 && (uintptr_t)y % 16 == 0)
+    return convert_rows(dt_in, dt_out, x, y, 1, n, n, s);
   convert_kernel<<<grid_for(n, 256), 256, 0, s>>>(dt_in, dt_out, x, y, n);
   return check_launch();
 }
@@ -1152,27 +1155,39 @@ __global__ void convert_rows_kernel(int dt_in, int dt_out, const void* x, void* 
     store_from_float(y, dt_out, e, load_as_float(x, dt_in, r * Kp + k));
   }
 }
-// Two-byte rows of pitch Kp (a multiple of 8) -> dense fp32 rows of K: a thread reads one 16-byte piece and writes its
-// (up to) eight values; neighbouring threads write neighbouring floats.
+// Two-byte rows of pitch Kp -> dense fp32 rows of K.  Neighbouring threads write neighbouring floats (a warp's store is
+// one contiguous run): four values per thread as one 16-byte store when the rows allow it, one value per thread otherwise.
 template <typename IN>
-__global__ void convert_rows_h_f32_kernel(const uint4* __restrict__ x, float* __restrict__ y, int64_t rows, int K, int Kp8) {
-  const int64_t total = rows * Kp8;
-  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = e / Kp8;
-    const int k0 = (int)(e - r * Kp8) * 8;
-    const uint4 u = x[e];
+__global__ void convert_rows_h_f32_v4_kernel(const IN* __restrict__ x, float4* __restrict__ y, int64_t total4, int K4, int64_t Kp) {
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total4; e += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = e / K4;
+    const int k = (int)(e - r * K4) * 4;
+    const uint2 u = *(const uint2*)(x + r * Kp + k);
     const IN* h = (const IN*)&u;
-    float* o = y + r * K + k0;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) if (k0 + j < K) o[j] = (float)h[j];
+    y[e] = make_float4((float)h[0], (float)h[1], (float)h[2], (float)h[3]);
+  }
+}
+template <typename IN>
+__global__ void convert_rows_h_f32_flat_kernel(const IN* __restrict__ x, float* __restrict__ y, int64_t total, int K, int64_t Kp) {
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = e / K;
+    y[e] = (float)x[r * Kp + (e - r * K)];
   }
 }
 int convert_rows(int dt_in, int dt_out, const void* x, void* y, int64_t rows, int64_t K, int64_t Kp, cudaStream_t s) {
   if (rows * K <= 0) return 0;
-  if ((dt_in == DT_F16 || dt_in == DT_BF16) && dt_out == DT_F32 && Kp % 8 == 0 && (uintptr_t)x % 16 == 0 && K < (1 << 30)) {
-    const int grid = grid_for(rows * (Kp / 8), 256);
-    if (dt_in == DT_F16) convert_rows_h_f32_kernel<__half><<<grid, 256, 0, s>>>((const uint4*)x, (float*)y, rows, (int)K, (int)(Kp / 8));
-    else convert_rows_h_f32_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const uint4*)x, (float*)y, rows, (int)K, (int)(Kp / 8));
+  if ((dt_in == DT_F16 || dt_in == DT_BF16) && dt_out == DT_F32 && K < (1 << 30)) {
+    const bool v4 = K % 4 == 0 && Kp % 4 == 0 && (uintptr_t)x % 8 == 0 && (uintptr_t)y % 16 == 0;
+    if (v4) {
+      const int64_t total4 = rows * (K / 4);
+      const int grid = grid_for(total4, 256);
+      if (dt_in == DT_F16) convert_rows_h_f32_v4_kernel<__half><<<grid, 256, 0, s>>>((const __half*)x, (float4*)y, total4, (int)(K / 4), Kp);
+      else convert_rows_h_f32_v4_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, (float4*)y, total4, (int)(K / 4), Kp);
+    } else {
+      const int grid = grid_for(rows * K, 256);
+      if (dt_in == DT_F16) convert_rows_h_f32_flat_kernel<__half><<<grid, 256, 0, s>>>((const __half*)x, (float*)y, rows * K, (int)K, Kp);
+      else convert_rows_h_f32_flat_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, (float*)y, rows * K, (int)K, Kp);
+    }
     return check_launch();
   }
   convert_rows_kernel<<<grid_for(rows * K, 256), 256, 0, s>>>(dt_in, dt_out, x, y, rows, K, Kp);
