@@ -67,3 +67,35 @@ extern "C" int odla_b200_conv_umma(const odla_b200_conv_desc* d, const void* x, 
   cudaFree(status);
   return rc;
 }
+
+// Raw fused attention over device pointers (see AttnLaunch in kernels.h): dtype 0 = fp16, 1 = bf16.  Synchronous.
+// Returns 0, -1 (unsupported arguments), -2 (CUDA failure) or -3 (a bounded wait inside the kernel expired).
+extern "C" int odla_b200_attention(int dtype, const void* q, const void* k, const void* v, void* y, long long batch, int heads, int positions, int channels,
+                                   float scale, int merge_heads, void* stream) {
+  if (!q || !k || !v || !y || batch <= 0 || heads <= 0) return -1;
+  if (visible_devices() <= 0) {
+    fprintf(stderr, "[odla_b200] odla_b200_attention: no CUDA device (there is no CPU fallback)\n");
+    return -2;
+  }
+  const int dt = dtype == 0 ? DT_F16 : dtype == 1 ? DT_BF16 : -1;
+  if (dt < 0 || !attn_supported(dt, positions, channels)) return -1;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int* status = nullptr;
+  if (cudaMalloc((void**)&status, kStatusBytes) != cudaSuccess) return -2;
+  cudaMemsetAsync(status, 0, kStatusBytes, (cudaStream_t)stream);
+  AttnLaunch* L = attn_prepare(dt, q, k, v, y, batch, heads, scale, merge_heads != 0, status, sms);
+  if (!L) { cudaFree(status); return -2; }
+  int rc = attn_run(L, (cudaStream_t)stream);
+  int host_status[2] = {0, 0};
+  if (rc == 0 && cudaMemcpyAsync(host_status, status, sizeof(host_status), cudaMemcpyDeviceToHost, (cudaStream_t)stream) != cudaSuccess) rc = -2;
+  if (cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess) rc = -2;
+  attn_destroy(L);
+  cudaFree(status);
+  if (rc == 0 && host_status[0] != 0) {
+    fprintf(stderr, "[odla_b200] odla_b200_attention: bounded wait expired (code %d, block %d)\n", host_status[0], host_status[1]);
+    return -3;
+  }
+  return rc;
+}

@@ -119,6 +119,16 @@ UmmaLaunch* umma_conv_prepare(const UmmaConv& p, const void* x, const void* w, v
 int umma_conv_run(UmmaLaunch* l, cudaStream_t stream);
 void umma_conv_destroy(UmmaLaunch* l);
 
+// Fused attention for one shape family: softmax(scale * Q K^T) V over `batch * heads` heads of 128 positions x 64
+// channels, q / k / v laid out [batch][heads][128][64] in a two-byte type; the result is stored in the same layout or,
+// with merge_heads, as [batch][128][heads][64].  The scores stay in tensor memory.
+struct AttnLaunch;
+bool attn_supported(int dt, int64_t positions, int64_t channels);
+AttnLaunch* attn_prepare(int dt, const void* q, const void* k, const void* v, void* y, int64_t batch, int heads, float scale, bool merge_heads,
+                         int* status_word, int device_sms);
+int attn_run(AttnLaunch* l, cudaStream_t stream);
+void attn_destroy(AttnLaunch* l);
+
 // ---- memory-bound kernels (kernels_simt.cu) ----
 struct PoolGeom {
   int N, H, W, C, P, Q, R, S, stride_h, stride_w, pad_t, pad_l;

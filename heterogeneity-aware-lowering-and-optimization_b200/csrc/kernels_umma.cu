@@ -1375,6 +1375,197 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
+// ------------------------------------------------------------ fused attention ----
+// softmax(scale * Q K^T) V for heads of 128 positions x 64 channels (two-byte types): one CTA works on one head at a
+// time and keeps the 128 x 128 scores in tensor memory -- they never reach global memory.  Roles: warp 0 brings Q, K, V
+// in with TMA and sends the result out, warp 1 issues the two products, warps 2-5 (one TMEM lane quarter each, a thread
+// per query row) do the soft-max between them and the final scaling.  Shared memory holds one head (no double buffer):
+// two CTAs share an SM and fill each other's gaps.  The probabilities go to the second product unnormalised
+// (exp(s - max), rounded to the two-byte type) and the row sums divide the result, as in any online soft-max.
+struct AttnParams {
+  int tiles, NH, merge;          // heads in all; heads per batch element; 1: the result is stored [B][S][NH][D], 0: [B][NH][S][D]
+  float scale_log2e;             // scale * log2(e)
+  uint32_t idesc_s, idesc_o, desc_hi;
+  uint32_t spin_limit;
+  int bf16;
+  int* status;
+};
+constexpr int kAttnS = 128, kAttnD = 64, kAttnThreads = 192;
+constexpr uint32_t kAttnBox = 16384;   // 128 rows x 128 bytes
+
+template <bool BF16>
+__global__ void __launch_bounds__(kAttnThreads, 2)
+attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+            const __grid_constant__ CUtensorMap tmY, const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;                 // [128 rows][64] K-major
+  uint8_t* sK = sQ + kAttnBox;        // [128 keys][64] K-major
+  uint8_t* sV = sK + kAttnBox;        // [128 keys][64 channels]: the second product reads it MN-major
+  uint8_t* sP = sV + kAttnBox;        // two k-blocks of [128 rows][64 keys]
+  uint8_t* sY = sP + 2 * kAttnBox;    // result box
+  uint64_t* bars = (uint64_t*)(sY + kAttnBox);
+  uint64_t *b_full = bars, *b_s = bars + 1, *b_p = bars + 2, *b_o = bars + 3, *b_e = bars + 4, *b_sf = bars + 5;
+  uint32_t* tmem_slot = (uint32_t*)(bars + 8);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    mbar_init(b_full, 1); mbar_init(b_s, 1); mbar_init(b_p, 4); mbar_init(b_o, 1); mbar_init(b_e, 4); mbar_init(b_sf, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128u;
+
+  if (warp == 0) {
+    // ------------------------------------------------ loads and the result's store ----
+    if (elect_one()) {
+      uint32_t it = 0;
+      for (int tile = blockIdx.x; tile < p.tiles; tile += gridDim.x, ++it) {
+        // the previous head's products have finished reading Q, K, V and P
+        if (it > 0 && !mbar_wait(b_o, (it - 1) & 1, abort_flag, p.status, 11, p.spin_limit)) break;
+        mbar_expect_tx(b_full, 3u * kAttnBox);
+        tma_load_2d(sQ, &tmQ, b_full, 0, tile * kAttnS);
+        tma_load_2d(sK, &tmK, b_full, 0, tile * kAttnS);
+        tma_load_2d(sV, &tmV, b_full, 0, tile * kAttnS);
+        if (!mbar_wait(b_e, it & 1, abort_flag, p.status, 12, p.spin_limit)) break;
+        if (p.merge) {
+          const int b = tile / p.NH, h = tile - b * p.NH;
+          asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"((uint64_t)&tmY), "r"(smem_u32(sY)), "r"(0),
+                       "r"(h), "r"(0), "r"(b)
+                       : "memory");
+        } else {
+          asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"((uint64_t)&tmY), "r"(smem_u32(sY)), "r"(0),
+                       "r"(tile * kAttnS)
+                       : "memory");
+        }
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        mbar_arrive(b_sf);
+      }
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+      // copies that were armed but never consumed (an aborted run) get a bounded chance to land
+      if (*abort_flag)
+        for (uint32_t k = 0; k < 4096; ++k)
+          if (mbar_try_wait(b_full, 0) || mbar_try_wait(b_full, 1)) break;
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- the two products ----
+    if (elect_one()) {
+      const uint64_t fixed = ((uint64_t)p.desc_hi << 32) | (1ull << 16);
+      const uint64_t dq = fixed | (uint64_t)((smem_u32(sQ) & 0x3FFFF) >> 4), dk = fixed | (uint64_t)((smem_u32(sK) & 0x3FFFF) >> 4);
+      const uint64_t dv = fixed | (uint64_t)((smem_u32(sV) & 0x3FFFF) >> 4), dp = fixed | (uint64_t)((smem_u32(sP) & 0x3FFFF) >> 4);
+      uint32_t it = 0;
+      for (int tile = blockIdx.x; tile < p.tiles; tile += gridDim.x, ++it) {
+        if (!mbar_wait(b_full, it & 1, abort_flag, p.status, 13, p.spin_limit)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 4; ++k) umma_f16(tmem_s, dq + 2 * k, dk + 2 * k, p.idesc_s, k ? 1u : 0u);        // S = Q K^T, 64 deep
+        umma_commit(b_s);
+        if (!mbar_wait(b_p, it & 1, abort_flag, p.status, 14, p.spin_limit)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k)   // O = P V, 128 deep: P advances 32 bytes per step inside a k-block, V sixteen rows
+          umma_f16(tmem_o, dp + (uint64_t)((k >> 2) * (kAttnBox >> 4) + 2 * (k & 3)), dv + (uint64_t)(128 * k), p.idesc_o, k ? 1u : 0u);
+        umma_commit(b_o);
+      }
+    }
+  } else {
+    // ------------------------------------------------ soft-max and the final scaling ----
+    const int quarter = warp & 3, row = quarter * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const uint32_t p_row = smem_u32(sP) + (uint32_t)row * 128u, y_row = smem_u32(sY) + (uint32_t)row * 128u;
+    const int rx = row & 7;
+    uint32_t it = 0;
+    for (int tile = blockIdx.x; tile < p.tiles; tile += gridDim.x, ++it) {
+      if (!mbar_wait(b_s, it & 1, abort_flag, p.status, 15, p.spin_limit)) break;
+      tc_fence_after();
+      float mx = -3.402823466e+38f;
+#pragma unroll 1
+      for (int c = 0; c < 8; ++c) {
+        uint32_t r[16];
+        tmem_ld16(tmem_s + lane_addr + (uint32_t)(c * 16), r);
+        tmem_ld_wait_regs<16>(r);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) mx = fmaxf(mx, __uint_as_float(r[j]) * p.scale_log2e);
+      }
+      float sum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 8; ++c) {
+        uint32_t r[16];
+        tmem_ld16(tmem_s + lane_addr + (uint32_t)(c * 16), r);
+        tmem_ld_wait_regs<16>(r);
+        float e[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          e[j] = fmaf(__uint_as_float(r[j]), p.scale_log2e, -mx);
+          asm("ex2.approx.ftz.f32 %0, %0;" : "+f"(e[j]));
+          sum += e[j];
+        }
+        // keys c*16 .. c*16+15 are pieces (c & 3) * 2, +1 of this row in k-block c >> 2
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          uint4 u;
+          uint32_t* w = (uint32_t*)&u;
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            if (BF16) { __nv_bfloat162 h = __floats2bfloat162_rn(e[q * 8 + 2 * t], e[q * 8 + 2 * t + 1]); w[t] = *(uint32_t*)&h; }
+            else { __half2 h = __floats2half2_rn(e[q * 8 + 2 * t], e[q * 8 + 2 * t + 1]); w[t] = *(uint32_t*)&h; }
+          }
+          sts128(p_row + (uint32_t)(c >> 2) * kAttnBox + (uint32_t)(((((c & 3) << 1) + q) ^ rx) << 4), u);
+        }
+      }
+      tc_fence_before();
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the tensor cores read P through the async proxy
+      __syncwarp();
+      if (lane == 0) mbar_arrive(b_p);
+      const float inv = __fdividef(1.0f, sum);
+      if (!mbar_wait(b_o, it & 1, abort_flag, p.status, 16, p.spin_limit)) break;
+      tc_fence_after();
+      // the store of the previous head has finished reading the result box
+      if (it > 0 && !mbar_wait(b_sf, (it - 1) & 1, abort_flag, p.status, 17, p.spin_limit)) break;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[16];
+        tmem_ld16(tmem_o + lane_addr + (uint32_t)(c * 16), r);
+        tmem_ld_wait_regs<16>(r);
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          uint4 u;
+          uint32_t* w = (uint32_t*)&u;
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const float a = __uint_as_float(r[q * 8 + 2 * t]) * inv, b = __uint_as_float(r[q * 8 + 2 * t + 1]) * inv;
+            if (BF16) { __nv_bfloat162 h = __floats2bfloat162_rn(a, b); w[t] = *(uint32_t*)&h; }
+            else { __half2 h = __floats2half2_rn(a, b); w[t] = *(uint32_t*)&h; }
+          }
+          sts128(y_row + (uint32_t)((((c << 1) + q) ^ rx) << 4), u);
+        }
+      }
+      tc_fence_before();
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(b_e);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
+  }
+}
+
 // ------------------------------------------------------------- host: tensor maps ----
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -1724,5 +1915,84 @@ int umma_conv_run(UmmaLaunch* L, cudaStream_t stream) {
   return 0;
 }
 void umma_conv_destroy(UmmaLaunch* L) { delete L; }
+
+// ---- fused attention: host side ----
+struct AttnLaunch {
+  CUtensorMap tmQ, tmK, tmV, tmY;
+  AttnParams p;
+  int grid;
+  size_t smem;
+  bool bf16;
+};
+bool attn_supported(int dt, int64_t S, int64_t D) { return (dt == DT_F16 || dt == DT_BF16) && S == kAttnS && D == kAttnD; }
+AttnLaunch* attn_prepare(int dt, const void* q, const void* k, const void* v, void* y, int64_t batch, int heads, float scale, bool merge_heads, int* status,
+                         int sms) {
+  if (!attn_supported(dt, kAttnS, kAttnD) || batch * heads <= 0 || batch * heads * kAttnS >= (1ll << 31) || !load_driver_entry_points()) return nullptr;
+  if ((uintptr_t)q % 16 || (uintptr_t)k % 16 || (uintptr_t)v % 16 || (uintptr_t)y % 16) return nullptr;
+  auto* L = new AttnLaunch();
+  AttnParams& p = L->p;
+  p.tiles = (int)(batch * heads); p.NH = heads; p.merge = merge_heads ? 1 : 0;
+  p.scale_log2e = scale * 1.4426950408889634f;
+  p.bf16 = dt == DT_BF16; L->bf16 = dt == DT_BF16;
+  const uint32_t fmt = dt == DT_BF16 ? 1u : 0u;
+  p.idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(kAttnS >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+  p.idesc_o = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((uint32_t)(kAttnD >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);   // B (= V) is MN-major
+  p.desc_hi = ((uint32_t)(8 * 128) >> 4) | (1u << 14) | (2u << 29);
+  p.spin_limit = kSpinLimit;
+  p.status = status;
+  L->grid = p.tiles < 2 * sms ? p.tiles : 2 * sms;
+  L->smem = 6 * (size_t)kAttnBox + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  const CUtensorMapDataType tdt = dt == DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const cuuint64_t rows = (cuuint64_t)p.tiles * kAttnS;
+  cuuint64_t dims[2] = {(cuuint64_t)kAttnD, rows};
+  cuuint64_t strides[1] = {(cuuint64_t)kAttnD * 2};
+  cuuint32_t box[2] = {(cuuint32_t)kAttnD, (cuuint32_t)kAttnS};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = CUDA_SUCCESS;
+  const void* src[3] = {q, k, v};
+  CUtensorMap* maps[3] = {&L->tmQ, &L->tmK, &L->tmV};
+  for (int i = 0; i < 3 && r == CUDA_SUCCESS; ++i)
+    r = g_encode_tiled(maps[i], tdt, 2, (void*)src[i], dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                       CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_SUCCESS) {
+    if (merge_heads) {   // [B][S][NH][D]: a head's 128 rows lie NH * D elements apart
+      cuuint64_t d4[4] = {(cuuint64_t)kAttnD, (cuuint64_t)heads, (cuuint64_t)kAttnS, (cuuint64_t)batch};
+      cuuint64_t s4[3] = {(cuuint64_t)kAttnD * 2, (cuuint64_t)heads * kAttnD * 2, (cuuint64_t)kAttnS * heads * kAttnD * 2};
+      cuuint32_t b4[4] = {(cuuint32_t)kAttnD, 1, (cuuint32_t)kAttnS, 1};
+      cuuint32_t e4[4] = {1, 1, 1, 1};
+      r = g_encode_tiled(&L->tmY, tdt, 4, y, d4, s4, b4, e4, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else {
+      r = g_encode_tiled(&L->tmY, tdt, 2, y, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
+  }
+  if (r != CUDA_SUCCESS) { fprintf(stderr, "[odla_b200] tensor map (attention) encode failed: %d\n", (int)r); delete L; return nullptr; }
+  if (cudaFuncSetAttribute(attn_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L->smem) != cudaSuccess ||
+      cudaFuncSetAttribute(attn_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L->smem) != cudaSuccess) {
+    cudaGetLastError(); delete L; return nullptr;
+  }
+  return L;
+}
+int attn_run(AttnLaunch* L, cudaStream_t stream) {
+  if (!L) return -1;
+  if (L->p.tiles <= 0) return 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)L->grid);
+  cfg.blockDim = dim3(kAttnThreads);
+  cfg.dynamicSmemBytes = L->smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  static const bool pdl = !getenv("ODLA_B200_NO_PDL");
+  int na = 0;
+  if (pdl) { attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization; attr[na].val.programmaticStreamSerializationAllowed = 1; ++na; }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  cudaError_t le = L->bf16 ? cudaLaunchKernelEx(&cfg, attn_kernel<true>, L->tmQ, L->tmK, L->tmV, L->tmY, L->p)
+                           : cudaLaunchKernelEx(&cfg, attn_kernel<false>, L->tmQ, L->tmK, L->tmV, L->tmY, L->p);
+  if (le != cudaSuccess) { fprintf(stderr, "[odla_b200] attention launch failed: %s\n", cudaGetErrorString(le)); cudaGetLastError(); return -2; }
+  return 0;
+}
+void attn_destroy(AttnLaunch* L) { delete L; }
 
 }  // namespace b200

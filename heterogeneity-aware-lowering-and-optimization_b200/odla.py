@@ -186,6 +186,7 @@ _OPTIONAL = {
     "odla_b200_GetQuantTable": (C.c_int, [_V, C.POINTER(QuantInfo), C.c_int]),
     "odla_b200_PlanShards": (C.c_int, [_V, C.c_longlong, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_longlong), C.POINTER(C.c_longlong), C.c_int]),
     "odla_b200_conv_umma": (C.c_int, [C.POINTER(ConvDesc), _V, _V, _V, _V, _V, _V, _V]),
+    "odla_b200_attention": (C.c_int, [C.c_int, _V, _V, _V, _V, C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, _V]),
     "odla_b200_reduce_mean_noalloc": (C.c_int, [_V, _V, C.c_int, C.POINTER(C.c_longlong), C.c_int, C.POINTER(C.c_int), C.c_int, _V]),
     "odla_cpuref_UsesReference": (C.c_int, []),
     "odla_cpuref_Threads": (C.c_int, []),

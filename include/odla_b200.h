@@ -453,6 +453,17 @@ int odla_b200_conv_umma(const odla_b200_conv_desc* desc, const void* x, const vo
                         const float* mul, const float* add, const void* residual, void* y,
                         void* stream);
 
+/* Extension (no counterpart in the reference, which leaves attention to separate MatMul / Softmax / MatMul calls:
+ * lib/target/generic_cpp/matmul.cc:24-68, softmax.cc).  softmax(scale * Q K^T) V over batch * heads heads on the
+ * tensor cores, the scores kept in tensor memory.  q, k, v: device pointers to [batch][heads][positions][channels] in
+ * fp16 (dtype 0) or bf16 (dtype 1); only positions = 128 and channels = 64 are supported (-1 otherwise).  y is written
+ * in the same layout, or as [batch][positions][heads][channels] when merge_heads is non-zero.  Synchronous on `stream`.
+ * Returns 0, -1 (unsupported arguments), -2 (CUDA failure), -3 (a bounded wait inside the kernel expired).  The graph
+ * path uses the same kernel when it meets this pattern (Gemm with a transposed right operand, scalar Mul, Softmax over
+ * the last axis, Gemm). */
+int odla_b200_attention(int dtype, const void* q, const void* k, const void* v, void* y, long long batch, int heads,
+                        int positions, int channels, float scale, int merge_heads, void* stream);
+
 /* odla_b200_reduce_mean_noalloc -- this entry point has no counterpart in the reference.
  *
  * Mean over `n_axes` axes of a dense tensor in device memory, reduced one axis after the other in
