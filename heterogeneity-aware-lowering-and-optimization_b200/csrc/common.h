@@ -114,6 +114,7 @@ struct Plan {
   int* status = nullptr;           // device status block (kStatusBytes): word 0 non-zero when a bounded wait expired
   std::vector<void*> extra_allocs; // uploaded constants and scratch
   std::vector<UmmaLaunch*> umma;   // prepared tensor-core launches (own their tensor maps)
+  std::vector<AttnLaunch*> attn;   // prepared fused-attention launches
   std::map<const _odla_value*, unsigned*> pp_counts;  // odla_PostProcess: where a node's per-class counts are on the device
   cudaGraphExec_t graph = nullptr; // captured launch list (optional)
   bool graph_failed = false;       // capture was tried and refused: stay on plain launches

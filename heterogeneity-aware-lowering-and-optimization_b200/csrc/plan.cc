@@ -38,6 +38,7 @@ Plan::~Plan() {
   if (graph) cudaGraphExecDestroy(graph);
   for (auto& l : launches) l.fn = nullptr;
   for (auto* u : umma) umma_conv_destroy(u);
+  for (auto* a : attn) attn_destroy(a);
   for (void* p : extra_allocs) cudaFree(p);
   if (arena) cudaFree(arena);
   if (status) cudaFree(status);
@@ -149,6 +150,10 @@ struct Item {               // one launch-list entry before emission
   std::vector<V> reads;     // materialised values it reads (after alias resolution)
   const Fused* fused = nullptr;
   V extra_out = nullptr;    // a second value the same launch writes (the int8 copy a LayerNorm makes for a following Quantize)
+  // fused attention: this item is the context product; the scores product and the soft-max in front of it have no
+  // items of their own, their operands are read here
+  V attn_q = nullptr, attn_k = nullptr;
+  float attn_scale = 1.f;
 };
 
 class Builder {
@@ -237,6 +242,7 @@ class Builder {
   void try_fuse(V root);
   odla_status place();
   odla_status emit();
+  void try_attention(Item& it, const Fused& f);
   odla_status emit_fused(const Item& it);
   odla_status emit_plain(const Item& it);
   void add_launch(const char* op, V out, double flops, double bytes, std::function<int(cudaStream_t)> fn) {
@@ -338,6 +344,8 @@ odla_status Builder::analyse() {
       if (f->res) it.reads.push_back(f->res);
       if (root->kind == OP_GEMM && root->in[2] && root->in[2]->kind != OP_CONST) it.reads.push_back(root->in[2]);
       dt_[v] = f->quant_scale ? DT_S8 : FS();
+      // softmax(scale * Q K^T) V with heads of 128 positions x 64 channels: one launch, the scores stay on chip
+      if (root->kind == OP_GEMM) try_attention(it, *f);
     } else {
       for (auto i : v->in) {
         if (!i || i->kind == OP_CONST) continue;
@@ -586,7 +594,67 @@ odla_status Builder::place() {
   return ODLA_SUCCESS;
 }
 
+// Recognises Gemm(Softmax(Mul(Gemm(q, k^T), scale), last axis), v) whose intermediates have no other reader, in the one
+// shape family the fused kernel serves; on success the items of the scores product and of the soft-max are taken out
+// of the launch list and `it` (the context product) reads q, k and v itself.
+void Builder::try_attention(Item& it, const Fused& f) {
+  if (getenv("ODLA_B200_NO_ATTENTION") || getenv("ODLA_B200_NO_UMMA")) return;
+  const int fs = FS();
+  if (fs != DT_F16 && fs != DT_BF16) return;
+  V root = f.root;
+  auto plain = [](const Fused& g) { return !g.int8 && !g.add_const && !g.res && g.act == ACT_NONE && !g.quant_scale; };
+  if (!plain(f) || f.has_scalar_mul || root->ia[0] != 0 || root->ia[1] != 0 || root->fa[0] != 1.f || (root->in[2] && root->fa[1] != 0.f)) return;
+  if (!f.w || f.w->kind == OP_CONST || (f.perm_mode != 0 && f.perm_mode != 2)) return;
+  V sm = resolve(f.x);
+  if (!sm || sm->kind != OP_SOFTMAX || sm->ia[1] != 0 || users_[sm] != 1 || sm->is_output) return;
+  const auto& ps = sm->type.shape;
+  if (ps.size != 4 || (sm->ia[0] != 3 && sm->ia[0] != -1)) return;
+  V sc_out = resolve(sm->in[0]);
+  if (!sc_out || users_[sc_out] != 1 || sc_out->is_output) return;
+  auto fi = fused_into_.find(sc_out);
+  V sc_root = sc_out->kind == OP_GEMM ? sc_out : (fi != fused_into_.end() ? fi->second : nullptr);
+  if (!sc_root || sc_root->kind != OP_GEMM || !fused_.count(sc_root)) return;
+  const Fused& g = *fused_[sc_root];
+  if (g.out != sc_out || !plain(g) || g.perm_mode != 0 || sc_root->ia[0] != 0 || sc_root->ia[1] == 0 || (sc_root->in[2] && sc_root->fa[1] != 0.f)) return;
+  if (!g.w || g.w->kind == OP_CONST) return;
+  V q = resolve(g.x), k = resolve(g.w), v = resolve(f.w);
+  const auto &qs = q->type.shape, &ks = k->type.shape, &vs = v->type.shape;
+  if (qs.size != 4 || ks.size != 4 || vs.size != 4) return;
+  const int64_t B = qs.dims[0], NH = qs.dims[1], S = qs.dims[2], D = qs.dims[3];
+  if (!attn_supported(fs, S, D)) return;
+  for (int d = 0; d < 4; ++d) if (ks.dims[d] != qs.dims[d] || vs.dims[d] != qs.dims[d]) return;
+  if (ps.dims[0] != B || ps.dims[1] != NH || ps.dims[2] != S || ps.dims[3] != S) return;
+  if (f.perm_mode == 2 && (f.perm_NH != NH || f.perm_S != S || f.perm_D != D)) return;
+  if (dt_[q] != fs || dt_[k] != fs || dt_[v] != fs || alias_.count(q) || alias_.count(k) || alias_.count(v)) return;
+  if (pitch_.count(q) || pitch_.count(k) || pitch_.count(v)) return;
+  // the two earlier launches go; nothing else reads what they would have written
+  size_t removed = 0;
+  for (size_t i = items_.size(); i-- > 0;)
+    if (items_[i].out == sm || items_[i].out == sc_out) { items_.erase(items_.begin() + (long)i); ++removed; }
+  if (removed != 2) { B2_WARN("attention pattern at '%s' matched but its producers were not separate launches", root->name.c_str()); }
+  it.attn_q = q;
+  it.attn_k = k;
+  it.attn_scale = sc_root->fa[0] * g.scalar_mul;
+  it.reads.clear();
+  it.reads.push_back(q); it.reads.push_back(k); it.reads.push_back(v);
+}
+
 odla_status Builder::emit_fused(const Item& it) {
+  if (it.attn_q) {
+    const Fused& f = *it.fused;
+    const auto& qs = it.attn_q->type.shape;
+    const int64_t B = shape(it.attn_q).dims[0], NH = qs.dims[1], S = qs.dims[2], D = qs.dims[3];
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, p_->device);
+    AttnLaunch* al = attn_prepare(FS(), dev_ptr(it.attn_q), dev_ptr(it.attn_k), dev_ptr(f.w), dev_ptr(f.out), B, (int)NH, it.attn_scale, f.perm_mode == 2,
+                                  p_->status, sms);
+    if (!al) return fail(ODLA_FAILURE, "'" + f.root->name + "': fused attention could not be prepared");
+    p_->attn.push_back(al);
+    const double flops = 2.0 * 2.0 * (double)B * NH * S * S * D;
+    const double bytes = 4.0 * (double)B * NH * S * D * storage_size(FS());
+    add_launch("attention", f.out, flops, bytes, [al](cudaStream_t s) { return attn_run(al, s); });
+    return ODLA_SUCCESS;
+  }
   const Fused& f = *it.fused;
   V root = f.root;
   int in_dt = f.int8 ? DT_S8 : FS();

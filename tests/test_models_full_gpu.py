@@ -128,7 +128,8 @@ def test_bert_base_12_layers_match_the_fixture(odla, gpu_lib, models, form, mode
     tol, mean_tol = {("float", "fp32"): (2e-3, 2.5e-4), ("float", "fp16"): (3e-2, 4e-3), ("int8", "fp32"): (0.25, 0.04), ("int8", "fp16"): (0.25, 0.04)}[(form, mode)]
     assert err <= tol and mean_err <= mean_tol, (err, mean_err)
     if mode == "fp16":
-        assert desc.count("gemm_umma") == 8 * cfg["layers"]     # Q, K, V, out, two FFN layers, scores, context
+        assert desc.count("gemm_umma") == 6 * cfg["layers"]     # Q, K, V, out, two FFN layers
+        assert desc.count("attention") == cfg["layers"] and "softmax" not in desc   # scores, soft-max and context in one launch
         assert "transpose" not in desc
     if form == "int8":
         # x (shared by Q, K, V) and x1 come out of a LayerNorm, which writes their int8 copies itself when the storage

@@ -161,12 +161,14 @@ def test_bert_encoder_matches_oracle(odla, gpu_lib, ref, models, mode, cfg):
     err = float(np.abs(got["encoder_out"] - want["encoder_out"]).max())
     assert err <= (2e-4 if mode == "fp32" else 3e-2), err
     if mode == "fp16":
-        # Q/K/V/out/FFN always; the two batched attention products too when the sequence fills 128-row tiles
-        per_layer = 8 if cfg["seq"] % 128 == 0 else 6
-        assert desc.count("gemm_umma") == per_layer * cfg["layers"] and "layernorm" in desc and "gather" in desc
-        if per_layer == 8:
-            assert "binary       l0_scaled" not in desc      # the 1/sqrt(d) Mul is folded into the score product
-        assert "transpose" not in desc                        # head split / merge ride on the Gemm stores
+        # Q/K/V/out/FFN on the tensor-core Gemm; heads of 128 positions x 64 channels take the fused attention launch
+        # (scores product, 1/sqrt(d) Mul, soft-max and context product in one), other shapes the separate kernels
+        fused_attention = cfg["seq"] == 128 and cfg["hidden"] // cfg["heads"] == 64
+        assert desc.count("gemm_umma") == 6 * cfg["layers"] and "layernorm" in desc and "gather" in desc
+        assert desc.count("attention") == (cfg["layers"] if fused_attention else 0)
+        if fused_attention:
+            assert "softmax" not in desc and "binary       l0_scaled" not in desc
+        assert "transpose" not in desc                        # head split / merge ride on the Gemm / attention stores
 
 
 def test_halo_style_model_runs_against_both_libraries(tmp_path, odla, gpu_lib, ref, models):
