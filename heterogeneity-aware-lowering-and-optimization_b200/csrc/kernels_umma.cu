@@ -1379,8 +1379,9 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // softmax(scale * Q K^T) V for heads of 128 positions x 64 channels (two-byte types): one CTA works on one head at a
 // time and keeps the 128 x 128 scores in tensor memory -- they never reach global memory.  Roles: warp 0 brings Q, K, V
 // in with TMA and sends the result out, warp 1 issues the two products, warps 2-5 (one TMEM lane quarter each, a thread
-// per query row) do the soft-max between them and the final scaling.  Shared memory holds one head (no double buffer):
-// two CTAs share an SM and fill each other's gaps.  The probabilities go to the second product unnormalised
+// per query row) do the soft-max between them and the final scaling.  Shared memory holds one head (no double buffer)
+// and is reused inside the head -- the probabilities overwrite Q and K, the result accumulates over the scores' tensor
+// memory columns -- so that three CTAs share an SM and fill each other's gaps.  The probabilities go to the second product unnormalised
 // (exp(s - max), rounded to the two-byte type) and the row sums divide the result, as in any online soft-max.
 struct AttnParams {
   int tiles, NH, merge;          // heads in all; heads per batch element; 1: the result is stored [B][S][NH][D], 0: [B][NH][S][D]
@@ -1394,7 +1395,7 @@ constexpr int kAttnS = 128, kAttnD = 64, kAttnThreads = 192;
 constexpr uint32_t kAttnBox = 16384;   // 128 rows x 128 bytes
 
 template <bool BF16>
-__global__ void __launch_bounds__(kAttnThreads, 2)
+__global__ void __launch_bounds__(kAttnThreads, 3)
 attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
             const __grid_constant__ CUtensorMap tmY, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -1402,8 +1403,8 @@ attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
   uint8_t* sQ = smem;                 // [128 rows][64] K-major
   uint8_t* sK = sQ + kAttnBox;        // [128 keys][64] K-major
   uint8_t* sV = sK + kAttnBox;        // [128 keys][64 channels]: the second product reads it MN-major
-  uint8_t* sP = sV + kAttnBox;        // two k-blocks of [128 rows][64 keys]
-  uint8_t* sY = sP + 2 * kAttnBox;    // result box
+  uint8_t* sP = sQ;                   // two k-blocks of [128 rows][64 keys], written once the first product has read Q and K
+  uint8_t* sY = sV + kAttnBox;        // result box
   uint64_t* bars = (uint64_t*)(sY + kAttnBox);
   uint64_t *b_full = bars, *b_s = bars + 1, *b_p = bars + 2, *b_o = bars + 3, *b_e = bars + 4, *b_sf = bars + 5;
   uint32_t* tmem_slot = (uint32_t*)(bars + 8);
@@ -1416,7 +1417,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256u) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(128u) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -1425,7 +1426,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
   const uint32_t tmem_base = *tmem_slot;
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128u;
+  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base;   // the result's 64 columns replace the first 64 of the scores
 
   if (warp == 0) {
     // ------------------------------------------------ loads and the result's store ----
@@ -1562,7 +1563,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(128u) : "memory");
   }
 }
 
@@ -1940,8 +1941,8 @@ AttnLaunch* attn_prepare(int dt, const void* q, const void* k, const void* v, vo
   p.desc_hi = ((uint32_t)(8 * 128) >> 4) | (1u << 14) | (2u << 29);
   p.spin_limit = kSpinLimit;
   p.status = status;
-  L->grid = p.tiles < 2 * sms ? p.tiles : 2 * sms;
-  L->smem = 6 * (size_t)kAttnBox + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  L->grid = p.tiles < 3 * sms ? p.tiles : 3 * sms;
+  L->smem = 4 * (size_t)kAttnBox + 1024 /*alignment slack*/ + 256 /*barriers*/;
   const CUtensorMapDataType tdt = dt == DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   const cuuint64_t rows = (cuuint64_t)p.tiles * kAttnS;
   cuuint64_t dims[2] = {(cuuint64_t)kAttnD, rows};
