@@ -1381,7 +1381,7 @@ umma_conv_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // in with TMA and sends the result out, warp 1 issues the two products, warps 2-5 (one TMEM lane quarter each, a thread
 // per query row) do the soft-max between them and the final scaling.  Shared memory holds one head (no double buffer)
 // and is reused inside the head -- the probabilities overwrite Q and K, the result accumulates over the scores' tensor
-// memory columns -- so that three CTAs share an SM and fill each other's gaps.  The probabilities go to the second product unnormalised
+// memory columns, the result box overwrites V -- so that four CTAs share an SM and fill each other's gaps.  The probabilities go to the second product unnormalised
 // (exp(s - max), rounded to the two-byte type) and the row sums divide the result, as in any online soft-max.
 struct AttnParams {
   int tiles, NH, merge;          // heads in all; heads per batch element; 1: the result is stored [B][S][NH][D], 0: [B][NH][S][D]
@@ -1395,7 +1395,7 @@ constexpr int kAttnS = 128, kAttnD = 64, kAttnThreads = 192;
 constexpr uint32_t kAttnBox = 16384;   // 128 rows x 128 bytes
 
 template <bool BF16>
-__global__ void __launch_bounds__(kAttnThreads, 3)
+__global__ void __launch_bounds__(kAttnThreads, 4)
 attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
             const __grid_constant__ CUtensorMap tmY, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -1404,8 +1404,8 @@ attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
   uint8_t* sK = sQ + kAttnBox;        // [128 keys][64] K-major
   uint8_t* sV = sK + kAttnBox;        // [128 keys][64 channels]: the second product reads it MN-major
   uint8_t* sP = sQ;                   // two k-blocks of [128 rows][64 keys], written once the first product has read Q and K
-  uint8_t* sY = sV + kAttnBox;        // result box
-  uint64_t* bars = (uint64_t*)(sY + kAttnBox);
+  uint8_t* sY = sV;                   // result box, written once the second product has read V
+  uint64_t* bars = (uint64_t*)(sV + kAttnBox);
   uint64_t *b_full = bars, *b_s = bars + 1, *b_p = bars + 2, *b_o = bars + 3, *b_e = bars + 4, *b_sf = bars + 5;
   uint32_t* tmem_slot = (uint32_t*)(bars + 8);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
@@ -1941,8 +1941,8 @@ AttnLaunch* attn_prepare(int dt, const void* q, const void* k, const void* v, vo
   p.desc_hi = ((uint32_t)(8 * 128) >> 4) | (1u << 14) | (2u << 29);
   p.spin_limit = kSpinLimit;
   p.status = status;
-  L->grid = p.tiles < 3 * sms ? p.tiles : 3 * sms;
-  L->smem = 4 * (size_t)kAttnBox + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  L->grid = p.tiles < 4 * sms ? p.tiles : 4 * sms;
+  L->smem = 3 * (size_t)kAttnBox + 1024 /*alignment slack*/ + 256 /*barriers*/;
   const CUtensorMapDataType tdt = dt == DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   const cuuint64_t rows = (cuuint64_t)p.tiles * kAttnS;
   cuuint64_t dims[2] = {(cuuint64_t)kAttnD, rows};
