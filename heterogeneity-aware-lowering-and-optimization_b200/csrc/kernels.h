@@ -158,7 +158,11 @@ int softmax(int dt, const void* x, void* y, int64_t outer, int64_t dim, int64_t 
             cudaStream_t stream);
 // Mean over one axis, sum in ascending order then a single division (bit-reproducible).
 int reduce_mean_axis(int dt_in, int dt_out, const void* x, void* y, int64_t before, int64_t dim, int64_t after,
-                     cudaStream_t stream, float in_scale = 1.f);  // in_scale: dequantisation scale of an int8 input
+                     cudaStream_t stream, float in_scale = 1.f);
+// Two adjacent axes (d1, then d2) in one launch with the same arithmetic as two reduce_mean_axis passes; returns 1
+// without launching when the shape is not one it serves (7 x 7, 16-byte channel vectors).
+int reduce_mean_two_axes(int dt_in, int dt_out, const void* x, void* y, int64_t before, int64_t d1, int64_t d2, int64_t after, cudaStream_t stream,
+                         float in_scale = 1.f);  // in_scale: dequantisation scale of an int8 input
 int layernorm(int dt, const void* x, void* y, const float* gamma, const float* beta, int64_t rows, int64_t dim,
               float eps, cudaStream_t stream);
 // The same, also writing q = sat(rne(y / scale[0])) as int8 for the rounded two-byte result y (what a per-tensor

@@ -978,6 +978,48 @@ __global__ void reduce_mean_axis_vec_kernel(int dt_out, const IN* __restrict__ x
     for (int q = 0; q < VEC; ++q) store_from_float(y, dt_out, i * after + k + q, __fdiv_rn(s[q], d));
   }
 }
+// Two adjacent axes of D1 x D2 (a global average pool: 7 x 7) in one pass, with the arithmetic of the two single-axis
+// passes: per second-axis index the first axis is summed left to right and divided, those quotients are summed left to
+// right and divided.  All D1 * D2 loads of a thread are independent, so they overlap instead of waiting in a loop.
+template <typename IN, int D1, int D2>
+__global__ void reduce_mean_two_axes_kernel(int dt_out, const IN* __restrict__ x, void* __restrict__ y, int64_t before, int64_t after, float in_scale) {
+  constexpr int VEC = RedVec<IN>::N;
+  const int64_t av = after / VEC, total = before * av;
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t i = e / av, k = (e - i * av) * VEC;
+    const IN* p = x + i * (D1 * D2) * after + k;
+    float u[VEC];
+#pragma unroll
+    for (int w = 0; w < D2; ++w) {
+      float s[VEC], t[VEC];
+      red_load<IN>(p + (int64_t)w * after, in_scale, s);
+#pragma unroll
+      for (int h = 1; h < D1; ++h) {
+        red_load<IN>(p + ((int64_t)h * D2 + w) * after, in_scale, t);
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) s[q] = __fadd_rn(s[q], t[q]);
+      }
+#pragma unroll
+      for (int q = 0; q < VEC; ++q) {
+        const float m = __fdiv_rn(s[q], (float)D1);
+        u[q] = w == 0 ? m : __fadd_rn(u[q], m);
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < VEC; ++q) store_from_float(y, dt_out, i * after + k + q, __fdiv_rn(u[q], (float)D2));
+  }
+}
+int reduce_mean_two_axes(int dt_in, int dt_out, const void* x, void* y, int64_t before, int64_t d1, int64_t d2, int64_t after, cudaStream_t s, float in_scale) {
+  const int esz = dt_in == DT_F32 ? 4 : (dt_in == DT_S8 ? 1 : 2), vec = 16 / esz;
+  if (d1 != 7 || d2 != 7 || after % vec != 0 || (uintptr_t)x % 16 != 0 || before * after <= 0) return 1;   // not taken: the caller runs the two passes
+  if (!(dt_in == DT_F32 || dt_in == DT_F16 || dt_in == DT_BF16 || dt_in == DT_S8)) return 1;
+  const int grid = grid_for(before * (after / vec), 128);
+  if (dt_in == DT_F32) reduce_mean_two_axes_kernel<float, 7, 7><<<grid, 128, 0, s>>>(dt_out, (const float*)x, y, before, after, in_scale);
+  else if (dt_in == DT_F16) reduce_mean_two_axes_kernel<__half, 7, 7><<<grid, 128, 0, s>>>(dt_out, (const __half*)x, y, before, after, in_scale);
+  else if (dt_in == DT_BF16) reduce_mean_two_axes_kernel<__nv_bfloat16, 7, 7><<<grid, 128, 0, s>>>(dt_out, (const __nv_bfloat16*)x, y, before, after, in_scale);
+  else reduce_mean_two_axes_kernel<int8_t, 7, 7><<<grid, 128, 0, s>>>(dt_out, (const int8_t*)x, y, before, after, in_scale);
+  return check_launch();
+}
 __global__ void reduce_mean_axis_s8_kernel(int dt_out, const int8_t* x, void* y, int64_t before, int64_t dim, int64_t after, float in_scale) {
   int64_t total = before * after;
   for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {

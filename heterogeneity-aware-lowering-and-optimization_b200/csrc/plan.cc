@@ -1233,12 +1233,21 @@ odla_status Builder::emit_plain(const Item& it) {
         passes.push_back({cur, dst, cdt, ddt, before, d[a], after});
         d[a] = 1; cur = dst; cdt = ddt;
       }
+      // two adjacent axes in rising order (a global average pool): one launch when the kernel serves the shape
+      const bool adjacent = n_axes == 2 && v->ia[2] == v->ia[1] + 1 && passes[0].after == passes[1].dim * passes[1].after &&
+                            passes[1].before == passes[0].before && !getenv("ODLA_B200_REDUCE_TWO_PASSES");
+      const int vec = cdt == DT_F32 && xdt == DT_F32 ? 4 : (xdt == DT_S8 ? 16 : (xdt == DT_F32 ? 4 : 8));
+      const bool one_launch = adjacent && passes[0].dim == 7 && passes[1].dim == 7 && passes[1].after % vec == 0;
       add_launch("reduce_mean", v, 0, tensor_bytes(xin) + out_bytes, [=](cudaStream_t s) {
+        if (adjacent) {
+          int r = reduce_mean_two_axes(passes[0].sdt, passes[1].ddt, passes[0].src, passes[1].dst, passes[0].before, passes[0].dim, passes[1].dim, passes[1].after, s, in_scale);
+          if (r <= 0) return r;
+        }
         bool first = true;
         for (auto& p : passes) { int r = reduce_mean_axis(p.sdt, p.ddt, p.src, p.dst, p.before, p.dim, p.after, s, first ? in_scale : 1.f); if (r) return r; first = false; }
         return 0;
       });
-      p_->launches.back().n_kernels = (int)passes.size();
+      p_->launches.back().n_kernels = one_launch ? 1 : (int)passes.size();
       return ODLA_SUCCESS;
     }
     case OP_LAYERNORM: {
